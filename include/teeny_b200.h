@@ -1,0 +1,169 @@
+/*
+ * teeny_b200 -- C ABI of the sm_100a (B200) backend for teenygrad's GEMM / attention / Qwen3-forward path.
+ *
+ * Every entry point
+ *   - takes DEVICE pointers owned by the caller, sizes as plain ints, and a CUDA stream last;
+ *   - enqueues its kernels on that stream and returns without synchronising;
+ *   - allocates nothing (kernels that need scratch take it as an argument, like the `global_scratch` pointer the
+ *     reference's launcher appends to every kernel's arguments, drivers/teeny-cuda/src/device/mod.rs:336-362);
+ *   - returns 0 on success, a negative TEENY_ERR_* code for a rejected call, or a positive cudaError_t value.
+ *
+ * Names and leading argument order are those of the reference's kernel entry points (symbol
+ * "{kernel_fn}_entry_point", macros/teeny-macros/src/macros/kernel.rs:544,600-615); the reference monomorphises per
+ * dtype, C has no generics, hence the _f32 / _bf16 suffixes.  bf16 values are raw 16-bit patterns (uint16_t here).
+ * Reference paths below are relative to the teenygrad repository root.
+ */
+#ifndef TEENY_B200_H_
+#define TEENY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* teeny_stream_t; /* cudaStream_t / CUstream */
+typedef uint16_t teeny_bf16;
+
+enum {
+  TEENY_OK = 0,
+  TEENY_ERR_BAD_ARG = -1,     /* null pointer, non-positive size, unsupported shape */
+  TEENY_ERR_ALIGNMENT = -2,   /* pointer / stride alignment the kernel needs is not met */
+  TEENY_ERR_SCRATCH = -3,     /* scratch missing or too small */
+  TEENY_ERR_DRIVER = -4,      /* CUDA driver entry point unavailable or tensor-map encode failed */
+  TEENY_ERR_DEVICE_WAIT = -5, /* a bounded wait inside a kernel expired (see teeny_device_error) */
+  TEENY_ERR_NCCL = -6
+};
+
+int teeny_version(void);
+const char* teeny_status_string(int status);
+/* Synchronises the device and returns the error word kernels set when one of their bounded waits expires
+ * (0 = none).  clear != 0 resets it.  The reference surfaces device faults by cuCtxSynchronize after each launch
+ * (drivers/teeny-cuda/src/device/mod.rs:369-381); here launches stay asynchronous and this is the explicit check. */
+int teeny_device_error(int clear);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * GEMM
+ * ------------------------------------------------------------------------------------------------------------- */
+/* C[M,N] = A[M,K] @ B[K,N], all row-major.  Replaces matmul_forward, kernels/teeny-kernels/src/math/gemm.rs:44-108
+ * (arguments a_ptr, b_ptr, c_ptr, M, N, K, :52-59).  f32: true f32 products and accumulation.  bf16: f32 accumulate.
+ * global_scratch may be NULL. */
+int matmul_forward_entry_point_f32(const float* a, const float* b, float* c, int M, int N, int K,
+                                   void* global_scratch, size_t global_scratch_bytes, teeny_stream_t stream);
+int matmul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* c, int M, int N, int K,
+                                    void* global_scratch, size_t global_scratch_bytes, teeny_stream_t stream);
+
+/* Y[M,N] = X[M,K] @ W[N,K]^T (+ bias[N], NULL for none); strides in elements.  Replaces linear_forward,
+ * kernels/teeny-kernels/src/nn/mlp/linear.rs:22-116 (arguments :31-45, packed by RuntimeOp for LinearForward
+ * :275-307).  bf16: when stride_xk == stride_wk == stride_yn == 1 and rows are 16-byte aligned the tcgen05 kernel
+ * runs; other layouts run on a CUDA-core kernel.  With M <= 128 and scratch of teeny_gemm_scratch_bytes() bytes
+ * (zero-filled once before first use; the kernel leaves it zeroed) K may be split across CTAs. */
+int linear_forward_entry_point_f32(const float* x, const float* w, const float* bias, float* y, int M, int N, int K,
+                                   int stride_xm, int stride_xk, int stride_wn, int stride_wk, int stride_ym,
+                                   int stride_yn, void* global_scratch, size_t global_scratch_bytes,
+                                   teeny_stream_t stream);
+int linear_forward_entry_point_bf16(const teeny_bf16* x, const teeny_bf16* w, const teeny_bf16* bias, teeny_bf16* y,
+                                    int M, int N, int K, int stride_xm, int stride_xk, int stride_wn, int stride_wk,
+                                    int stride_ym, int stride_yn, void* global_scratch, size_t global_scratch_bytes,
+                                    teeny_stream_t stream);
+/* Scratch the bf16 GEMM can use for split-K at this shape (0 when it never splits). */
+size_t teeny_gemm_scratch_bytes(int M, int N, int K);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Attention
+ * ------------------------------------------------------------------------------------------------------------- */
+/* O = softmax(Q K^T * scale) V, L = logsumexp; q/k/v/o [BH, n_ctx, head_dim] contiguous, l [BH, n_ctx_q] f32;
+ * non-causal, one KV head per query head.  Replaces flash_attention2_forward,
+ * kernels/teeny-kernels/src/nn/attention/flash_attn2.rs:53-156 (arguments :54-63).  In the reference BH is the
+ * launch grid's y extent and HEAD_DIM a const generic (tests/test_flash_attn2.rs:120-124); here they are the two
+ * arguments after neg_inf.  neg_inf is accepted for ABI parity and ignored.  l may be NULL. */
+int flash_attention2_forward_entry_point_f32(const float* q, const float* k, const float* v, float* o, float* l,
+                                             int n_ctx_q, int n_ctx_k, float softmax_scale, float neg_inf, int bh,
+                                             int head_dim, teeny_stream_t stream);
+int flash_attention2_forward_entry_point_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v,
+                                              teeny_bf16* o, float* l, int n_ctx_q, int n_ctx_k, float softmax_scale,
+                                              float neg_inf, int bh, int head_dim, teeny_stream_t stream);
+
+/* Strided, grouped-query, optionally causal attention.  The graph op it implements is
+ * Op::MultiHeadAttention{q_num_heads, kv_num_heads} (core/teeny-core/src/graph/mod.rs:1278), which the reference
+ * leaves unlowered (kernels/teeny-kernels/src/graph/mod.rs:2603-2607).  Element strides for (batch, head, sequence);
+ * head_dim is contiguous.  Causal masks are aligned to the end of the keys: query i sees keys j <= i + Skv - Sq. */
+typedef struct {
+  int B, Hq, Hkv, Sq, Skv, D;
+  long long q_sb, q_sh, q_ss;
+  long long k_sb, k_sh, k_ss;
+  long long v_sb, v_sh, v_ss;
+  long long o_sb, o_sh, o_ss;
+  float scale;
+  int causal;
+} teeny_attn_shape;
+/* Prefill: D == 128 runs the tcgen05 kernel; other head dims (<= 256) a CUDA-core kernel.  lse [B, Hq, Sq] or NULL. */
+int teeny_flash_attn_fwd_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o,
+                              float* lse, const teeny_attn_shape* shape, teeny_stream_t stream);
+/* Decode: Sq == 1, D == 128.  shape->Skv is the cache capacity; the live length is *kv_len_dev (device int, lets a
+ * captured CUDA graph advance) or kv_len when kv_len_dev is NULL.  scratch >= teeny_attn_decode_scratch_bytes(). */
+int teeny_flash_attn_decode_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o,
+                                 const teeny_attn_shape* shape, int kv_len, const int* kv_len_dev, void* scratch,
+                                 size_t scratch_bytes, teeny_stream_t stream);
+size_t teeny_attn_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * Normalisation and elementwise
+ * ------------------------------------------------------------------------------------------------------------- */
+/* rrms[r] = 1/sqrt(mean(x[r,:]^2) + eps); y = x * rrms * weight.  Replaces rms_norm_forward,
+ * kernels/teeny-kernels/src/nn/norm/rmsnorm.rs:40-118 (arguments :41-48).  rrms may be NULL.
+ * bf16 variant: statistics in f32, normalised row rounded to bf16, then multiplied by the bf16 weight (the cast
+ * points of the Qwen3 graph the reference records, support/teeny-torch/tests/data/qwen3_1.bin.gz). */
+int rms_norm_forward_entry_point_f32(const float* x, float* y, const float* weight, float* rrms, int M, int N,
+                                     float eps, teeny_stream_t stream);
+int rms_norm_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, const teeny_bf16* weight, float* rrms,
+                                      int M, int N, float eps, teeny_stream_t stream);
+/* y = x / (1 + exp(-x)).  Replaces silu_forward, kernels/teeny-kernels/src/nn/activation/sigmoid.rs:120-156. */
+int silu_forward_entry_point_f32(const float* x, float* y, int n, teeny_stream_t stream);
+int silu_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, int n, teeny_stream_t stream);
+/* out = a * b.  Replaces elemwise_mul_forward, kernels/teeny-kernels/src/nn/tensor/elemwise_binary.rs:206-250. */
+int elemwise_mul_forward_entry_point_f32(const float* a, const float* b, float* out, int n, teeny_stream_t stream);
+int elemwise_mul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* out, int n,
+                                          teeny_stream_t stream);
+/* out = a + b.  Replaces elemwise_add_forward, kernels/teeny-kernels/src/nn/tensor/elemwise_add.rs:29-69. */
+int elemwise_add_forward_entry_point_f32(const float* a, const float* b, float* out, int n, teeny_stream_t stream);
+int elemwise_add_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* out, int n,
+                                          teeny_stream_t stream);
+/* Row softmax.  Replaces softmax_forward, kernels/teeny-kernels/src/nn/activation/softmax.rs:39-69. */
+int softmax_forward_entry_point_f32(const float* x, float* y, int n_rows, int n_cols, teeny_stream_t stream);
+int softmax_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, int n_rows, int n_cols,
+                                     teeny_stream_t stream);
+
+/* Fused kernels of the Qwen3 layer.  The reference has no fused forms: Op::Fused and Op::RotaryEmbedding do not lower
+ * (kernels/teeny-kernels/src/graph/mod.rs:2953-2966, 2598-2602); each fuses the ops named. */
+/* residual <- residual + x (bf16 add); y <- rms_norm(residual).  Fuses elemwise_add_forward + rms_norm_forward. */
+int teeny_add_rms_norm_bf16(const teeny_bf16* x, teeny_bf16* residual, teeny_bf16* y, const teeny_bf16* weight, int M,
+                            int N, float eps, teeny_stream_t stream);
+/* out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i].  Fuses silu_forward + elemwise_mul_forward. */
+int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out, int T, int inter,
+                        teeny_stream_t stream);
+/* cos/sin tables [max_pos, D] from inv_freq[D/2] (f32 angles, one rounding to bf16). */
+int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* cos_table, teeny_bf16* sin_table, int max_pos, int D,
+                          teeny_stream_t stream);
+/* Per-head RMSNorm of q and k (D == 128), rotary embedding (rotate-half), KV-cache append.  qkv is the fused
+ * projection [T, (Hq + 2 Hkv) * D] with row stride ld; token t is sequence t / S at position pos0 + t % S
+ * (pos0 = *pos0_dev when non-NULL).  q is rewritten in place; caches are [B, Hkv, max_len, D]. */
+int teeny_qk_norm_rope_kv_bf16(teeny_bf16* qkv, long long ld, const teeny_bf16* q_norm_w, const teeny_bf16* k_norm_w,
+                               const teeny_bf16* cos_table, const teeny_bf16* sin_table, teeny_bf16* k_cache,
+                               teeny_bf16* v_cache, int T, int S, int Hq, int Hkv, int D, int max_len, int pos0,
+                               const int* pos0_dev, float eps, teeny_stream_t stream);
+/* out[t, :] = table[ids[t], :] */
+int teeny_embedding_bf16(const int* ids, const teeny_bf16* table, teeny_bf16* out, int T, int hidden, int vocab,
+                         teeny_stream_t stream);
+/* Row argmax, lowest index on ties: best_val[r] (f32), best_idx[r] = index + idx_offset. */
+int teeny_argmax_bf16(const teeny_bf16* logits, long long ld, float* best_val, int* best_idx, int rows, int cols,
+                      int idx_offset, teeny_stream_t stream);
+/* Merge `parts` candidates per row (vals / idx laid out [parts, rows]) into out_idx[rows]. */
+int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows,
+                         teeny_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEENY_B200_H_ */

@@ -1,0 +1,276 @@
+// C ABI (include/teeny_b200.h): argument checks, dtype / layout dispatch, and the few process-wide helpers
+// (tensor-map encoding through the driver entry point, per-device error word, SM count).
+#include <mutex>
+
+#include "../../include/teeny_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+__device__ int g_error_word = 0;  // one instance per device that loads this module
+
+std::mutex g_mutex;
+int* g_error_ptr[kMaxDevices] = {};
+int g_sm_count[kMaxDevices] = {};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int current_device() {
+  int d = 0;
+  cudaGetDevice(&d);
+  return (d >= 0 && d < kMaxDevices) ? d : 0;
+}
+
+}  // namespace
+
+int* device_error_word() {
+  const int d = current_device();
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_error_ptr[d]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_error_word) != cudaSuccess) return nullptr;
+    g_error_ptr[d] = static_cast<int*>(p);
+  }
+  return g_error_ptr[d];
+}
+
+int sm_count() {
+  const int d = current_device();
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_sm_count[d]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+    g_sm_count[d] = n;
+  }
+  return g_sm_count[d];
+}
+
+int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+          qres != cudaDriverEntryPointSuccess || !fn)
+        return TEENY_ERR_DRIVER;
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  }
+  if (rank < 1 || rank > 5) return TEENY_ERR_BAD_ARG;
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i + 1 < rank; ++i) {
+    if (strides_bytes[i] == 0 || (strides_bytes[i] & 15)) return TEENY_ERR_ALIGNMENT;
+    gstr[i] = strides_bytes[i];
+  }
+  if (reinterpret_cast<uintptr_t>(base) & 15) return TEENY_ERR_ALIGNMENT;
+  const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                              const_cast<void*>(base), gdim, gstr, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TEENY_OK : TEENY_ERR_DRIVER;
+}
+
+}  // namespace teeny
+
+using namespace teeny;
+
+namespace {
+inline const bf16* B(const teeny_bf16* p) { return reinterpret_cast<const bf16*>(p); }
+inline bf16* B(teeny_bf16* p) { return reinterpret_cast<bf16*>(p); }
+inline cudaStream_t S(teeny_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+AttnShape to_shape(const teeny_attn_shape& t) {
+  AttnShape s;
+  s.B = t.B; s.Hq = t.Hq; s.Hkv = t.Hkv; s.Sq = t.Sq; s.Skv = t.Skv; s.D = t.D;
+  s.q_sb = t.q_sb; s.q_sh = t.q_sh; s.q_ss = t.q_ss;
+  s.k_sb = t.k_sb; s.k_sh = t.k_sh; s.k_ss = t.k_ss;
+  s.v_sb = t.v_sb; s.v_sh = t.v_sh; s.v_ss = t.v_ss;
+  s.o_sb = t.o_sb; s.o_sh = t.o_sh; s.o_ss = t.o_ss;
+  s.scale = t.scale; s.causal = t.causal;
+  return s;
+}
+
+AttnShape contiguous_shape(int bh, int nq, int nk, int d, float scale) {
+  AttnShape s;
+  s.B = 1; s.Hq = bh; s.Hkv = bh; s.Sq = nq; s.Skv = nk; s.D = d;
+  s.q_sb = static_cast<long long>(bh) * nq * d; s.q_sh = static_cast<long long>(nq) * d; s.q_ss = d;
+  s.k_sb = static_cast<long long>(bh) * nk * d; s.k_sh = static_cast<long long>(nk) * d; s.k_ss = d;
+  s.v_sb = s.k_sb; s.v_sh = s.k_sh; s.v_ss = d;
+  s.o_sb = s.q_sb; s.o_sh = s.q_sh; s.o_ss = d;
+  s.scale = scale; s.causal = 0;
+  return s;
+}
+}  // namespace
+
+extern "C" {
+
+int teeny_version(void) { return 100; }
+
+const char* teeny_status_string(int status) {
+  switch (status) {
+    case TEENY_OK: return "ok";
+    case TEENY_ERR_BAD_ARG: return "bad argument (null pointer, non-positive size or unsupported shape)";
+    case TEENY_ERR_ALIGNMENT: return "pointer or stride alignment not met";
+    case TEENY_ERR_SCRATCH: return "scratch missing or too small";
+    case TEENY_ERR_DRIVER: return "CUDA driver entry point unavailable or tensor-map encode failed";
+    case TEENY_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
+    case TEENY_ERR_NCCL: return "NCCL error";
+    default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
+  }
+}
+
+int teeny_device_error(int clear) {
+  int* p = device_error_word();
+  if (!p) return TEENY_ERR_DRIVER;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  int v = 0;
+  e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (clear && v != 0) {
+    const int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  }
+  return v;
+}
+
+// ---- GEMM ----
+int matmul_forward_entry_point_f32(const float* a, const float* b, float* c, int M, int N, int K, void*, size_t,
+                                   teeny_stream_t stream) {
+  return gemm_f32(a, K, 1, b, N, 1, nullptr, c, N, 1, M, N, K, S(stream));
+}
+
+int matmul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* c, int M, int N, int K,
+                                    void* scratch, size_t scratch_bytes, teeny_stream_t stream) {
+  if (!a || !b || !c || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  const bool tma_ok = (K % 8 == 0) && (N % 8 == 0) &&
+                      !((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15);
+  if (tma_ok) return gemm_bf16(B(a), K, B(b), N, /*w_is_kn=*/true, nullptr, B(c), N, M, N, K, scratch, scratch_bytes, S(stream));
+  return gemm_bf16_generic(B(a), K, 1, B(b), N, 1, nullptr, B(c), N, 1, M, N, K, S(stream));
+}
+
+int linear_forward_entry_point_f32(const float* x, const float* w, const float* bias, float* y, int M, int N, int K,
+                                   int sxm, int sxk, int swn, int swk, int sym, int syn, void*, size_t,
+                                   teeny_stream_t stream) {
+  return gemm_f32(x, sxm, sxk, w, swk, swn, bias, y, sym, syn, M, N, K, S(stream));
+}
+
+int linear_forward_entry_point_bf16(const teeny_bf16* x, const teeny_bf16* w, const teeny_bf16* bias, teeny_bf16* y,
+                                    int M, int N, int K, int sxm, int sxk, int swn, int swk, int sym, int syn,
+                                    void* scratch, size_t scratch_bytes, teeny_stream_t stream) {
+  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  const bool tma_ok = sxk == 1 && swk == 1 && syn == 1 && (sxm % 8 == 0) && (swn % 8 == 0) && sxm >= K && swn >= K &&
+                      !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15);
+  if (tma_ok)
+    return gemm_bf16(B(x), sxm, B(w), swn, /*w_is_kn=*/false, B(bias), B(y), sym, M, N, K, scratch, scratch_bytes, S(stream));
+  return gemm_bf16_generic(B(x), sxm, sxk, B(w), swk, swn, B(bias), B(y), sym, syn, M, N, K, S(stream));
+}
+
+size_t teeny_gemm_scratch_bytes(int M, int N, int K) { return gemm_bf16_scratch_bytes(M, N, K); }
+
+// ---- attention ----
+int flash_attention2_forward_entry_point_f32(const float* q, const float* k, const float* v, float* o, float* l,
+                                             int n_ctx_q, int n_ctx_k, float softmax_scale, float, int bh,
+                                             int head_dim, teeny_stream_t stream) {
+  if (bh <= 0 || n_ctx_q <= 0 || n_ctx_k <= 0 || head_dim <= 0) return TEENY_ERR_BAD_ARG;
+  return attention_generic<float>(q, k, v, o, l, contiguous_shape(bh, n_ctx_q, n_ctx_k, head_dim, softmax_scale), S(stream));
+}
+
+int flash_attention2_forward_entry_point_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v,
+                                              teeny_bf16* o, float* l, int n_ctx_q, int n_ctx_k, float softmax_scale,
+                                              float, int bh, int head_dim, teeny_stream_t stream) {
+  if (bh <= 0 || n_ctx_q <= 0 || n_ctx_k <= 0 || head_dim <= 0) return TEENY_ERR_BAD_ARG;
+  teeny_attn_shape t;
+  const AttnShape s = contiguous_shape(bh, n_ctx_q, n_ctx_k, head_dim, softmax_scale);
+  t.B = s.B; t.Hq = s.Hq; t.Hkv = s.Hkv; t.Sq = s.Sq; t.Skv = s.Skv; t.D = s.D;
+  t.q_sb = s.q_sb; t.q_sh = s.q_sh; t.q_ss = s.q_ss; t.k_sb = s.k_sb; t.k_sh = s.k_sh; t.k_ss = s.k_ss;
+  t.v_sb = s.v_sb; t.v_sh = s.v_sh; t.v_ss = s.v_ss; t.o_sb = s.o_sb; t.o_sh = s.o_sh; t.o_ss = s.o_ss;
+  t.scale = s.scale; t.causal = 0;
+  return teeny_flash_attn_fwd_bf16(q, k, v, o, l, &t, stream);
+}
+
+int teeny_flash_attn_fwd_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o, float* lse,
+                              const teeny_attn_shape* shape, teeny_stream_t stream) {
+  if (!shape) return TEENY_ERR_BAD_ARG;
+  const AttnShape s = to_shape(*shape);
+  if (s.D == 128) {
+    const int rc = attention_prefill_bf16(B(q), B(k), B(v), B(o), lse, s, S(stream));
+    if (rc != TEENY_ERR_ALIGNMENT) return rc;  // unaligned views fall through to the CUDA-core kernel
+  }
+  return attention_generic<bf16>(B(q), B(k), B(v), B(o), lse, s, S(stream));
+}
+
+int teeny_flash_attn_decode_bf16(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o,
+                                 const teeny_attn_shape* shape, int kv_len, const int* kv_len_dev, void* scratch,
+                                 size_t scratch_bytes, teeny_stream_t stream) {
+  if (!shape) return TEENY_ERR_BAD_ARG;
+  return attention_decode_bf16(B(q), B(k), B(v), B(o), to_shape(*shape), kv_len, kv_len_dev, scratch, scratch_bytes, S(stream));
+}
+
+size_t teeny_attn_decode_scratch_bytes(int Bn, int Hq, int D, int max_kv) {
+  return attention_decode_scratch_bytes(Bn, Hq, D, max_kv);
+}
+
+// ---- normalisation / elementwise ----
+int rms_norm_forward_entry_point_f32(const float* x, float* y, const float* w, float* rrms, int M, int N, float eps,
+                                     teeny_stream_t stream) {
+  return rms_norm_f32(x, y, w, rrms, M, N, eps, S(stream));
+}
+int rms_norm_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, const teeny_bf16* w, float* rrms, int M,
+                                      int N, float eps, teeny_stream_t stream) {
+  return rms_norm_bf16(B(x), N, B(y), N, B(w), rrms, M, N, eps, S(stream));
+}
+int silu_forward_entry_point_f32(const float* x, float* y, int n, teeny_stream_t s) { return silu_f32(x, y, n, S(s)); }
+int silu_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, int n, teeny_stream_t s) { return silu_bf16(B(x), B(y), n, S(s)); }
+int elemwise_mul_forward_entry_point_f32(const float* a, const float* b, float* o, int n, teeny_stream_t s) { return mul_f32(a, b, o, n, S(s)); }
+int elemwise_mul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* o, int n, teeny_stream_t s) { return mul_bf16(B(a), B(b), B(o), n, S(s)); }
+int elemwise_add_forward_entry_point_f32(const float* a, const float* b, float* o, int n, teeny_stream_t s) { return add_f32(a, b, o, n, S(s)); }
+int elemwise_add_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* o, int n, teeny_stream_t s) { return add_bf16(B(a), B(b), B(o), n, S(s)); }
+int softmax_forward_entry_point_f32(const float* x, float* y, int r, int c, teeny_stream_t s) { return softmax_f32(x, y, r, c, S(s)); }
+int softmax_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, int r, int c, teeny_stream_t s) { return softmax_bf16(B(x), B(y), r, c, S(s)); }
+
+int teeny_add_rms_norm_bf16(const teeny_bf16* x, teeny_bf16* residual, teeny_bf16* y, const teeny_bf16* w, int M, int N,
+                            float eps, teeny_stream_t s) {
+  return add_rms_norm_bf16(B(x), B(residual), B(y), B(w), M, N, eps, S(s));
+}
+int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out, int T, int inter, teeny_stream_t s) {
+  return silu_mul_bf16(B(gate_up), ld, B(out), T, inter, S(s));
+}
+int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* c, teeny_bf16* sn, int max_pos, int D, teeny_stream_t s) {
+  return rope_table_bf16(inv_freq, B(c), B(sn), max_pos, D, S(s));
+}
+int teeny_qk_norm_rope_kv_bf16(teeny_bf16* qkv, long long ld, const teeny_bf16* qw, const teeny_bf16* kw,
+                               const teeny_bf16* c, const teeny_bf16* sn, teeny_bf16* kc, teeny_bf16* vc, int T, int Sx,
+                               int Hq, int Hkv, int D, int max_len, int pos0, const int* pos0_dev, float eps,
+                               teeny_stream_t s) {
+  return qk_norm_rope_kv_bf16(B(qkv), ld, B(qw), B(kw), B(c), B(sn), B(kc), B(vc), T, Sx, Hq, Hkv, D, max_len, pos0,
+                              pos0_dev, eps, S(s));
+}
+int teeny_embedding_bf16(const int* ids, const teeny_bf16* table, teeny_bf16* out, int T, int hidden, int vocab,
+                         teeny_stream_t s) {
+  return embedding_bf16(ids, B(table), B(out), T, hidden, vocab, S(s));
+}
+int teeny_argmax_bf16(const teeny_bf16* logits, long long ld, float* bv, int* bi, int rows, int cols, int off,
+                      teeny_stream_t s) {
+  return argmax_bf16(B(logits), ld, bv, bi, rows, cols, off, S(s));
+}
+int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, teeny_stream_t s) {
+  return argmax_combine(vals, idx, out_idx, parts, rows, S(s));
+}
+
+}  // extern "C"

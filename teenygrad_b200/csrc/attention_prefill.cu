@@ -1,0 +1,337 @@
+// Causal grouped-query flash-attention forward for sm_100a, head_dim 128, bf16 in/out, f32 softmax.
+//
+// One CTA per (128-query tile, query head, batch); keys/values stream through in tiles of 128.
+//   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings (128-byte swizzle, separate barriers
+//               for K and V so QK^T can start before V lands);
+//   warp 1      MMA issuer: S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of two S buffers in
+//               TMEM, and O += P V (P K-major from shared memory, V MN-major straight from its [key][d] tile);
+//               QK^T of tile j+1 is issued before P V of tile j so the tensor pipe works while softmax runs;
+//   warp 2      allocates / frees tensor memory;
+//   warps 4-7   softmax: thread = query row; tcgen05.ld the S row, scale into the log2 domain, causal / tail mask,
+//               running max with lazy rescale (O in TMEM is only rescaled when the max grows by more than 2^8),
+//               P = exp2(s - m) as bf16 into shared memory in the swizzled K-major layout, row sums in f32.
+// Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+constexpr int kQT = 128;
+constexpr int kKT = 128;
+constexpr int kHD = 128;
+constexpr int kThreads = 256;
+constexpr int kTileBytes = kKT * kHD * 2;       // 32 KB: two 16 KB boxes of [128 rows][64 d]
+constexpr int kBoxBytes = 128 * 64 * 2;         // 16 KB
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kSmemQ + kTileBytes;     // 2 stages
+constexpr int kSmemV = kSmemK + 2 * kTileBytes; // 2 stages
+constexpr int kSmemP = kSmemV + 2 * kTileBytes; // 2 buffers
+constexpr int kSmemBar = kSmemP + 2 * kTileBytes;
+constexpr int kSmemTotal = kSmemBar + 256 + 1024;
+constexpr float kRescaleThreshold = 8.0f;       // log2 units
+
+struct PrefillArgs {
+  bf16* o;
+  float* lse;
+  int B, Hq, Hkv, Sq, Skv;
+  long long o_sb, o_sh, o_ss;
+  float scale_log2;
+  int causal;
+  int* err;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const PrefillArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar0 = base + kSmemBar;
+  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty |
+  //           13,14 p_full | 15,16 pv_done ; then the TMEM base address
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
+                PV_DONE = 15;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * 17);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* err = args.err;
+
+  // heavier (later) query tiles first: with causal masking they have the most key tiles
+  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (args.Hq / args.Hkv);
+  const int q0 = qt * kQT;
+  const int off = args.Skv - args.Sq;  // causal: query i sees keys <= i + off
+  int kv_end = args.Skv;
+  if (args.causal) kv_end = min(args.Skv, q0 + kQT + off);
+  const int n_tiles = (kv_end + kKT - 1) / kKT;  // >= 1 (host guarantees Skv >= Sq >= 1 when causal)
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    for (int i = 0; i < 17; ++i) {
+      const bool softmax_arrives = (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1);
+      mbar_init(bar(i), softmax_arrives ? 128 : 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(base + kSmemBar + 8 * 17, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(Q_FULL), kTileBytes);
+      tma_load_4d(base + kSmemQ, &tmap_q, bar(Q_FULL), 0, q0, h, b);
+      tma_load_4d(base + kSmemQ + kBoxBytes, &tmap_q, bar(Q_FULL), 64, q0, h, b);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
+        mbar_expect_tx(bar(K_FULL + st), kTileBytes);
+        tma_load_4d(base + kSmemK + st * kTileBytes, &tmap_k, bar(K_FULL + st), 0, j * kKT, hk, b);
+        tma_load_4d(base + kSmemK + st * kTileBytes + kBoxBytes, &tmap_k, bar(K_FULL + st), 64, j * kKT, hk, b);
+        if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
+        mbar_expect_tx(bar(V_FULL + st), kTileBytes);
+        tma_load_4d(base + kSmemV + st * kTileBytes, &tmap_v, bar(V_FULL + st), 0, j * kKT, hk, b);
+        tma_load_4d(base + kSmemV + st * kTileBytes + kBoxBytes, &tmap_v, bar(V_FULL + st), 64, j * kKT, hk, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kQT, kKT, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kQT, kHD, false, true);
+      bool ok = mbar_wait(bar(Q_FULL), 0, err, DEVERR_ATTN_MMA);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(K_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_MMA)) return false;
+        tc_fence_after();
+        const uint32_t qb = base + kSmemQ, kb = base + kSmemK + st * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // 16 d per step; 4 steps per 64-wide box
+          const uint32_t o = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
+          umma_bf16_ss(tmem_s0 + st * 128, make_smem_desc_sw128(qb + o, 16, 1024),
+                       make_smem_desc_sw128(kb + o, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(K_EMPTY + st));
+        umma_commit(bar(S_FULL + st));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(bar(V_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        if (!mbar_wait(bar(P_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        tc_fence_after();
+        const uint32_t pb = base + kSmemP + st * kTileBytes, vb = base + kSmemV + st * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step
+          const uint64_t pd = make_smem_desc_sw128(pb + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
+          // V tile: rows = keys (128 B = 64 d each), two boxes = two 64-wide d chunks (leading offset 16 KB),
+          // 8-key groups 1 KB apart; 16 keys = 2 KB per step.
+          const uint64_t vd = make_smem_desc_sw128(vb + ks * 2048, kBoxBytes, 1024);
+          umma_bf16_ss(tmem_o, pd, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(V_EMPTY + st));
+        umma_commit(bar(PV_DONE + st));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (ok) ok = issue_pv(j);
+      }
+    }
+  } else if (warp >= 4) {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // query row in the tile == TMEM lane
+    const int qi = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    float m = -INFINITY, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(bar(S_FULL + st), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(tmem_s0 + lane_addr + st * 128 + c * 32, t);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]) * args.scale_log2;
+      }
+      tc_fence_before();
+      mbar_arrive(bar(S_EMPTY + st));  // S is in registers: the buffer can take QK^T of tile j+2
+
+      const int k0 = j * kKT;
+      const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
+      if (need_mask) {
+        const int limit = args.causal ? min(args.Skv - 1, qi + off) : args.Skv - 1;  // last visible key
+#pragma unroll
+        for (int e = 0; e < 128; ++e)
+          if (k0 + e > limit) s[e] = -INFINITY;
+      }
+      float tmax = s[0];
+#pragma unroll
+      for (int e = 1; e < 128; ++e) tmax = fmaxf(tmax, s[e]);
+      const float m_new = fmaxf(m, tmax);
+      if (j == 0) {
+        m = m_new;  // key 0 is visible to every row, so m is finite from here on
+      } else {
+        const bool grow = m_new > m + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          // O must be final for tile j-1 before it is rescaled
+          if (!mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+          tc_fence_after();
+          const float alpha = fast_exp2(m - m_new);
+          l *= alpha;
+          m = m_new;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t t[32];
+            tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
+            tmem_st_32x32(tmem_o + lane_addr + c * 32, t);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+      }
+      // the P buffer was last read by P V of tile j-2
+      if (j >= 2) {
+        if (!mbar_wait(bar(PV_DONE + st), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+      }
+      uint8_t* prow = gen + kSmemP + st * kTileBytes + r * 128;
+      float lsum = 0.0f;
+#pragma unroll
+      for (int ch = 0; ch < 16; ++ch) {  // 8 keys = one 16-byte chunk; chunk position XOR-swizzled by row & 7
+        float p[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          p[e] = fast_exp2(s[ch * 8 + e] - m);
+          lsum += p[e];
+        }
+        uint4 pk;
+        pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
+        pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
+        const int box = ch >> 3, cib = ch & 7;
+        *reinterpret_cast<uint4*>(prow + box * kBoxBytes + ((cib ^ (r & 7)) << 4)) = pk;
+      }
+      l += lsum;
+      fence_proxy_async_smem();
+      mbar_arrive(bar(P_FULL + st));
+    }
+    if (ok) ok = mbar_wait(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const bool valid = qi < args.Sq;
+      bf16* dst = args.o + b * args.o_sb + h * args.o_sh + static_cast<long long>(qi) * args.o_ss;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o4;
+            o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
+            o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
+            o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
+            o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
+          }
+        }
+      }
+      if (valid && args.lse)
+        args.lse[(static_cast<long long>(b) * args.Hq + h) * args.Sq + qi] = 0.6931471805599453f * (m + log2f(l));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile int*>(err) != 0) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+int make_map(CUtensorMap* m, const bf16* p, int S, int H, int B, long long ss, long long sh, long long sb) {
+  const uint64_t dims[4] = {kHD, static_cast<uint64_t>(S), static_cast<uint64_t>(H), static_cast<uint64_t>(B)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sh) * 2,
+                               static_cast<uint64_t>(sb) * 2};
+  const uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tensor_map_bf16(m, p, 4, dims, strides, box);
+}
+
+}  // namespace
+
+int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, float* lse, const AttnShape& s,
+                           cudaStream_t stream) {
+  if (!q || !k || !v || !o || s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Sq <= 0 || s.Skv <= 0) return TEENY_ERR_BAD_ARG;
+  if (s.D != kHD || s.Hq % s.Hkv != 0) return TEENY_ERR_BAD_ARG;
+  if (s.causal && s.Skv < s.Sq) return TEENY_ERR_BAD_ARG;
+  const long long strides[] = {s.q_sb, s.q_sh, s.q_ss, s.k_sb, s.k_sh, s.k_ss, s.v_sb, s.v_sh, s.v_ss, s.o_ss, s.o_sh, s.o_sb};
+  for (long long st : strides)
+    if (st % 8 != 0) return TEENY_ERR_ALIGNMENT;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return TEENY_ERR_ALIGNMENT;
+  if (s.Hq > 65535 || s.B > 65535) return TEENY_ERR_BAD_ARG;
+  CUtensorMap mq, mk, mv;
+  int rc;
+  // a dimension of extent 1 still needs a legal (multiple-of-16-byte, non-zero) stride
+  auto fix = [](long long st, long long fallback) { return st > 0 ? st : fallback; };
+  if ((rc = make_map(&mq, q, s.Sq, s.Hq, s.B, s.q_ss, fix(s.q_sh, s.q_ss), fix(s.q_sb, s.q_ss)))) return rc;
+  if ((rc = make_map(&mk, k, s.Skv, s.Hkv, s.B, s.k_ss, fix(s.k_sh, s.k_ss), fix(s.k_sb, s.k_ss)))) return rc;
+  if ((rc = make_map(&mv, v, s.Skv, s.Hkv, s.B, s.v_ss, fix(s.v_sh, s.v_ss), fix(s.v_sb, s.v_ss)))) return rc;
+
+  PrefillArgs a{};
+  a.o = o; a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
+  a.o_sb = s.o_sb; a.o_sh = s.o_sh; a.o_ss = s.o_ss;
+  a.scale_log2 = s.scale * 1.4426950408889634f;
+  a.causal = s.causal;
+  a.err = device_error_word();
+
+  static int attr_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (attr_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_device = dev;
+  }
+  dim3 grid((s.Sq + kQT - 1) / kQT, s.Hq, s.B);
+  attention_prefill_kernel<<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace teeny

@@ -1,0 +1,550 @@
+// Bandwidth-bound kernels of the Qwen3 forward path: RMSNorm (+ fused residual add), per-head QK-norm + RoPE +
+// KV-cache append, SiLU*up, residual add, embedding gather, softmax, argmax.  All use 128-bit coalesced global
+// accesses where alignment allows and warp shuffles for the row reductions; arithmetic is f32 with the same
+// rounding points as the PyTorch graph the reference records for Qwen3 (bf16 tensors between ops).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+constexpr int kEwThreads = 256;
+
+inline int ew_grid(long long work_items, int per_block) {
+  long long g = (work_items + per_block - 1) / per_block;
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return static_cast<int>(g);
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x * (1.0f / (1.0f + expf(-x))); }
+
+struct OpSilu { __device__ float operator()(float a, float) const { return silu_f(a); } };
+struct OpMul { __device__ float operator()(float a, float b) const { return a * b; } };
+struct OpAdd { __device__ float operator()(float a, float b) const { return a + b; } };
+
+// ---- flat elementwise, f32 ----
+template <typename Op, bool BINARY>
+__global__ void ew_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o,
+                              long long n, bool vec) {
+  Op op;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (vec) {
+    const long long n4 = n >> 2;
+    for (long long v = i; v < n4; v += stride) {
+      const float4 x = reinterpret_cast<const float4*>(a)[v];
+      float4 y = BINARY ? reinterpret_cast<const float4*>(b)[v] : make_float4(0, 0, 0, 0);
+      float4 r;
+      r.x = op(x.x, y.x); r.y = op(x.y, y.y); r.z = op(x.z, y.z); r.w = op(x.w, y.w);
+      reinterpret_cast<float4*>(o)[v] = r;
+    }
+    for (long long t = (n4 << 2) + i; t < n; t += stride) o[t] = op(a[t], BINARY ? b[t] : 0.0f);
+  } else {
+    for (; i < n; i += stride) o[i] = op(a[i], BINARY ? b[i] : 0.0f);
+  }
+}
+
+// ---- flat elementwise, bf16 (f32 math, one rounding) ----
+template <typename Op, bool BINARY>
+__global__ void ew_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ o,
+                               long long n, bool vec) {
+  Op op;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (vec) {
+    const long long n8 = n >> 3;
+    for (long long v = i; v < n8; v += stride) {
+      const uint4 x = reinterpret_cast<const uint4*>(a)[v];
+      const uint4 y = BINARY ? reinterpret_cast<const uint4*>(b)[v] : make_uint4(0, 0, 0, 0);
+      uint4 r;
+      r.x = pack_bf16x2(op(bf16_lo(x.x), bf16_lo(y.x)), op(bf16_hi(x.x), bf16_hi(y.x)));
+      r.y = pack_bf16x2(op(bf16_lo(x.y), bf16_lo(y.y)), op(bf16_hi(x.y), bf16_hi(y.y)));
+      r.z = pack_bf16x2(op(bf16_lo(x.z), bf16_lo(y.z)), op(bf16_hi(x.z), bf16_hi(y.z)));
+      r.w = pack_bf16x2(op(bf16_lo(x.w), bf16_lo(y.w)), op(bf16_hi(x.w), bf16_hi(y.w)));
+      reinterpret_cast<uint4*>(o)[v] = r;
+    }
+    for (long long t = (n8 << 3) + i; t < n; t += stride)
+      o[t] = __float2bfloat16_rn(op(__bfloat162float(a[t]), BINARY ? __bfloat162float(b[t]) : 0.0f));
+  } else {
+    for (; i < n; i += stride)
+      o[i] = __float2bfloat16_rn(op(__bfloat162float(a[i]), BINARY ? __bfloat162float(b[i]) : 0.0f));
+  }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename Op, bool BINARY>
+int launch_ew_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st) {
+  if (!a || !o || (BINARY && !b) || n < 0) return TEENY_ERR_BAD_ARG;
+  if (n == 0) return TEENY_OK;
+  const bool vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
+  ew_f32_kernel<Op, BINARY><<<ew_grid((n + 3) / 4, kEwThreads), kEwThreads, 0, st>>>(a, b, o, n, vec);
+  return static_cast<int>(cudaGetLastError());
+}
+template <typename Op, bool BINARY>
+int launch_ew_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st) {
+  if (!a || !o || (BINARY && !b) || n < 0) return TEENY_ERR_BAD_ARG;
+  if (n == 0) return TEENY_OK;
+  const bool vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
+  ew_bf16_kernel<Op, BINARY><<<ew_grid((n + 7) / 8, kEwThreads), kEwThreads, 0, st>>>(a, b, o, n, vec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- RMSNorm, f32, one CTA per row (reference semantics: y = x * rrms * w) ----
+__global__ void rms_norm_f32_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w,
+                                    float* __restrict__ rrms, int N, float eps) {
+  __shared__ float red[32];
+  const float* xr = x + static_cast<size_t>(blockIdx.x) * N;
+  float* yr = y + static_cast<size_t>(blockIdx.x) * N;
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) sq += xr[c] * xr[c];
+  sq = block_sum(sq, red);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+  if (threadIdx.x == 0 && rrms) rrms[blockIdx.x] = rr;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) yr[c] = xr[c] * rr * w[c];
+}
+
+// ---- RMSNorm, bf16, Qwen3 rounding.  One CTA per row; the row stays in registers between the two phases. ----
+// VPT = 16-byte vectors per thread (N <= VPT * 8 * blockDim).  ADD: x is added into `res` first (bf16 add).
+template <int VPT, bool ADD>
+__global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
+                                     bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
+                                     float* __restrict__ rrms, int N, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
+  uint4* rr4 = ADD ? reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldx) : nullptr;
+  const int nv = N >> 3;
+  float v[VPT][8];
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      uint4 a = xr[idx];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      if (ADD) {
+        const uint4 b = rr4[idx];
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          // bf16 + bf16 rounded to bf16: the residual stream stays a bf16 tensor
+          const float lo = bf16_round(bf16_lo(aw[e]) + bf16_lo(bw[e]));
+          const float hi = bf16_round(bf16_hi(aw[e]) + bf16_hi(bw[e]));
+          v[i][2 * e] = lo;
+          v[i][2 * e + 1] = hi;
+          ow[e] = pack_bf16x2(lo, hi);
+        }
+        rr4[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[i][2 * e] = bf16_lo(aw[e]);
+          v[i][2 * e + 1] = bf16_hi(aw[e]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
+    }
+  }
+  sq = block_sum(sq, red);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+  if (threadIdx.x == 0 && rrms) rrms[row] = rr;
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      const uint4 g = wr[idx];
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]);
+        const float hi = bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]);
+        ow[e] = pack_bf16x2(lo, hi);
+      }
+      yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+}
+
+// Any N / alignment: scalar accesses, row re-read from L2 in the second phase.
+template <bool ADD>
+__global__ void rms_norm_bf16_scalar_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
+                                            bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
+                                            float* __restrict__ rrms, int N, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const bf16* xr = x + static_cast<size_t>(row) * ldx;
+  bf16* rs = ADD ? res + static_cast<size_t>(row) * ldx : nullptr;
+  float sq = 0.0f;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    float h = __bfloat162float(xr[c]);
+    if (ADD) {
+      h = bf16_round(h + __bfloat162float(rs[c]));
+      rs[c] = __float2bfloat16_rn(h);
+    }
+    sq += h * h;
+  }
+  sq = block_sum(sq, red);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+  if (threadIdx.x == 0 && rrms) rrms[row] = rr;
+  bf16* yr = y + static_cast<size_t>(row) * ldy;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    const float h = __bfloat162float(ADD ? rs[c] : xr[c]);
+    yr[c] = __float2bfloat16_rn(bf16_round(h * rr) * __bfloat162float(w[c]));
+  }
+}
+
+template <bool ADD>
+int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, bf16* y, long long ldy, const bf16* w, float* rrms,
+                    int M, int N, float eps, cudaStream_t st) {
+  if (!x || !y || !w || (ADD && !res) || M < 0 || N <= 0) return TEENY_ERR_BAD_ARG;
+  if (M == 0) return TEENY_OK;
+  const bool vec = (N % 8 == 0) && (ldx % 8 == 0) && (ldy % 8 == 0) && aligned16(x) && aligned16(y) && aligned16(w) &&
+                   (!ADD || aligned16(res));
+  const int nv = N / 8;
+  if (vec && nv <= 8 * 256) {
+    int threads = 128;
+    if (nv <= 32) threads = 32;
+    else if (nv <= 64) threads = 64;
+    else if (nv > 4 * 128) threads = 256;
+    const int vpt = (nv + threads - 1) / threads;
+#define TEENY_RMS_CASE(V)                                                                                    \
+  rms_norm_bf16_kernel<V, ADD><<<M, threads, 0, st>>>(x, ldx, res, y, ldy, w, rrms, N, eps)
+    if (vpt <= 1) TEENY_RMS_CASE(1);
+    else if (vpt <= 2) TEENY_RMS_CASE(2);
+    else if (vpt <= 4) TEENY_RMS_CASE(4);
+    else TEENY_RMS_CASE(8);
+#undef TEENY_RMS_CASE
+  } else {
+    rms_norm_bf16_scalar_kernel<ADD><<<M, 256, 0, st>>>(x, ldx, res, y, ldy, w, rrms, N, eps);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- SiLU(gate) * up on the fused [T, 2*inter] projection ----
+__global__ void silu_mul_bf16_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
+                                     int inter) {
+  const int vec_per_row = inter >> 3;
+  const long long total = static_cast<long long>(T) * vec_per_row;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long t = i / vec_per_row;
+    const int c = static_cast<int>(i - t * vec_per_row) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gu + t * ld + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(gu + t * ld + inter + c);
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t ow[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float lo = bf16_round(silu_f(bf16_lo(gw[e]))) * bf16_lo(uw[e]);
+      const float hi = bf16_round(silu_f(bf16_hi(gw[e]))) * bf16_hi(uw[e]);
+      ow[e] = pack_bf16x2(lo, hi);
+    }
+    *reinterpret_cast<uint4*>(out + t * inter + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+  }
+}
+__global__ void silu_mul_bf16_scalar_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
+                                            int inter) {
+  const long long total = static_cast<long long>(T) * inter;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const long long t = i / inter;
+    const int c = static_cast<int>(i - t * inter);
+    const float g = __bfloat162float(gu[t * ld + c]), u = __bfloat162float(gu[t * ld + inter + c]);
+    out[t * inter + c] = __float2bfloat16_rn(bf16_round(silu_f(g)) * u);
+  }
+}
+
+// ---- embedding gather: one warp per 16-byte vector strip ----
+__global__ void embedding_bf16_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
+                                      bf16* __restrict__ out, int T, int hidden, int vocab, bool vec) {
+  const int row = blockIdx.x;
+  if (row >= T) return;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host; clamp keeps loads in range
+  const bf16* src = table + static_cast<size_t>(id) * hidden;
+  bf16* dst = out + static_cast<size_t>(row) * hidden;
+  if (vec) {
+    for (int c = threadIdx.x; c < (hidden >> 3); c += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else {
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c];
+  }
+}
+
+// ---- RoPE tables ----
+__global__ void rope_table_kernel(const float* __restrict__ inv_freq, bf16* __restrict__ cos_t,
+                                  bf16* __restrict__ sin_t, int max_pos, int D) {
+  const int half = D >> 1;
+  const long long total = static_cast<long long>(max_pos) * half;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int pos = static_cast<int>(i / half), j = static_cast<int>(i % half);
+    const float angle = inv_freq[j] * static_cast<float>(pos);  // f32 product, as the traced graph computes it
+    // cos/sin of the f32 angle evaluated in double and rounded once: stays within half an ulp of the f32 result
+    const bf16 c = __float2bfloat16_rn(static_cast<float>(cos(static_cast<double>(angle))));
+    const bf16 s = __float2bfloat16_rn(static_cast<float>(sin(static_cast<double>(angle))));
+    cos_t[static_cast<size_t>(pos) * D + j] = c;
+    cos_t[static_cast<size_t>(pos) * D + half + j] = c;
+    sin_t[static_cast<size_t>(pos) * D + j] = s;
+    sin_t[static_cast<size_t>(pos) * D + half + j] = s;
+  }
+}
+
+// ---- per-head RMSNorm + RoPE + KV-cache append; D == 128, one warp per (token, head) ----
+// Lane l holds elements [4l, 4l+4); its rotate-half partner elements live in lane l ^ 16.
+__global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, const bf16* __restrict__ q_w,
+                                       const bf16* __restrict__ k_w, const bf16* __restrict__ cos_t,
+                                       const bf16* __restrict__ sin_t, bf16* __restrict__ k_cache,
+                                       bf16* __restrict__ v_cache, int T, int S, int Hq, int Hkv, int max_len,
+                                       int pos0, const int* __restrict__ pos0_dev, float eps) {
+  constexpr int D = 128;
+  const int heads = Hq + 2 * Hkv;
+  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_id >= static_cast<long long>(T) * heads) return;
+  const int t = static_cast<int>(warp_id / heads);
+  const int h = static_cast<int>(warp_id - static_cast<long long>(t) * heads);
+  const int b = t / S;
+  const int pos = (pos0_dev ? *pos0_dev : pos0) + (t - b * S);
+  bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  if (h >= Hq + Hkv) {  // V head: straight copy into the cache
+    if (pos < max_len) {
+      bf16* dst = v_cache + ((static_cast<size_t>(b) * Hkv + (h - Hq - Hkv)) * max_len + pos) * D + lane * 4;
+      *reinterpret_cast<uint2*>(dst) = raw;
+    }
+    return;
+  }
+  const bool is_q = h < Hq;
+  float x[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+  float sq = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+  sq = warp_sum(sq);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / D) + eps);
+  const uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? q_w : k_w) + lane * 4);
+  const float wv[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
+  float n[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) n[e] = bf16_round(bf16_round(x[e] * rr) * wv[e]);  // normed head, bf16 tensor
+  const int tp = pos < max_len ? pos : max_len - 1;  // table has max_len rows
+  const uint2 craw = *reinterpret_cast<const uint2*>(cos_t + static_cast<size_t>(tp) * D + lane * 4);
+  const uint2 sraw = *reinterpret_cast<const uint2*>(sin_t + static_cast<size_t>(tp) * D + lane * 4);
+  const float cv[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
+  const float sv[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
+  float r[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float partner = __shfl_xor_sync(0xffffffffu, n[e], 16);
+    const float rot = (lane < 16) ? -partner : partner;  // rotate_half: first half gets -x[d + 64]
+    const float a = bf16_round(n[e] * cv[e]);
+    const float bb = bf16_round(rot * sv[e]);
+    r[e] = a + bb;  // rounded to bf16 by the pack below
+  }
+  const uint2 outv = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+  if (is_q) {
+    *reinterpret_cast<uint2*>(src) = outv;
+  } else if (pos < max_len) {
+    bf16* dst = k_cache + ((static_cast<size_t>(b) * Hkv + (h - Hq)) * max_len + pos) * D + lane * 4;
+    *reinterpret_cast<uint2*>(dst) = outv;
+  }
+}
+
+// ---- softmax rows (f32 math) ----
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <typename T>
+__global__ void softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int cols) {
+  __shared__ float red[32];
+  const T* xr = x + static_cast<size_t>(blockIdx.x) * cols;
+  T* yr = y + static_cast<size_t>(blockIdx.x) * cols;
+  float mx = -INFINITY;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) mx = fmaxf(mx, ldf(xr + c));
+  mx = warp_max(mx);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = mx;
+  __syncthreads();
+  mx = warp_max(lane < nw ? red[lane] : -INFINITY);
+  __syncthreads();
+  float sum = 0.0f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) sum += expf(ldf(xr + c) - mx);
+  sum = block_sum(sum, red);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) stf(yr + c, expf(ldf(xr + c) - mx) / sum);
+}
+
+// ---- argmax over the last dim (lowest index wins ties) ----
+__device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+__global__ void argmax_bf16_kernel(const bf16* __restrict__ logits, long long ld, float* __restrict__ best_val,
+                                   int* __restrict__ best_idx, int cols, int idx_offset, bool vec) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const bf16* row = logits + static_cast<size_t>(blockIdx.x) * ld;
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  if (vec) {
+    for (int c = threadIdx.x; c < (cols >> 3); c += blockDim.x) {
+      const uint4 a = reinterpret_cast<const uint4*>(row)[c];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        argmax_merge(v, idx, bf16_lo(aw[e]), c * 8 + 2 * e);
+        argmax_merge(v, idx, bf16_hi(aw[e]), c * 8 + 2 * e + 1);
+      }
+    }
+    for (int c = (cols & ~7) + threadIdx.x; c < cols; c += blockDim.x) argmax_merge(v, idx, __bfloat162float(row[c]), c);
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) argmax_merge(v, idx, __bfloat162float(row[c]), c);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    argmax_merge(v, idx, ov, oi);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) { sv[warp] = v; si[warp] = idx; }
+  __syncthreads();
+  if (warp == 0) {
+    v = lane < nw ? sv[lane] : -INFINITY;
+    idx = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      argmax_merge(v, idx, ov, oi);
+    }
+    if (lane == 0) {
+      best_val[blockIdx.x] = v;
+      best_idx[blockIdx.x] = idx + idx_offset;
+    }
+  }
+}
+__global__ void argmax_combine_kernel(const float* __restrict__ vals, const int* __restrict__ idx,
+                                      int* __restrict__ out_idx, int parts, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float v = -INFINITY;
+  int i = 0x7fffffff;
+  for (int p = 0; p < parts; ++p) argmax_merge(v, i, vals[static_cast<size_t>(p) * rows + r], idx[static_cast<size_t>(p) * rows + r]);
+  out_idx[r] = i;
+}
+
+}  // namespace
+
+int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, int N, float eps, cudaStream_t st) {
+  if (!x || !y || !w || M < 0 || N <= 0) return TEENY_ERR_BAD_ARG;
+  if (M == 0) return TEENY_OK;
+  rms_norm_f32_kernel<<<M, 128, 0, st>>>(x, y, w, rrms, N, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
+                  float eps, cudaStream_t st) {
+  return launch_rms_bf16<false>(x, ldx, nullptr, y, ldy, w, rrms, M, N, eps, st);
+}
+int add_rms_norm_bf16(const bf16* x, bf16* residual, bf16* y, const bf16* w, int M, int N, float eps,
+                      cudaStream_t st) {
+  return launch_rms_bf16<true>(x, N, residual, y, N, w, nullptr, M, N, eps, st);
+}
+int silu_f32(const float* x, float* y, long long n, cudaStream_t st) { return launch_ew_f32<OpSilu, false>(x, nullptr, y, n, st); }
+int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st) { return launch_ew_bf16<OpSilu, false>(x, nullptr, y, n, st); }
+int mul_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st) { return launch_ew_f32<OpMul, true>(a, b, o, n, st); }
+int mul_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st) { return launch_ew_bf16<OpMul, true>(a, b, o, n, st); }
+int add_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st) { return launch_ew_f32<OpAdd, true>(a, b, o, n, st); }
+int add_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st) { return launch_ew_bf16<OpAdd, true>(a, b, o, n, st); }
+
+int softmax_f32(const float* x, float* y, int rows, int cols, cudaStream_t st) {
+  if (!x || !y || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  softmax_kernel<float><<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+int softmax_bf16(const bf16* x, bf16* y, int rows, int cols, cudaStream_t st) {
+  if (!x || !y || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  softmax_kernel<bf16><<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, cols);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int silu_mul_bf16(const bf16* gate_up, long long ld, bf16* out, int T, int inter, cudaStream_t st) {
+  if (!gate_up || !out || T < 0 || inter <= 0) return TEENY_ERR_BAD_ARG;
+  if (T == 0) return TEENY_OK;
+  const bool vec = (inter % 8 == 0) && (ld % 8 == 0) && aligned16(gate_up) && aligned16(out);
+  if (vec)
+    silu_mul_bf16_kernel<<<ew_grid(static_cast<long long>(T) * (inter / 8), kEwThreads), kEwThreads, 0, st>>>(gate_up, ld, out, T, inter);
+  else
+    silu_mul_bf16_scalar_kernel<<<ew_grid(static_cast<long long>(T) * inter, kEwThreads), kEwThreads, 0, st>>>(gate_up, ld, out, T, inter);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int embedding_bf16(const int* ids, const bf16* table, bf16* out, int T, int hidden, int vocab, cudaStream_t st) {
+  if (!ids || !table || !out || T < 0 || hidden <= 0 || vocab <= 0) return TEENY_ERR_BAD_ARG;
+  if (T == 0) return TEENY_OK;
+  const bool vec = (hidden % 8 == 0) && aligned16(table) && aligned16(out);
+  embedding_bf16_kernel<<<T, 128, 0, st>>>(ids, table, out, T, hidden, vocab, vec);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int rope_table_bf16(const float* inv_freq, bf16* cos_t, bf16* sin_t, int max_pos, int D, cudaStream_t st) {
+  if (!inv_freq || !cos_t || !sin_t || max_pos <= 0 || D <= 0 || (D & 1)) return TEENY_ERR_BAD_ARG;
+  rope_table_kernel<<<ew_grid(static_cast<long long>(max_pos) * (D / 2), kEwThreads), kEwThreads, 0, st>>>(inv_freq, cos_t, sin_t, max_pos, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int qk_norm_rope_kv_bf16(bf16* qkv, long long ld, const bf16* q_w, const bf16* k_w, const bf16* cos_t,
+                         const bf16* sin_t, bf16* k_cache, bf16* v_cache, int T, int S, int Hq, int Hkv, int D,
+                         int max_len, int pos0, const int* pos0_dev, float eps, cudaStream_t st) {
+  if (!qkv || !q_w || !k_w || !cos_t || !sin_t || !k_cache || !v_cache || T < 0 || S <= 0 || Hq <= 0 || Hkv <= 0 ||
+      max_len <= 0)
+    return TEENY_ERR_BAD_ARG;
+  if (D != 128) return TEENY_ERR_BAD_ARG;  // head_dim of every Qwen3 size
+  if ((ld % 4) || (reinterpret_cast<uintptr_t>(qkv) & 7)) return TEENY_ERR_ALIGNMENT;
+  if (T == 0) return TEENY_OK;
+  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const long long blocks = (warps + 7) / 8;
+  if (blocks > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
+  qk_norm_rope_kv_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(qkv, ld, q_w, k_w, cos_t, sin_t, k_cache, v_cache,
+                                                                   T, S, Hq, Hkv, max_len, pos0, pos0_dev, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int argmax_bf16(const bf16* logits, long long ld, float* best_val, int* best_idx, int rows, int cols, int idx_offset,
+                cudaStream_t st) {
+  if (!logits || !best_val || !best_idx || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  const bool vec = aligned16(logits) && (ld % 8 == 0);
+  argmax_bf16_kernel<<<rows, 1024, 0, st>>>(logits, ld, best_val, best_idx, cols, idx_offset, vec);
+  return static_cast<int>(cudaGetLastError());
+}
+int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, cudaStream_t st) {
+  if (!vals || !idx || !out_idx || parts <= 0 || rows < 0) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  argmax_combine_kernel<<<(rows + 127) / 128, 128, 0, st>>>(vals, idx, out_idx, parts, rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace teeny

@@ -1,0 +1,470 @@
+// bf16 GEMM for sm_100a: D[i, j] = sum_k P[i, k] * Q[j, k] with f32 accumulation in tensor memory.
+//
+// One persistent, warp-specialised kernel (one CTA per SM):
+//   warp 0      TMA producer: P tile [128 x 64] and Q tile [BN x 64] per k-block into a ring of shared-memory
+//               stages (128-byte swizzle), completion on `full` mbarriers;
+//   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four times per k-block,
+//               tcgen05.commit releases the stage (`empty`) and finally publishes the accumulator (`acc_full`);
+//   warps 2-5   epilogue: tcgen05.ld the 128 x BN f32 accumulator (thread = row), convert to bf16, store.
+// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue of tile t overlaps the main loop
+// of tile t+1.
+//
+// Two operand assignments share the kernel:
+//   normal  P = activations X [M, K], Q = weights W [N, K]  -> Y[m, n] tile 128 x BN
+//   swapped P = weights W [N, K],     Q = activations X     -> Y^T tile; used when M is small (decode), so the
+//           128-row MMA dimension is filled by weight rows and the token count only sets N of the MMA.
+// B may also be MN-major ([K, N] row-major, the matmul_forward layout): its tiles are [64 k][64 n] boxes and the
+// descriptor uses the MN-major canonical layout.
+//
+// Split-K (small-M shapes that would leave SMs idle): each split writes its f32 partial tile to scratch, then
+// bumps a per-tile counter; the CTA that arrives last sums the partials in split order (deterministic), writes
+// bf16 and resets the counter.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+constexpr int kBM = 128;  // rows of P per tile (MMA M)
+constexpr int kBK = 64;   // k-block: 64 bf16 = one 128-byte swizzle row
+constexpr int kNumThreads = 192;
+constexpr int kEpilogueThreads = 128;
+
+struct GemmArgs {
+  int M, N, K;            // Y[M, N] = X[M, K] * W[N, K]^T
+  int ldy;                // row stride of Y in elements
+  bf16* y;
+  const bf16* bias;       // [N] or null
+  int tiles_p, tiles_q;   // tiles along P rows and along Q rows
+  int k_blocks;           // ceil(K / 64)
+  int split_k;            // >= 1
+  int kb_per_split;       // k-blocks per split
+  float* partial;         // split-K scratch: [tiles][split][BN][128] f32
+  int* counters;          // split-K scratch: [tiles]
+  int* err;
+};
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kStageP = kBM * kBK * 2;
+  static constexpr int kStageQ = BN * kBK * 2;
+  static constexpr int kStageBytes = kStageP + kStageQ;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_p, int tiles_q, int& tp, int& tq) {
+  // Grouped raster: 8 consecutive P-tiles share each Q-tile before moving on, so the tiles in flight across
+  // the SMs reuse both operands out of L2.
+  constexpr int kGroup = 8;
+  const int per_group = kGroup * tiles_q;
+  const int g = tile / per_group;
+  const int first_p = g * kGroup;
+  const int size_p = min(kGroup, tiles_p - first_p);
+  const int r = tile - g * per_group;
+  tp = first_p + r % size_p;
+  tq = r / size_p;
+}
+
+template <int BN, bool SWAP, bool Q_MN_MAJOR>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
+                 const GemmArgs args) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  // barrier layout (8 B each): full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr, flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + b); };
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
+  const uint32_t tmem_slot = bar_base + 8u * (2 * Cfg::kStages + 4);
+  const uint32_t flag_slot = tmem_slot + 4;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 4));
+  volatile int* flag_ptr = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
+  (void)flag_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int* err = args.err;
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_p);
+    tma_prefetch_desc(&tmap_q);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full_bar(b), 1);
+      mbar_init(acc_empty_bar(b), kEpilogueThreads / 32);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const int num_tiles = args.tiles_p * args.tiles_q;
+  const int num_work = num_tiles * args.split_k;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x) {
+        const int tile = w / args.split_k;
+        const int split = w - tile * args.split_k;
+        int tp, tq;
+        tile_coords(tile, args.tiles_p, args.tiles_q, tp, tq);
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) { ok = false; break; }
+          const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t sq = sp + Cfg::kStageP;
+          mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          tma_load_2d(sp, &tmap_p, full_bar(stage), kb * kBK, tp * kBM);
+          if constexpr (Q_MN_MAJOR) {
+            // Q is [K, N] row-major: boxes of [64 k][64 n]; BN/64 boxes per stage, 8 KB each.
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sq + c * (kBK * 128), &tmap_q, full_bar(stage), tq * BN + c * 64, kb * kBK);
+          } else {
+            tma_load_2d(sq, &tmap_q, full_bar(stage), kb * kBK, tq * BN);
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, Q_MN_MAJOR);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x, ++local) {
+        const int tile = w / args.split_k;
+        const int split = w - tile * args.split_k;
+        const int kb0 = split * args.kb_per_split;
+        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, err, DEVERR_GEMM_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t sq = sp + Cfg::kStageP;
+          const uint64_t pdesc = make_smem_desc_sw128(sp, 16, 1024);
+          const uint64_t qdesc = Q_MN_MAJOR ? make_smem_desc_sw128(sq, kBK * 128, 1024)
+                                            : make_smem_desc_sw128(sq, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            // K-major: 16 elements along k = 32 bytes inside the swizzled row -> +2 in the address field.
+            // MN-major: 16 k = two 8-row groups of 1024 bytes -> +128.
+            const uint64_t pd = pdesc + static_cast<uint64_t>(k * 2);
+            const uint64_t qd = qdesc + static_cast<uint64_t>(Q_MN_MAJOR ? k * 128 : k * 2);
+            umma_bf16_ss(d_tmem, pd, qd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(acc_full_bar(buf));
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp % 4) ----------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    bool ok = true;
+    int local = 0;
+    for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x, ++local) {
+      const int tile = w / args.split_k;
+      const int split = w - tile * args.split_k;
+      int tp, tq;
+      tile_coords(tile, args.tiles_p, args.tiles_q, tp, tq);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(acc_full_bar(buf), acc_phase, err, DEVERR_GEMM_EPILOGUE)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const int prow = tp * kBM + row_in_tile;  // index along P rows
+      constexpr int kChunk = (BN >= 32) ? 32 : 16;
+
+      if (args.split_k == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kChunk) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
+          tmem_wait_ld();
+          const int qcol0 = tq * BN + c0;  // index along Q rows
+          if constexpr (!SWAP) {
+            // thread owns Y[prow, qcol0 .. qcol0+kChunk)
+            if (prow < args.M) {
+              bf16* dst = args.y + static_cast<size_t>(prow) * args.ldy + qcol0;
+              const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (qcol0 + kChunk <= args.N);
+              if (vec_ok) {
+#pragma unroll
+                for (int v = 0; v < kChunk / 8; ++v) {
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    f[e] = __uint_as_float(r[v * 8 + e]);
+                    if (args.bias) f[e] += __bfloat162float(args.bias[qcol0 + v * 8 + e]);
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                  o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                  *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < kChunk; ++e) {
+                  const int n = qcol0 + e;
+                  if (n < args.N) {
+                    float f = __uint_as_float(r[e]);
+                    if (args.bias) f += __bfloat162float(args.bias[n]);
+                    dst[e] = __float2bfloat16_rn(f);
+                  }
+                }
+              }
+            }
+          } else {
+            // thread owns Y[qcol0 + e, prow] for e in the chunk (prow indexes N); lanes are consecutive in n.
+            if (prow < args.N) {
+              const float b = args.bias ? __bfloat162float(args.bias[prow]) : 0.0f;
+#pragma unroll
+              for (int e = 0; e < kChunk; ++e) {
+                const int m = qcol0 + e;
+                if (m < args.M)
+                  args.y[static_cast<size_t>(m) * args.ldy + prow] = __float2bfloat16_rn(__uint_as_float(r[e]) + b);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+      } else {
+        // ---- split-K: f32 partial to scratch, last arriver reduces ----
+        float* part = args.partial + (static_cast<size_t>(tile) * args.split_k + split) * (BN * kBM);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += kChunk) {
+          uint32_t r[kChunk];
+          if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < kChunk; ++e) __stcg(part + (c0 + e) * kBM + row_in_tile, __uint_as_float(r[e]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+        __threadfence();
+        named_barrier_sync(1, kEpilogueThreads);
+        if (epi_tid == 0) {
+          const int old = atomicAdd(args.counters + tile, 1);
+          *flag_ptr = (old == args.split_k - 1) ? 1 : 0;
+        }
+        named_barrier_sync(1, kEpilogueThreads);
+        const bool last = (*flag_ptr != 0);
+        named_barrier_sync(1, kEpilogueThreads);  // flag consumed before the next work item rewrites it
+        if (last) {
+          __threadfence();
+          const float* base = args.partial + static_cast<size_t>(tile) * args.split_k * (BN * kBM);
+#pragma unroll 1
+          for (int c = 0; c < BN; ++c) {
+            float acc = 0.0f;
+            for (int s = 0; s < args.split_k; ++s)
+              acc += __ldcg(base + static_cast<size_t>(s) * (BN * kBM) + c * kBM + row_in_tile);
+            const int qidx = tq * BN + c;
+            if constexpr (!SWAP) {
+              if (prow < args.M && qidx < args.N) {
+                if (args.bias) acc += __bfloat162float(args.bias[qidx]);
+                args.y[static_cast<size_t>(prow) * args.ldy + qidx] = __float2bfloat16_rn(acc);
+              }
+            } else {
+              if (prow < args.N && qidx < args.M) {
+                if (args.bias) acc += __bfloat162float(args.bias[prow]);
+                args.y[static_cast<size_t>(qidx) * args.ldy + prow] = __float2bfloat16_rn(acc);
+              }
+            }
+          }
+          if (epi_tid == 0) args.counters[tile] = 0;  // ready for the next launch
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile int*>(err) != 0) {
+      // A wait gave up: let copies / MMAs that are still in flight drain before the memory is released.
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host launcher
+// ------------------------------------------------------------------------------------------------
+template <int BN, bool SWAP, bool Q_MN>
+int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs& a, int grid, cudaStream_t st) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, SWAP, Q_MN>;
+  static bool attr_set = false;  // per template instance; cudaFuncSetAttribute is per device but idempotent
+  static int attr_device = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set || attr_device != dev) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+    attr_device = dev;
+  }
+  kern<<<grid, kNumThreads, Cfg::kSmemBytes, st>>>(tp, tq, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+// Largest token count that takes the swapped (weights on the 128-row MMA side) path.
+constexpr int kSwapMaxM = 128;
+
+static int swap_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
+
+// Scratch layout: [counters: one int per 128-row weight tile, padded to 256 B][f32 partial tiles].
+static size_t scratch_counter_bytes(int N) {
+  return (static_cast<size_t>(ceil_div(N, kBM)) * sizeof(int) + 255) & ~static_cast<size_t>(255);
+}
+
+size_t gemm_bf16_scratch_bytes(int M, int N, int K) {
+  (void)K;
+  if (M > kSwapMaxM) return 0;  // large-M shapes never split K
+  const size_t max_work = static_cast<size_t>(kGemmMaxWorkPerSm) * sm_count();
+  return scratch_counter_bytes(N) + max_work * swap_bn(M) * kBM * sizeof(float);
+}
+
+// Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
+int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
+              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 7) || (ldw & 7))
+    return TEENY_ERR_ALIGNMENT;
+
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
+  a.k_blocks = ceil_div(K, kBK);
+  a.split_k = 1;
+  a.kb_per_split = a.k_blocks;
+  a.err = device_error_word();
+  const int sms = sm_count();
+
+  CUtensorMap tmx, tmw;
+  const bool swap = (!w_is_kn) && (M <= kSwapMaxM);
+  int bn;
+  if (swap) {
+    bn = swap_bn(M);
+  } else if (w_is_kn) {
+    bn = (N <= 64) ? 64 : 128;
+  } else {
+    bn = (N <= 128 || (static_cast<long long>(ceil_div(M, kBM)) * ceil_div(N, 256) < sms)) ? 128 : 256;
+  }
+
+  // activations X: K-major rows; box = 64 k x (128 rows normally, bn rows when swapped)
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+    const uint32_t box[2] = {kBK, static_cast<uint32_t>(swap ? bn : kBM)};
+    int rc = encode_tensor_map_bf16(&tmx, x, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  if (w_is_kn) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldw) * 2};
+    const uint32_t box[2] = {64, kBK};
+    int rc = encode_tensor_map_bf16(&tmw, w, 2, dims, strides, box);
+    if (rc) return rc;
+  } else {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldw) * 2};
+    const uint32_t box[2] = {kBK, static_cast<uint32_t>(swap ? kBM : bn)};
+    int rc = encode_tensor_map_bf16(&tmw, w, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+
+  if (swap) {
+    a.tiles_p = ceil_div(N, kBM);
+    a.tiles_q = 1;
+    // Split K when whole tiles would leave SMs idle or the last wave mostly empty: pick the split count with
+    // the best wave efficiency (work / (waves * SMs)), charging a little for each extra partial pass.
+    const int tiles = a.tiles_p;
+    int split = 1;
+    if (scratch && scratch_bytes >= gemm_bf16_scratch_bytes(M, N, K)) {
+      const int max_split = min(kGemmMaxSplitK, a.k_blocks / 4);
+      auto score = [&](int s) {
+        const int kbps = ceil_div(a.k_blocks, s);
+        const int work = tiles * ceil_div(a.k_blocks, kbps);
+        const int waves = ceil_div(work, sms);
+        return static_cast<float>(work) / (static_cast<float>(waves) * sms) - 0.01f * (s - 1);
+      };
+      float best = score(1);
+      for (int s = 2; s <= max_split; ++s) {
+        if (static_cast<long long>(tiles) * s > static_cast<long long>(kGemmMaxWorkPerSm) * sms) break;
+        const float sc = score(s);
+        if (sc > best + 0.03f) { best = sc; split = s; }
+      }
+    }
+    a.kb_per_split = ceil_div(a.k_blocks, split);
+    a.split_k = ceil_div(a.k_blocks, a.kb_per_split);  // drop empty splits
+    if (a.split_k > 1) {
+      a.counters = static_cast<int*>(scratch);
+      a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + scratch_counter_bytes(N));
+    }
+    const int work = tiles * a.split_k;
+    const int grid = work < sms ? work : sms;
+    switch (bn) {
+      case 16: return launch_variant<16, true, false>(tmw, tmx, a, grid, stream);
+      case 32: return launch_variant<32, true, false>(tmw, tmx, a, grid, stream);
+      case 64: return launch_variant<64, true, false>(tmw, tmx, a, grid, stream);
+      default: return launch_variant<128, true, false>(tmw, tmx, a, grid, stream);
+    }
+  }
+
+  a.tiles_p = ceil_div(M, kBM);
+  a.tiles_q = ceil_div(N, bn);
+  const int work = a.tiles_p * a.tiles_q;
+  const int grid = work < sms ? work : sms;
+  if (w_is_kn) {
+    if (bn == 64) return launch_variant<64, false, true>(tmx, tmw, a, grid, stream);
+    return launch_variant<128, false, true>(tmx, tmw, a, grid, stream);
+  }
+  if (bn == 128) return launch_variant<128, false, false>(tmx, tmw, a, grid, stream);
+  return launch_variant<256, false, false>(tmx, tmw, a, grid, stream);
+}
+
+}  // namespace teeny

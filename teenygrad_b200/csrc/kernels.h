@@ -1,0 +1,81 @@
+// Internal launch functions behind the C ABI (include/teeny_b200.h).  Every function enqueues work on
+// `stream` and returns 0, a negative TEENY_ERR_* code, or a positive cudaError_t.  None allocates memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace teeny {
+
+typedef __nv_bfloat16 bf16;
+
+// ---- GEMM --------------------------------------------------------------------------------------
+constexpr int kGemmMaxSplitK = 16;     // most k-splits per output tile
+constexpr int kGemmMaxWorkPerSm = 8;   // split-K is only used while tiles*splits <= this * SM count
+
+size_t gemm_bf16_scratch_bytes(int M, int N, int K);
+int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
+              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream);
+// f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
+int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
+             const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);
+// bf16 GEMM on CUDA cores for shapes the TMA path cannot take (unaligned strides / pointers).
+int gemm_bf16_generic(const bf16* a, long long sam, long long sak, const bf16* b, long long sbk, long long sbn,
+                      const bf16* bias, bf16* c, long long scm, long long scn, int M, int N, int K,
+                      cudaStream_t stream);
+
+// ---- attention ---------------------------------------------------------------------------------
+struct AttnShape {
+  int B, Hq, Hkv, Sq, Skv, D;
+  long long q_sb, q_sh, q_ss;   // element strides of Q (batch, head, sequence); D is contiguous
+  long long k_sb, k_sh, k_ss;
+  long long v_sb, v_sh, v_ss;
+  long long o_sb, o_sh, o_ss;
+  float scale;
+  int causal;
+};
+int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, float* lse, const AttnShape& s,
+                           cudaStream_t stream);
+size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
+// One query token per sequence against the first *kv_len_dev (or kv_len if the pointer is null) cache entries.
+int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
+                          const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream);
+template <typename T>
+int attention_generic(const T* q, const T* k, const T* v, T* o, float* lse, const AttnShape& s, cudaStream_t stream);
+
+// ---- normalisation / elementwise ----------------------------------------------------------------
+int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, int N, float eps, cudaStream_t st);
+// bf16 with the Qwen3 rounding points: f32 statistics, round to bf16, then multiply by the bf16 weight.
+int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
+                  float eps, cudaStream_t st);
+// residual <- bf16(residual + x); y <- rms_norm(residual) (same rounding as rms_norm_bf16).
+int add_rms_norm_bf16(const bf16* x, bf16* residual, bf16* y, const bf16* w, int M, int N, float eps, cudaStream_t st);
+int silu_f32(const float* x, float* y, long long n, cudaStream_t st);
+int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st);
+int mul_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st);
+int mul_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st);
+int add_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st);
+int add_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st);
+int softmax_f32(const float* x, float* y, int rows, int cols, cudaStream_t st);
+int softmax_bf16(const bf16* x, bf16* y, int rows, int cols, cudaStream_t st);
+// out[t, i] = bf16(bf16(silu(gate_up[t, i])) * gate_up[t, inter + i])
+int silu_mul_bf16(const bf16* gate_up, long long ld, bf16* out, int T, int inter, cudaStream_t st);
+int embedding_bf16(const int* ids, const bf16* table, bf16* out, int T, int hidden, int vocab, cudaStream_t st);
+// cos/sin tables [max_pos, D] bf16 from f32 inv_freq[D/2]: angle = pos * inv_freq in f32, cos/sin, one rounding.
+int rope_table_bf16(const float* inv_freq, bf16* cos_t, bf16* sin_t, int max_pos, int D, cudaStream_t st);
+// Per-head RMSNorm of q and k, rotary embedding, and KV-cache append, reading the fused QKV projection.
+//   qkv [T, (Hq + 2 Hkv) * D]; token t belongs to sequence t / S at position pos0 + t % S, where
+//   pos0 = *pos0_dev if the pointer is non-null else pos0.  q is rewritten in place; k (normed + rotated) and v go
+//   to the caches laid out [B, Hkv, max_len, D].
+int qk_norm_rope_kv_bf16(bf16* qkv, long long ld, const bf16* q_w, const bf16* k_w, const bf16* cos_t,
+                         const bf16* sin_t, bf16* k_cache, bf16* v_cache, int T, int S, int Hq, int Hkv, int D,
+                         int max_len, int pos0, const int* pos0_dev, float eps, cudaStream_t st);
+// Row argmax with lowest index on ties; writes value (f32) and index + idx_offset.
+int argmax_bf16(const bf16* logits, long long ld, float* best_val, int* best_idx, int rows, int cols, int idx_offset,
+                cudaStream_t st);
+// Combine `parts` candidate (value, index) pairs per row: vals/idx [parts, rows] -> out_idx [rows].
+int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, cudaStream_t st);
+
+}  // namespace teeny
