@@ -1,0 +1,90 @@
+/*
+ * teeny_qwen3 -- C ABI of the Qwen3 decoder runner and its tensor-parallel plumbing (libteeny_b200.so).
+ *
+ * The runner is this backend's counterpart of the reference's model executor for one model family:
+ *   load / forward / capture / replay  <->  CudaModel::load, LoadedModel::forward, capture_graph, CudaGraphModel::run
+ *                                           (drivers/teeny-cuda/src/model/mod.rs:231, 524, 1245, 1799)
+ *   weights by name                    <->  LoadedModel::param_info_named / load_param_f32 (model/mod.rs:449, 476)
+ * executing the Qwen3 op sequence the reference records in support/teeny-torch/tests/data/qwen3_{1,2,3}.bin.gz
+ * (the reference itself runs that graph with PyTorch on the CPU, support/teeny-torch/python/teenygrad/atlas/module.py:42-45).
+ * The reference has no multi-GPU code; the teeny_tp_* functions have no counterpart there.
+ *
+ * All pointers are device pointers owned by the caller unless stated; nothing here allocates device memory.
+ * Status codes are those of teeny_b200.h.
+ */
+#ifndef TEENY_QWEN3_H_
+#define TEENY_QWEN3_H_
+
+#include "teeny_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+  int num_layers, hidden, num_q_heads, num_kv_heads, head_dim, intermediate, vocab;
+  float eps;          /* RMSNorm epsilon (1e-6) */
+  int max_batch;      /* sequences per generation */
+  int max_len;        /* KV-cache capacity per sequence (prompt + generated) */
+  int max_tokens;     /* most tokens in one prefill call (batch * prompt length) */
+  int max_new_tokens; /* capacity of the generated-token history */
+  int tp_rank, tp_size;
+} teeny_qwen3_config;
+
+typedef struct teeny_qwen3 teeny_qwen3;
+
+/* Weight slots.  Per-layer tensors are this rank's shard, fused where the layer fuses them (row-major bf16):
+ *   QKV      [(Hq/tp + 2 Hkv/tp) * 128, hidden]   rows: local q heads, then local k heads, then local v heads
+ *   O        [hidden, Hq/tp * 128]                 column slice of o_proj (row-parallel)
+ *   GATE_UP  [2 * intermediate/tp, hidden]         rows: local gate rows, then local up rows
+ *   DOWN     [hidden, intermediate/tp]             column slice of down_proj (row-parallel)
+ *   INPUT_LN, POST_LN [hidden]; Q_NORM, K_NORM [128]
+ * Model-level: EMBED [vocab, hidden] (replicated), FINAL_NORM [hidden], LM_HEAD [vocab/tp, hidden] (row slice; for
+ * tied embeddings a slice of EMBED), INV_FREQ f32 [64] (the rotary inv_freq buffer of the model). */
+enum {
+  TEENY_QWEN3_W_QKV = 0, TEENY_QWEN3_W_O, TEENY_QWEN3_W_GATE_UP, TEENY_QWEN3_W_DOWN, TEENY_QWEN3_W_INPUT_LN,
+  TEENY_QWEN3_W_POST_LN, TEENY_QWEN3_W_Q_NORM, TEENY_QWEN3_W_K_NORM,
+  TEENY_QWEN3_W_EMBED = 100, TEENY_QWEN3_W_FINAL_NORM, TEENY_QWEN3_W_LM_HEAD, TEENY_QWEN3_W_INV_FREQ
+};
+enum {
+  TEENY_QWEN3_BUF_LOGITS = 0, /* bf16 [batch, vocab/tp]: LM-head output of the last step (this rank's slice) */
+  TEENY_QWEN3_BUF_NEXT_IDS,   /* int32 [batch]: token chosen by the last step (input of the next) */
+  TEENY_QWEN3_BUF_HISTORY,    /* int32 [max_new_tokens, batch]: every token generated so far */
+  TEENY_QWEN3_BUF_STATE,      /* int32 [3]: next position, live KV length of the coming step, tokens generated */
+  TEENY_QWEN3_BUF_HIDDEN,     /* bf16 [batch, hidden]: final-norm output of the last step */
+  TEENY_QWEN3_BUF_K_CACHE,    /* bf16 [layers, max_batch, Hkv/tp, max_len, 128] */
+  TEENY_QWEN3_BUF_V_CACHE
+};
+
+/* Bytes of workspace (activations, KV cache, RoPE tables, scratch, generation state) for this configuration;
+ * 0 if the configuration is not supported (head_dim must be 128; heads, intermediate and vocab divisible by tp). */
+size_t teeny_qwen3_workspace_bytes(const teeny_qwen3_config* cfg);
+/* Creates the runner over a caller-allocated, 256-byte aligned workspace.  tp_comm: handle from teeny_tp_init when
+ * tp_size > 1, else NULL.  Only the small host-side object is allocated here; free it with teeny_qwen3_destroy. */
+int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t workspace_bytes, void* tp_comm,
+                       teeny_stream_t stream, teeny_qwen3** out);
+void teeny_qwen3_destroy(teeny_qwen3* model);
+int teeny_qwen3_set_weight(teeny_qwen3* model, int layer, int which, const void* device_ptr);
+/* Prefill: ids int32 [B, S] on the device.  Fills the KV cache, picks the first generated token of every sequence
+ * (greedy, lowest index on ties) and records it as history[0]. */
+int teeny_qwen3_prefill(teeny_qwen3* model, const int* ids, int B, int S, teeny_stream_t stream);
+/* One greedy decode step for the batch of the last prefill: consumes NEXT_IDS, appends to the cache, produces the
+ * next token.  teeny_qwen3_decode launches the kernels directly; capture_decode records one step into a CUDA graph
+ * (position and length live in device memory, so one graph serves every step) and decode_replay launches it. */
+int teeny_qwen3_decode(teeny_qwen3* model, teeny_stream_t stream);
+int teeny_qwen3_capture_decode(teeny_qwen3* model, teeny_stream_t stream);
+int teeny_qwen3_decode_replay(teeny_qwen3* model, teeny_stream_t stream);
+/* Device address of one of the runner's buffers inside the workspace (see enum above). */
+void* teeny_qwen3_buffer(teeny_qwen3* model, int which);
+
+/* Tensor-parallel plumbing over NCCL (loaded at run time; the process's already-loaded libnccl is reused).
+ * Rank 0 calls teeny_tp_unique_id and ships the 128 bytes to the other ranks by any host channel. */
+int teeny_tp_unique_id(void* out128);
+int teeny_tp_init(const void* id128, int rank, int world, void** comm_out);
+int teeny_tp_destroy(void* comm);
+int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TEENY_QWEN3_H_ */

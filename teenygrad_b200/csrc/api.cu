@@ -246,7 +246,7 @@ int softmax_forward_entry_point_bf16(const teeny_bf16* x, teeny_bf16* y, int r, 
 
 int teeny_add_rms_norm_bf16(const teeny_bf16* x, teeny_bf16* residual, teeny_bf16* y, const teeny_bf16* w, int M, int N,
                             float eps, teeny_stream_t s) {
-  return add_rms_norm_bf16(B(x), B(residual), B(y), B(w), M, N, eps, S(s));
+  return add_rms_norm_bf16(B(x), N, B(residual), N, B(y), N, B(w), M, N, eps, S(s));
 }
 int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out, int T, int inter, teeny_stream_t s) {
   return silu_mul_bf16(B(gate_up), ld, B(out), T, inter, S(s));

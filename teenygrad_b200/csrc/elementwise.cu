@@ -122,12 +122,12 @@ __global__ void rms_norm_f32_kernel(const float* __restrict__ x, float* __restri
 // VPT = 16-byte vectors per thread (N <= VPT * 8 * blockDim).  ADD: x is added into `res` first (bf16 add).
 template <int VPT, bool ADD>
 __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
-                                     bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
+                                     long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
                                      float* __restrict__ rrms, int N, float eps) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
-  uint4* rr4 = ADD ? reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldx) : nullptr;
+  uint4* rr4 = ADD ? reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr) : nullptr;
   const int nv = N >> 3;
   float v[VPT][8];
   float sq = 0.0f;
@@ -188,12 +188,12 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
 // Any N / alignment: scalar accesses, row re-read from L2 in the second phase.
 template <bool ADD>
 __global__ void rms_norm_bf16_scalar_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
-                                            bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
+                                            long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
                                             float* __restrict__ rrms, int N, float eps) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   const bf16* xr = x + static_cast<size_t>(row) * ldx;
-  bf16* rs = ADD ? res + static_cast<size_t>(row) * ldx : nullptr;
+  bf16* rs = ADD ? res + static_cast<size_t>(row) * ldr : nullptr;
   float sq = 0.0f;
   for (int c = threadIdx.x; c < N; c += blockDim.x) {
     float h = __bfloat162float(xr[c]);
@@ -214,12 +214,12 @@ __global__ void rms_norm_bf16_scalar_kernel(const bf16* __restrict__ x, long lon
 }
 
 template <bool ADD>
-int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, bf16* y, long long ldy, const bf16* w, float* rrms,
+int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16* y, long long ldy, const bf16* w, float* rrms,
                     int M, int N, float eps, cudaStream_t st) {
   if (!x || !y || !w || (ADD && !res) || M < 0 || N <= 0) return TEENY_ERR_BAD_ARG;
   if (M == 0) return TEENY_OK;
   const bool vec = (N % 8 == 0) && (ldx % 8 == 0) && (ldy % 8 == 0) && aligned16(x) && aligned16(y) && aligned16(w) &&
-                   (!ADD || aligned16(res));
+                   (!ADD || (aligned16(res) && ldr % 8 == 0));
   const int nv = N / 8;
   if (vec && nv <= 8 * 256) {
     int threads = 128;
@@ -228,14 +228,14 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, bf16* y, long long 
     else if (nv > 4 * 128) threads = 256;
     const int vpt = (nv + threads - 1) / threads;
 #define TEENY_RMS_CASE(V)                                                                                    \
-  rms_norm_bf16_kernel<V, ADD><<<M, threads, 0, st>>>(x, ldx, res, y, ldy, w, rrms, N, eps)
+  rms_norm_bf16_kernel<V, ADD><<<M, threads, 0, st>>>(x, ldx, res, ldr, y, ldy, w, rrms, N, eps)
     if (vpt <= 1) TEENY_RMS_CASE(1);
     else if (vpt <= 2) TEENY_RMS_CASE(2);
     else if (vpt <= 4) TEENY_RMS_CASE(4);
     else TEENY_RMS_CASE(8);
 #undef TEENY_RMS_CASE
   } else {
-    rms_norm_bf16_scalar_kernel<ADD><<<M, 256, 0, st>>>(x, ldx, res, y, ldy, w, rrms, N, eps);
+    rms_norm_bf16_scalar_kernel<ADD><<<M, 256, 0, st>>>(x, ldx, res, ldr, y, ldy, w, rrms, N, eps);
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -464,11 +464,11 @@ int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, i
 }
 int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
                   float eps, cudaStream_t st) {
-  return launch_rms_bf16<false>(x, ldx, nullptr, y, ldy, w, rrms, M, N, eps, st);
+  return launch_rms_bf16<false>(x, ldx, nullptr, 0, y, ldy, w, rrms, M, N, eps, st);
 }
-int add_rms_norm_bf16(const bf16* x, bf16* residual, bf16* y, const bf16* w, int M, int N, float eps,
-                      cudaStream_t st) {
-  return launch_rms_bf16<true>(x, N, residual, y, N, w, nullptr, M, N, eps, st);
+int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ldr, bf16* y, long long ldy,
+                      const bf16* w, int M, int N, float eps, cudaStream_t st) {
+  return launch_rms_bf16<true>(x, ldx, residual, ldr, y, ldy, w, nullptr, M, N, eps, st);
 }
 int silu_f32(const float* x, float* y, long long n, cudaStream_t st) { return launch_ew_f32<OpSilu, false>(x, nullptr, y, n, st); }
 int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st) { return launch_ew_bf16<OpSilu, false>(x, nullptr, y, n, st); }

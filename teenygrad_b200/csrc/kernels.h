@@ -51,7 +51,8 @@ int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, i
 int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
                   float eps, cudaStream_t st);
 // residual <- bf16(residual + x); y <- rms_norm(residual) (same rounding as rms_norm_bf16).
-int add_rms_norm_bf16(const bf16* x, bf16* residual, bf16* y, const bf16* w, int M, int N, float eps, cudaStream_t st);
+int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ldr, bf16* y, long long ldy,
+                      const bf16* w, int M, int N, float eps, cudaStream_t st);
 int silu_f32(const float* x, float* y, long long n, cudaStream_t st);
 int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st);
 int mul_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st);

@@ -1,0 +1,489 @@
+// Qwen3 decoder runner: the host-side executor that strings the kernels of this library into prefill and decode
+// steps, with Megatron-style tensor parallelism (one process per GPU, one NCCL all-reduce after each row-parallel
+// projection) and CUDA-graph replay of the decode step.
+//
+// It plays the role of the reference's model executor -- LoadedModel::forward walks the lowered graph and launches
+// one kernel per node, capture_graph records the same launches once and CudaGraphModel::run replays them
+// (drivers/teeny-cuda/src/model/mod.rs:524, 1245, 1799) -- for the one graph this backend serves: the Qwen3 layer
+// sequence recorded in support/teeny-torch/tests/data/qwen3_{1,2,3}.bin.gz.  Like the reference executor it owns no
+// weights: the caller passes device pointers (already sharded for this rank) and one workspace it allocated.
+//
+// Per layer (T tokens, local heads Hq/Hkv, local intermediate I):
+//   y = rms_norm(h [+ previous delta])            fused residual add + norm
+//   qkv = y Wqkv^T                                tcgen05 GEMM, fused [q | k | v] rows
+//   q,k <- head norm + RoPE; k,v -> cache         one kernel
+//   a = attention(q, cache)                       tcgen05 flash-attention (prefill) / split-KV decode kernel
+//   delta = a Wo^T ; all-reduce                   row-parallel
+//   y = rms_norm(h += delta)
+//   gu = y Wgu^T ; act = silu(g) * u ; delta = act Wd^T ; all-reduce
+// then final norm on the last position of each sequence, vocabulary-parallel LM head, local argmax, all-gather of
+// (value, index) candidates and a merge so every rank holds the same greedy token.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "../../include/teeny_b200.h"
+#include "../../include/teeny_qwen3.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+// ---- NCCL through dlopen: no link-time dependency, and the copy PyTorch already loaded is reused ----
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  bool ok = false;
+};
+NcclApi g_nccl;
+
+bool load_nccl() {
+  if (g_nccl.ok) return true;
+  if (!g_nccl.handle) g_nccl.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!g_nccl.handle) return false;
+  auto sym = [&](const char* n) { return dlsym(g_nccl.handle, n); };
+  g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(sym("ncclGetUniqueId"));
+  g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(sym("ncclCommInitRank"));
+  g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(sym("ncclCommDestroy"));
+  g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(sym("ncclAllReduce"));
+  g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(sym("ncclAllGather"));
+  g_nccl.GroupStart = reinterpret_cast<decltype(g_nccl.GroupStart)>(sym("ncclGroupStart"));
+  g_nccl.GroupEnd = reinterpret_cast<decltype(g_nccl.GroupEnd)>(sym("ncclGroupEnd"));
+  g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce &&
+              g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
+  return g_nccl.ok;
+}
+
+__global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __restrict__ cur_ids,
+                                   int* __restrict__ history, int* __restrict__ state, int B, int max_steps) {
+  // state[0] = position of the next token to append, state[1] = live KV length during the step (= state[0] + 1),
+  // state[2] = number of generated tokens so far
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = state[2];
+  if (b < B) {
+    const int id = next_ids[b];
+    cur_ids[b] = id;
+    if (step < max_steps) history[static_cast<size_t>(step) * B + b] = id;
+  }
+  __syncthreads();  // single block: every thread has read `step`
+  if (b == 0) {
+    state[0] += 1;
+    state[1] += 1;
+    state[2] = step + 1;
+  }
+}
+
+__global__ void set_state_kernel(int* state, int pos, int len, int steps) {
+  state[0] = pos;
+  state[1] = len;
+  state[2] = steps;
+}
+
+size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct LayerWeights {
+  const bf16 *qkv = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;
+  const bf16 *input_ln = nullptr, *post_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+};
+
+struct Workspace {
+  // offsets into the caller's workspace
+  size_t h, y, qkv, attn, delta, gu, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch;
+  size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
+  size_t gemm_scratch_bytes, attn_scratch_bytes, cache_layer_elems;
+};
+
+}  // namespace teeny
+
+using namespace teeny;
+
+struct teeny_qwen3 {
+  teeny_qwen3_config cfg;
+  int Hq, Hkv, I, Vl;  // local (per-rank) q heads, kv heads, intermediate, vocab rows
+  std::vector<LayerWeights> layers;
+  const bf16 *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
+  const float* inv_freq = nullptr;
+  uint8_t* ws = nullptr;
+  Workspace off;
+  ncclComm_t comm = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
+  int graph_batch = 0;
+  int batch = 0;  // batch of the running generation (set by prefill)
+  bool tables_ready = false;
+
+  template <typename T> T* at(size_t o) const { return reinterpret_cast<T*>(ws + o); }
+};
+
+namespace {
+
+bool valid_config(const teeny_qwen3_config& c) {
+  if (c.num_layers <= 0 || c.hidden <= 0 || c.num_q_heads <= 0 || c.num_kv_heads <= 0 || c.intermediate <= 0 ||
+      c.vocab <= 0 || c.max_batch <= 0 || c.max_len <= 0 || c.max_tokens <= 0 || c.tp_size <= 0 || c.tp_rank < 0 ||
+      c.tp_rank >= c.tp_size || c.max_new_tokens < 0)
+    return false;
+  if (c.head_dim != 128) return false;
+  if (c.num_q_heads % c.num_kv_heads || c.num_kv_heads % c.tp_size || c.intermediate % c.tp_size ||
+      c.vocab % c.tp_size)
+    return false;
+  if (c.hidden % 8 || (c.intermediate / c.tp_size) % 8 || (c.vocab / c.tp_size) % 8) return false;
+  if (c.max_tokens < c.max_batch) return false;
+  return true;
+}
+
+Workspace plan(const teeny_qwen3_config& c) {
+  Workspace w{};
+  const int tp = c.tp_size;
+  const size_t Hq = c.num_q_heads / tp, Hkv = c.num_kv_heads / tp, I = c.intermediate / tp, Vl = c.vocab / tp;
+  const size_t T = c.max_tokens, D = c.head_dim, H = c.hidden, Bm = c.max_batch;
+  size_t o = 0;
+  auto take = [&](size_t bytes) { const size_t at = o; o += align_up(bytes); return at; };
+  w.h = take(T * H * 2);
+  w.y = take(T * H * 2);
+  w.qkv = take(T * (Hq + 2 * Hkv) * D * 2);
+  w.attn = take(T * Hq * D * 2);
+  w.delta = take(T * H * 2);
+  w.gu = take(T * 2 * I * 2);
+  w.act = take(T * I * 2);
+  w.logits = take(Bm * Vl * 2);
+  w.cache_layer_elems = Bm * Hkv * static_cast<size_t>(c.max_len) * D;
+  w.kcache = take(w.cache_layer_elems * 2 * c.num_layers);
+  w.vcache = take(w.cache_layer_elems * 2 * c.num_layers);
+  w.cos = take(static_cast<size_t>(c.max_len) * D * 2);
+  w.sin = take(static_cast<size_t>(c.max_len) * D * 2);
+  // split-K scratch: the largest need over the decode-shaped GEMMs of a layer and the LM head
+  size_t gs = 0;
+  const int Bi = c.max_batch;
+  const int shapes[5][2] = {{static_cast<int>((Hq + 2 * Hkv) * D), c.hidden},
+                            {c.hidden, static_cast<int>(Hq * D)},
+                            {static_cast<int>(2 * I), c.hidden},
+                            {c.hidden, static_cast<int>(I)},
+                            {static_cast<int>(Vl), c.hidden}};
+  for (auto& s : shapes) {
+    const size_t n = gemm_bf16_scratch_bytes(Bi, s[0], s[1]);
+    gs = n > gs ? n : gs;
+  }
+  w.gemm_scratch_bytes = gs;
+  w.gemm_scratch = take(gs);
+  w.attn_scratch_bytes = attention_decode_scratch_bytes(c.max_batch, static_cast<int>(Hq), c.head_dim, c.max_len);
+  w.attn_scratch = take(w.attn_scratch_bytes);
+  w.cand_val = take(Bm * 4);
+  w.cand_idx = take(Bm * 4);
+  w.gather_val = take(Bm * 4 * tp);
+  w.gather_idx = take(Bm * 4 * tp);
+  w.next_ids = take(Bm * 4);
+  w.cur_ids = take(Bm * 4);
+  w.history = take(Bm * 4 * static_cast<size_t>(c.max_new_tokens > 0 ? c.max_new_tokens : 1));
+  w.state = take(16);
+  w.total = o;
+  return w;
+}
+
+#define TEENY_TRY(expr)                  \
+  do {                                   \
+    const int rc_ = (expr);              \
+    if (rc_ != 0) return rc_;            \
+  } while (0)
+
+int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
+  if (m->cfg.tp_size == 1) return 0;
+  if (!m->comm) return TEENY_ERR_NCCL;
+  // chunked so each message stays within NCCL's comfortable size and later chunks can start while earlier ones drain
+  return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, m->comm, st) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
+}
+
+// The shared layer loop.  T tokens arranged [B, S]; pos0 is the position of the first token of every sequence
+// (device value when pos_dev != null).  decode selects the split-KV attention kernel (S == 1).
+int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const int* len_dev, bool decode,
+               cudaStream_t st) {
+  const teeny_qwen3_config& c = m->cfg;
+  const int T = B * S, H = c.hidden, D = c.head_dim, Hq = m->Hq, Hkv = m->Hkv, I = m->I;
+  const int qkv_n = (Hq + 2 * Hkv) * D;
+  bf16 *h = m->at<bf16>(m->off.h), *y = m->at<bf16>(m->off.y), *qkv = m->at<bf16>(m->off.qkv);
+  bf16 *attn = m->at<bf16>(m->off.attn), *delta = m->at<bf16>(m->off.delta), *gu = m->at<bf16>(m->off.gu);
+  bf16* act = m->at<bf16>(m->off.act);
+  void* gs = m->at<void>(m->off.gemm_scratch);
+  const size_t gsb = m->off.gemm_scratch_bytes;
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+
+  for (int l = 0; l < c.num_layers; ++l) {
+    const LayerWeights& w = m->layers[l];
+    bf16* kc = m->at<bf16>(m->off.kcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
+    bf16* vc = m->at<bf16>(m->off.vcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
+    if (l == 0) TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st));
+    else TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.input_ln, T, H, c.eps, st));
+    TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
+    TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                                   kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
+    AttnShape a{};
+    a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.scale = scale;
+    a.q_sb = static_cast<long long>(S) * qkv_n; a.q_sh = D; a.q_ss = qkv_n;
+    a.k_sb = static_cast<long long>(Hkv) * c.max_len * D; a.k_sh = static_cast<long long>(c.max_len) * D; a.k_ss = D;
+    a.v_sb = a.k_sb; a.v_sh = a.k_sh; a.v_ss = D;
+    a.o_sb = static_cast<long long>(S) * Hq * D; a.o_sh = D; a.o_ss = static_cast<long long>(Hq) * D;
+    if (decode) {
+      a.Sq = 1; a.Skv = c.max_len; a.causal = 0;
+      TEENY_TRY(attention_decode_bf16(qkv, kc, vc, attn, a, pos0 + 1, len_dev, m->at<void>(m->off.attn_scratch),
+                                      m->off.attn_scratch_bytes, st));
+    } else {
+      a.Sq = S; a.Skv = pos0 + S; a.causal = 1;
+      TEENY_TRY(attention_prefill_bf16(qkv, kc, vc, attn, nullptr, a, st));
+    }
+    TEENY_TRY(gemm_bf16(attn, Hq * D, w.o, Hq * D, false, nullptr, delta, H, T, H, Hq * D, gs, gsb, st));
+    TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
+    TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.post_ln, T, H, c.eps, st));
+    TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, gu, 2 * I, T, 2 * I, H, gs, gsb, st));
+    TEENY_TRY(silu_mul_bf16(gu, 2 * I, act, T, I, st));
+    TEENY_TRY(gemm_bf16(act, I, w.down, I, false, nullptr, delta, H, T, H, I, gs, gsb, st));
+    TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
+  }
+  return 0;
+}
+
+// Final norm on the last token of each sequence, LM head, greedy pick.  Leaves next ids in off.next_ids.
+int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
+  const teeny_qwen3_config& c = m->cfg;
+  const int H = c.hidden, Vl = m->Vl;
+  bf16 *h = m->at<bf16>(m->off.h), *y = m->at<bf16>(m->off.y), *delta = m->at<bf16>(m->off.delta);
+  bf16* logits = m->at<bf16>(m->off.logits);
+  const size_t last = static_cast<size_t>(S - 1) * H;
+  const long long ld = static_cast<long long>(S) * H;
+  // residual add + final norm on rows (b, S-1); y rows are packed [B, H]
+  TEENY_TRY(add_rms_norm_bf16(delta + last, ld, h + last, ld, y, H, m->final_norm, B, H, c.eps, st));
+  TEENY_TRY(gemm_bf16(y, H, m->lm_head, H, false, nullptr, logits, Vl, B, Vl, H, m->at<void>(m->off.gemm_scratch),
+                      m->off.gemm_scratch_bytes, st));
+  float* cv = m->at<float>(m->off.cand_val);
+  int* ci = m->at<int>(m->off.cand_idx);
+  int* next = m->at<int>(m->off.next_ids);
+  if (c.tp_size == 1) {
+    TEENY_TRY(argmax_bf16(logits, Vl, cv, next, B, Vl, 0, st));
+    return 0;
+  }
+  TEENY_TRY(argmax_bf16(logits, Vl, cv, ci, B, Vl, c.tp_rank * Vl, st));
+  if (!m->comm) return TEENY_ERR_NCCL;
+  float* gv = m->at<float>(m->off.gather_val);
+  int* gi = m->at<int>(m->off.gather_idx);
+  // gathered layout [rank][max_batch]; only the first B of each rank's slot are meaningful
+  g_nccl.GroupStart();
+  ncclResult_t r1 = g_nccl.AllGather(cv, gv, c.max_batch, ncclFloat32, m->comm, st);
+  ncclResult_t r2 = g_nccl.AllGather(ci, gi, c.max_batch, ncclInt32, m->comm, st);
+  ncclResult_t r3 = g_nccl.GroupEnd();
+  if (r1 != ncclSuccess || r2 != ncclSuccess || r3 != ncclSuccess) return TEENY_ERR_NCCL;
+  // candidates of part p for row r sit at [p * max_batch + r]: combine with `rows` = max_batch stride
+  TEENY_TRY(argmax_combine(gv, gi, next, c.tp_size, c.max_batch, st));
+  return 0;
+}
+
+int decode_body(teeny_qwen3* m, int B, cudaStream_t st) {
+  const teeny_qwen3_config& c = m->cfg;
+  int* state = m->at<int>(m->off.state);
+  TEENY_TRY(embedding_bf16(m->at<int>(m->off.cur_ids), m->embed, m->at<bf16>(m->off.h), B, c.hidden, c.vocab, st));
+  TEENY_TRY(run_layers(m, B, 1, 0, state + 0, state + 1, true, st));
+  TEENY_TRY(run_head(m, B, 1, st));
+  finish_step_kernel<<<1, 1024, 0, st>>>(m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
+                                         m->at<int>(m->off.history), state, B, c.max_new_tokens);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t teeny_qwen3_workspace_bytes(const teeny_qwen3_config* cfg) {
+  if (!cfg || !valid_config(*cfg)) return 0;
+  return plan(*cfg).total;
+}
+
+int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t workspace_bytes, void* tp_comm,
+                       teeny_stream_t stream, teeny_qwen3** out) {
+  if (!cfg || !out || !workspace || !valid_config(*cfg)) return TEENY_ERR_BAD_ARG;
+  if (cfg->max_batch > 1024) return TEENY_ERR_BAD_ARG;
+  if (cfg->tp_size > 1 && !tp_comm) return TEENY_ERR_NCCL;
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return TEENY_ERR_ALIGNMENT;
+  const Workspace w = plan(*cfg);
+  if (workspace_bytes < w.total) return TEENY_ERR_SCRATCH;
+  teeny_qwen3* m = new (std::nothrow) teeny_qwen3();
+  if (!m) return TEENY_ERR_BAD_ARG;
+  m->cfg = *cfg;
+  m->Hq = cfg->num_q_heads / cfg->tp_size;
+  m->Hkv = cfg->num_kv_heads / cfg->tp_size;
+  m->I = cfg->intermediate / cfg->tp_size;
+  m->Vl = cfg->vocab / cfg->tp_size;
+  m->layers.resize(cfg->num_layers);
+  m->ws = static_cast<uint8_t*>(workspace);
+  m->off = w;
+  m->comm = static_cast<ncclComm_t>(tp_comm);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // split-K counters must start at zero; generation state too
+  cudaError_t e = cudaMemsetAsync(m->ws + w.gemm_scratch, 0, w.gemm_scratch_bytes, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(m->ws + w.state, 0, 16, st);
+  if (e != cudaSuccess) {
+    delete m;
+    return static_cast<int>(e);
+  }
+  *out = m;
+  return 0;
+}
+
+void teeny_qwen3_destroy(teeny_qwen3* m) {
+  if (!m) return;
+  if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  delete m;
+}
+
+int teeny_qwen3_set_weight(teeny_qwen3* m, int layer, int which, const void* ptr) {
+  if (!m || !ptr) return TEENY_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(ptr) & 15) return TEENY_ERR_ALIGNMENT;
+  const bf16* p = static_cast<const bf16*>(ptr);
+  if (which >= TEENY_QWEN3_W_EMBED) {
+    switch (which) {
+      case TEENY_QWEN3_W_EMBED: m->embed = p; return 0;
+      case TEENY_QWEN3_W_FINAL_NORM: m->final_norm = p; return 0;
+      case TEENY_QWEN3_W_LM_HEAD: m->lm_head = p; return 0;
+      case TEENY_QWEN3_W_INV_FREQ: m->inv_freq = static_cast<const float*>(ptr); m->tables_ready = false; return 0;
+      default: return TEENY_ERR_BAD_ARG;
+    }
+  }
+  if (layer < 0 || layer >= m->cfg.num_layers) return TEENY_ERR_BAD_ARG;
+  LayerWeights& w = m->layers[layer];
+  switch (which) {
+    case TEENY_QWEN3_W_QKV: w.qkv = p; break;
+    case TEENY_QWEN3_W_O: w.o = p; break;
+    case TEENY_QWEN3_W_GATE_UP: w.gate_up = p; break;
+    case TEENY_QWEN3_W_DOWN: w.down = p; break;
+    case TEENY_QWEN3_W_INPUT_LN: w.input_ln = p; break;
+    case TEENY_QWEN3_W_POST_LN: w.post_ln = p; break;
+    case TEENY_QWEN3_W_Q_NORM: w.q_norm = p; break;
+    case TEENY_QWEN3_W_K_NORM: w.k_norm = p; break;
+    default: return TEENY_ERR_BAD_ARG;
+  }
+  return 0;
+}
+
+static int check_ready(teeny_qwen3* m, cudaStream_t st) {
+  if (!m->embed || !m->final_norm || !m->lm_head || !m->inv_freq) return TEENY_ERR_BAD_ARG;
+  for (const LayerWeights& w : m->layers)
+    if (!w.qkv || !w.o || !w.gate_up || !w.down || !w.input_ln || !w.post_ln || !w.q_norm || !w.k_norm)
+      return TEENY_ERR_BAD_ARG;
+  if (!m->tables_ready) {
+    TEENY_TRY(rope_table_bf16(m->inv_freq, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin), m->cfg.max_len,
+                              m->cfg.head_dim, st));
+    m->tables_ready = true;
+  }
+  return 0;
+}
+
+int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stream_t stream) {
+  if (!m || !ids || B <= 0 || S <= 0) return TEENY_ERR_BAD_ARG;
+  const teeny_qwen3_config& c = m->cfg;
+  if (B > c.max_batch || S > c.max_len || static_cast<long long>(B) * S > c.max_tokens) return TEENY_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  TEENY_TRY(check_ready(m, st));
+  m->batch = B;
+  int* state = m->at<int>(m->off.state);
+  TEENY_TRY(embedding_bf16(ids, m->embed, m->at<bf16>(m->off.h), B * S, c.hidden, c.vocab, st));
+  TEENY_TRY(run_layers(m, B, S, 0, nullptr, nullptr, false, st));
+  TEENY_TRY(run_head(m, B, S, st));
+  // generation state: next position S, live length during the next step S + 1, no tokens recorded yet
+  set_state_kernel<<<1, 1, 0, st>>>(state, S - 1, S, 0);
+  finish_step_kernel<<<1, 1024, 0, st>>>(m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
+                                         m->at<int>(m->off.history), state, B, c.max_new_tokens);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int teeny_qwen3_decode(teeny_qwen3* m, teeny_stream_t stream) {
+  if (!m || m->batch <= 0) return TEENY_ERR_BAD_ARG;
+  return decode_body(m, m->batch, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int teeny_qwen3_capture_decode(teeny_qwen3* m, teeny_stream_t stream) {
+  if (!m || m->batch <= 0) return TEENY_ERR_BAD_ARG;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (m->graph_exec) {
+    cudaGraphExecDestroy(m->graph_exec);
+    m->graph_exec = nullptr;
+  }
+  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int rc = decode_body(m, m->batch, st);
+  cudaGraph_t graph = nullptr;
+  e = cudaStreamEndCapture(st, &graph);
+  if (rc != 0) {
+    if (graph) cudaGraphDestroy(graph);
+    return rc;
+  }
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  m->graph_batch = m->batch;
+  return 0;
+}
+
+int teeny_qwen3_decode_replay(teeny_qwen3* m, teeny_stream_t stream) {
+  if (!m || !m->graph_exec || m->graph_batch != m->batch) return TEENY_ERR_BAD_ARG;
+  return static_cast<int>(cudaGraphLaunch(m->graph_exec, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+void* teeny_qwen3_buffer(teeny_qwen3* m, int which) {
+  if (!m) return nullptr;
+  switch (which) {
+    case TEENY_QWEN3_BUF_LOGITS: return m->ws + m->off.logits;
+    case TEENY_QWEN3_BUF_NEXT_IDS: return m->ws + m->off.cur_ids;
+    case TEENY_QWEN3_BUF_HISTORY: return m->ws + m->off.history;
+    case TEENY_QWEN3_BUF_STATE: return m->ws + m->off.state;
+    case TEENY_QWEN3_BUF_HIDDEN: return m->ws + m->off.y;
+    case TEENY_QWEN3_BUF_K_CACHE: return m->ws + m->off.kcache;
+    case TEENY_QWEN3_BUF_V_CACHE: return m->ws + m->off.vcache;
+    default: return nullptr;
+  }
+}
+
+// ---- tensor-parallel plumbing ----
+int teeny_tp_unique_id(void* out128) {
+  if (!out128) return TEENY_ERR_BAD_ARG;
+  if (!load_nccl()) return TEENY_ERR_NCCL;
+  static_assert(sizeof(ncclUniqueId) == 128, "ncclUniqueId size");
+  ncclUniqueId id;
+  if (g_nccl.GetUniqueId(&id) != ncclSuccess) return TEENY_ERR_NCCL;
+  std::memcpy(out128, &id, sizeof(id));
+  return 0;
+}
+
+int teeny_tp_init(const void* id128, int rank, int world, void** comm_out) {
+  if (!id128 || !comm_out || world <= 0 || rank < 0 || rank >= world) return TEENY_ERR_BAD_ARG;
+  if (!load_nccl()) return TEENY_ERR_NCCL;
+  ncclUniqueId id;
+  std::memcpy(&id, id128, sizeof(id));
+  ncclComm_t comm = nullptr;
+  if (g_nccl.CommInitRank(&comm, world, id, rank) != ncclSuccess) return TEENY_ERR_NCCL;
+  *comm_out = comm;
+  return 0;
+}
+
+int teeny_tp_destroy(void* comm) {
+  if (!comm) return 0;
+  if (!load_nccl()) return TEENY_ERR_NCCL;
+  return g_nccl.CommDestroy(static_cast<ncclComm_t>(comm)) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
+}
+
+int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_stream_t stream) {
+  if (!comm || !buf) return TEENY_ERR_BAD_ARG;
+  if (!load_nccl()) return TEENY_ERR_NCCL;
+  return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(comm),
+                          reinterpret_cast<cudaStream_t>(stream)) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
+}
+
+}  // extern "C"
