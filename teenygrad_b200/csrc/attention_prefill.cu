@@ -294,6 +294,17 @@ int make_map(CUtensorMap* m, const bf16* p, int S, int H, int B, long long ss, l
 
 }  // namespace
 
+int attention_prefill_prepare() {
+  static unsigned long long done = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 64) done |= 1ull << dev;
+  return 0;
+}
+
 int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, float* lse, const AttnShape& s,
                            cudaStream_t stream) {
   if (!q || !k || !v || !o || s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Sq <= 0 || s.Skv <= 0) return TEENY_ERR_BAD_ARG;
@@ -321,13 +332,9 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
   a.causal = s.causal;
   a.err = device_error_word();
 
-  static int attr_device = -1;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (attr_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_device = dev;
+  {
+    const int prc = attention_prefill_prepare();
+    if (prc) return prc;
   }
   dim3 grid((s.Sq + kQT - 1) / kQT, s.Hq, s.B);
   attention_prefill_kernel<<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, a);

@@ -332,25 +332,41 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
 // ------------------------------------------------------------------------------------------------
 // host launcher
 // ------------------------------------------------------------------------------------------------
+// Raises the kernel's dynamic shared-memory limit once per device (bit d of `done` = device d prepared).
 template <int BN, bool SWAP, bool Q_MN>
-int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs& a, int grid, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, SWAP, Q_MN>;
-  static bool attr_set = false;  // per template instance; cudaFuncSetAttribute is per device but idempotent
-  static int attr_device = -1;
+int prepare_variant() {
+  static unsigned long long done = 0;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set || attr_device != dev) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-    attr_device = dev;
-  }
-  kern<<<grid, kNumThreads, Cfg::kSmemBytes, st>>>(tp, tq, a);
+  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, SWAP, Q_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       GemmCfg<BN>::kSmemBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 64) done |= 1ull << dev;
+  return 0;
+}
+
+template <int BN, bool SWAP, bool Q_MN>
+int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs& a, int grid, cudaStream_t st) {
+  const int rc = prepare_variant<BN, SWAP, Q_MN>();
+  if (rc) return rc;
+  gemm_bf16_kernel<BN, SWAP, Q_MN><<<grid, kNumThreads, GemmCfg<BN>::kSmemBytes, st>>>(tp, tq, a);
   return static_cast<int>(cudaGetLastError());
 }
 
 }  // namespace
+
+int gemm_bf16_prepare() {
+  int rc = 0;
+  if ((rc = prepare_variant<16, true, false>())) return rc;
+  if ((rc = prepare_variant<32, true, false>())) return rc;
+  if ((rc = prepare_variant<64, true, false>())) return rc;
+  if ((rc = prepare_variant<128, true, false>())) return rc;
+  if ((rc = prepare_variant<128, false, false>())) return rc;
+  if ((rc = prepare_variant<256, false, false>())) return rc;
+  if ((rc = prepare_variant<64, false, true>())) return rc;
+  return prepare_variant<128, false, true>();
+}
 
 // Largest token count that takes the swapped (weights on the 128-row MMA side) path.
 constexpr int kSwapMaxM = 128;

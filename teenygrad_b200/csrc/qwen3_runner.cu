@@ -120,6 +120,7 @@ struct teeny_qwen3 {
   Workspace off;
   ncclComm_t comm = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
+  cudaStream_t capture_stream = nullptr;
   int graph_batch = 0;
   int batch = 0;  // batch of the running generation (set by prefill)
   bool tables_ready = false;
@@ -326,6 +327,13 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   m->off = w;
   m->comm = static_cast<ncclComm_t>(tp_comm);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // function attributes (dynamic shared memory) are set once per device here, outside any stream capture
+  int prc = gemm_bf16_prepare();
+  if (prc == 0) prc = attention_prefill_prepare();
+  if (prc != 0) {
+    delete m;
+    return prc;
+  }
   // split-K counters must start at zero; generation state too
   cudaError_t e = cudaMemsetAsync(m->ws + w.gemm_scratch, 0, w.gemm_scratch_bytes, st);
   if (e == cudaSuccess) e = cudaMemsetAsync(m->ws + w.state, 0, 16, st);
@@ -340,6 +348,7 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
 void teeny_qwen3_destroy(teeny_qwen3* m) {
   if (!m) return;
   if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
+  if (m->capture_stream) cudaStreamDestroy(m->capture_stream);
   delete m;
 }
 
@@ -410,12 +419,16 @@ int teeny_qwen3_decode(teeny_qwen3* m, teeny_stream_t stream) {
 
 int teeny_qwen3_capture_decode(teeny_qwen3* m, teeny_stream_t stream) {
   if (!m || m->batch <= 0) return TEENY_ERR_BAD_ARG;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  (void)stream;  // recording needs a non-default stream of its own; the graph is replayed on the caller's stream
   if (m->graph_exec) {
     cudaGraphExecDestroy(m->graph_exec);
     m->graph_exec = nullptr;
   }
-  cudaError_t e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  cudaError_t e = cudaSuccess;
+  if (!m->capture_stream) e = cudaStreamCreateWithFlags(&m->capture_stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  cudaStream_t st = m->capture_stream;
+  e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
   if (e != cudaSuccess) return static_cast<int>(e);
   const int rc = decode_body(m, m->batch, st);
   cudaGraph_t graph = nullptr;
