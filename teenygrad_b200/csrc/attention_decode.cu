@@ -101,35 +101,44 @@ attention_decode_kernel(const DecodeArgs a) {
       for (int e = 0; e < 4; ++e) acc[ps][i][e] = 0.0f;
   float m = -INFINITY, l = 0.0f;  // per row g (replicated over the 4 lanes of the group)
 
-  for (int kb = key_begin + warp * 16; kb < key_end; kb += kDecWarps * 16) {
+  // K and V fragments of one 16-key slice (64 registers).  The slice after the current one is loaded before the
+  // current one is consumed, so every warp keeps 8 KB of cache reads in flight while its tensor-core work runs.
+  struct Slice { uint4 kf[2][4]; uint4 vf[2][4]; };
+  auto load_slice = [&](Slice& f, int kb) {
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      const int key = min(kb + nb * 8 + g, L - 1);  // clamp: masked later, but the load must stay in valid rows
+      const bf16* kp = kbase + static_cast<long long>(key) * a.k_ss + 8 * c;
+#pragma unroll
+      for (int p = 0; p < 4; ++p) f.kf[nb][p] = ldg_nc(kp + 32 * p);
+    }
+    const int k0 = min(kb + 2 * c, L - 1), k1 = min(kb + 2 * c + 1, L - 1);
+    const int k2 = min(kb + 8 + 2 * c, L - 1), k3 = min(kb + 9 + 2 * c, L - 1);
+#pragma unroll
+    for (int ps = 0; ps < 2; ++ps) {
+      const int d0 = 64 * ps + 8 * g;
+      f.vf[ps][0] = ldg_nc(vbase + static_cast<long long>(k0) * a.v_ss + d0);
+      f.vf[ps][1] = ldg_nc(vbase + static_cast<long long>(k1) * a.v_ss + d0);
+      f.vf[ps][2] = ldg_nc(vbase + static_cast<long long>(k2) * a.v_ss + d0);
+      f.vf[ps][3] = ldg_nc(vbase + static_cast<long long>(k3) * a.v_ss + d0);
+    }
+  };
+  constexpr int kStride = kDecWarps * 16;
+  Slice cur;
+  if (key_begin + warp * 16 < key_end) load_slice(cur, key_begin + warp * 16);
+#pragma unroll 2
+  for (int kb = key_begin + warp * 16; kb < key_end; kb += kStride) {
+    Slice nxt;
+    if (kb + kStride < key_end) load_slice(nxt, kb + kStride);
     // ---- S = Q K^T for 16 keys (two 8-key column blocks) ----
     float s[2][4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
-      const int key = min(kb + nb * 8 + g, L - 1);  // clamp: masked below, but the load must stay in valid rows
-      const bf16* kp = kbase + static_cast<long long>(key) * a.k_ss + 8 * c;
-      uint4 kf[4];
-#pragma unroll
-      for (int p = 0; p < 4; ++p) kf[p] = ldg_nc(kp + 32 * p);
       s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
-        mma_bf16_16816(s[nb], qf[p].x, 0u, qf[p].y, 0u, kf[p].x, kf[p].y);
-        mma_bf16_16816(s[nb], qf[p].z, 0u, qf[p].w, 0u, kf[p].z, kf[p].w);
-      }
-    }
-    // ---- V loads issued before the softmax so they overlap it ----
-    uint4 vf[2][4];
-    {
-      const int k0 = min(kb + 2 * c, L - 1), k1 = min(kb + 2 * c + 1, L - 1);
-      const int k2 = min(kb + 8 + 2 * c, L - 1), k3 = min(kb + 9 + 2 * c, L - 1);
-#pragma unroll
-      for (int ps = 0; ps < 2; ++ps) {
-        const int d0 = 64 * ps + 8 * g;
-        vf[ps][0] = ldg_nc(vbase + static_cast<long long>(k0) * a.v_ss + d0);
-        vf[ps][1] = ldg_nc(vbase + static_cast<long long>(k1) * a.v_ss + d0);
-        vf[ps][2] = ldg_nc(vbase + static_cast<long long>(k2) * a.v_ss + d0);
-        vf[ps][3] = ldg_nc(vbase + static_cast<long long>(k3) * a.v_ss + d0);
+        mma_bf16_16816(s[nb], qf[p].x, 0u, qf[p].y, 0u, cur.kf[nb][p].x, cur.kf[nb][p].y);
+        mma_bf16_16816(s[nb], qf[p].z, 0u, qf[p].w, 0u, cur.kf[nb][p].z, cur.kf[nb][p].w);
       }
     }
     // ---- online softmax on row g: this lane holds keys kb + nb*8 + 2c + {0,1} ----
@@ -170,10 +179,10 @@ attention_decode_kernel(const DecodeArgs a) {
     // ---- O += P V ----
 #pragma unroll
     for (int ps = 0; ps < 2; ++ps) {
-      const uint32_t w0[4] = {vf[ps][0].x, vf[ps][0].y, vf[ps][0].z, vf[ps][0].w};
-      const uint32_t w1[4] = {vf[ps][1].x, vf[ps][1].y, vf[ps][1].z, vf[ps][1].w};
-      const uint32_t w2[4] = {vf[ps][2].x, vf[ps][2].y, vf[ps][2].z, vf[ps][2].w};
-      const uint32_t w3[4] = {vf[ps][3].x, vf[ps][3].y, vf[ps][3].z, vf[ps][3].w};
+      const uint32_t w0[4] = {cur.vf[ps][0].x, cur.vf[ps][0].y, cur.vf[ps][0].z, cur.vf[ps][0].w};
+      const uint32_t w1[4] = {cur.vf[ps][1].x, cur.vf[ps][1].y, cur.vf[ps][1].z, cur.vf[ps][1].w};
+      const uint32_t w2[4] = {cur.vf[ps][2].x, cur.vf[ps][2].y, cur.vf[ps][2].z, cur.vf[ps][2].w};
+      const uint32_t w3[4] = {cur.vf[ps][3].x, cur.vf[ps][3].y, cur.vf[ps][3].z, cur.vf[ps][3].w};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
@@ -182,6 +191,7 @@ attention_decode_kernel(const DecodeArgs a) {
         mma_bf16_16816(acc[ps][i], pa0, 0u, pa2, 0u, b0, b1);
       }
     }
+    cur = nxt;
   }
 
   // ---- merge the warps of this CTA ----

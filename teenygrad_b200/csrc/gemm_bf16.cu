@@ -1,24 +1,28 @@
 // bf16 GEMM for sm_100a: D[i, j] = sum_k P[i, k] * Q[j, k] with f32 accumulation in tensor memory.
 //
-// One persistent, warp-specialised kernel (one CTA per SM):
+// Kernel 1 -- gemm_bf16_kernel: persistent, warp-specialised, one CTA per SM.
 //   warp 0      TMA producer: P tile [128 x 64] and Q tile [BN x 64] per k-block into a ring of shared-memory
 //               stages (128-byte swizzle), completion on `full` mbarriers;
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=BN, K=16) four times per k-block,
 //               tcgen05.commit releases the stage (`empty`) and finally publishes the accumulator (`acc_full`);
 //   warps 2-5   epilogue: tcgen05.ld the 128 x BN f32 accumulator (thread = row), convert to bf16, store.
-// The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue of tile t overlaps the main loop
-// of tile t+1.
+//   The accumulator is double buffered in TMEM (2 x BN columns) so the epilogue of tile t overlaps the main loop
+//   of tile t+1.
 //
-// Two operand assignments share the kernel:
+// Two operand assignments share the code:
 //   normal  P = activations X [M, K], Q = weights W [N, K]  -> Y[m, n] tile 128 x BN
 //   swapped P = weights W [N, K],     Q = activations X     -> Y^T tile; used when M is small (decode), so the
 //           128-row MMA dimension is filled by weight rows and the token count only sets N of the MMA.
 // B may also be MN-major ([K, N] row-major, the matmul_forward layout): its tiles are [64 k][64 n] boxes and the
 // descriptor uses the MN-major canonical layout.
 //
-// Split-K (small-M shapes that would leave SMs idle): each split writes its f32 partial tile to scratch, then
-// bumps a per-tile counter; the CTA that arrives last sums the partials in split order (deterministic), writes
-// bf16 and resets the counter.
+// Kernel 2 -- gemm_bf16_skinny_kernel: the swapped assignment for weight matrices with too few 128-row tiles to
+// occupy the GPU (decode: M <= 128 tokens, N of a few thousand).  These GEMMs only stream weights, so the job is to
+// get every SM pulling from HBM: K is split across a thread-block cluster (2, 4 or 8 CTAs per weight tile, one
+// k-range each, small enough that two CTAs share an SM), every CTA accumulates its partial tile in TMEM, parks it
+// in its own shared memory, and after a cluster barrier the CTAs sum the partials through distributed shared
+// memory -- each CTA reduces its own slice of the token columns, in cluster-rank order, so the result is
+// bit-reproducible.  No global scratch, no atomics.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -40,10 +44,7 @@ struct GemmArgs {
   const bf16* bias;       // [N] or null
   int tiles_p, tiles_q;   // tiles along P rows and along Q rows
   int k_blocks;           // ceil(K / 64)
-  int split_k;            // >= 1
-  int kb_per_split;       // k-blocks per split
-  float* partial;         // split-K scratch: [tiles][split][BN][128] f32
-  int* counters;          // split-K scratch: [tiles]
+  int kb_per_split;       // skinny kernel: k-blocks per cluster rank
   int* err;
 };
 
@@ -70,6 +71,22 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_p, int tiles_q, 
   tq = r / size_p;
 }
 
+// One k-block of MMAs: four K=16 steps over the 64-wide stage.
+template <int BN, bool Q_MN_MAJOR>
+__device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t sp, uint32_t sq, bool first) {
+  constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, Q_MN_MAJOR);
+  const uint64_t pdesc = make_smem_desc_sw128(sp, 16, 1024);
+  const uint64_t qdesc = Q_MN_MAJOR ? make_smem_desc_sw128(sq, kBK * 128, 1024) : make_smem_desc_sw128(sq, 16, 1024);
+#pragma unroll
+  for (int k = 0; k < kBK / 16; ++k) {
+    // K-major: 16 elements along k = 32 bytes inside the swizzled row -> +2 in the address field.
+    // MN-major: 16 k = two 8-row groups of 1024 bytes -> +128.
+    const uint64_t pd = pdesc + static_cast<uint64_t>(k * 2);
+    const uint64_t qd = qdesc + static_cast<uint64_t>(Q_MN_MAJOR ? k * 128 : k * 2);
+    umma_bf16_ss(d_tmem, pd, qd, idesc, (!first || k > 0) ? 1u : 0u);
+  }
+}
+
 template <int BN, bool SWAP, bool Q_MN_MAJOR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_q,
@@ -78,18 +95,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
-  // barrier layout (8 B each): full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr, flag
+  // barrier layout (8 B each): full[kStages], empty[kStages], acc_full[2], acc_empty[2], then the TMEM address
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + b); };
   auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * Cfg::kStages + 2 + b); };
   const uint32_t tmem_slot = bar_base + 8u * (2 * Cfg::kStages + 4);
-  const uint32_t flag_slot = tmem_slot + 4;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 4));
-  volatile int* flag_ptr = reinterpret_cast<volatile int*>(tmem_slot_ptr + 1);
-  (void)flag_slot;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -117,8 +131,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  const int num_tiles = args.tiles_p * args.tiles_q;
-  const int num_work = num_tiles * args.split_k;
+  const int num_work = args.tiles_p * args.tiles_q;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -127,13 +140,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
       uint32_t phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x) {
-        const int tile = w / args.split_k;
-        const int split = w - tile * args.split_k;
         int tp, tq;
-        tile_coords(tile, args.tiles_p, args.tiles_q, tp, tq);
-        const int kb0 = split * args.kb_per_split;
-        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        tile_coords(w, args.tiles_p, args.tiles_q, tp, tq);
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) { ok = false; break; }
           const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
           const uint32_t sq = sp + Cfg::kStageP;
@@ -154,37 +163,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, Q_MN_MAJOR);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
       for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x, ++local) {
-        const int tile = w / args.split_k;
-        const int split = w - tile * args.split_k;
-        const int kb0 = split * args.kb_per_split;
-        const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         if (!mbar_wait(acc_empty_bar(buf), acc_phase ^ 1, err, DEVERR_GEMM_MMA)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_MMA)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
-          const uint32_t sq = sp + Cfg::kStageP;
-          const uint64_t pdesc = make_smem_desc_sw128(sp, 16, 1024);
-          const uint64_t qdesc = Q_MN_MAJOR ? make_smem_desc_sw128(sq, kBK * 128, 1024)
-                                            : make_smem_desc_sw128(sq, 16, 1024);
-#pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            // K-major: 16 elements along k = 32 bytes inside the swizzled row -> +2 in the address field.
-            // MN-major: 16 k = two 8-row groups of 1024 bytes -> +128.
-            const uint64_t pd = pdesc + static_cast<uint64_t>(k * 2);
-            const uint64_t qd = qdesc + static_cast<uint64_t>(Q_MN_MAJOR ? k * 128 : k * 2);
-            umma_bf16_ss(d_tmem, pd, qd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          issue_kblock<BN, Q_MN_MAJOR>(d_tmem, sp, sp + Cfg::kStageP, kb == 0);
           umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
         }
@@ -195,14 +188,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
     // ---------------- epilogue (warps 2..5; TMEM lane quarter = warp % 4) ----------------
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
-    const int epi_tid = (warp - 2) * 32 + lane;
     bool ok = true;
     int local = 0;
     for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x, ++local) {
-      const int tile = w / args.split_k;
-      const int split = w - tile * args.split_k;
       int tp, tq;
-      tile_coords(tile, args.tiles_p, args.tiles_q, tp, tq);
+      tile_coords(w, args.tiles_p, args.tiles_q, tp, tq);
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(acc_full_bar(buf), acc_phase, err, DEVERR_GEMM_EPILOGUE)) { ok = false; break; }
@@ -210,108 +200,59 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const int prow = tp * kBM + row_in_tile;  // index along P rows
       constexpr int kChunk = (BN >= 32) ? 32 : 16;
-
-      if (args.split_k == 1) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += kChunk) {
-          uint32_t r[kChunk];
-          if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
-          tmem_wait_ld();
-          const int qcol0 = tq * BN + c0;  // index along Q rows
-          if constexpr (!SWAP) {
-            // thread owns Y[prow, qcol0 .. qcol0+kChunk)
-            if (prow < args.M) {
-              bf16* dst = args.y + static_cast<size_t>(prow) * args.ldy + qcol0;
-              const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (qcol0 + kChunk <= args.N);
-              if (vec_ok) {
+      for (int c0 = 0; c0 < BN; c0 += kChunk) {
+        uint32_t r[kChunk];
+        if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
+        tmem_wait_ld();
+        const int qcol0 = tq * BN + c0;  // index along Q rows
+        if constexpr (!SWAP) {
+          // thread owns Y[prow, qcol0 .. qcol0+kChunk)
+          if (prow < args.M) {
+            bf16* dst = args.y + static_cast<size_t>(prow) * args.ldy + qcol0;
+            const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (qcol0 + kChunk <= args.N);
+            if (vec_ok) {
 #pragma unroll
-                for (int v = 0; v < kChunk / 8; ++v) {
-                  float f[8];
+              for (int v = 0; v < kChunk / 8; ++v) {
+                float f[8];
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) {
-                    f[e] = __uint_as_float(r[v * 8 + e]);
-                    if (args.bias) f[e] += __bfloat162float(args.bias[qcol0 + v * 8 + e]);
-                  }
-                  uint4 o;
-                  o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
-                  o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
-                  *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                for (int e = 0; e < 8; ++e) {
+                  f[e] = __uint_as_float(r[v * 8 + e]);
+                  if (args.bias) f[e] += __bfloat162float(args.bias[qcol0 + v * 8 + e]);
                 }
-              } else {
-#pragma unroll
-                for (int e = 0; e < kChunk; ++e) {
-                  const int n = qcol0 + e;
-                  if (n < args.N) {
-                    float f = __uint_as_float(r[e]);
-                    if (args.bias) f += __bfloat162float(args.bias[n]);
-                    dst[e] = __float2bfloat16_rn(f);
-                  }
-                }
-              }
-            }
-          } else {
-            // thread owns Y[qcol0 + e, prow] for e in the chunk (prow indexes N); lanes are consecutive in n.
-            if (prow < args.N) {
-              const float b = args.bias ? __bfloat162float(args.bias[prow]) : 0.0f;
-#pragma unroll
-              for (int e = 0; e < kChunk; ++e) {
-                const int m = qcol0 + e;
-                if (m < args.M)
-                  args.y[static_cast<size_t>(m) * args.ldy + prow] = __float2bfloat16_rn(__uint_as_float(r[e]) + b);
-              }
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
-      } else {
-        // ---- split-K: f32 partial to scratch, last arriver reduces ----
-        float* part = args.partial + (static_cast<size_t>(tile) * args.split_k + split) * (BN * kBM);
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += kChunk) {
-          uint32_t r[kChunk];
-          if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < kChunk; ++e) __stcg(part + (c0 + e) * kBM + row_in_tile, __uint_as_float(r[e]));
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty_bar(buf));
-        __threadfence();
-        named_barrier_sync(1, kEpilogueThreads);
-        if (epi_tid == 0) {
-          const int old = atomicAdd(args.counters + tile, 1);
-          *flag_ptr = (old == args.split_k - 1) ? 1 : 0;
-        }
-        named_barrier_sync(1, kEpilogueThreads);
-        const bool last = (*flag_ptr != 0);
-        named_barrier_sync(1, kEpilogueThreads);  // flag consumed before the next work item rewrites it
-        if (last) {
-          __threadfence();
-          const float* base = args.partial + static_cast<size_t>(tile) * args.split_k * (BN * kBM);
-#pragma unroll 1
-          for (int c = 0; c < BN; ++c) {
-            float acc = 0.0f;
-            for (int s = 0; s < args.split_k; ++s)
-              acc += __ldcg(base + static_cast<size_t>(s) * (BN * kBM) + c * kBM + row_in_tile);
-            const int qidx = tq * BN + c;
-            if constexpr (!SWAP) {
-              if (prow < args.M && qidx < args.N) {
-                if (args.bias) acc += __bfloat162float(args.bias[qidx]);
-                args.y[static_cast<size_t>(prow) * args.ldy + qidx] = __float2bfloat16_rn(acc);
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + v * 8) = o;
               }
             } else {
-              if (prow < args.N && qidx < args.M) {
-                if (args.bias) acc += __bfloat162float(args.bias[prow]);
-                args.y[static_cast<size_t>(qidx) * args.ldy + prow] = __float2bfloat16_rn(acc);
+#pragma unroll
+              for (int e = 0; e < kChunk; ++e) {
+                const int n = qcol0 + e;
+                if (n < args.N) {
+                  float f = __uint_as_float(r[e]);
+                  if (args.bias) f += __bfloat162float(args.bias[n]);
+                  dst[e] = __float2bfloat16_rn(f);
+                }
               }
             }
           }
-          if (epi_tid == 0) args.counters[tile] = 0;  // ready for the next launch
+        } else {
+          // thread owns Y[qcol0 + e, prow] for e in the chunk (prow indexes N); lanes are consecutive in n.
+          if (prow < args.N) {
+            const float b = args.bias ? __bfloat162float(args.bias[prow]) : 0.0f;
+#pragma unroll
+            for (int e = 0; e < kChunk; ++e) {
+              const int m = qcol0 + e;
+              if (m < args.M)
+                args.y[static_cast<size_t>(m) * args.ldy + prow] = __float2bfloat16_rn(__uint_as_float(r[e]) + b);
+            }
+          }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(buf));
     }
   }
 
@@ -330,7 +271,176 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
 }
 
 // ------------------------------------------------------------------------------------------------
-// host launcher
+// Kernel 2: cluster split-K for the swapped (small-M) assignment
+// ------------------------------------------------------------------------------------------------
+template <int BN>
+struct SkinnyCfg {
+  static constexpr int kStageP = kBM * kBK * 2;
+  static constexpr int kStageQ = BN * kBK * 2;
+  static constexpr int kStageBytes = kStageP + kStageQ;
+  static constexpr int kStages = (BN >= 128) ? 3 : 4;
+  static constexpr int kPartialBytes = BN * kBM * 4;  // f32 partial tile, column-major [BN][128]
+  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 128;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// grid (S, tiles): blockIdx.x = cluster rank = k-split, blockIdx.y = 128-row weight tile.
+template <int BN>
+__global__ void __launch_bounds__(kNumThreads, 2)
+gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                        const GemmArgs args) {
+  using Cfg = SkinnyCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t part_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = part_base + Cfg::kPartialBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
+  const uint32_t acc_full_bar = bar_base + 8u * (2 * Cfg::kStages);
+  const uint32_t tmem_slot = acc_full_bar + 8;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  float* part_gen = reinterpret_cast<float*>(smem_gen + Cfg::kStages * Cfg::kStageBytes);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      smem_gen + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes + 8 * (2 * Cfg::kStages + 1));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* err = args.err;
+  const uint32_t S = cluster_size(), rank = cluster_rank();
+  const int tile = blockIdx.y;
+  const int kb0 = static_cast<int>(rank) * args.kb_per_split;
+  const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) break;
+        const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
+        mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+        tma_load_2d(sp, &tmap_w, full_bar(stage), kb * kBK, tile * kBM);
+        tma_load_2d(sp + Cfg::kStageP, &tmap_x, full_bar(stage), kb * kBK, 0);
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_MMA)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
+        issue_kblock<BN, false>(tmem_base, sp, sp + Cfg::kStageP, kb == kb0);
+        umma_commit(empty_bar(stage));
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      }
+      if (ok) umma_commit(acc_full_bar);
+    }
+  } else {
+    // accumulator -> this CTA's partial tile in shared memory, column-major so a thread's stores and the later
+    // per-column reads are both conflict-free (consecutive rows = consecutive words)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    if (mbar_wait(acc_full_bar, 0, err, DEVERR_GEMM_EPILOGUE)) {
+      tc_fence_after();
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      constexpr int kChunk = (BN >= 32) ? 32 : 16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += kChunk) {
+        uint32_t r[kChunk];
+        if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < kChunk; ++e) part_gen[(c0 + e) * kBM + row] = __uint_as_float(r[e]);
+      }
+      tc_fence_before();
+    }
+  }
+
+  // every partial tile of the cluster is in place
+  __syncwarp();
+  cluster_sync_all();
+
+  if (warp >= 2) {
+    // CTA `rank` finishes token columns [rank * cw, (rank + 1) * cw): sum over the cluster in rank order
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int n = tile * kBM + row;
+    const int cw = BN / static_cast<int>(S);
+    const float bias = (args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
+    const bool live = *reinterpret_cast<volatile int*>(err) == 0;
+#pragma unroll 4
+    for (int j = 0; j < cw; ++j) {
+      const int c = static_cast<int>(rank) * cw + j;
+      const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + row) * 4);
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(addr, q) : 0.0f;
+      float acc = v[0];
+#pragma unroll
+      for (int q = 1; q < 8; ++q) acc += v[q];
+      if (live && c < args.M && n < args.N)
+        args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(acc + bias);
+    }
+  }
+
+  // nobody leaves (and frees its shared memory) while a peer may still be reading it
+  __syncwarp();
+  cluster_sync_all();
+  if (warp == 2) {
+    if (*reinterpret_cast<volatile int*>(err) != 0) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host launchers
 // ------------------------------------------------------------------------------------------------
 // Raises the kernel's dynamic shared-memory limit once per device (bit d of `done` = device d prepared).
 template <int BN, bool SWAP, bool Q_MN>
@@ -346,6 +456,19 @@ int prepare_variant() {
   return 0;
 }
 
+template <int BN>
+int prepare_skinny() {
+  static unsigned long long done = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SkinnyCfg<BN>::kSmemBytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 64) done |= 1ull << dev;
+  return 0;
+}
+
 template <int BN, bool SWAP, bool Q_MN>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs& a, int grid, cudaStream_t st) {
   const int rc = prepare_variant<BN, SWAP, Q_MN>();
@@ -353,6 +476,30 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs&
   gemm_bf16_kernel<BN, SWAP, Q_MN><<<grid, kNumThreads, GemmCfg<BN>::kSmemBytes, st>>>(tp, tq, a);
   return static_cast<int>(cudaGetLastError());
 }
+
+template <int BN>
+int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int split, int tiles,
+                  cudaStream_t st) {
+  const int rc = prepare_skinny<BN>();
+  if (rc) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(split, tiles, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = SkinnyCfg<BN>::kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<BN>, tw, tx, a));
+}
+
+// Largest token count that takes the swapped (weights on the 128-row MMA side) assignment.
+constexpr int kSwapMaxM = 128;
+int swap_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
 
 }  // namespace
 
@@ -365,29 +512,19 @@ int gemm_bf16_prepare() {
   if ((rc = prepare_variant<128, false, false>())) return rc;
   if ((rc = prepare_variant<256, false, false>())) return rc;
   if ((rc = prepare_variant<64, false, true>())) return rc;
-  return prepare_variant<128, false, true>();
+  if ((rc = prepare_variant<128, false, true>())) return rc;
+  if ((rc = prepare_skinny<16>())) return rc;
+  if ((rc = prepare_skinny<32>())) return rc;
+  if ((rc = prepare_skinny<64>())) return rc;
+  return prepare_skinny<128>();
 }
 
-// Largest token count that takes the swapped (weights on the 128-row MMA side) path.
-constexpr int kSwapMaxM = 128;
-
-static int swap_bn(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); }
-
-// Scratch layout: [counters: one int per 128-row weight tile, padded to 256 B][f32 partial tiles].
-static size_t scratch_counter_bytes(int N) {
-  return (static_cast<size_t>(ceil_div(N, kBM)) * sizeof(int) + 255) & ~static_cast<size_t>(255);
-}
-
-size_t gemm_bf16_scratch_bytes(int M, int N, int K) {
-  (void)K;
-  if (M > kSwapMaxM) return 0;  // large-M shapes never split K
-  const size_t max_work = static_cast<size_t>(kGemmMaxWorkPerSm) * sm_count();
-  return scratch_counter_bytes(N) + max_work * swap_bn(M) * kBM * sizeof(float);
-}
+// The GEMM keeps its split-K partials in distributed shared memory: no global scratch at any shape.
+size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
 // Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+              int M, int N, int K, void*, size_t, cudaStream_t stream) {
   if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 7) || (ldw & 7))
     return TEENY_ERR_ALIGNMENT;
@@ -395,7 +532,6 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   GemmArgs a{};
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
   a.k_blocks = ceil_div(K, kBK);
-  a.split_k = 1;
   a.kb_per_split = a.k_blocks;
   a.err = device_error_word();
   const int sms = sm_count();
@@ -434,35 +570,27 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   }
 
   if (swap) {
-    a.tiles_p = ceil_div(N, kBM);
-    a.tiles_q = 1;
-    // Split K when whole tiles would leave SMs idle or the last wave mostly empty: pick the split count with
-    // the best wave efficiency (work / (waves * SMs)), charging a little for each extra partial pass.
-    const int tiles = a.tiles_p;
-    int split = 1;
-    if (scratch && scratch_bytes >= gemm_bf16_scratch_bytes(M, N, K)) {
-      const int max_split = min(kGemmMaxSplitK, a.k_blocks / 4);
-      auto score = [&](int s) {
-        const int kbps = ceil_div(a.k_blocks, s);
-        const int work = tiles * ceil_div(a.k_blocks, kbps);
-        const int waves = ceil_div(work, sms);
-        return static_cast<float>(work) / (static_cast<float>(waves) * sms) - 0.01f * (s - 1);
-      };
-      float best = score(1);
-      for (int s = 2; s <= max_split; ++s) {
-        if (static_cast<long long>(tiles) * s > static_cast<long long>(kGemmMaxWorkPerSm) * sms) break;
-        const float sc = score(s);
-        if (sc > best + 0.03f) { best = sc; split = s; }
+    const int tiles = ceil_div(N, kBM);
+    if (tiles < 4 * sms && tiles <= 65535) {
+      // Few weight tiles: cluster split-K.  Smallest power-of-two split that puts about two small CTAs on every
+      // SM, keeping at least four k-blocks per CTA.
+      int split = 1;
+      while (split < 8 && tiles * split < (7 * sms) / 2 && a.k_blocks / (split * 2) >= 4) split *= 2;
+      a.kb_per_split = ceil_div(a.k_blocks, split);
+      while (split > 1 && a.kb_per_split * (split - 1) >= a.k_blocks) {  // never leave a rank without k-blocks
+        split /= 2;
+        a.kb_per_split = ceil_div(a.k_blocks, split);
+      }
+      switch (bn) {
+        case 16: return launch_skinny<16>(tmw, tmx, a, split, tiles, stream);
+        case 32: return launch_skinny<32>(tmw, tmx, a, split, tiles, stream);
+        case 64: return launch_skinny<64>(tmw, tmx, a, split, tiles, stream);
+        default: return launch_skinny<128>(tmw, tmx, a, split, tiles, stream);
       }
     }
-    a.kb_per_split = ceil_div(a.k_blocks, split);
-    a.split_k = ceil_div(a.k_blocks, a.kb_per_split);  // drop empty splits
-    if (a.split_k > 1) {
-      a.counters = static_cast<int*>(scratch);
-      a.partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + scratch_counter_bytes(N));
-    }
-    const int work = tiles * a.split_k;
-    const int grid = work < sms ? work : sms;
+    a.tiles_p = tiles;
+    a.tiles_q = 1;
+    const int grid = tiles < sms ? tiles : sms;
     switch (bn) {
       case 16: return launch_variant<16, true, false>(tmw, tmx, a, grid, stream);
       case 32: return launch_variant<32, true, false>(tmw, tmx, a, grid, stream);
