@@ -33,7 +33,8 @@ enum {
   TEENY_ERR_SCRATCH = -3,     /* scratch missing or too small */
   TEENY_ERR_DRIVER = -4,      /* CUDA driver entry point unavailable or tensor-map encode failed */
   TEENY_ERR_DEVICE_WAIT = -5, /* a bounded wait inside a kernel expired (see teeny_device_error) */
-  TEENY_ERR_NCCL = -6
+  TEENY_ERR_NCCL = -6,
+  TEENY_ERR_STATIC_LIMIT = -7 /* shape needs more scratch than a no-allocation entry point has built in */
 };
 
 int teeny_version(void);
@@ -107,6 +108,20 @@ int teeny_flash_attn_decode_bf16(const teeny_bf16* q, const teeny_bf16* k, const
                                  const teeny_attn_shape* shape, int kv_len, const int* kv_len_dev, void* scratch,
                                  size_t scratch_bytes, teeny_stream_t stream);
 size_t teeny_attn_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
+/* Decode attention for callers that cannot provide scratch memory.  (No counterpart in the reference, whose launcher
+ * allocates scratch for every launch.)  Meant for hosts where a device allocation is not an option once serving has
+ * started: the framework's pool already owns all of HBM, or a cudaMalloc -- which synchronises the device -- would
+ * stall every stream in the decode loop.  Same arguments and result as teeny_flash_attn_decode_bf16 minus the scratch:
+ * the split-KV partials go to an 8 MiB array that is part of the library image (each GPU that loads the library keeps
+ * those 8 MiB until the process ends).  Shapes with teeny_attn_decode_scratch_bytes(B, Hq, D, shape->Skv) above
+ * teeny_attn_decode_static_limit() return TEENY_ERR_STATIC_LIMIT.  The call allocates nothing.  Its first call on a
+ * device looks up the array's device address (one runtime query); make that first call before any stream capture.
+ * Every call on a device uses the same array (contents are whatever the previous call left; none of it has to be
+ * zero), so calls that could run at the same time on the GPU, e.g. on two streams, race: serialise them. */
+int teeny_flash_attn_decode_bf16_static(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o,
+                                        const teeny_attn_shape* shape, int kv_len, const int* kv_len_dev,
+                                        teeny_stream_t stream);
+size_t teeny_attn_decode_static_limit(void);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * Normalisation and elementwise

@@ -36,6 +36,8 @@ SIGNATURES = {
     "teeny_flash_attn_fwd_bf16": (i32, [vp, vp, vp, vp, vp, C.POINTER(AttnShape), vp]),
     "teeny_flash_attn_decode_bf16": (i32, [vp, vp, vp, vp, C.POINTER(AttnShape), i32, vp, vp, sz, vp]),
     "teeny_attn_decode_scratch_bytes": (sz, [i32, i32, i32, i32]),
+    "teeny_flash_attn_decode_bf16_static": (i32, [vp, vp, vp, vp, C.POINTER(AttnShape), i32, vp, vp]),
+    "teeny_attn_decode_static_limit": (sz, []),
     "rms_norm_forward_entry_point_f32": (i32, [vp, vp, vp, vp, i32, i32, f32, vp]),
     "rms_norm_forward_entry_point_bf16": (i32, [vp, vp, vp, vp, i32, i32, f32, vp]),
     "silu_forward_entry_point_f32": (i32, [vp, vp, i32, vp]),

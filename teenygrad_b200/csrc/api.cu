@@ -130,6 +130,7 @@ const char* teeny_status_string(int status) {
     case TEENY_ERR_DRIVER: return "CUDA driver entry point unavailable or tensor-map encode failed";
     case TEENY_ERR_DEVICE_WAIT: return "a bounded wait inside a kernel expired";
     case TEENY_ERR_NCCL: return "NCCL error";
+    case TEENY_ERR_STATIC_LIMIT: return "shape needs more scratch than the no-allocation entry point has built in";
     default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
   }
 }
@@ -221,6 +222,15 @@ int teeny_flash_attn_decode_bf16(const teeny_bf16* q, const teeny_bf16* k, const
   if (!shape) return TEENY_ERR_BAD_ARG;
   return attention_decode_bf16(B(q), B(k), B(v), B(o), to_shape(*shape), kv_len, kv_len_dev, scratch, scratch_bytes, S(stream));
 }
+
+int teeny_flash_attn_decode_bf16_static(const teeny_bf16* q, const teeny_bf16* k, const teeny_bf16* v, teeny_bf16* o,
+                                        const teeny_attn_shape* shape, int kv_len, const int* kv_len_dev,
+                                        teeny_stream_t stream) {
+  if (!shape) return TEENY_ERR_BAD_ARG;
+  return attention_decode_bf16_static(B(q), B(k), B(v), B(o), to_shape(*shape), kv_len, kv_len_dev, S(stream));
+}
+
+size_t teeny_attn_decode_static_limit(void) { return attention_decode_static_scratch_limit(); }
 
 size_t teeny_attn_decode_scratch_bytes(int Bn, int Hq, int D, int max_kv) {
   return attention_decode_scratch_bytes(Bn, Hq, D, max_kv);

@@ -364,6 +364,48 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------------------
+// Decode attention without a caller-provided scratch buffer.
+//
+// Some hosts cannot hand this library device memory beyond the tensors themselves: an inference server whose
+// allocator reserved every byte of HBM at start-up, or a steady-state decode loop in which a driver allocation is
+// forbidden because cudaMalloc synchronises the whole device.  For them the split-KV partials live in the
+// fixed-size device array below (part of the library image: every GPU that loads the library holds these bytes
+// until the process exits).  Shapes whose partials do not fit are rejected, not truncated.
+//
+// All calls on one device share the array.  Nothing in it needs to start at zero -- every partial that the
+// combine step reads was written by the same call -- but two calls that overlap on the GPU (different streams)
+// would write the same slots, so such calls race and must be serialised by the caller.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticDecodeScratchBytes = size_t(8) << 20;  // 8 MiB, e.g. B=32, Hq=32, cache capacity 4096
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticDecodeScratchBytes];
+void* g_static_decode_scratch_ptr[64] = {};  // per device: resolved address of the array
+}  // namespace
+
+size_t attention_decode_static_scratch_limit() { return kStaticDecodeScratchBytes; }
+
+int attention_decode_bf16_static(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
+                                 const int* kv_len_dev, cudaStream_t stream) {
+  const size_t need = attention_decode_scratch_bytes(s.B, s.Hq, s.D, s.Skv);
+  if (need == 0) return TEENY_ERR_BAD_ARG;
+  if (need > kStaticDecodeScratchBytes) return TEENY_ERR_STATIC_LIMIT;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= 64) return TEENY_ERR_BAD_ARG;
+  if (!g_static_decode_scratch_ptr[dev]) {
+    // In host code the array's name is only a handle: the address a kernel can use comes from the runtime, once
+    // per device, with that device current.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_decode_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_static_decode_scratch_ptr[dev] = p;
+  }
+  return attention_decode_bf16(q, k, v, o, s, kv_len, kv_len_dev, g_static_decode_scratch_ptr[dev],
+                               kStaticDecodeScratchBytes, stream);
+}
+
 template <typename T>
 int attention_generic(const T* q, const T* k, const T* v, T* o, float* lse, const AttnShape& s, cudaStream_t stream) {
   if (!q || !k || !v || !o || s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Sq <= 0 || s.Skv <= 0 || s.D <= 0)

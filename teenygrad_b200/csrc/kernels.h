@@ -45,6 +45,10 @@ size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
 // One query token per sequence against the first *kv_len_dev (or kv_len if the pointer is null) cache entries.
 int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
                           const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream);
+// Same as attention_decode_bf16 with the partials in a fixed-size array inside the library image (no caller scratch).
+size_t attention_decode_static_scratch_limit();
+int attention_decode_bf16_static(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
+                                 const int* kv_len_dev, cudaStream_t stream);
 template <typename T>
 int attention_generic(const T* q, const T* k, const T* v, T* o, float* lse, const AttnShape& s, cudaStream_t stream);
 
