@@ -30,6 +30,12 @@ int current_device() {
 
 }  // namespace
 
+namespace {
+thread_local bool t_pdl_enabled = false;
+}
+bool pdl_enabled() { return t_pdl_enabled; }
+void pdl_set_enabled(bool on) { t_pdl_enabled = on; }
+
 int* device_error_word() {
   const int d = current_device();
   std::lock_guard<std::mutex> lock(g_mutex);

@@ -71,6 +71,7 @@ __device__ __forceinline__ uint4 ldg_nc(const bf16* p) {
 template <int G>
 __global__ void __launch_bounds__(kDecThreads)
 attention_decode_kernel(const DecodeArgs a) {
+  pdl_wait();
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int L = a.kv_len_dev ? *a.kv_len_dev : a.kv_len;
   const int key_begin = chunk * kDecChunk;
@@ -194,6 +195,7 @@ attention_decode_kernel(const DecodeArgs a) {
     cur = nxt;
   }
 
+  pdl_trigger();  // cache streaming done; what follows is the small merge
   // ---- merge the warps of this CTA ----
   __shared__ float sm_ml[kDecWarps][8][2];
   __shared__ float sm_o[kDecWarps][G][kHD];
@@ -237,6 +239,7 @@ attention_decode_kernel(const DecodeArgs a) {
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ o, long long o_sb, long long o_sh, int Hkv, int G,
                                                 int max_chunks, int kv_len, const int* __restrict__ kv_len_dev) {
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int L = kv_len_dev ? *kv_len_dev : kv_len;
   const int chunks = (L + kDecChunk - 1) / kDecChunk;
@@ -265,6 +268,7 @@ __device__ __forceinline__ void st_from_f(bf16* p, float v) { *p = __float2bfloa
 template <typename T>
 __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                                          T* __restrict__ o, float* __restrict__ lse, const AttnShape s) {
+  pdl_wait();
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long rows = static_cast<long long>(s.B) * s.Hq * s.Sq;
@@ -352,14 +356,14 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   a.scale_log2 = s.scale * 1.4426950408889634f;
   dim3 grid(max_chunks, s.Hkv, s.B);
   switch (G) {
-    case 1: attention_decode_kernel<1><<<grid, kDecThreads, 0, stream>>>(a); break;
-    case 2: attention_decode_kernel<2><<<grid, kDecThreads, 0, stream>>>(a); break;
-    case 4: attention_decode_kernel<4><<<grid, kDecThreads, 0, stream>>>(a); break;
-    default: attention_decode_kernel<8><<<grid, kDecThreads, 0, stream>>>(a); break;
+    case 1: launch_kernel(attention_decode_kernel<1>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
+    case 2: launch_kernel(attention_decode_kernel<2>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
+    case 4: launch_kernel(attention_decode_kernel<4>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
+    default: launch_kernel(attention_decode_kernel<8>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  attention_decode_combine_kernel<<<dim3(s.Hq, s.B), kHD, 0, stream>>>(a.part_o, a.part_ml, o, s.o_sb, s.o_sh, s.Hkv,
+  launch_kernel(attention_decode_combine_kernel, dim3(dim3(s.Hq, s.B)), dim3(kHD), 0, stream, 1, a.part_o, a.part_ml, o, s.o_sb, s.o_sh, s.Hkv,
                                                                        G, max_chunks, kv_len, kv_len_dev);
   return static_cast<int>(cudaGetLastError());
 }
@@ -414,7 +418,7 @@ int attention_generic(const T* q, const T* k, const T* v, T* o, float* lse, cons
   const long long rows = static_cast<long long>(s.B) * s.Hq * s.Sq;
   const long long blocks = (rows + 3) / 4;
   if (blocks > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
-  attention_generic_kernel<T><<<static_cast<int>(blocks), 128, 0, stream>>>(q, k, v, o, lse, s);
+  launch_kernel(attention_generic_kernel<T>, dim3(static_cast<int>(blocks)), dim3(128), 0, stream, 1, q, k, v, o, lse, s);
   return static_cast<int>(cudaGetLastError());
 }
 template int attention_generic<float>(const float*, const float*, const float*, float*, float*, const AttnShape&, cudaStream_t);

@@ -94,6 +94,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -337,7 +338,7 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
     if (prc) return prc;
   }
   dim3 grid((s.Sq + kQT - 1) / kQT, s.Hq, s.B);
-  attention_prefill_kernel<<<grid, kThreads, kSmemTotal, stream>>>(mq, mk, mv, a);
+  launch_kernel(attention_prefill_kernel, dim3(grid), dim3(kThreads), kSmemTotal, stream, 1, mq, mk, mv, a);
   return static_cast<int>(cudaGetLastError());
 }
 

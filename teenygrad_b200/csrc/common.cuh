@@ -53,6 +53,52 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// programmatic dependent launch
+// ------------------------------------------------------------------------------------------------
+// Every kernel of this library calls pdl_wait() before it first touches memory that an earlier kernel in the
+// stream may still be writing; whatever it does before that (barrier init, TMEM allocation, prefetch of weights,
+// which no kernel writes) overlaps the tail of its predecessor.  The long kernels call pdl_trigger() when their
+// main loop is done, which lets the next kernel become resident then; for the others the trigger is implicit at
+// exit.  (Triggering at kernel entry was measured slower: CTAs of several later kernels then sit resident and
+// waiting next to the running one.)  Both calls are no-ops for a kernel launched the ordinary way.  Every thread of
+// every CTA executes pdl_wait(), so a grid never completes before its predecessor has.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Host: whether launches on this thread carry the programmatic-stream-serialization attribute (the Qwen3 runner
+// turns it on around its kernel sequences).
+bool pdl_enabled();
+void pdl_set_enabled(bool on);
+
+// Launch through cudaLaunchKernelEx so the attribute can be attached; `cluster` > 1 also sets the cluster width.
+template <typename... KArgs, typename... Args>
+inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                         unsigned cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
+// ------------------------------------------------------------------------------------------------
 // mbarrier
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

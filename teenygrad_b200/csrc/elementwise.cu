@@ -40,6 +40,7 @@ struct OpAdd { __device__ float operator()(float a, float b) const { return a + 
 template <typename Op, bool BINARY>
 __global__ void ew_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o,
                               long long n, bool vec) {
+  pdl_wait();
   Op op;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -62,6 +63,7 @@ __global__ void ew_f32_kernel(const float* __restrict__ a, const float* __restri
 template <typename Op, bool BINARY>
 __global__ void ew_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ o,
                                long long n, bool vec) {
+  pdl_wait();
   Op op;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -92,7 +94,7 @@ int launch_ew_f32(const float* a, const float* b, float* o, long long n, cudaStr
   if (!a || !o || (BINARY && !b) || n < 0) return TEENY_ERR_BAD_ARG;
   if (n == 0) return TEENY_OK;
   const bool vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
-  ew_f32_kernel<Op, BINARY><<<ew_grid((n + 3) / 4, kEwThreads), kEwThreads, 0, st>>>(a, b, o, n, vec);
+  launch_kernel(ew_f32_kernel<Op, BINARY>, dim3(ew_grid((n + 3) / 4, kEwThreads)), dim3(kEwThreads), 0, st, 1, a, b, o, n, vec);
   return static_cast<int>(cudaGetLastError());
 }
 template <typename Op, bool BINARY>
@@ -100,13 +102,14 @@ int launch_ew_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStrea
   if (!a || !o || (BINARY && !b) || n < 0) return TEENY_ERR_BAD_ARG;
   if (n == 0) return TEENY_OK;
   const bool vec = aligned16(a) && aligned16(o) && (!BINARY || aligned16(b));
-  ew_bf16_kernel<Op, BINARY><<<ew_grid((n + 7) / 8, kEwThreads), kEwThreads, 0, st>>>(a, b, o, n, vec);
+  launch_kernel(ew_bf16_kernel<Op, BINARY>, dim3(ew_grid((n + 7) / 8, kEwThreads)), dim3(kEwThreads), 0, st, 1, a, b, o, n, vec);
   return static_cast<int>(cudaGetLastError());
 }
 
 // ---- RMSNorm, f32, one CTA per row (reference semantics: y = x * rrms * w) ----
 __global__ void rms_norm_f32_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ w,
                                     float* __restrict__ rrms, int N, float eps) {
+  pdl_wait();
   __shared__ float red[32];
   const float* xr = x + static_cast<size_t>(blockIdx.x) * N;
   float* yr = y + static_cast<size_t>(blockIdx.x) * N;
@@ -124,6 +127,7 @@ template <int VPT, bool ADD>
 __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
                                      long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
                                      float* __restrict__ rrms, int N, float eps) {
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
@@ -190,6 +194,7 @@ template <bool ADD>
 __global__ void rms_norm_bf16_scalar_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
                                             long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
                                             float* __restrict__ rrms, int N, float eps) {
+  pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const bf16* xr = x + static_cast<size_t>(row) * ldx;
@@ -228,14 +233,14 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
     else if (nv > 4 * 128) threads = 256;
     const int vpt = (nv + threads - 1) / threads;
 #define TEENY_RMS_CASE(V)                                                                                    \
-  rms_norm_bf16_kernel<V, ADD><<<M, threads, 0, st>>>(x, ldx, res, ldr, y, ldy, w, rrms, N, eps)
+  launch_kernel(rms_norm_bf16_kernel<V, ADD>, dim3(M), dim3(threads), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps)
     if (vpt <= 1) TEENY_RMS_CASE(1);
     else if (vpt <= 2) TEENY_RMS_CASE(2);
     else if (vpt <= 4) TEENY_RMS_CASE(4);
     else TEENY_RMS_CASE(8);
 #undef TEENY_RMS_CASE
   } else {
-    rms_norm_bf16_scalar_kernel<ADD><<<M, 256, 0, st>>>(x, ldx, res, ldr, y, ldy, w, rrms, N, eps);
+    launch_kernel(rms_norm_bf16_scalar_kernel<ADD>, dim3(M), dim3(256), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps);
   }
   return static_cast<int>(cudaGetLastError());
 }
@@ -243,6 +248,7 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
 // ---- SiLU(gate) * up on the fused [T, 2*inter] projection ----
 __global__ void silu_mul_bf16_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
                                      int inter) {
+  pdl_wait();
   const int vec_per_row = inter >> 3;
   const long long total = static_cast<long long>(T) * vec_per_row;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -264,6 +270,7 @@ __global__ void silu_mul_bf16_kernel(const bf16* __restrict__ gu, long long ld, 
 }
 __global__ void silu_mul_bf16_scalar_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
                                             int inter) {
+  pdl_wait();
   const long long total = static_cast<long long>(T) * inter;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -277,6 +284,7 @@ __global__ void silu_mul_bf16_scalar_kernel(const bf16* __restrict__ gu, long lo
 // ---- embedding gather: one warp per 16-byte vector strip ----
 __global__ void embedding_bf16_kernel(const int* __restrict__ ids, const bf16* __restrict__ table,
                                       bf16* __restrict__ out, int T, int hidden, int vocab, bool vec) {
+  pdl_wait();
   const int row = blockIdx.x;
   if (row >= T) return;
   int id = ids[row];
@@ -294,6 +302,7 @@ __global__ void embedding_bf16_kernel(const int* __restrict__ ids, const bf16* _
 // ---- RoPE tables ----
 __global__ void rope_table_kernel(const float* __restrict__ inv_freq, bf16* __restrict__ cos_t,
                                   bf16* __restrict__ sin_t, int max_pos, int D) {
+  pdl_wait();
   const int half = D >> 1;
   const long long total = static_cast<long long>(max_pos) * half;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
@@ -317,6 +326,7 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
                                        const bf16* __restrict__ sin_t, bf16* __restrict__ k_cache,
                                        bf16* __restrict__ v_cache, int T, int S, int Hq, int Hkv, int max_len,
                                        int pos0, const int* __restrict__ pos0_dev, float eps) {
+  pdl_wait();
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
   const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -378,6 +388,7 @@ __device__ __forceinline__ void stf(bf16* p, float v) { *p = __float2bfloat16_rn
 
 template <typename T>
 __global__ void softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int cols) {
+  pdl_wait();
   __shared__ float red[32];
   const T* xr = x + static_cast<size_t>(blockIdx.x) * cols;
   T* yr = y + static_cast<size_t>(blockIdx.x) * cols;
@@ -401,6 +412,7 @@ __device__ __forceinline__ void argmax_merge(float& v, int& i, float ov, int oi)
 }
 __global__ void argmax_bf16_kernel(const bf16* __restrict__ logits, long long ld, float* __restrict__ best_val,
                                    int* __restrict__ best_idx, int cols, int idx_offset, bool vec) {
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const bf16* row = logits + static_cast<size_t>(blockIdx.x) * ld;
@@ -446,6 +458,7 @@ __global__ void argmax_bf16_kernel(const bf16* __restrict__ logits, long long ld
 }
 __global__ void argmax_combine_kernel(const float* __restrict__ vals, const int* __restrict__ idx,
                                       int* __restrict__ out_idx, int parts, int rows) {
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float v = -INFINITY;
@@ -459,7 +472,7 @@ __global__ void argmax_combine_kernel(const float* __restrict__ vals, const int*
 int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, int N, float eps, cudaStream_t st) {
   if (!x || !y || !w || M < 0 || N <= 0) return TEENY_ERR_BAD_ARG;
   if (M == 0) return TEENY_OK;
-  rms_norm_f32_kernel<<<M, 128, 0, st>>>(x, y, w, rrms, N, eps);
+  launch_kernel(rms_norm_f32_kernel, dim3(M), dim3(128), 0, st, 1, x, y, w, rrms, N, eps);
   return static_cast<int>(cudaGetLastError());
 }
 int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
@@ -480,13 +493,13 @@ int add_bf16(const bf16* a, const bf16* b, bf16* o, long long n, cudaStream_t st
 int softmax_f32(const float* x, float* y, int rows, int cols, cudaStream_t st) {
   if (!x || !y || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
   if (rows == 0) return TEENY_OK;
-  softmax_kernel<float><<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, cols);
+  launch_kernel(softmax_kernel<float>, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, st, 1, x, y, cols);
   return static_cast<int>(cudaGetLastError());
 }
 int softmax_bf16(const bf16* x, bf16* y, int rows, int cols, cudaStream_t st) {
   if (!x || !y || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
   if (rows == 0) return TEENY_OK;
-  softmax_kernel<bf16><<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, y, cols);
+  launch_kernel(softmax_kernel<bf16>, dim3(rows), dim3(cols >= 1024 ? 256 : 128), 0, st, 1, x, y, cols);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -495,9 +508,9 @@ int silu_mul_bf16(const bf16* gate_up, long long ld, bf16* out, int T, int inter
   if (T == 0) return TEENY_OK;
   const bool vec = (inter % 8 == 0) && (ld % 8 == 0) && aligned16(gate_up) && aligned16(out);
   if (vec)
-    silu_mul_bf16_kernel<<<ew_grid(static_cast<long long>(T) * (inter / 8), kEwThreads), kEwThreads, 0, st>>>(gate_up, ld, out, T, inter);
+    launch_kernel(silu_mul_bf16_kernel, dim3(ew_grid(static_cast<long long>(T) * (inter / 8), kEwThreads)), dim3(kEwThreads), 0, st, 1, gate_up, ld, out, T, inter);
   else
-    silu_mul_bf16_scalar_kernel<<<ew_grid(static_cast<long long>(T) * inter, kEwThreads), kEwThreads, 0, st>>>(gate_up, ld, out, T, inter);
+    launch_kernel(silu_mul_bf16_scalar_kernel, dim3(ew_grid(static_cast<long long>(T) * inter, kEwThreads)), dim3(kEwThreads), 0, st, 1, gate_up, ld, out, T, inter);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -505,13 +518,13 @@ int embedding_bf16(const int* ids, const bf16* table, bf16* out, int T, int hidd
   if (!ids || !table || !out || T < 0 || hidden <= 0 || vocab <= 0) return TEENY_ERR_BAD_ARG;
   if (T == 0) return TEENY_OK;
   const bool vec = (hidden % 8 == 0) && aligned16(table) && aligned16(out);
-  embedding_bf16_kernel<<<T, 128, 0, st>>>(ids, table, out, T, hidden, vocab, vec);
+  launch_kernel(embedding_bf16_kernel, dim3(T), dim3(128), 0, st, 1, ids, table, out, T, hidden, vocab, vec);
   return static_cast<int>(cudaGetLastError());
 }
 
 int rope_table_bf16(const float* inv_freq, bf16* cos_t, bf16* sin_t, int max_pos, int D, cudaStream_t st) {
   if (!inv_freq || !cos_t || !sin_t || max_pos <= 0 || D <= 0 || (D & 1)) return TEENY_ERR_BAD_ARG;
-  rope_table_kernel<<<ew_grid(static_cast<long long>(max_pos) * (D / 2), kEwThreads), kEwThreads, 0, st>>>(inv_freq, cos_t, sin_t, max_pos, D);
+  launch_kernel(rope_table_kernel, dim3(ew_grid(static_cast<long long>(max_pos) * (D / 2), kEwThreads)), dim3(kEwThreads), 0, st, 1, inv_freq, cos_t, sin_t, max_pos, D);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -527,7 +540,7 @@ int qk_norm_rope_kv_bf16(bf16* qkv, long long ld, const bf16* q_w, const bf16* k
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
   const long long blocks = (warps + 7) / 8;
   if (blocks > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
-  qk_norm_rope_kv_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(qkv, ld, q_w, k_w, cos_t, sin_t, k_cache, v_cache,
+  launch_kernel(qk_norm_rope_kv_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 1, qkv, ld, q_w, k_w, cos_t, sin_t, k_cache, v_cache,
                                                                    T, S, Hq, Hkv, max_len, pos0, pos0_dev, eps);
   return static_cast<int>(cudaGetLastError());
 }
@@ -537,13 +550,13 @@ int argmax_bf16(const bf16* logits, long long ld, float* best_val, int* best_idx
   if (!logits || !best_val || !best_idx || rows < 0 || cols <= 0) return TEENY_ERR_BAD_ARG;
   if (rows == 0) return TEENY_OK;
   const bool vec = aligned16(logits) && (ld % 8 == 0);
-  argmax_bf16_kernel<<<rows, 1024, 0, st>>>(logits, ld, best_val, best_idx, cols, idx_offset, vec);
+  launch_kernel(argmax_bf16_kernel, dim3(rows), dim3(1024), 0, st, 1, logits, ld, best_val, best_idx, cols, idx_offset, vec);
   return static_cast<int>(cudaGetLastError());
 }
 int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, cudaStream_t st) {
   if (!vals || !idx || !out_idx || parts <= 0 || rows < 0) return TEENY_ERR_BAD_ARG;
   if (rows == 0) return TEENY_OK;
-  argmax_combine_kernel<<<(rows + 127) / 128, 128, 0, st>>>(vals, idx, out_idx, parts, rows);
+  launch_kernel(argmax_combine_kernel, dim3((rows + 127) / 128), dim3(128), 0, st, 1, vals, idx, out_idx, parts, rows);
   return static_cast<int>(cudaGetLastError());
 }
 

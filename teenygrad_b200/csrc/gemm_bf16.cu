@@ -130,6 +130,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();  // set-up above overlapped the previous kernel; operands and outputs are touched from here on
 
   const int num_work = args.tiles_p * args.tiles_q;
 
@@ -257,6 +258,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
   }
 
   // ---------------- teardown ----------------
+  pdl_trigger();  // this CTA has no more tiles to start: the next kernel may begin its set-up
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {
@@ -352,9 +354,19 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   if (warp == 0) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      // Weights are never written by a kernel of the stream, so the first ring of weight tiles is requested while
+      // the previous kernel may still be running; the activation tiles follow once it has finished.
+      const int pre = min(kb1 - kb0, Cfg::kStages);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
+        tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_w, full_bar(i), (kb0 + i) * kBK, tile * kBM);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kStageP, &tmap_x, full_bar(i), (kb0 + i) * kBK, 0);
+      int stage = pre == Cfg::kStages ? 0 : pre;
+      uint32_t phase = pre == Cfg::kStages ? 1 : 0;
+      for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) break;
         const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
         mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
@@ -362,8 +374,11 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tma_load_2d(sp + Cfg::kStageP, &tmap_x, full_bar(stage), kb * kBK, 0);
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -381,6 +396,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   } else {
     // accumulator -> this CTA's partial tile in shared memory, column-major so a thread's stores and the later
     // per-column reads are both conflict-free (consecutive rows = consecutive words)
+    pdl_wait();
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     if (mbar_wait(acc_full_bar, 0, err, DEVERR_GEMM_EPILOGUE)) {
@@ -401,6 +417,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   // every partial tile of the cluster is in place
   __syncwarp();
+  pdl_trigger();  // main loop done: the next kernel's set-up (and weight prefetch) overlaps the reduction below
   cluster_sync_all();
 
   if (warp >= 2) {
@@ -473,7 +490,7 @@ template <int BN, bool SWAP, bool Q_MN>
 int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs& a, int grid, cudaStream_t st) {
   const int rc = prepare_variant<BN, SWAP, Q_MN>();
   if (rc) return rc;
-  gemm_bf16_kernel<BN, SWAP, Q_MN><<<grid, kNumThreads, GemmCfg<BN>::kSmemBytes, st>>>(tp, tq, a);
+  launch_kernel(gemm_bf16_kernel<BN, SWAP, Q_MN>, dim3(grid), dim3(kNumThreads), GemmCfg<BN>::kSmemBytes, st, 1, tp, tq, a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -482,19 +499,8 @@ int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& 
                   cudaStream_t st) {
   const int rc = prepare_skinny<BN>();
   if (rc) return rc;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(split, tiles, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
-  cfg.dynamicSmemBytes = SkinnyCfg<BN>::kSmemBytes;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = split;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<BN>, tw, tx, a));
+  return launch_kernel(gemm_bf16_skinny_kernel<BN>, dim3(split, tiles, 1), dim3(kNumThreads, 1, 1),
+                       SkinnyCfg<BN>::kSmemBytes, st, static_cast<unsigned>(split), tw, tx, a);
 }
 
 // Largest token count that takes the swapped (weights on the 128-row MMA side) assignment.

@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ a, long long sam, long long sak, const T* __restrict__ b, long long sbk,
                  long long sbn, const T* __restrict__ bias, T* __restrict__ c, long long scm, long long scn, int M,
                  int N, int K) {
+  pdl_wait();
   __shared__ float as[kTK][kTM + 4];
   __shared__ float bs[kTK][kTN + 4];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -83,7 +84,7 @@ int launch(const T* a, long long sam, long long sak, const T* b, long long sbk, 
   if (!a || !b || !c || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
   dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
   if (grid.y > 65535) return TEENY_ERR_BAD_ARG;
-  gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, sam, sak, b, sbk, sbn, bias, c, scm, scn, M, N, K);
+  launch_kernel(gemm_simt_kernel<T>, dim3(grid), dim3(256), 0, st, 1, a, sam, sak, b, sbk, sbn, bias, c, scm, scn, M, N, K);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -67,6 +67,7 @@ bool load_nccl() {
 
 __global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __restrict__ cur_ids,
                                    int* __restrict__ history, int* __restrict__ state, int B, int max_steps) {
+  pdl_wait();
   // state[0] = position of the next token to append, state[1] = live KV length during the step (= state[0] + 1),
   // state[2] = number of generated tokens so far
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
@@ -85,6 +86,7 @@ __global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __rest
 }
 
 __global__ void set_state_kernel(int* state, int pos, int len, int steps) {
+  pdl_wait();
   state[0] = pos;
   state[1] = len;
   state[2] = steps;
@@ -287,13 +289,21 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
   return 0;
 }
 
+// While alive, this thread's launches carry the programmatic-dependent-launch attribute, so each kernel's set-up
+// (and the decode GEMMs' first weight tiles) overlaps the tail of the kernel before it.
+struct PdlScope {
+  PdlScope() { pdl_set_enabled(true); }
+  ~PdlScope() { pdl_set_enabled(false); }
+};
+
 int decode_body(teeny_qwen3* m, int B, cudaStream_t st) {
+  PdlScope pdl;
   const teeny_qwen3_config& c = m->cfg;
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(m->at<int>(m->off.cur_ids), m->embed, m->at<bf16>(m->off.h), B, c.hidden, c.vocab, st));
   TEENY_TRY(run_layers(m, B, 1, 0, state + 0, state + 1, true, st));
   TEENY_TRY(run_head(m, B, 1, st));
-  finish_step_kernel<<<1, 1024, 0, st>>>(m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
+  launch_kernel(finish_step_kernel, dim3(1), dim3(1024), 0, st, 1, m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
                                          m->at<int>(m->off.history), state, B, c.max_new_tokens);
   return static_cast<int>(cudaGetLastError());
 }
@@ -400,14 +410,15 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
   if (B > c.max_batch || S > c.max_len || static_cast<long long>(B) * S > c.max_tokens) return TEENY_ERR_BAD_ARG;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   TEENY_TRY(check_ready(m, st));
+  PdlScope pdl;
   m->batch = B;
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(ids, m->embed, m->at<bf16>(m->off.h), B * S, c.hidden, c.vocab, st));
   TEENY_TRY(run_layers(m, B, S, 0, nullptr, nullptr, false, st));
   TEENY_TRY(run_head(m, B, S, st));
   // generation state: next position S, live length during the next step S + 1, no tokens recorded yet
-  set_state_kernel<<<1, 1, 0, st>>>(state, S - 1, S, 0);
-  finish_step_kernel<<<1, 1024, 0, st>>>(m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
+  launch_kernel(set_state_kernel, dim3(1), dim3(1), 0, st, 1, state, S - 1, S, 0);
+  launch_kernel(finish_step_kernel, dim3(1), dim3(1024), 0, st, 1, m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
                                          m->at<int>(m->off.history), state, B, c.max_new_tokens);
   return static_cast<int>(cudaGetLastError());
 }

@@ -29,7 +29,7 @@ def main():
         r = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + steps, max_new_tokens=steps, tp_rank=rank, tp_size=world,
                               comm=comm)
         r.load_state_dict(sd)
-        got = r.generate(ids, steps, use_graph=graph).clone()
+        got = r.generate(ids, steps, use_graph=graph).contiguous()
         torch.cuda.synchronize()
         assert qwen3.lib.teeny_device_error(1) == 0
         results.append(got)
