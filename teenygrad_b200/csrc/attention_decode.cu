@@ -1,11 +1,12 @@
 // Attention kernels that are not tcgen05-shaped.
 //
 // 1. attention_decode_bf16: one query token per sequence against a long KV cache.  HBM-bound (every K and V byte is
-//    read once, the query heads of a KV group share it), so the design goal is streaming the cache with 16-byte
-//    coalesced loads and enough loads in flight; the arithmetic runs on warp-level mma.sync tiles fed straight from
-//    registers (a 128-row tcgen05 tile would be 97 % padding for 4 query heads).  Split over the sequence: each CTA
-//    takes kDecChunk keys of one (batch, kv head), every warp a 16-key slice at a time with an online softmax, warps
-//    are merged through shared memory, per-chunk partials (m, l, O) go to scratch and a second kernel merges chunks.
+//    read once, the query heads of a KV group share it), so the design goal is streaming the cache: a producer warp
+//    keeps a ring of TMA tile copies in flight (data in flight costs no registers) and four consumer warps run the
+//    arithmetic on warp-level mma.sync tiles fed by ldmatrix (a 128-row tcgen05 tile would be 97 % padding for 4 query
+//    heads).  Split over the sequence: each CTA takes kDecChunk keys of one (batch, kv head), every consumer warp 16
+//    keys of each 64-key tile with an online softmax, warps are merged through shared memory, per-chunk partials
+//    (m, l, O) go to scratch and a second kernel merges chunks.
 // 2. attention_generic<T>: any head_dim <= 256, f32 or bf16, one warp per query row, sequential online softmax --
 //    the reference kernel's own recurrence; used for the f32 entry point and for shapes the tcgen05 kernel
 //    does not cover.
@@ -17,20 +18,7 @@ namespace teeny {
 namespace {
 
 constexpr int kDecChunk = 512;
-constexpr int kDecWarps = 4;
-constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kHD = 128;
-
-struct DecodeArgs {
-  const bf16 *q, *k, *v;
-  float* part_o;   // [B, Hkv, chunks, G, 128]
-  float* part_ml;  // [B, Hkv, chunks, G, 2]
-  long long q_sb, q_sh, k_sb, k_sh, k_ss, v_sb, v_sh, v_ss;
-  int Hkv, G, max_chunks;
-  int kv_len;
-  const int* kv_len_dev;
-  float scale_log2;
-};
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
@@ -39,178 +27,216 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-  uint32_t r;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-  return r;
-}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ uint4 ldg_nc(const bf16* p) {
-  uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "l"(p));
-  return r;
+
+// ---- decode kernel: TMA-fed shared-memory ring + mma.sync ----
+// CTA = one (batch, kv head, chunk of kDecChunk keys).  Warp 4 is the producer: for every 64-key tile it requests the
+// K rows and the V rows (two [64 keys][64 d] boxes each, 128-byte swizzle) into a kDecStages-deep ring and the copies
+// signal a `full` mbarrier; nothing in flight costs registers.  Warps 0-3 each own 16 keys of a tile:
+//   S = Q K^T   A = Q from registers (rows = the G query heads of the group, padded to 16), B = K fragments through
+//               ldmatrix (a matrix row is one key's 16 bytes, so the swizzle makes the eight rows conflict-free);
+//   softmax     online, log2 domain, in the C-fragment registers (lane group g = head, lane c = key pair);
+//   O += P V    A = P straight from the S fragments, B = V fragments through ldmatrix.trans (pairs of keys per d).
+// Fragment layout (mma.m16n8k16, g = lane / 4, c = lane % 4): A a0 = (row g, k 2c..2c+1), a2 = (row g, k 2c+8..);
+// B b0 = (k 2c..2c+1, col g), b1 = (k 2c+8.., col g); C c0,c1 = (row g, cols 2c, 2c+1); rows 8..15 are padding.
+struct DecodeArgs {
+  const bf16* q;
+  float* part_o;   // [B, Hkv, chunks, G, 128]
+  float* part_ml;  // [B, Hkv, chunks, G, 2]
+  long long q_sb, q_sh;
+  int Hkv, G, max_chunks;
+  int kv_len;
+  const int* kv_len_dev;
+  float scale_log2;
+  int* err;
+};
+
+constexpr int kDecTile = 64;                     // keys per ring stage
+constexpr int kDecStages = 3;
+constexpr int kDecBox = kDecTile * 64 * 2;       // 8 KB: [64 keys][64 d]
+constexpr int kDecStageBytes = 4 * kDecBox;      // K (2 boxes) + V (2 boxes) = 32 KB
+constexpr int kDecSmem = kDecStages * kDecStageBytes + 1024 + 64;
+constexpr int kDecThreads = 160;                 // 4 consumer warps + 1 producer warp
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
-// Fragment conventions (mma.m16n8k16, g = lane / 4, c = lane % 4):
-//   A (16 x 16, rows = query heads of the group, rows >= G are zero): a0 = (row g, k 2c..2c+1), a2 = (row g, k 2c+8..)
-//   B (16 x 8): b0 = (k 2c..2c+1, col g), b1 = (k 2c+8.., col g)
-//   C (16 x 8): c0,c1 = (row g, cols 2c, 2c+1); c2,c3 = rows g+8 (padding, stays zero)
-// The contraction index of Q K^T is d, and any permutation of d may be used as long as A and B agree: lane (g, c)
-// loads the 16 contiguous bytes d = 32p + 8c .. +8 of "its" key (B side) or head (A side), p = 0..3, and feeds the
-// first four values to k-step 2p and the last four to k-step 2p+1.  Each warp-wide load therefore covers 8 key rows
-// x 64 contiguous bytes.
-// For P V the contraction index is the key and the output column is d (again any labelling works): lane (g, c) loads
-// d = 64 ps + 8g .. +8 of keys 2c, 2c+1, 2c+8, 2c+9 and byte-permutes pairs of keys into one register; MMA (ps, i)
-// then produces O[head][d = 64 ps + 8 n + i] in column n.
 template <int G>
-__global__ void __launch_bounds__(kDecThreads)
-attention_decode_kernel(const DecodeArgs a) {
-  pdl_wait();
+__global__ void __launch_bounds__(kDecThreads, 2)
+attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                        const DecodeArgs a) {
+  extern __shared__ uint8_t dec_smem_raw[];
+  __shared__ float sm_ml[4][8][2];
+  __shared__ float sm_o[4][G][kHD];
+  const uint32_t base = (smem_u32(dec_smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = dec_smem_raw + (base - smem_u32(dec_smem_raw));
+  const uint32_t bar0 = base + kDecStages * kDecStageBytes;
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kDecStages + s); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    for (int s = 0; s < kDecStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 4);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_wait();  // the cache rows of this step and the live length come from earlier kernels of the stream
   const int L = a.kv_len_dev ? *a.kv_len_dev : a.kv_len;
   const int key_begin = chunk * kDecChunk;
-  if (key_begin >= L) return;
   const int key_end = min(L, key_begin + kDecChunk);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = key_begin < L ? (key_end - key_begin + kDecTile - 1) / kDecTile : 0;
   const int g = lane >> 2, c = lane & 3;
+  float acc[16][4];
+  float m = -INFINITY, l = 0.0f;
+  if (n_tiles == 0) return;  // chunk lies beyond the live length (uniform for the CTA)
 
-  // Q fragments: head = hk * G + g (zero rows beyond G)
-  uint4 qf[4];
-  if (g < G) {
-    const bf16* qp = a.q + b * a.q_sb + (hk * G + g) * a.q_sh;
-#pragma unroll
-    for (int p = 0; p < 4; ++p) qf[p] = *reinterpret_cast<const uint4*>(qp + 32 * p + 8 * c);
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      for (int t = 0; t < n_tiles; ++t) {
+        const int st = t % kDecStages;
+        const uint32_t ph = (t / kDecStages) & 1;
+        if (!mbar_wait(empty_bar(st), ph ^ 1, a.err, DEVERR_ATTN_PRODUCER)) break;
+        const uint32_t dst = base + st * kDecStageBytes;
+        const int key0 = key_begin + t * kDecTile;
+        mbar_expect_tx(full_bar(st), kDecStageBytes);
+        tma_load_4d(dst, &tmap_k, full_bar(st), 0, key0, hk, b);
+        tma_load_4d(dst + kDecBox, &tmap_k, full_bar(st), 64, key0, hk, b);
+        tma_load_4d(dst + 2 * kDecBox, &tmap_v, full_bar(st), 0, key0, hk, b);
+        tma_load_4d(dst + 3 * kDecBox, &tmap_v, full_bar(st), 64, key0, hk, b);
+      }
+    }
   } else {
+    // ---------------- consumers: warp w owns keys [16 w, 16 w + 16) of every tile ----------------
 #pragma unroll
-    for (int p = 0; p < 4; ++p) qf[p] = make_uint4(0, 0, 0, 0);
-  }
-  const bf16* kbase = a.k + b * a.k_sb + hk * a.k_sh;
-  const bf16* vbase = a.v + b * a.v_sb + hk * a.v_sh;
-
-  float acc[2][8][4];
+    for (int i = 0; i < 16; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+    // Q fragments: head hk * G + g; a0 = d 16 ks + 2c.., a2 = d 16 ks + 8 + 2c..; rows >= G are zero
+    uint32_t qa[8][2];
+    {
+      const bf16* qp = a.q + b * a.q_sb + (hk * G + (g < G ? g : 0)) * a.q_sh;
 #pragma unroll
-  for (int ps = 0; ps < 2; ++ps)
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[ps][i][e] = 0.0f;
-  float m = -INFINITY, l = 0.0f;  // per row g (replicated over the 4 lanes of the group)
-
-  // K and V fragments of one 16-key slice (64 registers).  The slice after the current one is loaded before the
-  // current one is consumed, so every warp keeps 8 KB of cache reads in flight while its tensor-core work runs.
-  struct Slice { uint4 kf[2][4]; uint4 vf[2][4]; };
-  auto load_slice = [&](Slice& f, int kb) {
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-      const int key = min(kb + nb * 8 + g, L - 1);  // clamp: masked later, but the load must stay in valid rows
-      const bf16* kp = kbase + static_cast<long long>(key) * a.k_ss + 8 * c;
-#pragma unroll
-      for (int p = 0; p < 4; ++p) f.kf[nb][p] = ldg_nc(kp + 32 * p);
-    }
-    const int k0 = min(kb + 2 * c, L - 1), k1 = min(kb + 2 * c + 1, L - 1);
-    const int k2 = min(kb + 8 + 2 * c, L - 1), k3 = min(kb + 9 + 2 * c, L - 1);
-#pragma unroll
-    for (int ps = 0; ps < 2; ++ps) {
-      const int d0 = 64 * ps + 8 * g;
-      f.vf[ps][0] = ldg_nc(vbase + static_cast<long long>(k0) * a.v_ss + d0);
-      f.vf[ps][1] = ldg_nc(vbase + static_cast<long long>(k1) * a.v_ss + d0);
-      f.vf[ps][2] = ldg_nc(vbase + static_cast<long long>(k2) * a.v_ss + d0);
-      f.vf[ps][3] = ldg_nc(vbase + static_cast<long long>(k3) * a.v_ss + d0);
-    }
-  };
-  constexpr int kStride = kDecWarps * 16;
-  Slice cur;
-  if (key_begin + warp * 16 < key_end) load_slice(cur, key_begin + warp * 16);
-#pragma unroll 2
-  for (int kb = key_begin + warp * 16; kb < key_end; kb += kStride) {
-    Slice nxt;
-    if (kb + kStride < key_end) load_slice(nxt, kb + kStride);
-    // ---- S = Q K^T for 16 keys (two 8-key column blocks) ----
-    float s[2][4];
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb) {
-      s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
-#pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        mma_bf16_16816(s[nb], qf[p].x, 0u, qf[p].y, 0u, cur.kf[nb][p].x, cur.kf[nb][p].y);
-        mma_bf16_16816(s[nb], qf[p].z, 0u, qf[p].w, 0u, cur.kf[nb][p].z, cur.kf[nb][p].w);
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 2 * c);
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 8 + 2 * c);
+        qa[ks][0] = g < G ? lo : 0u;
+        qa[ks][1] = g < G ? hi : 0u;
       }
     }
-    // ---- online softmax on row g: this lane holds keys kb + nb*8 + 2c + {0,1} ----
-    float tmax = -INFINITY;
+    const int row_k = 16 * warp + (lane & 7);  // ldmatrix row this lane addresses for K: + 8 * n-block
+    const int mat = lane >> 3;                 // which of the four 8x8 matrices this lane addresses
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t % kDecStages;
+      const uint32_t ph = (t / kDecStages) & 1;
+      if (!mbar_wait(full_bar(st), ph, a.err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+      const uint32_t kt = base + st * kDecStageBytes, vt = kt + 2 * kDecBox;
+      const int kb = key_begin + t * kDecTile + 16 * warp;  // first key of this warp's slice
+      if (kb < key_end) {
+        if (kb + 16 > key_end) {
+          // rows past the live length hold whatever the cache had (possibly NaN patterns): their probabilities are
+          // zero, but 0 * NaN is NaN inside the MMA, so clear those V rows first
+          uint8_t* vrow = gen + st * kDecStageBytes + 2 * kDecBox;
+          for (int i = lane; i < 256; i += 32) {
+            const int r = i >> 4, ch = i & 15;
+            if (kb + r >= key_end)
+              *reinterpret_cast<uint4*>(vrow + (ch >> 3) * kDecBox + (16 * warp + r) * 128 + (ch & 7) * 16) =
+                  make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
+        }
+        // ---- S = Q K^T: two 8-key column blocks ----
+        float s[2][4];
 #pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
+        for (int nb = 0; nb < 2; ++nb) {
+          s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+          const int row = row_k + 8 * nb;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int key = kb + nb * 8 + 2 * c + e;
-        s[nb][e] = key < key_end ? s[nb][e] * a.scale_log2 : -INFINITY;
-        tmax = fmaxf(tmax, s[nb][e]);
+          for (int p = 0; p < 4; ++p) {  // 32 d per ldmatrix.x4: matrices = four 8-d chunks
+            uint32_t kf[4];
+            ldsm_x4(kf, kt + (p >> 1) * kDecBox + row * 128 + ((((p & 1) * 4 + mat) ^ (row & 7)) << 4));
+            mma_bf16_16816(s[nb], qa[2 * p][0], 0u, qa[2 * p][1], 0u, kf[0], kf[1]);
+            mma_bf16_16816(s[nb], qa[2 * p + 1][0], 0u, qa[2 * p + 1][1], 0u, kf[2], kf[3]);
+          }
+        }
+        // ---- online softmax on row g: this lane holds keys kb + nb*8 + 2c + {0,1} ----
+        float tmax = -INFINITY;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = kb + nb * 8 + 2 * c + e;
+            s[nb][e] = key < key_end ? s[nb][e] * a.scale_log2 : -INFINITY;
+            tmax = fmaxf(tmax, s[nb][e]);
+          }
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+        tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+        const float m_new = fmaxf(m, tmax);  // finite: key kb itself is < key_end
+        const float alpha = ex2(m - m_new);  // m = -inf on the first slice -> 0
+        m = m_new;
+        float p[2][2], psum = 0.0f;
+#pragma unroll
+        for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            p[nb][e] = ex2(s[nb][e] - m);
+            psum += p[nb][e];
+          }
+        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+        l = l * alpha + psum;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          acc[i][0] *= alpha;
+          acc[i][1] *= alpha;
+        }
+        const uint32_t pa0 = pack_bf16x2(p[0][0], p[0][1]);  // keys 2c, 2c+1
+        const uint32_t pa2 = pack_bf16x2(p[1][0], p[1][1]);  // keys 2c+8, 2c+9
+        // ---- O += P V: ldmatrix.trans yields (key pair, d) fragments; one x4 covers two 8-wide d blocks ----
+        const int row_v = 16 * warp + (mat & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int nbp = 0; nbp < 8; ++nbp) {
+          const int chunk16 = 2 * nbp + (mat >> 1);  // 8-d chunk index 0..15
+          uint32_t vf[4];
+          ldsm_x4_trans(vf, vt + (chunk16 >> 3) * kDecBox + row_v * 128 + (((chunk16 & 7) ^ (row_v & 7)) << 4));
+          mma_bf16_16816(acc[2 * nbp], pa0, 0u, pa2, 0u, vf[0], vf[1]);
+          mma_bf16_16816(acc[2 * nbp + 1], pa0, 0u, pa2, 0u, vf[2], vf[3]);
+        }
       }
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-    tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-    const float m_new = fmaxf(m, tmax);  // finite: key kb itself is always < key_end
-    const float alpha = ex2(m - m_new);  // m = -inf on the first slice -> 0
-    m = m_new;
-    float p[2][2], psum = 0.0f;
-#pragma unroll
-    for (int nb = 0; nb < 2; ++nb)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        p[nb][e] = ex2(s[nb][e] - m);
-        psum += p[nb][e];
-      }
-    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
-    l = l * alpha + psum;
-#pragma unroll
-    for (int ps = 0; ps < 2; ++ps)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        acc[ps][i][0] *= alpha;
-        acc[ps][i][1] *= alpha;
-      }
-    const uint32_t pa0 = pack_bf16x2(p[0][0], p[0][1]);  // keys 2c, 2c+1
-    const uint32_t pa2 = pack_bf16x2(p[1][0], p[1][1]);  // keys 2c+8, 2c+9
-    // ---- O += P V ----
-#pragma unroll
-    for (int ps = 0; ps < 2; ++ps) {
-      const uint32_t w0[4] = {cur.vf[ps][0].x, cur.vf[ps][0].y, cur.vf[ps][0].z, cur.vf[ps][0].w};
-      const uint32_t w1[4] = {cur.vf[ps][1].x, cur.vf[ps][1].y, cur.vf[ps][1].z, cur.vf[ps][1].w};
-      const uint32_t w2[4] = {cur.vf[ps][2].x, cur.vf[ps][2].y, cur.vf[ps][2].z, cur.vf[ps][2].w};
-      const uint32_t w3[4] = {cur.vf[ps][3].x, cur.vf[ps][3].y, cur.vf[ps][3].z, cur.vf[ps][3].w};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;
-        const uint32_t b0 = prmt(w0[i >> 1], w1[i >> 1], sel);  // (key 2c, key 2c+1) at d index i
-        const uint32_t b1 = prmt(w2[i >> 1], w3[i >> 1], sel);  // (key 2c+8, key 2c+9)
-        mma_bf16_16816(acc[ps][i], pa0, 0u, pa2, 0u, b0, b1);
-      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(st));  // this warp has read everything it needs from the stage
     }
-    cur = nxt;
+    (void)ok;
   }
 
   pdl_trigger();  // cache streaming done; what follows is the small merge
-  // ---- merge the warps of this CTA ----
-  __shared__ float sm_ml[kDecWarps][8][2];
-  __shared__ float sm_o[kDecWarps][G][kHD];
-  if (c == 0 && g < G) {
-    sm_ml[warp][g][0] = m;
-    sm_ml[warp][g][1] = l;
-  }
-  if (g < G) {
+  // ---- merge the four consumer warps ----
+  if (warp < 4) {
+    if (c == 0 && g < G) {
+      sm_ml[warp][g][0] = m;
+      sm_ml[warp][g][1] = l;
+    }
+    if (g < G) {
 #pragma unroll
-    for (int ps = 0; ps < 2; ++ps)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        sm_o[warp][g][64 * ps + 8 * (2 * c) + i] = acc[ps][i][0];
-        sm_o[warp][g][64 * ps + 8 * (2 * c + 1) + i] = acc[ps][i][1];
+      for (int nb = 0; nb < 16; ++nb) {
+        sm_o[warp][g][8 * nb + 2 * c] = acc[nb][0];
+        sm_o[warp][g][8 * nb + 2 * c + 1] = acc[nb][1];
       }
+    }
   }
   __syncthreads();
   const size_t slot = (static_cast<size_t>(b) * a.Hkv + hk) * a.max_chunks + chunk;
@@ -218,10 +244,10 @@ attention_decode_kernel(const DecodeArgs a) {
     const int gg = idx / kHD, d = idx - gg * kHD;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, sm_ml[w][gg][0]);  // warps without keys hold -inf
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[w][gg][0]);  // warps without keys hold -inf
     float ll = 0.0f, oo = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kDecWarps; ++w) {
+    for (int w = 0; w < 4; ++w) {
       const float wm = sm_ml[w][gg][0];
       const float sc = (wm == -INFINITY) ? 0.0f : ex2(wm - mm);
       ll += sm_ml[w][gg][1] * sc;
@@ -321,6 +347,21 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 
 }  // namespace
 
+// Raises the decode kernel's dynamic shared-memory limit once per device.
+int attention_decode_prepare() {
+  static unsigned long long done = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 64) done |= 1ull << dev;
+  return 0;
+}
+
 size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv) {
   if (B <= 0 || Hq <= 0 || D <= 0 || max_kv <= 0) return 0;
   const size_t chunks = (static_cast<size_t>(max_kv) + kDecChunk - 1) / kDecChunk;
@@ -344,22 +385,38 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   const int max_chunks = (s.Skv + kDecChunk - 1) / kDecChunk;
   if (s.Hkv > 65535 || s.B > 65535) return TEENY_ERR_BAD_ARG;
 
+  // K and V caches as 4-D tensors (d, key, kv head, batch); a tile is two [64 keys][64 d] boxes
+  CUtensorMap mk, mv;
+  {
+    const uint64_t dims[4] = {kHD, static_cast<uint64_t>(s.Skv), static_cast<uint64_t>(s.Hkv), static_cast<uint64_t>(s.B)};
+    const uint32_t box[4] = {64, kDecTile, 1, 1};
+    auto nz = [](long long st, long long fb) { return static_cast<uint64_t>(st > 0 ? st : fb) * 2; };
+    const uint64_t ks[3] = {static_cast<uint64_t>(s.k_ss) * 2, nz(s.k_sh, s.k_ss), nz(s.k_sb, s.k_ss)};
+    const uint64_t vs[3] = {static_cast<uint64_t>(s.v_ss) * 2, nz(s.v_sh, s.v_ss), nz(s.v_sb, s.v_ss)};
+    int rc = encode_tensor_map_bf16(&mk, k, 4, dims, ks, box);
+    if (rc) return rc;
+    rc = encode_tensor_map_bf16(&mv, v, 4, dims, vs, box);
+    if (rc) return rc;
+  }
+  {
+    const int rc = attention_decode_prepare();
+    if (rc) return rc;
+  }
   DecodeArgs a{};
-  a.q = q; a.k = k; a.v = v;
+  a.q = q;
   a.part_o = static_cast<float*>(scratch);
   a.part_ml = a.part_o + static_cast<size_t>(s.B) * s.Hq * max_chunks * kHD;
   a.q_sb = s.q_sb; a.q_sh = s.q_sh;
-  a.k_sb = s.k_sb; a.k_sh = s.k_sh; a.k_ss = s.k_ss;
-  a.v_sb = s.v_sb; a.v_sh = s.v_sh; a.v_ss = s.v_ss;
   a.Hkv = s.Hkv; a.G = G; a.max_chunks = max_chunks;
   a.kv_len = kv_len; a.kv_len_dev = kv_len_dev;
   a.scale_log2 = s.scale * 1.4426950408889634f;
+  a.err = device_error_word();
   dim3 grid(max_chunks, s.Hkv, s.B);
   switch (G) {
-    case 1: launch_kernel(attention_decode_kernel<1>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
-    case 2: launch_kernel(attention_decode_kernel<2>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
-    case 4: launch_kernel(attention_decode_kernel<4>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
-    default: launch_kernel(attention_decode_kernel<8>, dim3(grid), dim3(kDecThreads), 0, stream, 1, a); break;
+    case 1: launch_kernel(attention_decode_kernel<1>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
+    case 2: launch_kernel(attention_decode_kernel<2>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
+    case 4: launch_kernel(attention_decode_kernel<4>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
+    default: launch_kernel(attention_decode_kernel<8>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -19,6 +19,7 @@ size_t gemm_bf16_scratch_bytes(int M, int N, int K);
 // Set function attributes for every kernel variant on the current device (also done lazily at first launch).
 int gemm_bf16_prepare();
 int attention_prefill_prepare();
+int attention_decode_prepare();
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
               int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
