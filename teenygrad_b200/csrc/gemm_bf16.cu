@@ -280,10 +280,13 @@ struct SkinnyCfg {
   static constexpr int kStageP = kBM * kBK * 2;
   static constexpr int kStageQ = BN * kBK * 2;
   static constexpr int kStageBytes = kStageP + kStageQ;
-  static constexpr int kStages = (BN >= 128) ? 3 : 4;
-  static constexpr int kPartialBytes = BN * kBM * 4;  // f32 partial tile, column-major [BN][128]
+  // As many stages as let two CTAs share an SM (about 100 KB each): what streams the weights fast is the number of
+  // bytes in flight per SM, and two short-lived CTAs overlap each other's set-up and reduction.
+  static constexpr int kStages = (BN <= 32) ? 5 : (BN <= 64 ? 4 : 3);
+  static constexpr int kPartialBytes = BN * kBM * 4;  // f32 partial tile, column-major [BN][128]; reuses the ring
+  static_assert(kPartialBytes <= kStages * kStageBytes, "partial tile must fit in the stage ring");
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kPartialBytes + 1024 + 128;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 128;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -315,16 +318,18 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   using Cfg = SkinnyCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t part_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
-  const uint32_t bar_base = part_base + Cfg::kPartialBytes;
+  // The partial tile is written after the last MMA has completed, i.e. when no stage is in use any more, so it
+  // lives at the start of the ring.
+  const uint32_t part_base = smem_base;
+  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
   const uint32_t acc_full_bar = bar_base + 8u * (2 * Cfg::kStages);
   const uint32_t tmem_slot = acc_full_bar + 8;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  float* part_gen = reinterpret_cast<float*>(smem_gen + Cfg::kStages * Cfg::kStageBytes);
+  float* part_gen = reinterpret_cast<float*>(smem_gen);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
-      smem_gen + Cfg::kStages * Cfg::kStageBytes + Cfg::kPartialBytes + 8 * (2 * Cfg::kStages + 1));
+      smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 1));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* err = args.err;
@@ -425,12 +430,12 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int n = tile * kBM + row;
-    const int cw = BN / static_cast<int>(S);
+    const int cw = (BN + static_cast<int>(S) - 1) / static_cast<int>(S);  // columns per rank (last rank may get fewer)
+    const int c_end = min(BN, (static_cast<int>(rank) + 1) * cw);
     const float bias = (args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
     const bool live = *reinterpret_cast<volatile int*>(err) == 0;
 #pragma unroll 4
-    for (int j = 0; j < cw; ++j) {
-      const int c = static_cast<int>(rank) * cw + j;
+    for (int c = static_cast<int>(rank) * cw; c < c_end; ++c) {
       const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + row) * 4);
       float v[8];
 #pragma unroll
@@ -578,15 +583,16 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   if (swap) {
     const int tiles = ceil_div(N, kBM);
     if (tiles < 4 * sms && tiles <= 65535) {
-      // Few weight tiles: cluster split-K.  Smallest power-of-two split that puts about two small CTAs on every
-      // SM, keeping at least four k-blocks per CTA.
-      int split = 1;
-      while (split < 8 && tiles * split < (7 * sms) / 2 && a.k_blocks / (split * 2) >= 4) split *= 2;
+      // Few weight tiles: cluster split-K.  Measured on B200 (batch 32, K = 4096 / 12288): the kernel is fastest
+      // when all its CTAs are resident at once (two per SM) and share HBM evenly -- about 0.85 of the slots -- and a
+      // wider cluster than that only adds barrier and reduction cost; with at least as many tiles as SMs no split.
+      const int slots = sms * 2;
+      int split = (slots * 85 / 100) / tiles;
+      if (split > 8) split = 8;
+      while (split > 1 && (ceil_div(a.k_blocks, split) < 4 || ceil_div(a.k_blocks, split) * (split - 1) >= a.k_blocks))
+        --split;  // too thin, or a rank would be left without k-blocks
+      if (split < 1) split = 1;
       a.kb_per_split = ceil_div(a.k_blocks, split);
-      while (split > 1 && a.kb_per_split * (split - 1) >= a.k_blocks) {  // never leave a rank without k-blocks
-        split /= 2;
-        a.kb_per_split = ceil_div(a.k_blocks, split);
-      }
       switch (bn) {
         case 16: return launch_skinny<16>(tmw, tmx, a, split, tiles, stream);
         case 32: return launch_skinny<32>(tmw, tmx, a, split, tiles, stream);

@@ -104,7 +104,7 @@ class Qwen3Runner:
 
     def __del__(self):
         h = getattr(self, "_h", None)
-        if h:
+        if h and lib is not None:  # at interpreter shutdown the module globals may already be gone
             lib.teeny_qwen3_destroy(h)
             self._h = None
 
