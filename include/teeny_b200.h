@@ -158,6 +158,12 @@ int teeny_add_rms_norm_bf16(const teeny_bf16* x, teeny_bf16* residual, teeny_bf1
 /* out[t, i] = silu(gate_up[t, i]) * gate_up[t, inter + i].  Fuses silu_forward + elemwise_mul_forward. */
 int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out, int T, int inter,
                         teeny_stream_t stream);
+/* Y[M, N/2] = silu(X Wg^T) * (X Wu^T) in one GEMM: w is [N, K] with the gate and up projection rows interleaved in
+ * blocks of 64 channels (rows 128b .. 128b+63 = gate channels 64b .., rows 128b+64 .. 128b+127 = up channels 64b ..),
+ * N a multiple of 128.  Fuses linear_forward (twice) + silu_forward + elemwise_mul_forward; rounding points are those
+ * of the unfused bf16 graph.  Strides in elements; unit inner strides, 16-byte aligned rows. */
+int teeny_linear_swiglu_bf16(const teeny_bf16* x, long long ldx, const teeny_bf16* w, long long ldw, teeny_bf16* y,
+                             long long ldy, int M, int N, int K, teeny_stream_t stream);
 /* cos/sin tables [max_pos, D] from inv_freq[D/2] (f32 angles, one rounding to bf16). */
 int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* cos_table, teeny_bf16* sin_table, int max_pos, int D,
                           teeny_stream_t stream);

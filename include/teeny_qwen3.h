@@ -36,7 +36,8 @@ typedef struct teeny_qwen3 teeny_qwen3;
 /* Weight slots.  Per-layer tensors are this rank's shard, fused where the layer fuses them (row-major bf16):
  *   QKV      [(Hq/tp + 2 Hkv/tp) * 128, hidden]   rows: local q heads, then local k heads, then local v heads
  *   O        [hidden, Hq/tp * 128]                 column slice of o_proj (row-parallel)
- *   GATE_UP  [2 * intermediate/tp, hidden]         rows: local gate rows, then local up rows
+ *   GATE_UP  [2 * intermediate/tp, hidden]         local gate / up rows interleaved in blocks of 64 channels
+ *                                                  (see teeny_linear_swiglu_bf16)
  *   DOWN     [hidden, intermediate/tp]             column slice of down_proj (row-parallel)
  *   INPUT_LN, POST_LN [hidden]; Q_NORM, K_NORM [128]
  * Model-level: EMBED [vocab, hidden] (replicated), FINAL_NORM [hidden], LM_HEAD [vocab/tp, hidden] (row slice; for

@@ -50,6 +50,7 @@ SIGNATURES = {
     "softmax_forward_entry_point_bf16": (i32, [vp, vp, i32, i32, vp]),
     "teeny_add_rms_norm_bf16": (i32, [vp, vp, vp, vp, i32, i32, f32, vp]),
     "teeny_silu_mul_bf16": (i32, [vp, i64, vp, i32, i32, vp]),
+    "teeny_linear_swiglu_bf16": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, vp]),
     "teeny_rope_table_bf16": (i32, [vp, vp, vp, i32, i32, vp]),
     "teeny_qk_norm_rope_kv_bf16": (i32, [vp, i64, vp, vp, vp, vp, vp, vp] + [i32] * 7 + [vp, f32, vp]),
     "teeny_embedding_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),

@@ -267,6 +267,12 @@ int teeny_add_rms_norm_bf16(const teeny_bf16* x, teeny_bf16* residual, teeny_bf1
 int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out, int T, int inter, teeny_stream_t s) {
   return silu_mul_bf16(B(gate_up), ld, B(out), T, inter, S(s));
 }
+int teeny_linear_swiglu_bf16(const teeny_bf16* x, long long ldx, const teeny_bf16* w, long long ldw, teeny_bf16* y,
+                             long long ldy, int M, int N, int K, teeny_stream_t s) {
+  if (ldx > 0x7fffffffLL || ldw > 0x7fffffffLL || ldy > 0x7fffffffLL || ldx < K || ldw < K) return TEENY_ERR_BAD_ARG;
+  return gemm_bf16(B(x), static_cast<int>(ldx), B(w), static_cast<int>(ldw), false, nullptr, B(y),
+                   static_cast<int>(ldy), M, N, K, nullptr, 0, S(s), /*swiglu=*/true);
+}
 int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* c, teeny_bf16* sn, int max_pos, int D, teeny_stream_t s) {
   return rope_table_bf16(inv_freq, B(c), B(sn), max_pos, D, S(s));
 }

@@ -45,6 +45,7 @@ struct GemmArgs {
   int tiles_p, tiles_q;   // tiles along P rows and along Q rows
   int k_blocks;           // ceil(K / 64)
   int kb_per_split;       // skinny kernel: k-blocks per cluster rank
+  int swiglu;             // W rows interleave 64 gate / 64 up channels; Y[M, N/2] = silu(gate) * up
   int* err;
 };
 
@@ -69,6 +70,13 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_p, int tiles_q, 
   const int r = tile - g * per_group;
   tp = first_p + r % size_p;
   tq = r / size_p;
+}
+
+// SwiGLU on two projections of the same channel, with the rounding points of the unfused graph: both projections
+// are bf16 tensors, silu is evaluated in f32 and rounded to bf16, the product is rounded to bf16 by the caller.
+__device__ __forceinline__ float swiglu_f(float gate_acc, float up_acc) {
+  const float g = bf16_round(gate_acc), u = bf16_round(up_acc);
+  return bf16_round(g * (1.0f / (1.0f + expf(-g)))) * u;
 }
 
 // One k-block of MMAs: four K=16 steps over the 64-wide stage.
@@ -201,6 +209,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const int prow = tp * kBM + row_in_tile;  // index along P rows
       constexpr int kChunk = (BN >= 32) ? 32 : 16;
+      if constexpr (!SWAP && BN >= 128) {
+        if (args.swiglu) {
+          // columns come in groups of 128 weight rows = 64 gate + 64 up channels: emit 64 outputs per group
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 128) {
+#pragma unroll 1
+            for (int sub = 0; sub < 64; sub += 32) {
+              uint32_t gr[32], ur[32];
+              tmem_ld_32x32(t_addr + c0 + sub, gr);
+              tmem_ld_32x32(t_addr + c0 + 64 + sub, ur);
+              tmem_wait_ld();
+              const int ocol0 = (tq * BN + c0) / 2 + sub;
+              if (prow < args.M) {
+                bf16* dst = args.y + static_cast<size_t>(prow) * args.ldy + ocol0;
+                const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (ocol0 + 32 <= args.N / 2);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                  float f[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e)
+                    f[e] = swiglu_f(__uint_as_float(gr[v * 8 + e]), __uint_as_float(ur[v * 8 + e]));
+                  if (vec_ok) {
+                    uint4 o;
+                    o.x = pack_bf16x2(f[0], f[1]); o.y = pack_bf16x2(f[2], f[3]);
+                    o.z = pack_bf16x2(f[4], f[5]); o.w = pack_bf16x2(f[6], f[7]);
+                    *reinterpret_cast<uint4*>(dst + v * 8) = o;
+                  } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+                      if (ocol0 + v * 8 + e < args.N / 2) dst[v * 8 + e] = __float2bfloat16_rn(f[e]);
+                  }
+                }
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
@@ -434,6 +483,27 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const int c_end = min(BN, (static_cast<int>(rank) + 1) * cw);
     const float bias = (args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
     const bool live = *reinterpret_cast<volatile int*>(err) == 0;
+    if (args.swiglu) {
+      // the tile holds 64 gate rows then the 64 up rows of the same channels: a thread sums both rows of a channel
+      // (for every other column of this rank's slice) and writes silu(gate) * up
+      const int epi = (warp - 2) * 32 + lane, rp = epi & 63, half = epi >> 6;
+      const int n_out = tile * 64 + rp;
+#pragma unroll 2
+      for (int c = static_cast<int>(rank) * cw + half; c < c_end; c += 2) {
+        const uint32_t ga = part_base + static_cast<uint32_t>((c * kBM + rp) * 4);
+        float gv[8], uv[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          gv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(ga, q) : 0.0f;
+          uv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(ga + 64 * 4, q) : 0.0f;
+        }
+        float gs = gv[0], us = uv[0];
+#pragma unroll
+        for (int q = 1; q < 8; ++q) { gs += gv[q]; us += uv[q]; }
+        if (live && c < args.M && n_out < args.N / 2)
+          args.y[static_cast<size_t>(c) * args.ldy + n_out] = __float2bfloat16_rn(swiglu_f(gs, us));
+      }
+    } else
 #pragma unroll 4
     for (int c = static_cast<int>(rank) * cw; c < c_end; ++c) {
       const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + row) * 4);
@@ -535,8 +605,9 @@ size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
 // Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void*, size_t, cudaStream_t stream) {
+              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu) {
   if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  if (swiglu && (w_is_kn || bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 7) || (ldw & 7))
     return TEENY_ERR_ALIGNMENT;
 
@@ -544,6 +615,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
   a.k_blocks = ceil_div(K, kBK);
   a.kb_per_split = a.k_blocks;
+  a.swiglu = swiglu ? 1 : 0;
   a.err = device_error_word();
   const int sms = sm_count();
 
@@ -582,7 +654,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
 
   if (swap) {
     const int tiles = ceil_div(N, kBM);
-    if (tiles < 4 * sms && tiles <= 65535) {
+    if ((tiles < 4 * sms || swiglu) && tiles <= 65535) {
       // Few weight tiles: cluster split-K.  Measured on B200 (batch 32, K = 4096 / 12288): the kernel is fastest
       // when all its CTAs are resident at once (two per SM) and share HBM evenly -- about 0.85 of the slots -- and a
       // wider cluster than that only adds barrier and reduction cost; with at least as many tiles as SMs no split.

@@ -20,8 +20,10 @@ size_t gemm_bf16_scratch_bytes(int M, int N, int K);
 int gemm_bf16_prepare();
 int attention_prefill_prepare();
 int attention_decode_prepare();
+// swiglu: W is [N, K] with rows interleaved in blocks of 64 gate channels / 64 up channels (N = 2 * channels) and
+// Y is [M, N / 2] = silu(gate) * up, rounded as the unfused bf16 graph rounds (both projections, silu, product).
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream);
+              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
 int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
              const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);

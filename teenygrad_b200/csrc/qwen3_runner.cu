@@ -15,7 +15,8 @@
 //   a = attention(q, cache)                       tcgen05 flash-attention (prefill) / split-KV decode kernel
 //   delta = a Wo^T ; all-reduce                   row-parallel
 //   y = rms_norm(h += delta)
-//   gu = y Wgu^T ; act = silu(g) * u ; delta = act Wd^T ; all-reduce
+//   act = silu(y Wg^T) * (y Wu^T)                 one GEMM, SwiGLU in its epilogue
+//   delta = act Wd^T ; all-reduce
 // then final norm on the last position of each sequence, vocabulary-parallel LM head, local argmax, all-gather of
 // (value, index) candidates and a merge so every rank holds the same greedy token.
 #include <dlfcn.h>
@@ -103,7 +104,7 @@ struct LayerWeights {
 
 struct Workspace {
   // offsets into the caller's workspace
-  size_t h, y, qkv, attn, delta, gu, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch;
+  size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch;
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
   size_t gemm_scratch_bytes, attn_scratch_bytes, cache_layer_elems;
 };
@@ -141,7 +142,7 @@ bool valid_config(const teeny_qwen3_config& c) {
   if (c.num_q_heads % c.num_kv_heads || c.num_kv_heads % c.tp_size || c.intermediate % c.tp_size ||
       c.vocab % c.tp_size)
     return false;
-  if (c.hidden % 8 || (c.intermediate / c.tp_size) % 8 || (c.vocab / c.tp_size) % 8) return false;
+  if (c.hidden % 8 || (c.intermediate / c.tp_size) % 64 || (c.vocab / c.tp_size) % 8) return false;
   if (c.max_tokens < c.max_batch) return false;
   return true;
 }
@@ -158,7 +159,6 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.qkv = take(T * (Hq + 2 * Hkv) * D * 2);
   w.attn = take(T * Hq * D * 2);
   w.delta = take(T * H * 2);
-  w.gu = take(T * 2 * I * 2);
   w.act = take(T * I * 2);
   w.logits = take(Bm * Vl * 2);
   w.cache_layer_elems = Bm * Hkv * static_cast<size_t>(c.max_len) * D;
@@ -215,7 +215,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
   const int T = B * S, H = c.hidden, D = c.head_dim, Hq = m->Hq, Hkv = m->Hkv, I = m->I;
   const int qkv_n = (Hq + 2 * Hkv) * D;
   bf16 *h = m->at<bf16>(m->off.h), *y = m->at<bf16>(m->off.y), *qkv = m->at<bf16>(m->off.qkv);
-  bf16 *attn = m->at<bf16>(m->off.attn), *delta = m->at<bf16>(m->off.delta), *gu = m->at<bf16>(m->off.gu);
+  bf16 *attn = m->at<bf16>(m->off.attn), *delta = m->at<bf16>(m->off.delta);
   bf16* act = m->at<bf16>(m->off.act);
   void* gs = m->at<void>(m->off.gemm_scratch);
   const size_t gsb = m->off.gemm_scratch_bytes;
@@ -247,8 +247,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     TEENY_TRY(gemm_bf16(attn, Hq * D, w.o, Hq * D, false, nullptr, delta, H, T, H, Hq * D, gs, gsb, st));
     TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
     TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.post_ln, T, H, c.eps, st));
-    TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, gu, 2 * I, T, 2 * I, H, gs, gsb, st));
-    TEENY_TRY(silu_mul_bf16(gu, 2 * I, act, T, I, st));
+    TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, act, I, T, 2 * I, H, gs, gsb, st, /*swiglu=*/true));
     TEENY_TRY(gemm_bf16(act, I, w.down, I, false, nullptr, delta, H, T, H, I, gs, gsb, st));
     TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
   }

@@ -194,6 +194,25 @@ def silu_mul(gate_up):
     return out
 
 
+def interleave_gate_up(gate_w, up_w):
+    """Fused SwiGLU weight layout: blocks of 64 gate rows followed by the 64 up rows of the same channels."""
+    I, K = gate_w.shape
+    if I % 64:
+        raise ValueError("intermediate size must be a multiple of 64")
+    return torch.stack([gate_w.view(I // 64, 64, K), up_w.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def linear_swiglu(x, w_interleaved, out=None):
+    """silu(x @ Wg^T) * (x @ Wu^T) with Wg / Wu interleaved by ``interleave_gate_up``; x [M,K] -> [M, N/2]."""
+    _req(x, _BF16, "x"); _req(w_interleaved, _BF16, "w")
+    M, K = x.shape
+    N = w_interleaved.shape[0]
+    out = torch.empty(M, N // 2, dtype=_BF16, device=x.device) if out is None else out
+    check(lib.teeny_linear_swiglu_bf16(_ptr(x), x.stride(0), _ptr(w_interleaved), w_interleaved.stride(0), _ptr(out),
+                                       out.stride(0), M, N, K, _stream()), "linear_swiglu")
+    return out
+
+
 def rope_table(inv_freq, max_pos):
     _req(inv_freq, _F32, "inv_freq")
     D = inv_freq.numel() * 2

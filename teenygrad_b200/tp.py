@@ -1,7 +1,8 @@
 """Tensor-parallel host logic: Megatron-style weight sharding for Qwen3 and NCCL communicator set-up.
 
 Sharding (tp ranks, rank r):
-  column-parallel  q_proj (Hq/tp heads), k_proj / v_proj (Hkv/tp heads), gate_proj / up_proj (I/tp rows)
+  column-parallel  q_proj (Hq/tp heads), k_proj / v_proj (Hkv/tp heads), gate_proj / up_proj (I/tp rows, interleaved
+                   in blocks of 64 channels for the fused SwiGLU GEMM)
   row-parallel     o_proj (columns of the local q heads), down_proj (columns of the local intermediate slice)
   replicated       norms, embedding;  vocabulary-parallel LM head (vocab/tp rows)
 A rank's q heads [r*Hq/tp, (r+1)*Hq/tp) use exactly its kv heads [r*Hkv/tp, (r+1)*Hkv/tp), so attention is local.
@@ -18,6 +19,15 @@ def check_divisible(cfg, tp):
             raise ValueError(f"{name}={v} is not divisible by tp={tp}")
 
 
+def interleave_gate_up(gate, up):
+    """[2I, K] weight of the fused SwiGLU GEMM: blocks of 64 gate rows, each followed by the 64 up rows of the same
+    channels, so one 128-row weight tile holds both projections of 64 channels."""
+    inter, k = gate.shape
+    if inter % 64:
+        raise ValueError(f"intermediate shard {inter} is not a multiple of 64")
+    return torch.stack([gate.reshape(inter // 64, 64, k), up.reshape(inter // 64, 64, k)], dim=1).reshape(2 * inter, k).contiguous()
+
+
 def shard_layer(sd, cfg, layer, rank, tp):
     """Fused, sharded weights of one layer from an HF-named state dict (full tensors)."""
     check_divisible(cfg, tp)
@@ -32,7 +42,7 @@ def shard_layer(sd, cfg, layer, rank, tp):
     return {
         "qkv": torch.cat([q, k, v], dim=0).contiguous(),
         "o": sd[p + "self_attn.o_proj.weight"][:, rank * hq:(rank + 1) * hq].contiguous(),
-        "gate_up": torch.cat([gate, up], dim=0).contiguous(),
+        "gate_up": interleave_gate_up(gate, up),
         "down": sd[p + "mlp.down_proj.weight"][:, rank * il:(rank + 1) * il].contiguous(),
         "input_ln": sd[p + "input_layernorm.weight"].contiguous(),
         "post_ln": sd[p + "post_attention_layernorm.weight"].contiguous(),

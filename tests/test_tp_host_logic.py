@@ -37,7 +37,7 @@ def _worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from teenygrad_b200 import tp
-    cfg = oq.OracleQwen3Config(1, 64, 4, 2, 128, 96, 512, tied=False)
+    cfg = oq.OracleQwen3Config(1, 64, 4, 2, 128, 128, 512, tied=False)
     sd = oq.make_weights(cfg, 11)
     x = torch.randn(5, cfg.hidden, generator=torch.Generator().manual_seed(1))
     qkv_ref, o_ref, mlp_ref = _reference_layer(cfg, sd, x)
@@ -50,7 +50,8 @@ def _worker(rank, world, port, ret):
     o = F.linear(torch.tanh(qkv[:, :hq * D]), sh["o"])
     dist.all_reduce(o)
     gu = F.linear(x, sh["gate_up"])
-    mlp = F.linear(F.silu(gu[:, :il]) * gu[:, il:], sh["down"])
+    gu = gu.view(-1, il // 64, 2, 64)  # blocks of 64 gate channels followed by the same 64 up channels
+    mlp = F.linear((F.silu(gu[:, :, 0]) * gu[:, :, 1]).reshape(-1, il), sh["down"])
     dist.all_reduce(mlp)
     ok = ok and torch.allclose(o, o_ref, atol=1e-4) and torch.allclose(mlp, mlp_ref, atol=1e-4)
     # vocabulary-parallel greedy pick
