@@ -190,6 +190,9 @@ def workload_config(args, n):
 # ------------------------------------------------------------------------------------------------ GPU arm
 def main():
     args = parse_args()
+    # keep stdout to the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) would otherwise land there
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
     cfg_kwargs = dict(num_layers=args.layers, hidden=4096, num_q_heads=32, num_kv_heads=8, head_dim=128,
                       intermediate=12288, vocab=151936, eps=1e-6, rope_theta=1e6, tied=False)
     if args.impl == "reference":
@@ -223,6 +226,7 @@ def main():
     runner = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + NEW, max_tokens=B * S, max_new_tokens=NEW,
                                tp_rank=rank, tp_size=world, comm=comm)
     qwen3.load_random_weights(runner, seed=4)
+    tp_mode = "none" if world == 1 else ("peer-push" if lib.teeny_tp_peer_enabled(comm) else "nccl-allreduce")
     g = torch.Generator().manual_seed(4)
     prompts_host = torch.randint(0, cfg.vocab, (B, S), generator=g, dtype=torch.int32).pin_memory()
     prompts_dev = prompts_host.to(dev)
@@ -320,7 +324,9 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
         "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": workload_config(args, world),
+        "dtype": "bf16", "data": "synthetic",
+        "config": {**workload_config(args, world), "tp_decode_reduction": tp_mode, "tp_prefill_reduction":
+                   "none" if world == 1 else "nccl-allreduce"},
         "phases": {"prefill_ms": prefill_ms / steps, "decode_ms": decode_ms / steps,
                    "prefill_tok_s": B * S * steps / (prefill_ms * 1e-3),
                    "decode_tok_s": B * (NEW - 1) * steps / (decode_ms * 1e-3),

@@ -79,11 +79,17 @@ int teeny_qwen3_decode_replay(teeny_qwen3* model, teeny_stream_t stream);
 void* teeny_qwen3_buffer(teeny_qwen3* model, int which);
 
 /* Tensor-parallel plumbing over NCCL (loaded at run time; the process's already-loaded libnccl is reused).
- * Rank 0 calls teeny_tp_unique_id and ships the 128 bytes to the other ranks by any host channel. */
+ * Rank 0 calls teeny_tp_unique_id and ships the 128 bytes to the other ranks by any host channel.  teeny_tp_init
+ * allocates the small host-side context; teeny_qwen3_create may add a peer-mapped device buffer of
+ * 2 * tp_size * max_batch * hidden floats to it (the one device allocation this library makes, at set-up). */
 int teeny_tp_unique_id(void* out128);
 int teeny_tp_init(const void* id128, int rank, int world, void** comm_out);
 int teeny_tp_destroy(void* comm);
 int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_stream_t stream);
+/* 1 when the context's decode path pushes row-parallel partial sums straight into the peers' memory (set up by
+ * teeny_qwen3_create when tp_size > 1 and max_batch <= 128; needs CUDA IPC between the ranks' processes), 0 when it
+ * all-reduces through NCCL instead. */
+int teeny_tp_peer_enabled(void* comm);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,7 @@ enum : int {
   DEVERR_ATTN_PRODUCER = 0x201,
   DEVERR_ATTN_MMA = 0x202,
   DEVERR_ATTN_SOFTMAX = 0x203,
+  DEVERR_TP_GATHER = 0x301,
 };
 
 // Host side (defined in api.cu): device address of the per-device error word.

@@ -245,6 +245,90 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
   return static_cast<int>(cudaGetLastError());
 }
 
+// ---- tensor-parallel row-parallel epilogue: wait for every rank's pushed partial rows, sum, add, normalise ----
+// One CTA per token row (decode batches: a few dozen rows).  recv holds `world` f32 partial copies of the
+// projection, slot_elems apart; flag counts the CTAs of all ranks that have finished pushing.
+template <int VPT>
+__global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_t slot_elems, int world,
+                                           unsigned* flag, unsigned* done, unsigned expected,
+                                           bf16* __restrict__ res, long long ldr, bf16* __restrict__ y, long long ldy,
+                                           const bf16* __restrict__ w, int N, float eps, int* err) {
+  pdl_wait();
+  __shared__ float red[32];
+  if (threadIdx.x == 0) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= expected) break;
+      if ((it & 0x3f) == 0x3f) {
+        if (*reinterpret_cast<volatile int*>(err) != 0) break;
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); break; }
+      }
+    }
+  }
+  __syncthreads();
+  const int row = blockIdx.x, nv = N >> 3;
+  uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
+  float v[VPT][8];
+  float sq = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < world; ++p) {  // rank order: every rank adds in the same order -> identical results
+        const float4* src = reinterpret_cast<const float4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 2 * idx;
+        const float4 a = __ldcg(src), b = __ldcg(src + 1);  // L2: the lines were written by peers, never cache in L1
+        sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
+        sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
+      }
+      const uint4 h4 = rr4[idx];
+      const uint32_t hw[4] = {h4.x, h4.y, h4.z, h4.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = bf16_round(bf16_lo(hw[e]) + bf16_round(sum[2 * e]));      // projection is a bf16 tensor
+        const float hi = bf16_round(bf16_hi(hw[e]) + bf16_round(sum[2 * e + 1]));
+        v[i][2 * e] = lo;
+        v[i][2 * e + 1] = hi;
+        ow[e] = pack_bf16x2(lo, hi);
+      }
+      rr4[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
+    }
+  }
+  sq = block_sum(sq, red);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      const uint4 g = wr[idx];
+      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        ow[e] = pack_bf16x2(bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]), bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]));
+      yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+  // the last CTA to have consumed its row re-arms the counter for the round after next
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(done, 1u) == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned*>(done) = 0u;
+      atomicExch_system(flag, 0u);
+    }
+  }
+}
+
 // ---- SiLU(gate) * up on the fused [T, 2*inter] projection ----
 __global__ void silu_mul_bf16_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
                                      int inter) {
@@ -319,8 +403,9 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, bf16* __re
   }
 }
 
-// ---- per-head RMSNorm + RoPE + KV-cache append; D == 128, one warp per (token, head) ----
-// Lane l holds elements [4l, 4l+4); its rotate-half partner elements live in lane l ^ 16.
+// ---- per-head RMSNorm + RoPE + KV-cache append; D == 128, one half-warp per (token, head) ----
+// Lane s (0..15) of the half-warp holds elements [8s, 8s+8) as one 16-byte vector; its rotate-half partner elements
+// (d +- 64) live in lane s ^ 8.  V heads are copied into the cache unchanged.
 __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, const bf16* __restrict__ q_w,
                                        const bf16* __restrict__ k_w, const bf16* __restrict__ cos_t,
                                        const bf16* __restrict__ sin_t, bf16* __restrict__ k_cache,
@@ -329,52 +414,55 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
   pdl_wait();
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
-  const long long warp_id = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp_id >= static_cast<long long>(T) * heads) return;
-  const int t = static_cast<int>(warp_id / heads);
-  const int h = static_cast<int>(warp_id - static_cast<long long>(t) * heads);
+  const long long total = static_cast<long long>(T) * heads;
+  const long long unit_raw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const bool valid = unit_raw < total;
+  const long long unit = valid ? unit_raw : total - 1;  // inactive half-warps shadow the last unit (no stores)
+  const int sub = threadIdx.x & 15;
+  const int t = static_cast<int>(unit / heads);
+  const int h = static_cast<int>(unit - static_cast<long long>(t) * heads);
   const int b = t / S;
   const int pos = (pos0_dev ? *pos0_dev : pos0) + (t - b * S);
-  bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + lane * 4;
-  const uint2 raw = *reinterpret_cast<const uint2*>(src);
-  if (h >= Hq + Hkv) {  // V head: straight copy into the cache
-    if (pos < max_len) {
-      bf16* dst = v_cache + ((static_cast<size_t>(b) * Hkv + (h - Hq - Hkv)) * max_len + pos) * D + lane * 4;
-      *reinterpret_cast<uint2*>(dst) = raw;
-    }
-    return;
-  }
-  const bool is_q = h < Hq;
-  float x[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
-  float sq = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
-  sq = warp_sum(sq);
+  bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + sub * 8;
+  const uint4 raw = *reinterpret_cast<const uint4*>(src);
+  const bool is_v = h >= Hq + Hkv, is_q = h < Hq;
+  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+  float x[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { x[2 * e] = bf16_lo(rw[e]); x[2 * e + 1] = bf16_hi(rw[e]); }
+  float sq = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // stays inside the half-warp
   const float rr = 1.0f / sqrtf(sq * (1.0f / D) + eps);
-  const uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? q_w : k_w) + lane * 4);
-  const float wv[4] = {bf16_lo(wraw.x), bf16_hi(wraw.x), bf16_lo(wraw.y), bf16_hi(wraw.y)};
-  float n[4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) n[e] = bf16_round(bf16_round(x[e] * rr) * wv[e]);  // normed head, bf16 tensor
+  const uint4 wraw = *reinterpret_cast<const uint4*>((is_q ? q_w : k_w) + sub * 8);
   const int tp = pos < max_len ? pos : max_len - 1;  // table has max_len rows
-  const uint2 craw = *reinterpret_cast<const uint2*>(cos_t + static_cast<size_t>(tp) * D + lane * 4);
-  const uint2 sraw = *reinterpret_cast<const uint2*>(sin_t + static_cast<size_t>(tp) * D + lane * 4);
-  const float cv[4] = {bf16_lo(craw.x), bf16_hi(craw.x), bf16_lo(craw.y), bf16_hi(craw.y)};
-  const float sv[4] = {bf16_lo(sraw.x), bf16_hi(sraw.x), bf16_lo(sraw.y), bf16_hi(sraw.y)};
-  float r[4];
+  const uint4 craw = *reinterpret_cast<const uint4*>(cos_t + static_cast<size_t>(tp) * D + sub * 8);
+  const uint4 sraw = *reinterpret_cast<const uint4*>(sin_t + static_cast<size_t>(tp) * D + sub * 8);
+  const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w},
+                 sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+  float r[8];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float partner = __shfl_xor_sync(0xffffffffu, n[e], 16);
-    const float rot = (lane < 16) ? -partner : partner;  // rotate_half: first half gets -x[d + 64]
-    const float a = bf16_round(n[e] * cv[e]);
-    const float bb = bf16_round(rot * sv[e]);
-    r[e] = a + bb;  // rounded to bf16 by the pack below
+  for (int e = 0; e < 8; ++e) {
+    const float wv = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
+    const float cv = (e & 1) ? bf16_hi(cw[e >> 1]) : bf16_lo(cw[e >> 1]);
+    const float sv = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
+    const float n = bf16_round(bf16_round(x[e] * rr) * wv);  // normed head, a bf16 tensor in the traced graph
+    const float partner = __shfl_xor_sync(0xffffffffu, n, 8);
+    const float rot = (sub < 8) ? -partner : partner;         // rotate_half: first half gets -x[d + 64]
+    r[e] = bf16_round(n * cv) + bf16_round(rot * sv);         // rounded to bf16 by the pack below
   }
-  const uint2 outv = make_uint2(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]));
+  const uint4 outv = make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]),
+                                pack_bf16x2(r[6], r[7]));
+  if (!valid) return;
   if (is_q) {
-    *reinterpret_cast<uint2*>(src) = outv;
+    *reinterpret_cast<uint4*>(src) = outv;
   } else if (pos < max_len) {
-    bf16* dst = k_cache + ((static_cast<size_t>(b) * Hkv + (h - Hq)) * max_len + pos) * D + lane * 4;
-    *reinterpret_cast<uint2*>(dst) = outv;
+    bf16* cache = is_v ? v_cache : k_cache;
+    const int hh = is_v ? h - Hq - Hkv : h - Hq;
+    bf16* dst = cache + ((static_cast<size_t>(b) * Hkv + hh) * max_len + pos) * D + sub * 8;
+    *reinterpret_cast<uint4*>(dst) = is_v ? raw : outv;
   }
 }
 
@@ -483,6 +571,19 @@ int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ld
                       const bf16* w, int M, int N, float eps, cudaStream_t st) {
   return launch_rms_bf16<true>(x, ldx, residual, ldr, y, ldy, w, nullptr, M, N, eps, st);
 }
+int gather_add_rms_norm_bf16(const float* recv, size_t slot_elems, int world, unsigned* flag, unsigned* done,
+                             unsigned expected, bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w,
+                             int M, int N, float eps, cudaStream_t st) {
+  if (!recv || !flag || !done || !residual || !y || !w || world < 2 || M <= 0 || N <= 0) return TEENY_ERR_BAD_ARG;
+  if (N % 8 || ldr % 8 || ldy % 8 || N > 8 * 4 * 256) return TEENY_ERR_BAD_ARG;
+  if (!aligned16(recv) || !aligned16(residual) || !aligned16(y) || !aligned16(w) || (slot_elems % 4)) return TEENY_ERR_ALIGNMENT;
+  const int nv = N / 8, threads = 256, vpt = (nv + threads - 1) / threads;
+  int* err = device_error_word();
+  if (vpt <= 1) launch_kernel(gather_add_rms_norm_kernel<1>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
+  else if (vpt <= 2) launch_kernel(gather_add_rms_norm_kernel<2>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
+  else launch_kernel(gather_add_rms_norm_kernel<4>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
+  return static_cast<int>(cudaGetLastError());
+}
 int silu_f32(const float* x, float* y, long long n, cudaStream_t st) { return launch_ew_f32<OpSilu, false>(x, nullptr, y, n, st); }
 int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st) { return launch_ew_bf16<OpSilu, false>(x, nullptr, y, n, st); }
 int mul_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st) { return launch_ew_f32<OpMul, true>(a, b, o, n, st); }
@@ -535,10 +636,13 @@ int qk_norm_rope_kv_bf16(bf16* qkv, long long ld, const bf16* q_w, const bf16* k
       max_len <= 0)
     return TEENY_ERR_BAD_ARG;
   if (D != 128) return TEENY_ERR_BAD_ARG;  // head_dim of every Qwen3 size
-  if ((ld % 4) || (reinterpret_cast<uintptr_t>(qkv) & 7)) return TEENY_ERR_ALIGNMENT;
+  if ((ld % 8) || (reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(q_w) & 15) ||
+      (reinterpret_cast<uintptr_t>(k_w) & 15))
+    return TEENY_ERR_ALIGNMENT;
   if (T == 0) return TEENY_OK;
-  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
-  const long long blocks = (warps + 7) / 8;
+  const long long units = static_cast<long long>(T) * (Hq + 2 * Hkv);  // one half-warp each
+  const long long blocks = (units + 15) / 16;
   if (blocks > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
   launch_kernel(qk_norm_rope_kv_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 1, qkv, ld, q_w, k_w, cos_t, sin_t, k_cache, v_cache,
                                                                    T, S, Hq, Hkv, max_len, pos0, pos0_dev, eps);

@@ -46,6 +46,11 @@ struct GemmArgs {
   int k_blocks;           // ceil(K / 64)
   int kb_per_split;       // skinny kernel: k-blocks per cluster rank
   int swiglu;             // W rows interleave 64 gate / 64 up channels; Y[M, N/2] = silu(gate) * up
+  // Tensor-parallel push (skinny kernel only): instead of Y, the f32 row sums go to slot `rank` of every rank's
+  // receive buffer (peer-mapped memory, [M][N] f32 each) and each CTA then bumps every rank's arrival counter.
+  float* const* push_recv;    // device array [push_world]: where this rank writes inside rank p's buffer (or null)
+  unsigned* const* push_flag; // device array [push_world]: rank p's arrival counter
+  int push_world;
   int* err;
 };
 
@@ -513,8 +518,21 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       float acc = v[0];
 #pragma unroll
       for (int q = 1; q < 8; ++q) acc += v[q];
-      if (live && c < args.M && n < args.N)
-        args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(acc + bias);
+      if (live && c < args.M && n < args.N) {
+        if (args.push_recv) {
+          const size_t off = static_cast<size_t>(c) * args.N + n;
+          for (int p = 0; p < args.push_world; ++p) args.push_recv[p][off] = acc + bias;  // NVLink stores
+        } else {
+          args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(acc + bias);
+        }
+      }
+    }
+    if (args.push_recv) {
+      // every store of this CTA is visible system-wide before any rank's counter moves
+      __threadfence_system();
+      named_barrier_sync(1, kEpilogueThreads);
+      const int epi = (warp - 2) * 32 + lane;
+      if (epi < args.push_world) atomicAdd_system(args.push_flag[epi], 1u);
     }
   }
 
@@ -605,7 +623,7 @@ size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
 // Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu) {
+              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu, const GemmPush* push) {
   if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
   if (swiglu && (w_is_kn || bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 7) || (ldw & 7))
@@ -616,6 +634,12 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   a.k_blocks = ceil_div(K, kBK);
   a.kb_per_split = a.k_blocks;
   a.swiglu = swiglu ? 1 : 0;
+  if (push) {
+    if (swiglu || w_is_kn || M > kSwapMaxM || !push->recv || !push->flag || push->world < 2) return TEENY_ERR_BAD_ARG;
+    a.push_recv = push->recv;
+    a.push_flag = push->flag;
+    a.push_world = push->world;
+  }
   a.err = device_error_word();
   const int sms = sm_count();
 
@@ -654,7 +678,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
 
   if (swap) {
     const int tiles = ceil_div(N, kBM);
-    if ((tiles < 4 * sms || swiglu) && tiles <= 65535) {
+    if ((tiles < 4 * sms || swiglu || push) && tiles <= 65535) {
       // Few weight tiles: cluster split-K.  Measured on B200 (batch 32, K = 4096 / 12288): the kernel is fastest
       // when all its CTAs are resident at once (two per SM) and share HBM evenly -- about 0.85 of the slots -- and a
       // wider cluster than that only adds barrier and reduction cost; with at least as many tiles as SMs no split.
@@ -665,6 +689,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
         --split;  // too thin, or a rank would be left without k-blocks
       if (split < 1) split = 1;
       a.kb_per_split = ceil_div(a.k_blocks, split);
+      if (push) *push->ctas_out = tiles * split;
       switch (bn) {
         case 16: return launch_skinny<16>(tmw, tmx, a, split, tiles, stream);
         case 32: return launch_skinny<32>(tmw, tmx, a, split, tiles, stream);

@@ -22,8 +22,24 @@ int attention_prefill_prepare();
 int attention_decode_prepare();
 // swiglu: W is [N, K] with rows interleaved in blocks of 64 gate channels / 64 up channels (N = 2 * channels) and
 // Y is [M, N / 2] = silu(gate) * up, rounded as the unfused bf16 graph rounds (both projections, silu, product).
+// Tensor-parallel push mode of the decode GEMM (M <= 128): y is not written; every rank receives this rank's f32
+// result in its receive buffer and has its arrival counter bumped once per CTA (*ctas_out reports how many).
+struct GemmPush {
+  float* const* recv;      // device array [world]
+  unsigned* const* flag;   // device array [world]
+  int world;
+  int* ctas_out;           // host: CTAs that will signal
+};
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false);
+              int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false,
+              const GemmPush* push = nullptr);
+// Row-parallel epilogue of tensor parallelism: waits until `expected` CTAs (of all ranks) have pushed, sums the
+// `world` f32 partial rows [M][N] (stride slot_elems between ranks), rounds the sum to bf16 (the all-reduced
+// projection), adds it into the bf16 residual and RMS-normalises it: residual <- residual + sum; y <- norm(residual).
+// The last CTA to finish re-arms the counter.  Waits are bounded (device error word).
+int gather_add_rms_norm_bf16(const float* recv, size_t slot_elems, int world, unsigned* flag, unsigned* done,
+                             unsigned expected, bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w,
+                             int M, int N, float eps, cudaStream_t st);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
 int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
              const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);

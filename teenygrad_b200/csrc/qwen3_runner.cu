@@ -22,6 +22,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -64,6 +65,93 @@ bool load_nccl() {
   g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce &&
               g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
   return g_nccl.ok;
+}
+
+// Tensor-parallel context: the NCCL communicator plus, for decode, peer-mapped receive buffers through which the
+// row-parallel GEMMs push their partial rows straight into every rank's memory (no collective call on that path).
+struct TpContext {
+  ncclComm_t comm = nullptr;
+  int rank = 0, world = 1;
+  bool peer_ok = false;
+  size_t rows = 0, cols = 0, slot_elems = 0, data_bytes = 0;
+  uint8_t* local = nullptr;       // [2 parities][world][rows][cols] f32, then 2 arrival counters, 2 done counters
+  void* peer[8] = {};             // the same buffer of every rank (own entry = local)
+  float** recv_tab = nullptr;     // device [2][world]: where this rank writes inside rank q's buffer
+  unsigned** flag_tab = nullptr;  // device [2][world]: rank q's arrival counter
+  float* local_recv(int parity) const {
+    return reinterpret_cast<float*>(local) + static_cast<size_t>(parity) * world * slot_elems;
+  }
+  unsigned* flag(int parity) const { return reinterpret_cast<unsigned*>(local + data_bytes) + parity; }
+  unsigned* done(int parity) const { return reinterpret_cast<unsigned*>(local + data_bytes) + 2 + parity; }
+};
+
+// Collective over the communicator: allocate the receive buffer, exchange IPC handles, map the peers.  Leaves
+// peer_ok false (on every rank alike) if any rank could not set it up; the runner then all-reduces through NCCL.
+int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
+  if (c->peer_ok || c->world < 2 || c->world > 8) return 0;
+  c->rows = rows; c->cols = cols; c->slot_elems = rows * cols;
+  c->data_bytes = 2 * static_cast<size_t>(c->world) * c->slot_elems * sizeof(float);
+  int ok = 1;
+  cudaIpcMemHandle_t mine;
+  uint8_t* xbuf = nullptr;
+  if (cudaMalloc(&c->local, c->data_bytes + 256) != cudaSuccess) ok = 0;
+  if (ok && cudaMemsetAsync(c->local, 0, c->data_bytes + 256, st) != cudaSuccess) ok = 0;
+  if (ok && cudaIpcGetMemHandle(&mine, c->local) != cudaSuccess) ok = 0;
+  const size_t rec = sizeof(mine) + 8;
+  if (cudaMalloc(&xbuf, rec * c->world) != cudaSuccess) return TEENY_ERR_BAD_ARG;
+  // exchange [handle | ok] records
+  std::vector<uint8_t> host(rec * c->world, 0);
+  if (ok) std::memcpy(host.data() + rec * c->rank, &mine, sizeof(mine));
+  host[rec * c->rank + sizeof(mine)] = static_cast<uint8_t>(ok);
+  cudaMemcpyAsync(xbuf + rec * c->rank, host.data() + rec * c->rank, rec, cudaMemcpyHostToDevice, st);
+  if (g_nccl.AllGather(xbuf + rec * c->rank, xbuf, rec, ncclChar, c->comm, st) != ncclSuccess) {
+    cudaFree(xbuf);
+    return TEENY_ERR_NCCL;
+  }
+  cudaMemcpyAsync(host.data(), xbuf, rec * c->world, cudaMemcpyDeviceToHost, st);
+  if (cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaFree(xbuf);
+    return TEENY_ERR_NCCL;
+  }
+  for (int q = 0; q < c->world; ++q) ok &= host[rec * q + sizeof(mine)];
+  if (ok) {
+    for (int q = 0; q < c->world && ok; ++q) {
+      if (q == c->rank) { c->peer[q] = c->local; continue; }
+      cudaIpcMemHandle_t h;
+      std::memcpy(&h, host.data() + rec * q, sizeof(h));
+      if (cudaIpcOpenMemHandle(&c->peer[q], h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        ok = 0;
+        cudaGetLastError();
+      }
+    }
+  }
+  // second round: did every rank map every peer?
+  host[0] = static_cast<uint8_t>(ok);
+  cudaMemcpyAsync(xbuf + c->rank, host.data(), 1, cudaMemcpyHostToDevice, st);
+  if (g_nccl.AllGather(xbuf + c->rank, xbuf, 1, ncclChar, c->comm, st) != ncclSuccess) {
+    cudaFree(xbuf);
+    return TEENY_ERR_NCCL;
+  }
+  cudaMemcpyAsync(host.data(), xbuf, c->world, cudaMemcpyDeviceToHost, st);
+  cudaStreamSynchronize(st);
+  for (int q = 0; q < c->world; ++q) ok &= host[q];
+  cudaFree(xbuf);
+  if (!ok) return 0;  // stay on the NCCL path
+  std::vector<float*> rt(2 * c->world);
+  std::vector<unsigned*> ft(2 * c->world);
+  for (int par = 0; par < 2; ++par)
+    for (int q = 0; q < c->world; ++q) {
+      rt[par * c->world + q] =
+          reinterpret_cast<float*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
+      ft[par * c->world + q] = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(c->peer[q]) + c->data_bytes) + par;
+    }
+  if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(float*)) != cudaSuccess ||
+      cudaMalloc(&c->flag_tab, ft.size() * sizeof(unsigned*)) != cudaSuccess)
+    return 0;
+  cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(float*), cudaMemcpyHostToDevice);
+  cudaMemcpy(c->flag_tab, ft.data(), ft.size() * sizeof(unsigned*), cudaMemcpyHostToDevice);
+  c->peer_ok = true;
+  return 0;
 }
 
 __global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __restrict__ cur_ids,
@@ -122,6 +210,11 @@ struct teeny_qwen3 {
   uint8_t* ws = nullptr;
   Workspace off;
   ncclComm_t comm = nullptr;
+  TpContext* tp = nullptr;
+  int push_round = 0;           // parity of the next peer push within a decode step
+  bool pending_gather = false;  // a pushed projection waits to be summed by the next norm
+  int pending_parity = 0;
+  unsigned pending_expected = 0;
   cudaGraphExec_t graph_exec = nullptr;
   cudaStream_t capture_stream = nullptr;
   int graph_batch = 0;
@@ -207,6 +300,41 @@ int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
   return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, m->comm, st) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
 }
 
+// Row-parallel projection delta = x W^T followed by the cross-rank sum.  Decode with peer buffers: the GEMM pushes
+// its f32 rows into every rank's receive buffer and the sum happens inside the next norm kernel (pending_gather);
+// otherwise GEMM to `delta` and, with tp > 1, an NCCL all-reduce.
+int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const bf16* w, bf16* delta, int T, int N, int K, bool decode,
+                 cudaStream_t st) {
+  void* gs = m->at<void>(m->off.gemm_scratch);
+  TpContext* tp = m->tp;
+  if (decode && tp && tp->peer_ok && T <= static_cast<int>(tp->rows) && N == static_cast<int>(tp->cols)) {
+    const int parity = m->push_round & 1;
+    int ctas = 0;
+    GemmPush push{tp->recv_tab + parity * tp->world, tp->flag_tab + parity * tp->world, tp->world, &ctas};
+    TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st, false, &push));
+    m->pending_gather = true;
+    m->pending_parity = parity;
+    m->pending_expected = static_cast<unsigned>(ctas) * tp->world;
+    ++m->push_round;
+    return 0;
+  }
+  TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st));
+  return all_reduce(m, delta, static_cast<size_t>(T) * N, st);
+}
+
+// residual += projection; y = rms_norm(residual) on M rows (row strides ld for delta / residual, H for y).
+int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, const bf16* w, int M, cudaStream_t st) {
+  const teeny_qwen3_config& c = m->cfg;
+  if (m->pending_gather) {
+    m->pending_gather = false;
+    TpContext* tp = m->tp;
+    return gather_add_rms_norm_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world,
+                                    tp->flag(m->pending_parity), tp->done(m->pending_parity), m->pending_expected, h, ld,
+                                    y, c.hidden, w, M, c.hidden, c.eps, st);
+  }
+  return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
+}
+
 // The shared layer loop.  T tokens arranged [B, S]; pos0 is the position of the first token of every sequence
 // (device value when pos_dev != null).  decode selects the split-KV attention kernel (S == 1).
 int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const int* len_dev, bool decode,
@@ -226,7 +354,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     bf16* kc = m->at<bf16>(m->off.kcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
     bf16* vc = m->at<bf16>(m->off.vcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
     if (l == 0) TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st));
-    else TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.input_ln, T, H, c.eps, st));
+    else TEENY_TRY(residual_norm(m, delta, h, H, y, w.input_ln, T, st));
     TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
     TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
                                    kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
@@ -244,12 +372,10 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
       a.Sq = S; a.Skv = pos0 + S; a.causal = 1;
       TEENY_TRY(attention_prefill_bf16(qkv, kc, vc, attn, nullptr, a, st));
     }
-    TEENY_TRY(gemm_bf16(attn, Hq * D, w.o, Hq * D, false, nullptr, delta, H, T, H, Hq * D, gs, gsb, st));
-    TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
-    TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.post_ln, T, H, c.eps, st));
+    TEENY_TRY(row_parallel(m, attn, Hq * D, w.o, delta, T, H, Hq * D, decode, st));
+    TEENY_TRY(residual_norm(m, delta, h, H, y, w.post_ln, T, st));
     TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, act, I, T, 2 * I, H, gs, gsb, st, /*swiglu=*/true));
-    TEENY_TRY(gemm_bf16(act, I, w.down, I, false, nullptr, delta, H, T, H, I, gs, gsb, st));
-    TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(T) * H, st));
+    TEENY_TRY(row_parallel(m, act, I, w.down, delta, T, H, I, decode, st));
   }
   return 0;
 }
@@ -263,7 +389,7 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
   const size_t last = static_cast<size_t>(S - 1) * H;
   const long long ld = static_cast<long long>(S) * H;
   // residual add + final norm on rows (b, S-1); y rows are packed [B, H]
-  TEENY_TRY(add_rms_norm_bf16(delta + last, ld, h + last, ld, y, H, m->final_norm, B, H, c.eps, st));
+  TEENY_TRY(residual_norm(m, delta + last, h + last, ld, y, m->final_norm, B, st));
   TEENY_TRY(gemm_bf16(y, H, m->lm_head, H, false, nullptr, logits, Vl, B, Vl, H, m->at<void>(m->off.gemm_scratch),
                       m->off.gemm_scratch_bytes, st));
   float* cv = m->at<float>(m->off.cand_val);
@@ -297,6 +423,8 @@ struct PdlScope {
 
 int decode_body(teeny_qwen3* m, int B, cudaStream_t st) {
   PdlScope pdl;
+  m->push_round = 0;  // every step issues an even number of pushes, so the parity sequence repeats
+  m->pending_gather = false;
   const teeny_qwen3_config& c = m->cfg;
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(m->at<int>(m->off.cur_ids), m->embed, m->at<bf16>(m->off.h), B, c.hidden, c.vocab, st));
@@ -334,7 +462,12 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   m->layers.resize(cfg->num_layers);
   m->ws = static_cast<uint8_t*>(workspace);
   m->off = w;
-  m->comm = static_cast<ncclComm_t>(tp_comm);
+  m->tp = static_cast<TpContext*>(tp_comm);
+  m->comm = m->tp ? m->tp->comm : nullptr;
+  if (m->tp && (m->tp->world != cfg->tp_size || m->tp->rank != cfg->tp_rank)) {
+    delete m;
+    return TEENY_ERR_BAD_ARG;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // function attributes (dynamic shared memory) are set once per device here, outside any stream capture
   int prc = gemm_bf16_prepare();
@@ -343,6 +476,15 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   if (prc != 0) {
     delete m;
     return prc;
+  }
+  // decode-time peer buffers (collective: every rank creates its runner at the same point)
+  const char* peer_env = getenv("TEENY_TP_PEER");  // "0" keeps decode on NCCL all-reduce (for A/B measurements)
+  if (m->tp && cfg->tp_size > 1 && cfg->max_batch <= 128 && !(peer_env && peer_env[0] == '0')) {
+    const int trc = tp_enable_peer(m->tp, cfg->max_batch, cfg->hidden, reinterpret_cast<cudaStream_t>(stream));
+    if (trc != 0) {
+      delete m;
+      return trc;
+    }
   }
   // split-K counters must start at zero; generation state too
   cudaError_t e = cudaMemsetAsync(m->ws + w.gemm_scratch, 0, w.gemm_scratch_bytes, st);
@@ -493,21 +635,36 @@ int teeny_tp_init(const void* id128, int rank, int world, void** comm_out) {
   std::memcpy(&id, id128, sizeof(id));
   ncclComm_t comm = nullptr;
   if (g_nccl.CommInitRank(&comm, world, id, rank) != ncclSuccess) return TEENY_ERR_NCCL;
-  *comm_out = comm;
+  TpContext* c = new (std::nothrow) TpContext();
+  if (!c) return TEENY_ERR_BAD_ARG;
+  c->comm = comm;
+  c->rank = rank;
+  c->world = world;
+  *comm_out = c;
   return 0;
 }
 
-int teeny_tp_destroy(void* comm) {
-  if (!comm) return 0;
+int teeny_tp_destroy(void* ctx) {
+  if (!ctx) return 0;
   if (!load_nccl()) return TEENY_ERR_NCCL;
-  return g_nccl.CommDestroy(static_cast<ncclComm_t>(comm)) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
+  TpContext* c = static_cast<TpContext*>(ctx);
+  for (int q = 0; q < c->world; ++q)
+    if (c->peer_ok && q != c->rank && c->peer[q]) cudaIpcCloseMemHandle(c->peer[q]);
+  if (c->local) cudaFree(c->local);
+  if (c->recv_tab) cudaFree(c->recv_tab);
+  if (c->flag_tab) cudaFree(c->flag_tab);
+  const bool ok = g_nccl.CommDestroy(c->comm) == ncclSuccess;
+  delete c;
+  return ok ? 0 : TEENY_ERR_NCCL;
 }
 
-int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_stream_t stream) {
-  if (!comm || !buf) return TEENY_ERR_BAD_ARG;
+int teeny_tp_all_reduce_bf16(void* ctx, teeny_bf16* buf, size_t count, teeny_stream_t stream) {
+  if (!ctx || !buf) return TEENY_ERR_BAD_ARG;
   if (!load_nccl()) return TEENY_ERR_NCCL;
-  return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<ncclComm_t>(comm),
+  return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, static_cast<TpContext*>(ctx)->comm,
                           reinterpret_cast<cudaStream_t>(stream)) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
 }
+
+int teeny_tp_peer_enabled(void* ctx) { return ctx && static_cast<TpContext*>(ctx)->peer_ok ? 1 : 0; }
 
 }  // extern "C"

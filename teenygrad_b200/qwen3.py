@@ -37,6 +37,7 @@ SIGNATURES = {
     "teeny_tp_init": (i32, [C.c_char_p, i32, i32, C.POINTER(vp)]),
     "teeny_tp_destroy": (i32, [vp]),
     "teeny_tp_all_reduce_bf16": (i32, [vp, vp, sz, vp]),
+    "teeny_tp_peer_enabled": (i32, [vp]),
 }
 _lib.bind(SIGNATURES)
 

@@ -1,6 +1,6 @@
 """Worker for tests/test_gpu_tp.py: one process per GPU (torch.distributed.run).  Runs a small Qwen3-shaped model
-tensor-parallel over all ranks, with and without CUDA-graph replay, and checks on rank 0 that the greedy ids equal
-the CPU oracle's and that every rank produced the same ids."""
+tensor-parallel over all ranks, with and without CUDA-graph replay, and checks on rank 0 that every rank produced the
+same ids, that graph replay equals eager, and that logits and greedy ids agree with the CPU oracle up to bf16 near-ties."""
 import os
 import sys
 
@@ -24,25 +24,53 @@ def main():
     B, S, steps = 3, 40, 12
     ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(22))
     cfg = qwen3.Qwen3Config(layers, hidden, hq, hkv, 128, inter, vocab, tied=False)
-    results = []
+    results, logit_runs = [], []
     for graph in (False, True):
         r = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + steps, max_new_tokens=steps, tp_rank=rank, tp_size=world,
                               comm=comm)
         r.load_state_dict(sd)
-        got = r.generate(ids, steps, use_graph=graph).contiguous()
+        r.prefill(ids)
+        step_logits = [r.logits().clone()]
+        for _ in range(steps - 1):
+            r.decode_step(graph=graph)
+            step_logits.append(r.logits().clone())
+        got = r.history()[:steps].t().contiguous()
         torch.cuda.synchronize()
         assert qwen3.lib.teeny_device_error(1) == 0
+        peer = qwen3.lib.teeny_tp_peer_enabled(comm)
         results.append(got)
+        logit_runs.append(torch.stack(step_logits, 1).contiguous())  # [B, steps, vocab / world]
         del r
     assert torch.equal(results[0], results[1]), "graph replay differs from eager under tensor parallelism"
     gathered = [torch.empty_like(results[0]) for _ in range(world)]
     dist.all_gather(gathered, results[0])
+    slices = [torch.empty_like(logit_runs[0]) for _ in range(world)]
+    dist.all_gather(slices, logit_runs[0])
     if rank == 0:
         for g in gathered:
             assert torch.equal(g, gathered[0]), "ranks disagree on the generated ids"
-        want = oq.OracleQwen3(ocfg, sd).generate(ids, steps)
-        assert torch.equal(gathered[0].cpu().long(), want), (gathered[0].cpu(), want)
-        print(f"TP{world} OK", flush=True)
+        got = gathered[0].cpu().long()
+        logits = torch.cat(slices, dim=-1).float().cpu()  # [B, steps, vocab]
+        want, want_logits = oq.OracleQwen3(ocfg, sd).generate(ids, steps, return_logits=True)
+        want_logits = want_logits.float()
+        # The cross-rank sum changes the rounding of every row-parallel projection, so a greedy pick may flip where
+        # the oracle's two best logits are within bf16 noise.  Up to each row's first flip the logits must agree within
+        # the bf16 bar, and a flip is only accepted as a near-tie: the token picked must be within 2e-2 (of the logit
+        # range) of the oracle's best.
+        scale = float(want_logits.abs().max())
+        flips = 0
+        for b in range(B):
+            t_div = next((t for t in range(steps) if got[b, t] != want[b, t]), steps)
+            upto = min(t_div + 1, steps)
+            err = float((logits[b, :upto] - want_logits[b, :upto]).abs().max()) / scale
+            assert err < 2e-2, f"row {b}: logits differ from the oracle by {err} before any token flipped"
+            if t_div < steps:
+                flips += 1
+                gap = float(want_logits[b, t_div].max() - want_logits[b, t_div, got[b, t_div]]) / scale
+                assert gap < 2e-2, f"row {b} step {t_div}: picked a token {gap} below the oracle's best (not a near-tie)"
+            assert t_div >= 1, "first generated token (prefill) must match"
+        print(f"TP{world} OK (decode reduction: {'peer-push' if peer else 'nccl'}; near-tie flips in {flips} of {B} rows)",
+              flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
