@@ -44,6 +44,7 @@ struct GemmArgs {
   const bf16* bias;       // [N] or null
   int tiles_p, tiles_q;   // tiles along P rows and along Q rows
   int k_blocks;           // ceil(K / 64)
+  int group;              // persistent kernel: P-tiles per raster group
   int kb_per_split;       // skinny kernel: k-blocks per cluster rank
   int swiglu;             // W rows interleave 64 gate / 64 up channels; Y[M, N/2] = silu(gate) * up
   // Tensor-parallel push (skinny kernel only): instead of Y, the f32 row sums go to slot `rank` of every rank's
@@ -64,10 +65,9 @@ struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_p, int tiles_q, int& tp, int& tq) {
-  // Grouped raster: 8 consecutive P-tiles share each Q-tile before moving on, so the tiles in flight across
+__device__ __forceinline__ void tile_coords(int tile, int tiles_p, int tiles_q, int kGroup, int& tp, int& tq) {
+  // Grouped raster: kGroup consecutive P-tiles share each Q-tile before moving on, so the tiles in flight across
   // the SMs reuse both operands out of L2.
-  constexpr int kGroup = 8;
   const int per_group = kGroup * tiles_q;
   const int g = tile / per_group;
   const int first_p = g * kGroup;
@@ -155,7 +155,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
       bool ok = true;
       for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x) {
         int tp, tq;
-        tile_coords(w, args.tiles_p, args.tiles_q, tp, tq);
+        tile_coords(w, args.tiles_p, args.tiles_q, args.group, tp, tq);
         for (int kb = 0; kb < args.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) { ok = false; break; }
           const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
@@ -206,7 +206,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
     int local = 0;
     for (int w = blockIdx.x; ok && w < num_work; w += gridDim.x, ++local) {
       int tp, tq;
-      tile_coords(w, args.tiles_p, args.tiles_q, tp, tq);
+      tile_coords(w, args.tiles_p, args.tiles_q, args.group, tp, tq);
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       if (!mbar_wait(acc_full_bar(buf), acc_phase, err, DEVERR_GEMM_EPILOGUE)) { ok = false; break; }
@@ -633,6 +633,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
   a.k_blocks = ceil_div(K, kBK);
   a.kb_per_split = a.k_blocks;
+  a.group = 8;
   a.swiglu = swiglu ? 1 : 0;
   if (push) {
     if (swiglu || w_is_kn || M > kSwapMaxM || !push->recv || !push->flag || push->world < 2) return TEENY_ERR_BAD_ARG;
@@ -708,6 +709,9 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
     }
   }
 
+  // Enough 256 x 256 tiles to occupy every SM pair: the CTA-pair kernel (about a fifth faster at these sizes).
+  if (!w_is_kn && static_cast<long long>(ceil_div(M, 256)) * ceil_div(N, 256) >= sms / 2)
+    return gemm_bf16_2cta(x, ldx, w, ldw, bias, y, ldy, M, N, K, stream, swiglu);
   a.tiles_p = ceil_div(M, kBM);
   a.tiles_q = ceil_div(N, bn);
   const int work = a.tiles_p * a.tiles_q;

@@ -40,6 +40,10 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
 int gather_add_rms_norm_bf16(const float* recv, size_t slot_elems, int world, unsigned* flag, unsigned* done,
                              unsigned expected, bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w,
                              int M, int N, float eps, cudaStream_t st);
+// Large-M path on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); same contract as gemm_bf16 without the options.
+int gemm_bf16_2cta_prepare();
+int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* bias, bf16* y, int ldy, int M, int N,
+                   int K, cudaStream_t stream, bool swiglu = false);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
 int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
              const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);

@@ -471,6 +471,7 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // function attributes (dynamic shared memory) are set once per device here, outside any stream capture
   int prc = gemm_bf16_prepare();
+  if (prc == 0) prc = gemm_bf16_2cta_prepare();
   if (prc == 0) prc = attention_prefill_prepare();
   if (prc == 0) prc = attention_decode_prepare();
   if (prc != 0) {

@@ -102,7 +102,7 @@ def _gemm_inputs(M, N, K, seed=1):
 
 @pytest.mark.parametrize("M,N,K", [
     (128, 256, 64), (128, 128, 128), (256, 512, 512), (300, 200, 136), (4096, 512, 256), (129, 264, 72),
-    (1024, 1024, 1024),
+    (1024, 1024, 1024), (4096, 4096, 512), (2500, 5000, 264), (8192, 2304, 1088),
 ])
 def test_linear_bf16_large_m(ops, M, N, K):
     from oracle import cpu as oc
@@ -267,7 +267,7 @@ def test_silu_mul_bf16(ops):
 
 
 @pytest.mark.parametrize("M,I,K", [(32, 3072, 1024), (1, 128, 512), (7, 1536, 4096), (300, 1024, 512), (4096, 3072, 1024),
-                                   (128, 12288, 4096), (129, 640, 264)])
+                                   (128, 12288, 4096), (129, 640, 264), (8192, 3072, 512), (5000, 2496, 264)])
 def test_linear_swiglu_fused(ops, M, I, K):
     """One GEMM over interleaved gate/up rows must equal linear -> linear -> silu -> mul of the bf16 graph."""
     from oracle import cpu as oc
