@@ -4,7 +4,7 @@
 //    read once, the query heads of a KV group share it), so the design goal is streaming the cache: a producer warp
 //    keeps a ring of TMA tile copies in flight (data in flight costs no registers) and four consumer warps run the
 //    arithmetic on warp-level mma.sync tiles fed by ldmatrix (a 128-row tcgen05 tile would be 97 % padding for 4 query
-//    heads).  Split over the sequence: each CTA takes kDecChunk keys of one (batch, kv head), every consumer warp 16
+//    heads).  Split over the sequence only when B * Hkv alone cannot fill the GPU; every consumer warp takes 16
 //    keys of each 64-key tile with an online softmax, warps are merged through shared memory, per-chunk partials
 //    (m, l, O) go to scratch and a second kernel merges chunks.
 // 2. attention_generic<T>: any head_dim <= 256, f32 or bf16, one warp per query row, sequential online softmax --
@@ -34,7 +34,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 // ---- decode kernel: TMA-fed shared-memory ring + mma.sync ----
-// CTA = one (batch, kv head, chunk of kDecChunk keys).  Warp 4 is the producer: for every 64-key tile it requests the
+// CTA = one (batch, kv head, share of the live keys).  Warp 4 is the producer: for every 64-key tile it requests the
 // K rows and the V rows (two [64 keys][64 d] boxes each, 128-byte swizzle) into a kDecStages-deep ring and the copies
 // signal a `full` mbarrier; nothing in flight costs registers.  Warps 0-3 each own 16 keys of a tile:
 //   S = Q K^T   A = Q from registers (rows = the G query heads of the group, padded to 16), B = K fragments through
@@ -48,6 +48,8 @@ struct DecodeArgs {
   float* part_o;   // [B, Hkv, chunks, G, 128]
   float* part_ml;  // [B, Hkv, chunks, G, 2]
   long long q_sb, q_sh;
+  bf16* o;         // final output, written directly when the sequence is not split (gridDim.x == 1)
+  long long o_sb, o_sh;
   int Hkv, G, max_chunks;
   int kv_len;
   const int* kv_len_dev;
@@ -97,8 +99,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   __syncthreads();
   pdl_wait();  // the cache rows of this step and the live length come from earlier kernels of the stream
   const int L = a.kv_len_dev ? *a.kv_len_dev : a.kv_len;
-  const int key_begin = chunk * kDecChunk;
-  const int key_end = min(L, key_begin + kDecChunk);
+  // the live keys are divided evenly (in whole 64-key tiles) over the gridDim.x CTAs of this (batch, kv head)
+  const int span = ((L + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) + kDecTile - 1) / kDecTile * kDecTile;
+  const int key_begin = chunk * span;
+  const int key_end = min(L, key_begin + span);
   const int n_tiles = key_begin < L ? (key_end - key_begin + kDecTile - 1) / kDecTile : 0;
   const int g = lane >> 2, c = lane & 3;
   float acc[16][4];
@@ -253,6 +257,10 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       ll += sm_ml[w][gg][1] * sc;
       oo += sm_o[w][gg][d] * sc;
     }
+    if (gridDim.x == 1) {  // whole sequence in this CTA: finish here, no partials
+      a.o[b * a.o_sb + (hk * G + gg) * a.o_sh + d] = __float2bfloat16_rn(oo / ll);
+      continue;
+    }
     a.part_o[(slot * G + gg) * kHD + d] = oo;
     if (d == 0) {
       a.part_ml[(slot * G + gg) * 2 + 0] = mm;
@@ -264,11 +272,13 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
 // grid (Hq, B), 128 threads: thread d merges the valid chunks of head h.
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 bf16* __restrict__ o, long long o_sb, long long o_sh, int Hkv, int G,
-                                                int max_chunks, int kv_len, const int* __restrict__ kv_len_dev) {
+                                                int max_chunks, int n_split, int kv_len,
+                                                const int* __restrict__ kv_len_dev) {
   pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const int L = kv_len_dev ? *kv_len_dev : kv_len;
-  const int chunks = (L + kDecChunk - 1) / kDecChunk;
+  const int span = ((L + n_split - 1) / n_split + kDecTile - 1) / kDecTile * kDecTile;  // as in the main kernel
+  const int chunks = (L + span - 1) / span;
   const int hk = h / G, gg = h - hk * G;
   const size_t slot0 = (static_cast<size_t>(b) * Hkv + hk) * max_chunks;
   float mm = -INFINITY;
@@ -407,11 +417,18 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   a.part_o = static_cast<float*>(scratch);
   a.part_ml = a.part_o + static_cast<size_t>(s.B) * s.Hq * max_chunks * kHD;
   a.q_sb = s.q_sb; a.q_sh = s.q_sh;
+  a.o = o; a.o_sb = s.o_sb; a.o_sh = s.o_sh;
   a.Hkv = s.Hkv; a.G = G; a.max_chunks = max_chunks;
   a.kv_len = kv_len; a.kv_len_dev = kv_len_dev;
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.err = device_error_word();
-  dim3 grid(max_chunks, s.Hkv, s.B);
+  // Split the sequence only as far as needed to put a CTA in every slot (two per SM): with B * Hkv CTAs already
+  // filling the GPU each one walks its whole sequence and writes the output itself (no partials, no merge kernel).
+  const int bh = s.B * s.Hkv;
+  int n_split = (2 * sm_count() + bh / 2) / bh;
+  if (n_split > max_chunks) n_split = max_chunks;
+  if (n_split < 1) n_split = 1;
+  dim3 grid(n_split, s.Hkv, s.B);
   switch (G) {
     case 1: launch_kernel(attention_decode_kernel<1>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
     case 2: launch_kernel(attention_decode_kernel<2>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
@@ -420,8 +437,9 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  launch_kernel(attention_decode_combine_kernel, dim3(dim3(s.Hq, s.B)), dim3(kHD), 0, stream, 1, a.part_o, a.part_ml, o, s.o_sb, s.o_sh, s.Hkv,
-                                                                       G, max_chunks, kv_len, kv_len_dev);
+  if (n_split == 1) return 0;
+  launch_kernel(attention_decode_combine_kernel, dim3(s.Hq, s.B), dim3(kHD), 0, stream, 1, a.part_o, a.part_ml, o,
+                s.o_sb, s.o_sh, s.Hkv, G, max_chunks, n_split, kv_len, kv_len_dev);
   return static_cast<int>(cudaGetLastError());
 }
 
