@@ -32,7 +32,7 @@ if ROOT not in sys.path:
 METRIC = "qwen3_8b_tokens_per_s"
 UNIT = "tok/s"
 # bounded CPU sample of the workload (sized for roughly 10-30 s of host work on a 16-thread box)
-CPU_SAMPLE = dict(sample_layers=3, batch=8, prefill=2048, new_tokens=16)
+CPU_SAMPLE = dict(sample_layers=4, batch=16, prefill=2048, new_tokens=16)
 
 
 def parse_args():

@@ -58,8 +58,9 @@ int matmul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, te
 /* Y[M,N] = X[M,K] @ W[N,K]^T (+ bias[N], NULL for none); strides in elements.  Replaces linear_forward,
  * kernels/teeny-kernels/src/nn/mlp/linear.rs:22-116 (arguments :31-45, packed by RuntimeOp for LinearForward
  * :275-307).  bf16: when stride_xk == stride_wk == stride_yn == 1 and rows are 16-byte aligned the tcgen05 kernel
- * runs; other layouts run on a CUDA-core kernel.  With M <= 128 and scratch of teeny_gemm_scratch_bytes() bytes
- * (zero-filled once before first use; the kernel leaves it zeroed) K may be split across CTAs. */
+ * runs; other layouts run on a CUDA-core kernel.  With M <= 128 the tcgen05 kernel splits K across the CTAs of a
+ * thread-block cluster and sums the partial tiles through distributed shared memory, so it needs no global scratch:
+ * global_scratch is accepted for signature parity with the reference and may be NULL. */
 int linear_forward_entry_point_f32(const float* x, const float* w, const float* bias, float* y, int M, int N, int K,
                                    int stride_xm, int stride_xk, int stride_wn, int stride_wk, int stride_ym,
                                    int stride_yn, void* global_scratch, size_t global_scratch_bytes,
@@ -68,7 +69,8 @@ int linear_forward_entry_point_bf16(const teeny_bf16* x, const teeny_bf16* w, co
                                     int M, int N, int K, int stride_xm, int stride_xk, int stride_wn, int stride_wk,
                                     int stride_ym, int stride_yn, void* global_scratch, size_t global_scratch_bytes,
                                     teeny_stream_t stream);
-/* Scratch the bf16 GEMM can use for split-K at this shape (0 when it never splits). */
+/* Global scratch the bf16 GEMM wants at this shape.  Always 0 (split-K is reduced on chip); kept so hosts that size
+ * a scratch arena per shape, as the reference's launcher does, have one call to ask. */
 size_t teeny_gemm_scratch_bytes(int M, int N, int K);
 
 /* ---------------------------------------------------------------------------------------------------------------

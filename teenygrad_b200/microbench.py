@@ -1,0 +1,182 @@
+"""Kernel micro-benchmarks and profiler cases for libteeny_b200.so.
+
+    python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode]   # CUDA-event timings
+    python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
+    python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
+
+``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
+one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
+microseconds, are captured in a CUDA graph over rotating copies of their inputs (larger than L2 together) so neither
+host launch overhead nor a warm L2 enters the number.  ``case`` and ``layers`` exist to be run under ``ncu``.
+"""
+import sys
+
+import torch
+
+from . import ops
+
+HQ, HKV, D = 32, 8, 128
+
+
+def _graph_time(fns, reps=5):
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            for f in fns:
+                f()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps / len(fns)
+
+
+_flush = None
+
+
+def _flushed_time(fn, iters=8, warm=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _rand(*shape):
+    return (torch.rand(*shape, device="cuda") * 0.1 - 0.05).bfloat16()
+
+
+def time_gemm():
+    for (M, N, K) in [(4096, 4096, 4096), (4096, 12288, 4096), (8192, 8192, 8192), (65536, 6144, 4096), (65536, 4096, 12288)]:
+        x, w = _rand(M, K), _rand(N, K)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        t = _flushed_time(lambda: ops.linear_forward(x, w, out=y))
+        t2 = _flushed_time(lambda: torch.matmul(x, w.t(), out=y))
+        fl = 2 * M * N * K
+        print(f"linear bf16 {M}x{N}x{K}: {t:.4f} ms {fl / t / 1e9:.0f} TFLOP/s | cuBLAS {t2:.4f} ms {fl / t2 / 1e9:.0f} TFLOP/s", flush=True)
+
+
+def time_skinny():
+    for (M, N, K) in [(32, 24576, 4096), (32, 4096, 12288), (32, 6144, 4096), (32, 4096, 4096), (1, 4096, 4096),
+                      (128, 4096, 4096), (32, 151936, 4096)]:
+        n = max(2, int(1.5e9 // (N * K * 2)))
+        ws = [_rand(N, K) for _ in range(n)]
+        x = _rand(M, K)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        t = _graph_time([(lambda w=w: ops.linear_forward(x, w, out=y)) for w in ws])
+        t2 = _graph_time([(lambda w=w: torch.matmul(x, w.t(), out=y)) for w in ws])
+        by = 2 * (M * K + N * K + M * N)
+        print(f"linear bf16 {M}x{N}x{K}: {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s | cuBLAS {t2 * 1e3:.1f} us {by / t2 / 1e6:.0f} GB/s", flush=True)
+
+
+def time_prefill():
+    for (B, S) in [(4, 4096), (32, 2048)]:
+        q = torch.randn(B, HQ, S, D, device="cuda").bfloat16()
+        k = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+        v = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        t = _flushed_time(lambda: ops.flash_attn_fwd(q, k, v, D ** -0.5, causal=True, out=o))
+        t2 = _flushed_time(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True))
+        fl = 0.5 * 4 * B * HQ * S * S * D
+        print(f"flash-attn causal B{B} S{S}: {t:.3f} ms {fl / t / 1e9:.0f} TFLOP/s | torch SDPA {t2:.3f} ms {fl / t2 / 1e9:.0f} TFLOP/s", flush=True)
+
+
+def time_decode():
+    for (B, L) in [(32, 2304), (32, 2048), (4, 4096)]:
+        n = max(2, int(1.2e9 // (2 * B * HKV * L * D * 2)))
+        q = torch.randn(B, HQ, 1, D, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        kv = [(torch.randn(B, HKV, L, D, device="cuda").bfloat16(), torch.randn(B, HKV, L, D, device="cuda").bfloat16())
+              for _ in range(n)]
+        sc = torch.empty(ops.lib.teeny_attn_decode_scratch_bytes(B, HQ, D, L), dtype=torch.uint8, device="cuda")
+        t = _graph_time([(lambda k=k, v=v: ops.flash_attn_decode(q, k, v, L, D ** -0.5, out=o, scratch=sc)) for k, v in kv])
+        by = 2 * B * HKV * L * D * 2
+        print(f"flash-attn decode B{B} L{L}: {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s", flush=True)
+
+
+def case(which):
+    """A handful of launches of one kernel on inputs larger than L2 (for ncu -k ... -s 2 -c 2)."""
+    if which == "gemm":
+        M, N, K = 4096, 12288, 4096
+        x, w = _rand(M, K), _rand(N, K)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        for _ in range(4):
+            ops.linear_forward(x, w, out=y)
+    elif which == "skinny":
+        M, N, K = 32, 6144, 4096
+        x, ws = _rand(M, K), [_rand(N, K) for _ in range(4)]
+        y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        for w in ws:
+            ops.linear_forward(x, w, out=y)
+    elif which == "prefill":
+        B, S = 4, 4096
+        q = torch.randn(B, HQ, S, D, device="cuda").bfloat16()
+        k = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+        v = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        for _ in range(3):
+            ops.flash_attn_fwd(q, k, v, D ** -0.5, causal=True, out=o)
+    elif which == "decode":
+        B, L = 32, 2304
+        q = torch.randn(B, HQ, 1, D, device="cuda").bfloat16()
+        k = torch.randn(B, HKV, L, D, device="cuda").bfloat16()
+        v = torch.randn(B, HKV, L, D, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        for _ in range(4):
+            ops.flash_attn_decode(q, k, v, L, D ** -0.5, out=o)
+    else:
+        raise SystemExit(f"unknown case {which}")
+    torch.cuda.synchronize()
+
+
+def layers(n_layers):
+    """Prefill (batch 32 x 2048) and three eager decode steps of an n-layer Qwen3-8B-shaped model: every kernel of the
+    runner at its full per-launch size, few enough launches for a profiler launch list."""
+    from . import qwen3
+    cfg = qwen3.Qwen3Config(n_layers, 4096, 32, 8, 128, 12288, 151936, tied=False)
+    r = qwen3.Qwen3Runner(cfg, max_batch=32, max_len=2304, max_tokens=32 * 2048, max_new_tokens=8)
+    qwen3.load_random_weights(r, 4)
+    ids = torch.randint(0, cfg.vocab, (32, 2048), dtype=torch.int32)
+    r.prefill(ids)
+    for _ in range(3):
+        r.decode_step(graph=False)
+    torch.cuda.synchronize()
+
+
+def main(argv):
+    torch.cuda.set_device(0)
+    mode = argv[0] if argv else "time"
+    if mode == "time":
+        what = argv[1:] or ["gemm", "skinny", "prefill", "decode"]
+        for name in what:
+            {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode}[name]()
+    elif mode == "case":
+        case(argv[1])
+    elif mode == "layers":
+        layers(int(argv[1]) if len(argv) > 1 else 6)
+    else:
+        raise SystemExit(__doc__)
+    print("device error word:", ops.device_error())
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
