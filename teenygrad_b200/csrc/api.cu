@@ -296,3 +296,12 @@ int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int pa
 }
 
 }  // extern "C"
+
+// Kernel-timeline registry of development builds (-DTEENY_TRACE): one dump function per translation unit.
+#ifdef TEENY_TRACE
+namespace { struct TraceTu { const char* name; teeny_trace_dump_fn fn; }; TraceTu g_tus[16]; int g_ntu = 0; }
+extern "C" void teeny_trace_register(const char* tu, teeny_trace_dump_fn fn) { if (g_ntu < 16) g_tus[g_ntu++] = {tu, fn}; }
+extern "C" int teeny_trace_count() { return g_ntu; }
+extern "C" const char* teeny_trace_name(int i) { return g_tus[i].name; }
+extern "C" int teeny_trace_dump(int i, unsigned long long* out, unsigned cap, int reset) { return g_tus[i].fn(out, cap, reset); }
+#endif

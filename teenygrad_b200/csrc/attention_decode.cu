@@ -53,6 +53,10 @@ struct DecodeArgs {
   int Hkv, G, max_chunks;
   int kv_len;
   const int* kv_len_dev;
+  // >= 0: only the last `fresh_rows` live cache rows (and q) come from the kernel launched just before this one;
+  // the length and every older row were complete before that kernel started, so they may be read ahead of the
+  // dependency wait.  < 0: nothing is known, read everything after the wait.
+  int fresh_rows;
   float scale_log2;
   int* err;
 };
@@ -97,13 +101,38 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     mbar_fence_init();
   }
   __syncthreads();
-  pdl_wait();  // the cache rows of this step and the live length come from earlier kernels of the stream
-  const int L = a.kv_len_dev ? *a.kv_len_dev : a.kv_len;
   // the live keys are divided evenly (in whole 64-key tiles) over the gridDim.x CTAs of this (batch, kv head)
-  const int span = ((L + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) + kDecTile - 1) / kDecTile * kDecTile;
-  const int key_begin = chunk * span;
-  const int key_end = min(L, key_begin + span);
-  const int n_tiles = key_begin < L ? (key_end - key_begin + kDecTile - 1) / kDecTile : 0;
+  int L = 0, span = 0, key_begin = 0, key_end = 0, n_tiles = 0;
+  auto plan = [&]() {
+    L = a.kv_len_dev ? *a.kv_len_dev : a.kv_len;
+    span = ((L + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) + kDecTile - 1) / kDecTile * kDecTile;
+    key_begin = chunk * span;
+    key_end = min(L, key_begin + span);
+    n_tiles = key_begin < L ? (key_end - key_begin + kDecTile - 1) / kDecTile : 0;
+  };
+  auto load_tile = [&](int t) {
+    const int st = t % kDecStages;
+    const uint32_t dst = base + st * kDecStageBytes;
+    const int key0 = key_begin + t * kDecTile;
+    mbar_expect_tx(full_bar(st), kDecStageBytes);
+    tma_load_4d(dst, &tmap_k, full_bar(st), 0, key0, hk, b);
+    tma_load_4d(dst + kDecBox, &tmap_k, full_bar(st), 64, key0, hk, b);
+    tma_load_4d(dst + 2 * kDecBox, &tmap_v, full_bar(st), 0, key0, hk, b);
+    tma_load_4d(dst + 3 * kDecBox, &tmap_v, full_bar(st), 64, key0, hk, b);
+  };
+  int pre = 0;  // tiles requested ahead of the wait (producer thread only)
+  if (a.fresh_rows >= 0) {
+    plan();
+    if (threadIdx.x == 128) {
+      // first ring of tiles that hold none of the rows the previous kernel is still writing
+      while (pre < n_tiles && pre < kDecStages && key_begin + (pre + 1) * kDecTile <= L - a.fresh_rows) {
+        load_tile(pre);
+        ++pre;
+      }
+    }
+  }
+  pdl_wait();  // the cache rows of this step (and, unless declared stable, the live length) come from earlier kernels
+  if (a.fresh_rows < 0) plan();
   const int g = lane >> 2, c = lane & 3;
   float acc[16][4];
   float m = -INFINITY, l = 0.0f;
@@ -112,17 +141,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   if (warp == 4) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      for (int t = 0; t < n_tiles; ++t) {
+      for (int t = pre; t < n_tiles; ++t) {
         const int st = t % kDecStages;
         const uint32_t ph = (t / kDecStages) & 1;
         if (!mbar_wait(empty_bar(st), ph ^ 1, a.err, DEVERR_ATTN_PRODUCER)) break;
-        const uint32_t dst = base + st * kDecStageBytes;
-        const int key0 = key_begin + t * kDecTile;
-        mbar_expect_tx(full_bar(st), kDecStageBytes);
-        tma_load_4d(dst, &tmap_k, full_bar(st), 0, key0, hk, b);
-        tma_load_4d(dst + kDecBox, &tmap_k, full_bar(st), 64, key0, hk, b);
-        tma_load_4d(dst + 2 * kDecBox, &tmap_v, full_bar(st), 0, key0, hk, b);
-        tma_load_4d(dst + 3 * kDecBox, &tmap_v, full_bar(st), 64, key0, hk, b);
+        load_tile(t);
       }
     }
   } else {
@@ -267,6 +290,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       a.part_ml[(slot * G + gg) * 2 + 1] = ll;
     }
   }
+  TRACE_END();
 }
 
 // grid (Hq, B), 128 threads: thread d merges the valid chunks of head h.
@@ -379,7 +403,8 @@ size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv) {
 }
 
 int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
-                          const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream) {
+                          const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream,
+                          int fresh_rows) {
   if (!q || !k || !v || !o || !scratch || s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Skv <= 0) return TEENY_ERR_BAD_ARG;
   if (s.D != kHD || s.Hq % s.Hkv != 0 || s.Sq != 1) return TEENY_ERR_BAD_ARG;
   if (!kv_len_dev && (kv_len <= 0 || kv_len > s.Skv)) return TEENY_ERR_BAD_ARG;
@@ -420,6 +445,7 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   a.o = o; a.o_sb = s.o_sb; a.o_sh = s.o_sh;
   a.Hkv = s.Hkv; a.G = G; a.max_chunks = max_chunks;
   a.kv_len = kv_len; a.kv_len_dev = kv_len_dev;
+  a.fresh_rows = fresh_rows;
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.err = device_error_word();
   // Split the sequence only as far as needed to put a CTA in every slot (two per SM): with B * Hkv CTAs already

@@ -57,14 +57,68 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
 // programmatic dependent launch
 // ------------------------------------------------------------------------------------------------
 // Every kernel of this library calls pdl_wait() before it first touches memory that an earlier kernel in the
-// stream may still be writing; whatever it does before that (barrier init, TMEM allocation, prefetch of weights,
-// which no kernel writes) overlaps the tail of its predecessor.  The long kernels call pdl_trigger() when their
-// main loop is done, which lets the next kernel become resident then; for the others the trigger is implicit at
-// exit.  (Triggering at kernel entry was measured slower: CTAs of several later kernels then sit resident and
-// waiting next to the running one.)  Both calls are no-ops for a kernel launched the ordinary way.  Every thread of
-// every CTA executes pdl_wait(), so a grid never completes before its predecessor has.
+// stream may still be writing; whatever it does before that (barrier init, TMEM allocation, fetching weights,
+// which no kernel writes) overlaps the tail of its predecessor.  pdl_trigger() lets the next kernel become resident:
+// the long kernels call it when their main loop is done, the short ones (norms, rope) right after their own wait, so
+// that the GEMM or attention kernel behind them streams its first ring of weights or cache tiles while they run.
+// No kernel triggers before its own wait has returned: at most two later kernels are ever resident beside the
+// running one, and when a kernel starts, everything older than its immediate predecessor is complete.  (Triggering
+// at kernel entry everywhere was measured slower: CTAs of several later kernels then sit resident and waiting.)
+// Both calls are no-ops for a kernel launched the ordinary way.  Every thread of every CTA executes pdl_wait(), so a
+// grid never completes before its predecessor has.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#ifndef TEENY_TRACE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define TRACE_END() do {} while (0)
+#else
+// ------------------------------------------------------------------------------------------------
+// Kernel timeline (development builds only: make EXTRA=-DTEENY_TRACE).  Thread 0 of every CTA records the global
+// timer when it reaches pdl_wait() and when the wait returns, and kernels that call TRACE_END() also when the CTA
+// is done; records carry the source line of the call, the SM, the CTA index and the grid size.  Each translation
+// unit has its own buffer and registers a dump function with the C API (teeny_trace_count / _name / _dump), so
+// `python -m teenygrad_b200.microbench trace` can print when each kernel of a decode step became resident, was
+// released and finished.  The stamps cost an atomic and four stores per CTA: use the output for where time goes,
+// not for absolute kernel times.
+// ------------------------------------------------------------------------------------------------
+static __device__ unsigned long long g_trace[4u << 18];
+static __device__ unsigned g_trace_n;
+__device__ __forceinline__ void trace_put(unsigned long long t0, unsigned long long t1, int line) {
+  const unsigned idx = atomicAdd(&g_trace_n, 1u);
+  if (idx < (1u << 18)) {
+    unsigned sm;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    g_trace[idx * 4 + 0] = t0;
+    g_trace[idx * 4 + 1] = t1;
+    g_trace[idx * 4 + 2] = static_cast<unsigned long long>(line) | (static_cast<unsigned long long>(sm) << 32);
+    g_trace[idx * 4 + 3] = (blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) |
+                           (static_cast<unsigned long long>(gridDim.x * gridDim.y * gridDim.z) << 32);
+  }
+}
+__device__ __forceinline__ void pdl_wait_traced(int line) {
+  const unsigned long long t0 = global_timer_ns();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) trace_put(t0, global_timer_ns(), line);
+}
+#define pdl_wait() pdl_wait_traced(__LINE__)
+// end-of-CTA record (t0 == 0 marks it)
+#define TRACE_END() \
+  do { if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) trace_put(0, global_timer_ns(), __LINE__); } while (0)
+typedef int (*teeny_trace_dump_fn)(unsigned long long* out, unsigned cap, int reset);
+extern "C" void teeny_trace_register(const char* tu, teeny_trace_dump_fn fn);
+namespace {
+int trace_dump_tu(unsigned long long* out, unsigned cap, int reset) {
+  unsigned n = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, g_trace_n, sizeof(n));
+  if (n > (1u << 18)) n = 1u << 18;
+  if (n > cap) n = cap;
+  if (out && n) cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 4 * n);
+  if (reset) { unsigned z = 0; cudaMemcpyToSymbol(g_trace_n, &z, sizeof(z)); }
+  return static_cast<int>(n);
+}
+struct TraceReg { TraceReg() { teeny_trace_register(__BASE_FILE__, trace_dump_tu); } } g_trace_reg;
+}
+#endif
 
 // Host: whether launches on this thread carry the programmatic-stream-serialization attribute (the Qwen3 runner
 // turns it on around its kernel sequences).

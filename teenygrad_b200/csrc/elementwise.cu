@@ -127,12 +127,22 @@ template <int VPT, bool ADD>
 __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
                                      long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
                                      float* __restrict__ rrms, int N, float eps) {
+  // the norm weights are written by no kernel: fetch them while the producer of x is still running, and let the
+  // consumer of y become resident (and fetch its own weights) as soon as this kernel's input is complete
+  const int nv = N >> 3;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 g[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    g[i] = idx < nv ? __ldg(wr + idx) : make_uint4(0u, 0u, 0u, 0u);
+  }
   pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   const int row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * ldx);
   uint4* rr4 = ADD ? reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr) : nullptr;
-  const int nv = N >> 3;
   float v[VPT][8];
   float sq = 0.0f;
 #pragma unroll
@@ -170,13 +180,11 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
   if (threadIdx.x == 0 && rrms) rrms[row] = rr;
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
-  const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
-      const uint4 g = wr[idx];
-      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      const uint32_t gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
       uint32_t ow[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -187,6 +195,7 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
       yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
   }
+  TRACE_END();
 }
 
 // Any N / alignment: scalar accesses, row re-read from L2 in the second phase.
@@ -253,7 +262,16 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
                                            unsigned* flag, unsigned* done, unsigned expected,
                                            bf16* __restrict__ res, long long ldr, bf16* __restrict__ y, long long ldy,
                                            const bf16* __restrict__ w, int N, float eps, int* err) {
+  const int nv = N >> 3;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 g[VPT];  // norm weights: constant, fetched ahead of the wait
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    g[i] = idx < nv ? __ldg(wr + idx) : make_uint4(0u, 0u, 0u, 0u);
+  }
   pdl_wait();
+  pdl_trigger();
   __shared__ float red[32];
   if (threadIdx.x == 0) {
     uint64_t t0 = 0;
@@ -270,7 +288,7 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
     }
   }
   __syncthreads();
-  const int row = blockIdx.x, nv = N >> 3;
+  const int row = blockIdx.x;
   uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
   float v[VPT][8];
   float sq = 0.0f;
@@ -304,13 +322,11 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
   sq = block_sum(sq, red);
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
-  const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
-      const uint4 g = wr[idx];
-      const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+      const uint32_t gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
       uint32_t ow[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e)
@@ -411,7 +427,6 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
                                        const bf16* __restrict__ sin_t, bf16* __restrict__ k_cache,
                                        bf16* __restrict__ v_cache, int T, int S, int Hq, int Hkv, int max_len,
                                        int pos0, const int* __restrict__ pos0_dev, float eps) {
-  pdl_wait();
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
   const long long total = static_cast<long long>(T) * heads;
@@ -422,6 +437,10 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
   const int t = static_cast<int>(unit / heads);
   const int h = static_cast<int>(unit - static_cast<long long>(t) * heads);
   const int b = t / S;
+  // head-norm weights are constants: fetched ahead of the wait for the projection
+  const uint4 wraw = __ldg(reinterpret_cast<const uint4*>((h < Hq ? q_w : k_w) + sub * 8));
+  pdl_wait();
+  pdl_trigger();
   const int pos = (pos0_dev ? *pos0_dev : pos0) + (t - b * S);
   bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + sub * 8;
   const uint4 raw = *reinterpret_cast<const uint4*>(src);
@@ -436,7 +455,6 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // stays inside the half-warp
   const float rr = 1.0f / sqrtf(sq * (1.0f / D) + eps);
-  const uint4 wraw = *reinterpret_cast<const uint4*>((is_q ? q_w : k_w) + sub * 8);
   const int tp = pos < max_len ? pos : max_len - 1;  // table has max_len rows
   const uint4 craw = *reinterpret_cast<const uint4*>(cos_t + static_cast<size_t>(tp) * D + sub * 8);
   const uint4 sraw = *reinterpret_cast<const uint4*>(sin_t + static_cast<size_t>(tp) * D + sub * 8);

@@ -356,11 +356,14 @@ __device__ __forceinline__ uint32_t cluster_size() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+// 16 bytes of CTA `rank`'s shared memory at this CTA's address `local_addr`.  Volatile (so it stays behind the cluster
+// barrier, itself a volatile asm) but without a memory clobber: consecutive loads are all in flight together.
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
-  float v;
+  float4 v;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote));
   return v;
 }
 
@@ -453,8 +456,6 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       if (ok) umma_commit(acc_full_bar);
     }
   } else {
-    // accumulator -> this CTA's partial tile in shared memory, column-major so a thread's stores and the later
-    // per-column reads are both conflict-free (consecutive rows = consecutive words)
     pdl_wait();
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -462,83 +463,140 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
       constexpr int kChunk = (BN >= 32) ? 32 : 16;
+      const bool direct = (S == 1) && !args.swiglu;
+      const int n = tile * kBM + row;
+      const float bias = (direct && args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
         if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
         tmem_wait_ld();
+        if (direct) {
+          // the whole K range was this CTA's: registers -> global, a warp's 32 rows side by side in each token row
+          if (n < args.N) {
 #pragma unroll
-        for (int e = 0; e < kChunk; ++e) part_gen[(c0 + e) * kBM + row] = __uint_as_float(r[e]);
+            for (int e = 0; e < kChunk; ++e) {
+              const int c = c0 + e;
+              if (c < args.M) {
+                const float v = __uint_as_float(r[e]) + bias;
+                if (args.push_recv) {
+                  const size_t off = static_cast<size_t>(c) * args.N + n;
+                  for (int p = 0; p < args.push_world; ++p) args.push_recv[p][off] = v;  // NVLink stores
+                } else {
+                  args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(v);
+                }
+              }
+            }
+          }
+        } else {
+          // accumulator -> this CTA's partial tile in shared memory, column-major (a token column = 128 consecutive
+          // words), so these stores and the 16-byte reads of the reduction are both conflict-free
+#pragma unroll
+          for (int e = 0; e < kChunk; ++e) part_gen[(c0 + e) * kBM + row] = __uint_as_float(r[e]);
+        }
       }
       tc_fence_before();
     }
   }
 
-  // every partial tile of the cluster is in place
   __syncwarp();
   pdl_trigger();  // main loop done: the next kernel's set-up (and weight prefetch) overlaps the reduction below
-  cluster_sync_all();
+  const bool reduce = (S > 1) || args.swiglu;
+  // every partial tile of the cluster is in place
+  if (S > 1) cluster_sync_all(); else if (reduce) __syncthreads();
 
-  if (warp >= 2) {
-    // CTA `rank` finishes token columns [rank * cw, (rank + 1) * cw): sum over the cluster in rank order
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int n = tile * kBM + row;
+  if (warp >= 2 && reduce) {
+    // CTA `rank` finishes token columns [rank * cw, (rank + 1) * cw): per 16-byte unit (4 weight rows of one token
+    // column) all S partial values are requested at once and summed in rank order
     const int cw = (BN + static_cast<int>(S) - 1) / static_cast<int>(S);  // columns per rank (last rank may get fewer)
-    const int c_end = min(BN, (static_cast<int>(rank) + 1) * cw);
-    const float bias = (args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
-    const bool live = *reinterpret_cast<volatile int*>(err) == 0;
+    const int c_begin = static_cast<int>(rank) * cw;
+    const int ncols = min(BN, c_begin + cw) - c_begin;
+    const int epi = (warp - 2) * 32 + lane;
     if (args.swiglu) {
-      // the tile holds 64 gate rows then the 64 up rows of the same channels: a thread sums both rows of a channel
-      // (for every other column of this rank's slice) and writes silu(gate) * up
-      const int epi = (warp - 2) * 32 + lane, rp = epi & 63, half = epi >> 6;
-      const int n_out = tile * 64 + rp;
-#pragma unroll 2
-      for (int c = static_cast<int>(rank) * cw + half; c < c_end; c += 2) {
-        const uint32_t ga = part_base + static_cast<uint32_t>((c * kBM + rp) * 4);
-        float gv[8], uv[8];
+      // the tile holds 64 gate rows then the 64 up rows of the same channels: a unit = 4 channels of one column
+      const bool vec_ok = (args.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.y) & 7) == 0);
+      for (int u = epi; u < ncols * 16; u += kEpilogueThreads) {
+        const int c = c_begin + (u >> 4), j = u & 15;
+        const uint32_t ga = part_base + static_cast<uint32_t>((c * kBM + 4 * j) * 4);
+        float4 gv[8], uv[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          gv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(ga, q) : 0.0f;
-          uv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(ga + 64 * 4, q) : 0.0f;
+          gv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32x4(ga, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+          uv[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32x4(ga + 64 * 4, q) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        float gs = gv[0], us = uv[0];
+        float4 gs = gv[0], us = uv[0];
 #pragma unroll
-        for (int q = 1; q < 8; ++q) { gs += gv[q]; us += uv[q]; }
-        if (live && c < args.M && n_out < args.N / 2)
-          args.y[static_cast<size_t>(c) * args.ldy + n_out] = __float2bfloat16_rn(swiglu_f(gs, us));
+        for (int q = 1; q < 8; ++q) {
+          gs.x += gv[q].x; gs.y += gv[q].y; gs.z += gv[q].z; gs.w += gv[q].w;
+          us.x += uv[q].x; us.y += uv[q].y; us.z += uv[q].z; us.w += uv[q].w;
+        }
+        const int n_out = tile * 64 + 4 * j;
+        if (c < args.M) {
+          const float o[4] = {swiglu_f(gs.x, us.x), swiglu_f(gs.y, us.y), swiglu_f(gs.z, us.z), swiglu_f(gs.w, us.w)};
+          bf16* dst = args.y + static_cast<size_t>(c) * args.ldy + n_out;
+          if (vec_ok && n_out + 3 < args.N / 2) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+          } else {
+            for (int e = 0; e < 4; ++e)
+              if (n_out + e < args.N / 2) dst[e] = __float2bfloat16_rn(o[e]);
+          }
+        }
       }
-    } else
-#pragma unroll 4
-    for (int c = static_cast<int>(rank) * cw; c < c_end; ++c) {
-      const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + row) * 4);
-      float v[8];
+    } else {
+      const bool vec_ok = args.push_recv ? (args.N % 4 == 0)
+                                         : ((args.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.y) & 7) == 0));
+      for (int u = epi; u < ncols * 32; u += kEpilogueThreads) {
+        const int c = c_begin + (u >> 5), j = u & 31;
+        const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + 4 * j) * 4);
+        float4 v[8];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) v[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32(addr, q) : 0.0f;
-      float acc = v[0];
+        for (int q = 0; q < 8; ++q)
+          v[q] = (static_cast<uint32_t>(q) < S) ? ld_cluster_f32x4(addr, q) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 acc = v[0];
 #pragma unroll
-      for (int q = 1; q < 8; ++q) acc += v[q];
-      if (live && c < args.M && n < args.N) {
-        if (args.push_recv) {
-          const size_t off = static_cast<size_t>(c) * args.N + n;
-          for (int p = 0; p < args.push_world; ++p) args.push_recv[p][off] = acc + bias;  // NVLink stores
-        } else {
-          args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(acc + bias);
+        for (int q = 1; q < 8; ++q) { acc.x += v[q].x; acc.y += v[q].y; acc.z += v[q].z; acc.w += v[q].w; }
+        const int n = tile * kBM + 4 * j;
+        if (c < args.M && n < args.N) {
+          float o[4] = {acc.x, acc.y, acc.z, acc.w};
+          if (args.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (n + e < args.N) o[e] += __bfloat162float(args.bias[n + e]);
+          }
+          if (args.push_recv) {
+            const size_t off = static_cast<size_t>(c) * args.N + n;
+            for (int p = 0; p < args.push_world; ++p) {  // NVLink stores
+              if (vec_ok) {
+                *reinterpret_cast<float4*>(args.push_recv[p] + off) = make_float4(o[0], o[1], o[2], o[3]);
+              } else {
+                for (int e = 0; e < 4; ++e)
+                  if (n + e < args.N) args.push_recv[p][off + e] = o[e];
+              }
+            }
+          } else {
+            bf16* dst = args.y + static_cast<size_t>(c) * args.ldy + n;
+            if (vec_ok && n + 3 < args.N) {
+              *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+            } else {
+              for (int e = 0; e < 4; ++e)
+                if (n + e < args.N) dst[e] = __float2bfloat16_rn(o[e]);
+            }
+          }
         }
       }
     }
-    if (args.push_recv) {
-      // every store of this CTA is visible system-wide before any rank's counter moves
-      __threadfence_system();
-      named_barrier_sync(1, kEpilogueThreads);
-      const int epi = (warp - 2) * 32 + lane;
-      if (epi < args.push_world) atomicAdd_system(args.push_flag[epi], 1u);
-    }
+  }
+  if (warp >= 2 && args.push_recv) {
+    // every store of this CTA is visible system-wide before any rank's counter moves
+    __threadfence_system();
+    named_barrier_sync(1, kEpilogueThreads);
+    const int epi = (warp - 2) * 32 + lane;
+    if (epi < args.push_world) atomicAdd_system(args.push_flag[epi], 1u);
   }
 
   // nobody leaves (and frees its shared memory) while a peer may still be reading it
   __syncwarp();
-  cluster_sync_all();
+  if (S > 1) cluster_sync_all(); else __syncthreads();
   if (warp == 2) {
     if (*reinterpret_cast<volatile int*>(err) != 0) {
       const uint64_t t0 = global_timer_ns();
@@ -547,6 +605,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+  TRACE_END();
 }
 
 // ------------------------------------------------------------------------------------------------

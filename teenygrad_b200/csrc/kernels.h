@@ -66,8 +66,12 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
                            cudaStream_t stream);
 size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
 // One query token per sequence against the first *kv_len_dev (or kv_len if the pointer is null) cache entries.
+// fresh_rows >= 0 is a promise that matters only under programmatic dependent launch: the kernel launched just before
+// this one writes nothing this call reads except q and the last fresh_rows live cache rows, and *kv_len_dev is older
+// still; the kernel then starts streaming the older rows before its predecessor has finished.
 int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
-                          const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream);
+                          const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream,
+                          int fresh_rows = -1);
 // Same as attention_decode_bf16 with the partials in a fixed-size array inside the library image (no caller scratch).
 size_t attention_decode_static_scratch_limit();
 int attention_decode_bf16_static(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,

@@ -366,8 +366,9 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     a.o_sb = static_cast<long long>(S) * Hq * D; a.o_sh = D; a.o_ss = static_cast<long long>(Hq) * D;
     if (decode) {
       a.Sq = 1; a.Skv = c.max_len; a.causal = 0;
+      // the rope kernel just before appends exactly one row per sequence; the length was set a whole step earlier
       TEENY_TRY(attention_decode_bf16(qkv, kc, vc, attn, a, pos0 + 1, len_dev, m->at<void>(m->off.attn_scratch),
-                                      m->off.attn_scratch_bytes, st));
+                                      m->off.attn_scratch_bytes, st, 1));
     } else {
       a.Sq = S; a.Skv = pos0 + S; a.causal = 1;
       TEENY_TRY(attention_prefill_bf16(qkv, kc, vc, attn, nullptr, a, st));

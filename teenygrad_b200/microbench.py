@@ -3,11 +3,13 @@
     python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode]   # CUDA-event timings
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
+    python -m teenygrad_b200.microbench trace [N]                                 # timeline of one graph-replayed decode step
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
 one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
 microseconds, are captured in a CUDA graph over rotating copies of their inputs (larger than L2 together) so neither
 host launch overhead nor a warm L2 enters the number.  ``case`` and ``layers`` exist to be run under ``ncu``.
+``trace`` needs a library built with ``make -C teenygrad_b200/csrc EXTRA=-DTEENY_TRACE`` (per-CTA timer records).
 """
 import sys
 
@@ -162,6 +164,70 @@ def layers(n_layers):
     torch.cuda.synchronize()
 
 
+def trace(n_layers, until_us=600.0):
+    """Prints, for every kernel launch of one graph-replayed decode step (batch 32, cache length ~2050) of an
+    n-layer Qwen3-8B-shaped model: CTAs, first/last CTA resident, first/last CTA released by its dependency wait,
+    first/last CTA finished (where the kernel records it), in microseconds from the start of the step."""
+    import ctypes
+    from collections import defaultdict
+
+    import numpy as np
+
+    from . import qwen3
+    lib = ops.lib
+    if not hasattr(lib, "teeny_trace_count"):
+        raise SystemExit("library was built without -DTEENY_TRACE")
+    lib.teeny_trace_name.restype = ctypes.c_char_p
+    lib.teeny_trace_name.argtypes = [ctypes.c_int]
+    lib.teeny_trace_dump.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint, ctypes.c_int]
+
+    def dump():
+        ev = []
+        for i in range(lib.teeny_trace_count()):
+            name = lib.teeny_trace_name(i).decode().split("/")[-1]
+            buf = np.zeros((1 << 18, 4), dtype=np.uint64)
+            n = lib.teeny_trace_dump(i, buf.ctypes.data, 1 << 18, 1)
+            for r in buf[:n]:
+                ev.append((name, int(r[2]) & 0xFFFFFFFF, int(r[0]), int(r[1]), int(r[3]) >> 32))
+        return ev
+
+    cfg = qwen3.Qwen3Config(n_layers, 4096, 32, 8, 128, 12288, 151936, tied=False)
+    r = qwen3.Qwen3Runner(cfg, max_batch=32, max_len=2304, max_tokens=32 * 2048, max_new_tokens=16)
+    qwen3.load_random_weights(r, 4)
+    r.prefill(torch.randint(0, cfg.vocab, (32, 2048), dtype=torch.int32))
+    for _ in range(4):
+        r.decode_step(graph=True)
+    torch.cuda.synchronize()
+    dump()
+    r.decode_step(graph=True)
+    torch.cuda.synchronize()
+    ev = dump()
+    waits = sorted((e for e in ev if e[2] != 0), key=lambda e: e[2])
+    ends = defaultdict(list)
+    for e in ev:
+        if e[2] == 0:
+            ends[(e[0], e[4])].append(e[3])
+    t0 = waits[0][2]
+    launches = defaultdict(list)  # (file, line, grid) -> list of launches, each a list of records
+    for e in waits:
+        ls = launches[(e[0], e[1], e[4])]
+        if ls and len(ls[-1]) < e[4] and e[2] - ls[-1][0][2] < 300000:
+            ls[-1].append(e)
+        else:
+            ls.append([e])
+    flat = sorted(((k, l) for k, ls in launches.items() for l in ls), key=lambda kl: min(e[3] for e in kl[1]))
+    print(f"{'kernel (file:line of its wait)':34s} {'ctas':>5s} {'in0':>8s} {'inN':>8s} {'go0':>8s} {'goN':>8s} {'end0':>8s} {'endN':>8s}")
+    for (name, line, grid), l in flat:
+        us = lambda t: (t - t0) / 1e3
+        go0 = min(e[3] for e in l)
+        es = sorted(t for t in ends.get((name, grid), []) if go0 <= t < go0 + 300000)[:grid]
+        print(f"{name[:26] + ':' + str(line):34s} {len(l):5d} {us(min(e[2] for e in l)):8.1f} {us(max(e[2] for e in l)):8.1f} "
+              f"{us(go0):8.1f} {us(max(e[3] for e in l)):8.1f} "
+              f"{us(es[0]) if es else float('nan'):8.1f} {us(es[-1]) if es else float('nan'):8.1f}")
+        if us(go0) > until_us:
+            break
+
+
 def main(argv):
     torch.cuda.set_device(0)
     mode = argv[0] if argv else "time"
@@ -173,6 +239,8 @@ def main(argv):
         case(argv[1])
     elif mode == "layers":
         layers(int(argv[1]) if len(argv) > 1 else 6)
+    elif mode == "trace":
+        trace(int(argv[1]) if len(argv) > 1 else 8)
     else:
         raise SystemExit(__doc__)
     print("device error word:", ops.device_error())
