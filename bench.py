@@ -25,6 +25,8 @@ import sys
 import threading
 import time
 
+_JSON_OUT = None  # duplicate of the original stdout, opened in main()
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -176,7 +178,7 @@ def reference_arm(args, cfg_kwargs):
             "config": workload_config(args, args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
 
 
 def workload_config(args, n):
@@ -190,9 +192,13 @@ def workload_config(args, n):
 # ------------------------------------------------------------------------------------------------ GPU arm
 def main():
     args = parse_args()
-    # keep stdout to the one JSON line: NCCL's version banner (NCCL_DEBUG=VERSION) would otherwise land there
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # Keep stdout to the one JSON line: libraries write there at the file-descriptor level (NCCL prints its version
+    # banner to fd 1 at NCCL_DEBUG=VERSION and WARN), so fd 1 is pointed at stderr for the whole run and the line goes
+    # to a private duplicate of the original stdout.
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     cfg_kwargs = dict(num_layers=args.layers, hidden=4096, num_q_heads=32, num_kv_heads=8, head_dim=128,
                       intermediate=12288, vocab=151936, eps=1e-6, rope_theta=1e6, tied=False)
     if args.impl == "reference":
@@ -344,7 +350,7 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         v, desc, threads = cpu_generation_rate(cfg_kwargs, **CPU_SAMPLE)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
