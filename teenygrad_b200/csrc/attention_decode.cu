@@ -35,7 +35,7 @@ __device__ __forceinline__ float ex2(float x) {
 
 // ---- decode kernel: TMA-fed shared-memory ring + mma.sync ----
 // CTA = one (batch, kv head, share of the live keys).  Warp 4 is the producer: for every 64-key tile it requests the
-// K rows and the V rows (two [64 keys][64 d] boxes each, 128-byte swizzle) into a kDecStages-deep ring and the copies
+// K rows and the V rows (two [64 keys][64 d] boxes each, 128-byte swizzle) into a ring of 32 KB stages (three deep with two CTAs per SM, six with one) and the copies
 // signal a `full` mbarrier; nothing in flight costs registers.  Warps 0-3 each own 16 keys of a tile:
 //   S = Q K^T   A = Q from registers (rows = the G query heads of the group, padded to 16), B = K fragments through
 //               ldmatrix (a matrix row is one key's 16 bytes, so the swizzle makes the eight rows conflict-free);
@@ -57,15 +57,20 @@ struct DecodeArgs {
   // the length and every older row were complete before that kernel started, so they may be read ahead of the
   // dependency wait.  < 0: nothing is known, read everything after the wait.
   int fresh_rows;
+  int stages;          // ring depth of this launch
+  unsigned* counters;  // [B * Hkv] arrival counters (zero between calls) for the in-kernel merge, or null
   float scale_log2;
   int* err;
+  DecodeRope rope;  // rope.k_new == nullptr: q is final and the caches already hold the new rows
+  long long kc_sb, kc_sh, kc_ss, vc_sb, vc_sh, vc_ss;  // cache strides for the append
 };
 
 constexpr int kDecTile = 64;                     // keys per ring stage
-constexpr int kDecStages = 3;
+constexpr int kDecStagesShared = 3;  // ring depth when two CTAs share an SM
+constexpr int kDecStagesAlone = 6;   // ring depth when the grid has at most one CTA per SM
 constexpr int kDecBox = kDecTile * 64 * 2;       // 8 KB: [64 keys][64 d]
 constexpr int kDecStageBytes = 4 * kDecBox;      // K (2 boxes) + V (2 boxes) = 32 KB
-constexpr int kDecSmem = kDecStages * kDecStageBytes + 1024 + 64;
+constexpr int dec_smem_bytes(int stages) { return stages * kDecStageBytes + 1024 + 128; }
 constexpr int kDecThreads = 160;                 // 4 consumer warps + 1 producer warp
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -84,17 +89,19 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
   extern __shared__ uint8_t dec_smem_raw[];
   __shared__ float sm_ml[4][8][2];
   __shared__ float sm_o[4][G][kHD];
+  __shared__ __align__(16) bf16 sm_q[4][G][kHD];  // normed, rotated q heads, one copy per consumer warp (fused front end)
   const uint32_t base = (smem_u32(dec_smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = dec_smem_raw + (base - smem_u32(dec_smem_raw));
-  const uint32_t bar0 = base + kDecStages * kDecStageBytes;
+  const int n_stages = a.stages;
+  const uint32_t bar0 = base + n_stages * kDecStageBytes;
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (kDecStages + s); };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (n_stages + s); };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int chunk = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
-    for (int s = 0; s < kDecStages; ++s) {
+    for (int s = 0; s < n_stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 4);
     }
@@ -110,8 +117,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     key_end = min(L, key_begin + span);
     n_tiles = key_begin < L ? (key_end - key_begin + kDecTile - 1) / kDecTile : 0;
   };
-  auto load_tile = [&](int t) {
-    const int st = t % kDecStages;
+  auto load_tile = [&](int t, int st) {
     const uint32_t dst = base + st * kDecStageBytes;
     const int key0 = key_begin + t * kDecTile;
     mbar_expect_tx(full_bar(st), kDecStageBytes);
@@ -121,31 +127,66 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     tma_load_4d(dst + 3 * kDecBox, &tmap_v, full_bar(st), 64, key0, hk, b);
   };
   int pre = 0;  // tiles requested ahead of the wait (producer thread only)
+  int rope_pos = 0;
   if (a.fresh_rows >= 0) {
     plan();
+    if (a.rope.k_new) rope_pos = a.rope.pos_dev ? *a.rope.pos_dev : a.rope.pos;
     if (threadIdx.x == 128) {
       // first ring of tiles that hold none of the rows the previous kernel is still writing
-      while (pre < n_tiles && pre < kDecStages && key_begin + (pre + 1) * kDecTile <= L - a.fresh_rows) {
-        load_tile(pre);
+      while (pre < n_tiles && pre < n_stages && key_begin + (pre + 1) * kDecTile <= L - a.fresh_rows) {
+        load_tile(pre, pre);
         ++pre;
       }
     }
   }
   pdl_wait();  // the cache rows of this step (and, unless declared stable, the live length) come from earlier kernels
-  if (a.fresh_rows < 0) plan();
+  if (a.fresh_rows < 0) {
+    plan();
+    if (a.rope.k_new) rope_pos = a.rope.pos_dev ? *a.rope.pos_dev : a.rope.pos;
+  }
   const int g = lane >> 2, c = lane & 3;
   float acc[16][4];
   float m = -INFINITY, l = 0.0f;
   if (n_tiles == 0) return;  // chunk lies beyond the live length (uniform for the CTA)
 
+  // Fused front end (per-head RMSNorm + RoPE + cache append), one 128-wide head per half-warp.  No CTA-wide barrier:
+  // the producer warp norms / rotates the new key, appends it and the new value to the caches and goes on streaming;
+  // every consumer warp prepares its own copy of the G query heads.
+  const bool fused = a.rope.k_new != nullptr;
+  const int sub = lane & 15, hw = lane >> 4;
+  auto rope_head = [&](const bf16* src, const bf16* w, uint4& raw) {
+    raw = *reinterpret_cast<const uint4*>(src + sub * 8);
+    const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(w + sub * 8));
+    const int tp = rope_pos < a.rope.max_len ? rope_pos : a.rope.max_len - 1;
+    const uint4 craw = __ldg(reinterpret_cast<const uint4*>(a.rope.cos_t + static_cast<size_t>(tp) * kHD + sub * 8));
+    const uint4 sraw = __ldg(reinterpret_cast<const uint4*>(a.rope.sin_t + static_cast<size_t>(tp) * kHD + sub * 8));
+    return head_norm_rope(raw, wraw, craw, sraw, sub, a.rope.eps);
+  };
+
   if (warp == 4) {
     // ---------------- producer ----------------
+    if (fused) {
+      // half-warp 0: key head (normed, rotated); half-warp 1: value head (copied)
+      uint4 raw;
+      const uint4 outv = rope_head((hw == 0 ? a.rope.k_new : a.rope.v_new) + b * a.rope.new_sb + hk * kHD, a.rope.k_w, raw);
+      if (rope_pos >= key_begin && rope_pos < key_end && rope_pos < a.rope.max_len) {
+        if (hw == 0)
+          *reinterpret_cast<uint4*>(a.rope.k_cache + b * a.kc_sb + hk * a.kc_sh + rope_pos * a.kc_ss + sub * 8) = outv;
+        else
+          *reinterpret_cast<uint4*>(a.rope.v_cache + b * a.vc_sb + hk * a.vc_sh + rope_pos * a.vc_ss + sub * 8) = raw;
+      }
+      // the appended rows are read back by this warp's own TMA loads (async proxy): order them behind the stores
+      __threadfence();
+      asm volatile("fence.proxy.async;" ::: "memory");
+      __syncwarp();
+    }
     if (lane == 0) {
+      int st = pre == n_stages ? 0 : pre;
+      uint32_t ph = pre == n_stages ? 1 : 0;
       for (int t = pre; t < n_tiles; ++t) {
-        const int st = t % kDecStages;
-        const uint32_t ph = (t / kDecStages) & 1;
         if (!mbar_wait(empty_bar(st), ph ^ 1, a.err, DEVERR_ATTN_PRODUCER)) break;
-        load_tile(t);
+        load_tile(t, st);
+        if (++st == n_stages) { st = 0; ph ^= 1; }
       }
     }
   } else {
@@ -155,7 +196,17 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     // Q fragments: head hk * G + g; a0 = d 16 ks + 2c.., a2 = d 16 ks + 8 + 2c..; rows >= G are zero
     uint32_t qa[8][2];
     {
-      const bf16* qp = a.q + b * a.q_sb + (hk * G + (g < G ? g : 0)) * a.q_sh;
+      if (fused) {
+#pragma unroll
+        for (int h0 = 0; h0 < G; h0 += 2) {  // two heads per pass (a lone last head is done twice)
+          const int hsel = h0 + hw < G ? h0 + hw : G - 1;
+          uint4 raw;
+          const uint4 outv = rope_head(a.q + b * a.q_sb + (hk * G + hsel) * a.q_sh, a.rope.q_w, raw);
+          *reinterpret_cast<uint4*>(&sm_q[warp][hsel][sub * 8]) = outv;
+        }
+        __syncwarp();
+      }
+      const bf16* qp = fused ? &sm_q[warp][g < G ? g : 0][0] : a.q + b * a.q_sb + (hk * G + (g < G ? g : 0)) * a.q_sh;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t lo = *reinterpret_cast<const uint32_t*>(qp + 16 * ks + 2 * c);
@@ -167,9 +218,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     const int row_k = 16 * warp + (lane & 7);  // ldmatrix row this lane addresses for K: + 8 * n-block
     const int mat = lane >> 3;                 // which of the four 8x8 matrices this lane addresses
     bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int st = t % kDecStages;
-      const uint32_t ph = (t / kDecStages) & 1;
+    int st = 0;
+    uint32_t ph = 0;
+    for (int t = 0; t < n_tiles; ++t, st = (st + 1 == n_stages ? 0 : st + 1), ph ^= (st == 0 ? 1u : 0u)) {
       if (!mbar_wait(full_bar(st), ph, a.err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       const uint32_t kt = base + st * kDecStageBytes, vt = kt + 2 * kDecBox;
       const int kb = key_begin + t * kDecTile + 16 * warp;  // first key of this warp's slice
@@ -290,6 +341,37 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
       a.part_ml[(slot * G + gg) * 2 + 1] = ll;
     }
   }
+  if (gridDim.x > 1 && a.counters) {
+    // The last CTA of this (sequence, kv head) to have stored its partial merges them all: no second kernel.
+    __shared__ unsigned sm_last;
+    __threadfence();
+    __syncthreads();
+    const int chunks = (L + span - 1) / span;  // CTAs of this group that had keys
+    unsigned* ctr = a.counters + static_cast<size_t>(b) * a.Hkv + hk;
+    if (threadIdx.x == 0) {
+      const unsigned old = atomicAdd(ctr, 1u);
+      sm_last = (old == static_cast<unsigned>(chunks - 1)) ? 1u : 0u;
+      if (sm_last) *ctr = 0u;  // every CTA of the group has arrived: re-arm for the next call
+    }
+    __syncthreads();
+    if (sm_last) {
+      __threadfence();
+      const size_t slot0 = (static_cast<size_t>(b) * a.Hkv + hk) * a.max_chunks;
+      for (int idx = threadIdx.x; idx < G * kHD; idx += kDecThreads) {
+        const int gg = idx / kHD, d = idx - gg * kHD;
+        float mm = -INFINITY;
+        for (int ch = 0; ch < chunks; ++ch) mm = fmaxf(mm, __ldcg(a.part_ml + ((slot0 + ch) * G + gg) * 2));
+        float ll = 0.0f, oo = 0.0f;
+        for (int ch = 0; ch < chunks; ++ch) {
+          const size_t sl = (slot0 + ch) * G + gg;
+          const float sc = ex2(__ldcg(a.part_ml + sl * 2) - mm);
+          ll += __ldcg(a.part_ml + sl * 2 + 1) * sc;
+          oo += __ldcg(a.part_o + sl * kHD + d) * sc;
+        }
+        a.o[b * a.o_sb + (hk * G + gg) * a.o_sh + d] = __float2bfloat16_rn(oo / ll);
+      }
+    }
+  }
   TRACE_END();
 }
 
@@ -387,10 +469,10 @@ int attention_decode_prepare() {
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && (done >> dev) & 1ull) return 0;
-  cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecSmem);
+  cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 64) done |= 1ull << dev;
   return 0;
@@ -404,7 +486,7 @@ size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv) {
 
 int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
                           const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream,
-                          int fresh_rows) {
+                          int fresh_rows, const DecodeRope* rope, unsigned* counters) {
   if (!q || !k || !v || !o || !scratch || s.B <= 0 || s.Hq <= 0 || s.Hkv <= 0 || s.Skv <= 0) return TEENY_ERR_BAD_ARG;
   if (s.D != kHD || s.Hq % s.Hkv != 0 || s.Sq != 1) return TEENY_ERR_BAD_ARG;
   if (!kv_len_dev && (kv_len <= 0 || kv_len > s.Skv)) return TEENY_ERR_BAD_ARG;
@@ -446,24 +528,46 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   a.Hkv = s.Hkv; a.G = G; a.max_chunks = max_chunks;
   a.kv_len = kv_len; a.kv_len_dev = kv_len_dev;
   a.fresh_rows = fresh_rows;
+  if (rope) {
+    if (!rope->k_new || !rope->v_new || !rope->k_cache || !rope->v_cache || !rope->q_w || !rope->k_w || !rope->cos_t ||
+        !rope->sin_t || rope->max_len <= 0)
+      return TEENY_ERR_BAD_ARG;
+    if ((rope->new_sb % 8) || ((reinterpret_cast<uintptr_t>(rope->k_new) | reinterpret_cast<uintptr_t>(rope->v_new) |
+                                reinterpret_cast<uintptr_t>(rope->q_w) | reinterpret_cast<uintptr_t>(rope->k_w) |
+                                reinterpret_cast<uintptr_t>(rope->cos_t) | reinterpret_cast<uintptr_t>(rope->sin_t)) & 15))
+      return TEENY_ERR_ALIGNMENT;
+    a.rope = *rope;
+    a.kc_sb = s.k_sb; a.kc_sh = s.k_sh; a.kc_ss = s.k_ss;
+    a.vc_sb = s.v_sb; a.vc_sh = s.v_sh; a.vc_ss = s.v_ss;
+  }
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.err = device_error_word();
-  // Split the sequence only as far as needed to put a CTA in every slot (two per SM): with B * Hkv CTAs already
-  // filling the GPU each one walks its whole sequence and writes the output itself (no partials, no merge kernel).
-  const int bh = s.B * s.Hkv;
-  int n_split = (2 * sm_count() + bh / 2) / bh;
-  if (n_split > max_chunks) n_split = max_chunks;
-  if (n_split < 1) n_split = 1;
+  // Split the sequence only as far as needed to fill the GPU.  With B * Hkv at (or near) two CTAs per SM, each CTA
+  // walks its whole sequence behind a three-stage ring and writes the output itself.  With fewer, the grid is sized
+  // to at most one CTA per SM and each CTA gets the whole shared memory as a six-stage ring (the same bytes in flight
+  // per SM).  Split sequences are merged by the last CTA to finish when the caller provides arrival counters,
+  // otherwise by a second kernel.
+  const int bh = s.B * s.Hkv, sms = sm_count();
+  int n_split = 1;
+  a.stages = kDecStagesShared;
+  if (bh * 4 < sms * 2 * 3) {  // fewer than 3/4 of the two-per-SM slots
+    a.stages = kDecStagesAlone;
+    n_split = sms / bh;
+    if (n_split > max_chunks) n_split = max_chunks;
+    if (n_split < 1) n_split = 1;
+  }
+  a.counters = n_split > 1 ? counters : nullptr;
+  const int smem = dec_smem_bytes(a.stages);
   dim3 grid(n_split, s.Hkv, s.B);
   switch (G) {
-    case 1: launch_kernel(attention_decode_kernel<1>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
-    case 2: launch_kernel(attention_decode_kernel<2>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
-    case 4: launch_kernel(attention_decode_kernel<4>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
-    default: launch_kernel(attention_decode_kernel<8>, grid, dim3(kDecThreads), kDecSmem, stream, 1, mk, mv, a); break;
+    case 1: launch_kernel(attention_decode_kernel<1>, grid, dim3(kDecThreads), smem, stream, 1, mk, mv, a); break;
+    case 2: launch_kernel(attention_decode_kernel<2>, grid, dim3(kDecThreads), smem, stream, 1, mk, mv, a); break;
+    case 4: launch_kernel(attention_decode_kernel<4>, grid, dim3(kDecThreads), smem, stream, 1, mk, mv, a); break;
+    default: launch_kernel(attention_decode_kernel<8>, grid, dim3(kDecThreads), smem, stream, 1, mk, mv, a); break;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (n_split == 1) return 0;
+  if (n_split == 1 || a.counters) return 0;
   launch_kernel(attention_decode_combine_kernel, dim3(s.Hq, s.B), dim3(kHD), 0, stream, 1, a.part_o, a.part_ml, o,
                 s.o_sb, s.o_sh, s.Hkv, G, max_chunks, n_split, kv_len, kv_len_dev);
   return static_cast<int>(cudaGetLastError());

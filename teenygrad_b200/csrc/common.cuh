@@ -70,11 +70,12 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 #ifndef TEENY_TRACE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define TRACE_END() do {} while (0)
+#define TRACE_MARK(id, cond) do {} while (0)
 #else
 // ------------------------------------------------------------------------------------------------
 // Kernel timeline (development builds only: make EXTRA=-DTEENY_TRACE).  Thread 0 of every CTA records the global
 // timer when it reaches pdl_wait() and when the wait returns, and kernels that call TRACE_END() also when the CTA
-// is done; records carry the source line of the call, the SM, the CTA index and the grid size.  Each translation
+// is done (TRACE_MARK(id, cond) adds intermediate records); records carry the source line of the call, the SM, the CTA index and the grid size.  Each translation
 // unit has its own buffer and registers a dump function with the C API (teeny_trace_count / _name / _dump), so
 // `python -m teenygrad_b200.microbench trace` can print when each kernel of a decode step became resident, was
 // released and finished.  The stamps cost an atomic and four stores per CTA: use the output for where time goes,
@@ -103,6 +104,8 @@ __device__ __forceinline__ void pdl_wait_traced(int line) {
 // end-of-CTA record (t0 == 0 marks it)
 #define TRACE_END() \
   do { if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) trace_put(0, global_timer_ns(), __LINE__); } while (0)
+// intermediate record by the one thread for which `cond` holds (t0 = id, 1..15)
+#define TRACE_MARK(id, cond) do { if (cond) trace_put(id, global_timer_ns(), __LINE__); } while (0)
 typedef int (*teeny_trace_dump_fn)(unsigned long long* out, unsigned cap, int reset);
 extern "C" void teeny_trace_register(const char* tu, teeny_trace_dump_fn fn);
 namespace {
@@ -361,6 +364,39 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Per-head RMSNorm followed by rotate-half RoPE for one 128-wide head spread over a half-warp: lane `sub` (0..15)
+// holds elements [8 sub, 8 sub + 8) of the head (raw), of the norm weight (wraw) and of the position's cos / sin rows
+// (craw, sraw); the rotate-half partner elements (d +- 64) live in lane sub ^ 8.  Every lane of the warp must call
+// this (shuffles).  Rounding points follow the traced bf16 graph: the normed head, each product and the sum are
+// bf16 tensors.  Returns the eight rotated elements packed as bf16.
+__device__ __forceinline__ uint4 head_norm_rope(const uint4 raw, const uint4 wraw, const uint4 craw, const uint4 sraw,
+                                                int sub, float eps) {
+  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+  float x[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { x[2 * e] = bf16_lo(rw[e]); x[2 * e + 1] = bf16_hi(rw[e]); }
+  float sq = 0.0f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // stays inside the half-warp
+  const float rr = 1.0f / sqrtf(sq * (1.0f / 128.0f) + eps);
+  const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w},
+                 sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
+  float r[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float wv = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
+    const float cv = (e & 1) ? bf16_hi(cw[e >> 1]) : bf16_lo(cw[e >> 1]);
+    const float sv = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
+    const float n = bf16_round(bf16_round(x[e] * rr) * wv);  // normed head, a bf16 tensor in the traced graph
+    const float partner = __shfl_xor_sync(0xffffffffu, n, 8);
+    const float rot = (sub < 8) ? -partner : partner;         // rotate_half: first half gets -x[d + 64]
+    r[e] = bf16_round(n * cv) + bf16_round(rot * sv);         // rounded to bf16 by the pack below
+  }
+  return make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]), pack_bf16x2(r[6], r[7]));
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

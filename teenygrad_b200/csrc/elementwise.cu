@@ -145,15 +145,21 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
   uint4* rr4 = ADD ? reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr) : nullptr;
   float v[VPT][8];
   float sq = 0.0f;
+  // all loads first: the stores into `res` below would otherwise order every later load of it behind them
+  uint4 xa[VPT], xb[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    xa[i] = idx < nv ? xr[idx] : make_uint4(0u, 0u, 0u, 0u);
+    if (ADD) xb[i] = idx < nv ? rr4[idx] : make_uint4(0u, 0u, 0u, 0u);
+  }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
-      uint4 a = xr[idx];
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      const uint32_t aw[4] = {xa[i].x, xa[i].y, xa[i].z, xa[i].w};
       if (ADD) {
-        const uint4 b = rr4[idx];
-        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        const uint32_t bw[4] = {xb[i].x, xb[i].y, xb[i].z, xb[i].w};
         uint32_t ow[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -240,6 +246,8 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
     if (nv <= 32) threads = 32;
     else if (nv <= 64) threads = 64;
     else if (nv > 4 * 128) threads = 256;
+    // a few rows (decode): the kernel is one chain of latencies, so one vector per thread
+    if (M <= 512 && nv > threads) threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32;
     const int vpt = (nv + threads - 1) / threads;
 #define TEENY_RMS_CASE(V)                                                                                    \
   launch_kernel(rms_norm_bf16_kernel<V, ADD>, dim3(M), dim3(threads), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps)
@@ -292,6 +300,13 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
   uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
   float v[VPT][8];
   float sq = 0.0f;
+  // all loads of the residual first: the stores into it below would otherwise order every later load behind them
+  uint4 hb[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    hb[i] = idx < nv ? rr4[idx] : make_uint4(0u, 0u, 0u, 0u);
+  }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
@@ -303,8 +318,7 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
         sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
         sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
       }
-      const uint4 h4 = rr4[idx];
-      const uint32_t hw[4] = {h4.x, h4.y, h4.z, h4.w};
+      const uint32_t hw[4] = {hb[i].x, hb[i].y, hb[i].z, hb[i].w};
       uint32_t ow[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -445,34 +459,10 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
   bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + sub * 8;
   const uint4 raw = *reinterpret_cast<const uint4*>(src);
   const bool is_v = h >= Hq + Hkv, is_q = h < Hq;
-  const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-  float x[8];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) { x[2 * e] = bf16_lo(rw[e]); x[2 * e + 1] = bf16_hi(rw[e]); }
-  float sq = 0.0f;
-#pragma unroll
-  for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
-#pragma unroll
-  for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // stays inside the half-warp
-  const float rr = 1.0f / sqrtf(sq * (1.0f / D) + eps);
   const int tp = pos < max_len ? pos : max_len - 1;  // table has max_len rows
   const uint4 craw = *reinterpret_cast<const uint4*>(cos_t + static_cast<size_t>(tp) * D + sub * 8);
   const uint4 sraw = *reinterpret_cast<const uint4*>(sin_t + static_cast<size_t>(tp) * D + sub * 8);
-  const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w},
-                 sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
-  float r[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float wv = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
-    const float cv = (e & 1) ? bf16_hi(cw[e >> 1]) : bf16_lo(cw[e >> 1]);
-    const float sv = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
-    const float n = bf16_round(bf16_round(x[e] * rr) * wv);  // normed head, a bf16 tensor in the traced graph
-    const float partner = __shfl_xor_sync(0xffffffffu, n, 8);
-    const float rot = (sub < 8) ? -partner : partner;         // rotate_half: first half gets -x[d + 64]
-    r[e] = bf16_round(n * cv) + bf16_round(rot * sv);         // rounded to bf16 by the pack below
-  }
-  const uint4 outv = make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]),
-                                pack_bf16x2(r[6], r[7]));
+  const uint4 outv = head_norm_rope(raw, wraw, craw, sraw, sub, eps);
   if (!valid) return;
   if (is_q) {
     *reinterpret_cast<uint4*>(src) = outv;

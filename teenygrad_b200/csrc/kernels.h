@@ -65,13 +65,33 @@ struct AttnShape {
 int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, float* lse, const AttnShape& s,
                            cudaStream_t stream);
 size_t attention_decode_scratch_bytes(int B, int Hq, int D, int max_kv);
+// Optional front end of the decode attention kernel: per-head RMSNorm + RoPE of the step's q / k heads and the append
+// of the new k / v rows to the caches, done by the CTA that attends over them instead of by a kernel of its own.
+// q (the attention call's argument) then holds the raw projection and is left untouched.
+struct DecodeRope {
+  const bf16* k_new;   // raw K projection of the new token: k_new + b * new_sb + kv_head * 128; V likewise
+  const bf16* v_new;
+  long long new_sb;
+  bf16* k_cache;       // the caches the call attends over (same strides as in the AttnShape), writable
+  bf16* v_cache;
+  const bf16* q_w;     // [128] head-norm weights
+  const bf16* k_w;
+  const bf16* cos_t;   // [max_len, 128] tables
+  const bf16* sin_t;
+  const int* pos_dev;  // position of the new token (device word), or pos if null; the live length must be pos + 1
+  int pos;
+  int max_len;
+  float eps;
+};
 // One query token per sequence against the first *kv_len_dev (or kv_len if the pointer is null) cache entries.
 // fresh_rows >= 0 is a promise that matters only under programmatic dependent launch: the kernel launched just before
-// this one writes nothing this call reads except q and the last fresh_rows live cache rows, and *kv_len_dev is older
-// still; the kernel then starts streaming the older rows before its predecessor has finished.
+// this one writes nothing this call reads except q (and rope->k_new / v_new) and the last fresh_rows live cache rows,
+// and *kv_len_dev is older still; the kernel then starts streaming the older rows before its predecessor has finished.
+// counters: B * Hkv words, zero before the first call and left zero by every call; with them a split sequence is merged
+// by the last CTA to finish instead of by a second kernel (calls sharing the counters must not overlap).
 int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,
                           const int* kv_len_dev, void* scratch, size_t scratch_bytes, cudaStream_t stream,
-                          int fresh_rows = -1);
+                          int fresh_rows = -1, const DecodeRope* rope = nullptr, unsigned* counters = nullptr);
 // Same as attention_decode_bf16 with the partials in a fixed-size array inside the library image (no caller scratch).
 size_t attention_decode_static_scratch_limit();
 int attention_decode_bf16_static(const bf16* q, const bf16* k, const bf16* v, bf16* o, const AttnShape& s, int kv_len,

@@ -192,9 +192,9 @@ struct LayerWeights {
 
 struct Workspace {
   // offsets into the caller's workspace
-  size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch;
+  size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters;
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
-  size_t gemm_scratch_bytes, attn_scratch_bytes, cache_layer_elems;
+  size_t gemm_scratch_bytes, attn_scratch_bytes, attn_counter_bytes, cache_layer_elems;
 };
 
 }  // namespace teeny
@@ -275,6 +275,8 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.gemm_scratch = take(gs);
   w.attn_scratch_bytes = attention_decode_scratch_bytes(c.max_batch, static_cast<int>(Hq), c.head_dim, c.max_len);
   w.attn_scratch = take(w.attn_scratch_bytes);
+  w.attn_counter_bytes = Bm * static_cast<size_t>(c.num_kv_heads) * 4;  // arrival counters of the split-sequence merge
+  w.attn_counters = take(w.attn_counter_bytes);
   w.cand_val = take(Bm * 4);
   w.cand_idx = take(Bm * 4);
   w.gather_val = take(Bm * 4 * tp);
@@ -356,8 +358,11 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     if (l == 0) TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st));
     else TEENY_TRY(residual_norm(m, delta, h, H, y, w.input_ln, T, st));
     TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
-    TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
-                                   kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
+    // prefill: head norms, RoPE and the cache fill are one pass over the projection; in decode the attention kernel
+    // does them for its own (sequence, kv head) on the way in
+    if (!decode)
+      TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                                     kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
     AttnShape a{};
     a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.scale = scale;
     a.q_sb = static_cast<long long>(S) * qkv_n; a.q_sh = D; a.q_ss = qkv_n;
@@ -366,9 +371,18 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     a.o_sb = static_cast<long long>(S) * Hq * D; a.o_sh = D; a.o_ss = static_cast<long long>(Hq) * D;
     if (decode) {
       a.Sq = 1; a.Skv = c.max_len; a.causal = 0;
-      // the rope kernel just before appends exactly one row per sequence; the length was set a whole step earlier
+      DecodeRope rope{};
+      rope.k_new = qkv + static_cast<size_t>(Hq) * D;
+      rope.v_new = qkv + static_cast<size_t>(Hq + Hkv) * D;
+      rope.new_sb = qkv_n;
+      rope.k_cache = kc; rope.v_cache = vc;
+      rope.q_w = w.q_norm; rope.k_w = w.k_norm;
+      rope.cos_t = m->at<bf16>(m->off.cos); rope.sin_t = m->at<bf16>(m->off.sin);
+      rope.pos_dev = pos_dev; rope.pos = pos0; rope.max_len = c.max_len; rope.eps = c.eps;
+      // The kernel before this one (the QKV projection) writes only the projection buffer, the one new cache row per
+      // sequence is appended by the attention kernel itself, and the length was set a whole step earlier.
       TEENY_TRY(attention_decode_bf16(qkv, kc, vc, attn, a, pos0 + 1, len_dev, m->at<void>(m->off.attn_scratch),
-                                      m->off.attn_scratch_bytes, st, 1));
+                                      m->off.attn_scratch_bytes, st, 1, &rope, m->at<unsigned>(m->off.attn_counters)));
     } else {
       a.Sq = S; a.Skv = pos0 + S; a.causal = 1;
       TEENY_TRY(attention_prefill_bf16(qkv, kc, vc, attn, nullptr, a, st));
@@ -491,6 +505,7 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   // split-K counters must start at zero; generation state too
   cudaError_t e = cudaMemsetAsync(m->ws + w.gemm_scratch, 0, w.gemm_scratch_bytes, st);
   if (e == cudaSuccess) e = cudaMemsetAsync(m->ws + w.state, 0, 16, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(m->ws + w.attn_counters, 0, w.attn_counter_bytes, st);
   if (e != cudaSuccess) {
     delete m;
     return static_cast<int>(e);

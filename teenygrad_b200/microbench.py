@@ -3,7 +3,7 @@
     python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode]   # CUDA-event timings
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
-    python -m teenygrad_b200.microbench trace [N]                                 # timeline of one graph-replayed decode step
+    python -m teenygrad_b200.microbench trace [N [first [count]]]                 # timeline of one graph-replayed decode step
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
 one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
@@ -164,10 +164,12 @@ def layers(n_layers):
     torch.cuda.synchronize()
 
 
-def trace(n_layers, until_us=600.0):
+def trace(n_layers, first=0, count=48):
     """Prints, for every kernel launch of one graph-replayed decode step (batch 32, cache length ~2050) of an
     n-layer Qwen3-8B-shaped model: CTAs, first/last CTA resident, first/last CTA released by its dependency wait,
-    first/last CTA finished (where the kernel records it), in microseconds from the start of the step."""
+    first/last CTA finished (where the kernel records it), in microseconds from the start of the step.  Prints
+    ``count`` launches starting at launch number ``first`` (under tensor parallelism the first layer absorbs the
+    ranks' start skew, so look further in)."""
     import ctypes
     from collections import defaultdict
 
@@ -191,10 +193,20 @@ def trace(n_layers, until_us=600.0):
                 ev.append((name, int(r[2]) & 0xFFFFFFFF, int(r[0]), int(r[1]), int(r[3]) >> 32))
         return ev
 
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    comm = None
+    if world > 1:  # tensor parallel: launched by torch.distributed.run, rank 0 prints its own timeline
+        import torch.distributed as dist
+
+        from . import tp
+        dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+        comm = tp.init_comm(rank, world)
     cfg = qwen3.Qwen3Config(n_layers, 4096, 32, 8, 128, 12288, 151936, tied=False)
-    r = qwen3.Qwen3Runner(cfg, max_batch=32, max_len=2304, max_tokens=32 * 2048, max_new_tokens=16)
+    r = qwen3.Qwen3Runner(cfg, max_batch=32, max_len=2304, max_tokens=32 * 2048, max_new_tokens=16,
+                          tp_rank=rank, tp_size=world, comm=comm)
     qwen3.load_random_weights(r, 4)
-    r.prefill(torch.randint(0, cfg.vocab, (32, 2048), dtype=torch.int32))
+    r.prefill(torch.randint(0, cfg.vocab, (32, 2048), dtype=torch.int32, generator=torch.Generator().manual_seed(5)))
     for _ in range(4):
         r.decode_step(graph=True)
     torch.cuda.synchronize()
@@ -202,11 +214,17 @@ def trace(n_layers, until_us=600.0):
     r.decode_step(graph=True)
     torch.cuda.synchronize()
     ev = dump()
-    waits = sorted((e for e in ev if e[2] != 0), key=lambda e: e[2])
-    ends = defaultdict(list)
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        return
+    waits = sorted((e for e in ev if e[2] > 15), key=lambda e: e[2])
+    ends, marks = defaultdict(list), defaultdict(list)
     for e in ev:
         if e[2] == 0:
             ends[(e[0], e[4])].append(e[3])
+        elif e[2] <= 15:
+            marks[(e[0], e[4], e[2])].append(e[3])
     t0 = waits[0][2]
     launches = defaultdict(list)  # (file, line, grid) -> list of launches, each a list of records
     for e in waits:
@@ -217,19 +235,23 @@ def trace(n_layers, until_us=600.0):
             ls.append([e])
     flat = sorted(((k, l) for k, ls in launches.items() for l in ls), key=lambda kl: min(e[3] for e in kl[1]))
     print(f"{'kernel (file:line of its wait)':34s} {'ctas':>5s} {'in0':>8s} {'inN':>8s} {'go0':>8s} {'goN':>8s} {'end0':>8s} {'endN':>8s}")
-    for (name, line, grid), l in flat:
+    for (name, line, grid), l in flat[first:first + count]:
         us = lambda t: (t - t0) / 1e3
         go0 = min(e[3] for e in l)
         es = sorted(t for t in ends.get((name, grid), []) if go0 <= t < go0 + 300000)[:grid]
         print(f"{name[:26] + ':' + str(line):34s} {len(l):5d} {us(min(e[2] for e in l)):8.1f} {us(max(e[2] for e in l)):8.1f} "
               f"{us(go0):8.1f} {us(max(e[3] for e in l)):8.1f} "
-              f"{us(es[0]) if es else float('nan'):8.1f} {us(es[-1]) if es else float('nan'):8.1f}")
-        if us(go0) > until_us:
-            break
+              f"{us(es[0]) if es else float('nan'):8.1f} {us(es[-1]) if es else float('nan'):8.1f}", end="")
+        for mid in range(1, 16):  # intermediate marks: median over the launch's CTAs
+            ms = sorted(t for t in marks.get((name, grid, mid), []) if go0 <= t < go0 + 300000)[:grid]
+            if ms:
+                print(f"  m{mid}={us(ms[len(ms) // 2]):.1f}", end="")
+        print()
 
 
 def main(argv):
-    torch.cuda.set_device(0)
+    import os
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     mode = argv[0] if argv else "time"
     if mode == "time":
         what = argv[1:] or ["gemm", "skinny", "prefill", "decode"]
@@ -240,7 +262,7 @@ def main(argv):
     elif mode == "layers":
         layers(int(argv[1]) if len(argv) > 1 else 6)
     elif mode == "trace":
-        trace(int(argv[1]) if len(argv) > 1 else 8)
+        trace(*(int(v) for v in argv[1:4])) if len(argv) > 1 else trace(8)
     else:
         raise SystemExit(__doc__)
     print("device error word:", ops.device_error())
