@@ -262,12 +262,19 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
   return static_cast<int>(cudaGetLastError());
 }
 
-// ---- tensor-parallel row-parallel epilogue: wait for every rank's pushed partial rows, sum, add, normalise ----
-// One CTA per token row (decode batches: a few dozen rows).  recv holds `world` f32 partial copies of the
-// projection, slot_elems apart; flag counts the CTAs of all ranks that have finished pushing.
+// ---- tensor-parallel row-parallel epilogue: take every rank's pushed partial rows as they arrive, sum, add, normalise ----
+// One CTA per token row (decode batches: a few dozen rows).  recv holds `world` copies of the projection as
+// {f32 value, stamp} pairs, slot_elems elements apart; an element has arrived when its stamp equals this round's.
+// A 16-byte load holds two elements and may tear between them, so each carries its own stamp.
+__device__ __forceinline__ uint4 ld_volatile_u4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 template <int VPT>
-__global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_t slot_elems, int world,
-                                           unsigned* flag, unsigned* done, unsigned expected,
+__global__ void gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world,
+                                           const unsigned* __restrict__ epoch, unsigned round,
                                            bf16* __restrict__ res, long long ldr, bf16* __restrict__ y, long long ldy,
                                            const bf16* __restrict__ w, int N, float eps, int* err) {
   const int nv = N >> 3;
@@ -281,21 +288,7 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
   pdl_wait();
   pdl_trigger();
   __shared__ float red[32];
-  if (threadIdx.x == 0) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-      unsigned v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-      if (v >= expected) break;
-      if ((it & 0x3f) == 0x3f) {
-        if (*reinterpret_cast<volatile int*>(err) != 0) break;
-        const uint64_t now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); break; }
-      }
-    }
-  }
-  __syncthreads();
+  const unsigned stamp = __ldcg(epoch) * 1024u + round + 1u;
   const int row = blockIdx.x;
   uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
   float v[VPT][8];
@@ -307,16 +300,36 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
     const int idx = threadIdx.x + i * blockDim.x;
     hb[i] = idx < nv ? rr4[idx] : make_uint4(0u, 0u, 0u, 0u);
   }
+  uint64_t t0 = 0;
+  bool live = true;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int p = 0; p < world; ++p) {  // rank order: every rank adds in the same order -> identical results
-        const float4* src = reinterpret_cast<const float4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 2 * idx;
-        const float4 a = __ldcg(src), b = __ldcg(src + 1);  // L2: the lines were written by peers, never cache in L1
-        sum[0] += a.x; sum[1] += a.y; sum[2] += a.z; sum[3] += a.w;
-        sum[4] += b.x; sum[5] += b.y; sum[6] += b.z; sum[7] += b.w;
+        // eight elements = four 16-byte {v, stamp, v, stamp} lines
+        const uint4* src = reinterpret_cast<const uint4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 4 * idx;
+        uint4 q[4];
+        for (uint32_t it = 0;; ++it) {
+          bool all = true;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            q[k] = ld_volatile_u4(src + k);
+            all = all && (q[k].y == stamp) && (q[k].w == stamp);
+          }
+          if (all || !live) break;
+          if ((it & 0x3f) == 0x3f) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); live = false; }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          sum[2 * k] += __uint_as_float(q[k].x);
+          sum[2 * k + 1] += __uint_as_float(q[k].z);
+        }
       }
       const uint32_t hw[4] = {hb[i].x, hb[i].y, hb[i].z, hb[i].w};
       uint32_t ow[4];
@@ -346,15 +359,6 @@ __global__ void gather_add_rms_norm_kernel(const float* __restrict__ recv, size_
       for (int e = 0; e < 4; ++e)
         ow[e] = pack_bf16x2(bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]), bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]));
       yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-    }
-  }
-  // the last CTA to have consumed its row re-arms the counter for the round after next
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(done, 1u) == gridDim.x - 1) {
-      *reinterpret_cast<volatile unsigned*>(done) = 0u;
-      atomicExch_system(flag, 0u);
     }
   }
 }
@@ -579,17 +583,22 @@ int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ld
                       const bf16* w, int M, int N, float eps, cudaStream_t st) {
   return launch_rms_bf16<true>(x, ldx, residual, ldr, y, ldy, w, nullptr, M, N, eps, st);
 }
-int gather_add_rms_norm_bf16(const float* recv, size_t slot_elems, int world, unsigned* flag, unsigned* done,
-                             unsigned expected, bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w,
-                             int M, int N, float eps, cudaStream_t st) {
-  if (!recv || !flag || !done || !residual || !y || !w || world < 2 || M <= 0 || N <= 0) return TEENY_ERR_BAD_ARG;
-  if (N % 8 || ldr % 8 || ldy % 8 || N > 8 * 4 * 256) return TEENY_ERR_BAD_ARG;
-  if (!aligned16(recv) || !aligned16(residual) || !aligned16(y) || !aligned16(w) || (slot_elems % 4)) return TEENY_ERR_ALIGNMENT;
-  const int nv = N / 8, threads = 256, vpt = (nv + threads - 1) / threads;
+int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
+                             bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,
+                             float eps, cudaStream_t st) {
+  if (!recv || !epoch || !residual || !y || !w || world < 2 || M <= 0 || N <= 0 || round >= 1023) return TEENY_ERR_BAD_ARG;
+  if (N % 8 || ldr % 8 || ldy % 8 || N > 8 * 4 * 512) return TEENY_ERR_BAD_ARG;
+  if (!aligned16(recv) || !aligned16(residual) || !aligned16(y) || !aligned16(w) || (slot_elems % 2)) return TEENY_ERR_ALIGNMENT;
+  const int nv = N / 8;
+  const int threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32, vpt = (nv + threads - 1) / threads;
   int* err = device_error_word();
-  if (vpt <= 1) launch_kernel(gather_add_rms_norm_kernel<1>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
-  else if (vpt <= 2) launch_kernel(gather_add_rms_norm_kernel<2>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
-  else launch_kernel(gather_add_rms_norm_kernel<4>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, flag, done, expected, residual, ldr, y, ldy, w, N, eps, err);
+#define TEENY_GATHER_CASE(V)                                                                                       \
+  launch_kernel(gather_add_rms_norm_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, epoch, round, \
+                residual, ldr, y, ldy, w, N, eps, err)
+  if (vpt <= 1) TEENY_GATHER_CASE(1);
+  else if (vpt <= 2) TEENY_GATHER_CASE(2);
+  else TEENY_GATHER_CASE(4);
+#undef TEENY_GATHER_CASE
   return static_cast<int>(cudaGetLastError());
 }
 int silu_f32(const float* x, float* y, long long n, cudaStream_t st) { return launch_ew_f32<OpSilu, false>(x, nullptr, y, n, st); }

@@ -49,8 +49,9 @@ struct GemmArgs {
   int swiglu;             // W rows interleave 64 gate / 64 up channels; Y[M, N/2] = silu(gate) * up
   // Tensor-parallel push (skinny kernel only): instead of Y, the f32 row sums go to slot `rank` of every rank's
   // receive buffer (peer-mapped memory, [M][N] f32 each) and each CTA then bumps every rank's arrival counter.
-  float* const* push_recv;    // device array [push_world]: where this rank writes inside rank p's buffer (or null)
-  unsigned* const* push_flag; // device array [push_world]: rank p's arrival counter
+  uint2* const* push_recv;    // device array [push_world]: where this rank writes inside rank p's buffer (or null)
+  const unsigned* push_epoch; // stamp of the pushed {value, stamp} pairs = *push_epoch * 1024 + push_round + 1
+  unsigned push_round;
   int push_world;
   int* err;
 };
@@ -467,6 +468,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const bool direct = (S == 1) && !args.swiglu;
       const int n = tile * kBM + row;
       const float bias = (direct && args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
+      const unsigned stamp = (direct && args.push_recv) ? __ldcg(args.push_epoch) * 1024u + args.push_round + 1u : 0u;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
@@ -482,7 +484,8 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const float v = __uint_as_float(r[e]) + bias;
                 if (args.push_recv) {
                   const size_t off = static_cast<size_t>(c) * args.N + n;
-                  for (int p = 0; p < args.push_world; ++p) args.push_recv[p][off] = v;  // NVLink stores
+                  for (int p = 0; p < args.push_world; ++p)  // NVLink stores
+                    args.push_recv[p][off] = make_uint2(__float_as_uint(v), stamp);
                 } else {
                   args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(v);
                 }
@@ -547,6 +550,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     } else {
       const bool vec_ok = args.push_recv ? (args.N % 4 == 0)
                                          : ((args.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.y) & 7) == 0));
+      const unsigned stamp = args.push_recv ? __ldcg(args.push_epoch) * 1024u + args.push_round + 1u : 0u;
       for (int u = epi; u < ncols * 32; u += kEpilogueThreads) {
         const int c = c_begin + (u >> 5), j = u & 31;
         const uint32_t addr = part_base + static_cast<uint32_t>((c * kBM + 4 * j) * 4);
@@ -567,12 +571,14 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           }
           if (args.push_recv) {
             const size_t off = static_cast<size_t>(c) * args.N + n;
-            for (int p = 0; p < args.push_world; ++p) {  // NVLink stores
+            for (int p = 0; p < args.push_world; ++p) {  // NVLink stores: two 16-byte {v, stamp, v, stamp} lines
               if (vec_ok) {
-                *reinterpret_cast<float4*>(args.push_recv[p] + off) = make_float4(o[0], o[1], o[2], o[3]);
+                uint4* dst = reinterpret_cast<uint4*>(args.push_recv[p] + off);
+                dst[0] = make_uint4(__float_as_uint(o[0]), stamp, __float_as_uint(o[1]), stamp);
+                dst[1] = make_uint4(__float_as_uint(o[2]), stamp, __float_as_uint(o[3]), stamp);
               } else {
                 for (int e = 0; e < 4; ++e)
-                  if (n + e < args.N) args.push_recv[p][off + e] = o[e];
+                  if (n + e < args.N) args.push_recv[p][off + e] = make_uint2(__float_as_uint(o[e]), stamp);
               }
             }
           } else {
@@ -589,18 +595,6 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   }
   TRACE_MARK(3, threadIdx.x == 64);
-  if (warp >= 2 && args.push_recv) {
-    // Every store of this CTA must be visible system-wide before any rank's counter moves.  The CTA barrier orders
-    // the other threads' stores before thread 64's release, and a release at system scope is cumulative over them,
-    // so one thread fences (a system-scope fence by all 128 threads was measured at 7 us per kernel).
-    named_barrier_sync(1, kEpilogueThreads);
-    if (threadIdx.x == 64) {
-      asm volatile("fence.acq_rel.sys;" ::: "memory");
-      TRACE_MARK(4, true);
-      for (int p = 0; p < args.push_world; ++p)
-        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(args.push_flag[p]), "r"(1u) : "memory");
-    }
-  }
 
   // nobody leaves (and frees its shared memory) while a peer may still be reading it
   __syncwarp();
@@ -703,9 +697,11 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   a.group = 8;
   a.swiglu = swiglu ? 1 : 0;
   if (push) {
-    if (swiglu || w_is_kn || M > kSwapMaxM || !push->recv || !push->flag || push->world < 2) return TEENY_ERR_BAD_ARG;
+    if (swiglu || w_is_kn || M > kSwapMaxM || !push->recv || !push->epoch || push->world < 2 || push->round >= 1023)
+      return TEENY_ERR_BAD_ARG;
     a.push_recv = push->recv;
-    a.push_flag = push->flag;
+    a.push_epoch = push->epoch;
+    a.push_round = push->round;
     a.push_world = push->world;
   }
   a.err = device_error_word();
@@ -757,7 +753,6 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
         --split;  // too thin, or a rank would be left without k-blocks
       if (split < 1) split = 1;
       a.kb_per_split = ceil_div(a.k_blocks, split);
-      if (push) *push->ctas_out = tiles * split;
       switch (bn) {
         case 16: return launch_skinny<16>(tmw, tmx, a, split, tiles, stream);
         case 32: return launch_skinny<32>(tmw, tmx, a, split, tiles, stream);

@@ -23,23 +23,25 @@ int attention_decode_prepare();
 // swiglu: W is [N, K] with rows interleaved in blocks of 64 gate channels / 64 up channels (N = 2 * channels) and
 // Y is [M, N / 2] = silu(gate) * up, rounded as the unfused bf16 graph rounds (both projections, silu, product).
 // Tensor-parallel push mode of the decode GEMM (M <= 128): y is not written; every rank receives this rank's f32
-// result in its receive buffer and has its arrival counter bumped once per CTA (*ctas_out reports how many).
+// result in its receive buffer as {value, stamp} pairs (8 bytes per element, element (row, col) at row * N + col),
+// stamp = *epoch * 1024 + round + 1.  The receiver recognises arrived data by the stamp, so the sender needs no
+// fence, flag or counter; a buffer must not be written again with the same stamp.
 struct GemmPush {
-  float* const* recv;      // device array [world]
-  unsigned* const* flag;   // device array [world]
+  uint2* const* recv;     // device array [world]: this rank's slot inside every rank's buffer
   int world;
-  int* ctas_out;           // host: CTAs that will signal
+  const unsigned* epoch;  // device word, constant while the kernel runs
+  unsigned round;         // < 1023
 };
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
               int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false,
               const GemmPush* push = nullptr);
-// Row-parallel epilogue of tensor parallelism: waits until `expected` CTAs (of all ranks) have pushed, sums the
-// `world` f32 partial rows [M][N] (stride slot_elems between ranks), rounds the sum to bf16 (the all-reduced
-// projection), adds it into the bf16 residual and RMS-normalises it: residual <- residual + sum; y <- norm(residual).
-// The last CTA to finish re-arms the counter.  Waits are bounded (device error word).
-int gather_add_rms_norm_bf16(const float* recv, size_t slot_elems, int world, unsigned* flag, unsigned* done,
-                             unsigned expected, bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w,
-                             int M, int N, float eps, cudaStream_t st);
+// Row-parallel epilogue of tensor parallelism: sums the `world` f32 partial rows [M][N] that the ranks' GEMMs pushed
+// as {value, stamp} pairs (slot_elems elements between ranks), waiting for each element until it carries the stamp
+// *epoch * 1024 + round + 1; rounds the sum to bf16 (the all-reduced projection), adds it into the bf16 residual and
+// RMS-normalises it: residual <- residual + sum; y <- norm(residual).  Waits are bounded (device error word).
+int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
+                             bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,
+                             float eps, cudaStream_t st);
 // Large-M path on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); same contract as gemm_bf16 without the options.
 int gemm_bf16_2cta_prepare();
 int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* bias, bf16* y, int ldy, int M, int N,

@@ -74,15 +74,15 @@ struct TpContext {
   int rank = 0, world = 1;
   bool peer_ok = false;
   size_t rows = 0, cols = 0, slot_elems = 0, data_bytes = 0;
-  uint8_t* local = nullptr;       // [2 parities][world][rows][cols] f32, then 2 arrival counters, 2 done counters
-  void* peer[8] = {};             // the same buffer of every rank (own entry = local)
-  float** recv_tab = nullptr;     // device [2][world]: where this rank writes inside rank q's buffer
-  unsigned** flag_tab = nullptr;  // device [2][world]: rank q's arrival counter
-  float* local_recv(int parity) const {
-    return reinterpret_cast<float*>(local) + static_cast<size_t>(parity) * world * slot_elems;
+  uint8_t* local = nullptr;    // [2 parities][world][rows][cols] {f32 value, u32 stamp} pairs, then the epoch word
+  void* peer[8] = {};          // the same buffer of every rank (own entry = local)
+  uint2** recv_tab = nullptr;  // device [2][world]: where this rank writes inside rank q's buffer
+  const uint2* local_recv(int parity) const {
+    return reinterpret_cast<const uint2*>(local) + static_cast<size_t>(parity) * world * slot_elems;
   }
-  unsigned* flag(int parity) const { return reinterpret_cast<unsigned*>(local + data_bytes) + parity; }
-  unsigned* done(int parity) const { return reinterpret_cast<unsigned*>(local + data_bytes) + 2 + parity; }
+  // Counts the decode steps run over this context (by any runner): part of every stamp, so a buffer never sees the
+  // same stamp twice.  Local to the rank; the ranks step it in lockstep.
+  unsigned* epoch() const { return reinterpret_cast<unsigned*>(local + data_bytes); }
 };
 
 // Collective over the communicator: allocate the receive buffer, exchange IPC handles, map the peers.  Leaves
@@ -90,7 +90,7 @@ struct TpContext {
 int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   if (c->peer_ok || c->world < 2 || c->world > 8) return 0;
   c->rows = rows; c->cols = cols; c->slot_elems = rows * cols;
-  c->data_bytes = 2 * static_cast<size_t>(c->world) * c->slot_elems * sizeof(float);
+  c->data_bytes = 2 * static_cast<size_t>(c->world) * c->slot_elems * sizeof(uint2);
   int ok = 1;
   cudaIpcMemHandle_t mine;
   uint8_t* xbuf = nullptr;
@@ -137,25 +137,20 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   for (int q = 0; q < c->world; ++q) ok &= host[q];
   cudaFree(xbuf);
   if (!ok) return 0;  // stay on the NCCL path
-  std::vector<float*> rt(2 * c->world);
-  std::vector<unsigned*> ft(2 * c->world);
+  std::vector<uint2*> rt(2 * c->world);
   for (int par = 0; par < 2; ++par)
-    for (int q = 0; q < c->world; ++q) {
+    for (int q = 0; q < c->world; ++q)
       rt[par * c->world + q] =
-          reinterpret_cast<float*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
-      ft[par * c->world + q] = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(c->peer[q]) + c->data_bytes) + par;
-    }
-  if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(float*)) != cudaSuccess ||
-      cudaMalloc(&c->flag_tab, ft.size() * sizeof(unsigned*)) != cudaSuccess)
-    return 0;
-  cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(float*), cudaMemcpyHostToDevice);
-  cudaMemcpy(c->flag_tab, ft.data(), ft.size() * sizeof(unsigned*), cudaMemcpyHostToDevice);
+          reinterpret_cast<uint2*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
+  if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(uint2*)) != cudaSuccess) return 0;
+  cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(uint2*), cudaMemcpyHostToDevice);
   c->peer_ok = true;
   return 0;
 }
 
 __global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __restrict__ cur_ids,
-                                   int* __restrict__ history, int* __restrict__ state, int B, int max_steps) {
+                                   int* __restrict__ history, int* __restrict__ state, int B, int max_steps,
+                                   unsigned* __restrict__ tp_epoch) {
   pdl_wait();
   // state[0] = position of the next token to append, state[1] = live KV length during the step (= state[0] + 1),
   // state[2] = number of generated tokens so far
@@ -171,6 +166,7 @@ __global__ void finish_step_kernel(const int* __restrict__ next_ids, int* __rest
     state[0] += 1;
     state[1] += 1;
     state[2] = step + 1;
+    if (tp_epoch) *tp_epoch += 1u;  // the pushes of the next step carry new stamps
   }
 }
 
@@ -214,7 +210,7 @@ struct teeny_qwen3 {
   int push_round = 0;           // parity of the next peer push within a decode step
   bool pending_gather = false;  // a pushed projection waits to be summed by the next norm
   int pending_parity = 0;
-  unsigned pending_expected = 0;
+  unsigned pending_round = 0;
   cudaGraphExec_t graph_exec = nullptr;
   cudaStream_t capture_stream = nullptr;
   int graph_batch = 0;
@@ -311,12 +307,11 @@ int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const bf16* w, bf16* de
   TpContext* tp = m->tp;
   if (decode && tp && tp->peer_ok && T <= static_cast<int>(tp->rows) && N == static_cast<int>(tp->cols)) {
     const int parity = m->push_round & 1;
-    int ctas = 0;
-    GemmPush push{tp->recv_tab + parity * tp->world, tp->flag_tab + parity * tp->world, tp->world, &ctas};
+    GemmPush push{tp->recv_tab + parity * tp->world, tp->world, tp->epoch(), static_cast<unsigned>(m->push_round)};
     TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st, false, &push));
     m->pending_gather = true;
     m->pending_parity = parity;
-    m->pending_expected = static_cast<unsigned>(ctas) * tp->world;
+    m->pending_round = static_cast<unsigned>(m->push_round);
     ++m->push_round;
     return 0;
   }
@@ -330,9 +325,8 @@ int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, c
   if (m->pending_gather) {
     m->pending_gather = false;
     TpContext* tp = m->tp;
-    return gather_add_rms_norm_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world,
-                                    tp->flag(m->pending_parity), tp->done(m->pending_parity), m->pending_expected, h, ld,
-                                    y, c.hidden, w, M, c.hidden, c.eps, st);
+    return gather_add_rms_norm_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world, tp->epoch(),
+                                    m->pending_round, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
   }
   return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
 }
@@ -445,8 +439,9 @@ int decode_body(teeny_qwen3* m, int B, cudaStream_t st) {
   TEENY_TRY(embedding_bf16(m->at<int>(m->off.cur_ids), m->embed, m->at<bf16>(m->off.h), B, c.hidden, c.vocab, st));
   TEENY_TRY(run_layers(m, B, 1, 0, state + 0, state + 1, true, st));
   TEENY_TRY(run_head(m, B, 1, st));
+  unsigned* tp_epoch = (m->tp && m->tp->peer_ok) ? m->tp->epoch() : nullptr;
   launch_kernel(finish_step_kernel, dim3(1), dim3(1024), 0, st, 1, m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
-                                         m->at<int>(m->off.history), state, B, c.max_new_tokens);
+                                         m->at<int>(m->off.history), state, B, c.max_new_tokens, tp_epoch);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -495,7 +490,8 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   }
   // decode-time peer buffers (collective: every rank creates its runner at the same point)
   const char* peer_env = getenv("TEENY_TP_PEER");  // "0" keeps decode on NCCL all-reduce (for A/B measurements)
-  if (m->tp && cfg->tp_size > 1 && cfg->max_batch <= 128 && !(peer_env && peer_env[0] == '0')) {
+  // (two pushes per layer, each with its own round number below 1023)
+  if (m->tp && cfg->tp_size > 1 && cfg->max_batch <= 128 && 2 * cfg->num_layers < 1023 && !(peer_env && peer_env[0] == '0')) {
     const int trc = tp_enable_peer(m->tp, cfg->max_batch, cfg->hidden, reinterpret_cast<cudaStream_t>(stream));
     if (trc != 0) {
       delete m;
@@ -578,7 +574,8 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
   // generation state: next position S, live length during the next step S + 1, no tokens recorded yet
   launch_kernel(set_state_kernel, dim3(1), dim3(1), 0, st, 1, state, S - 1, S, 0);
   launch_kernel(finish_step_kernel, dim3(1), dim3(1024), 0, st, 1, m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
-                                         m->at<int>(m->off.history), state, B, c.max_new_tokens);
+                                         m->at<int>(m->off.history), state, B, c.max_new_tokens,
+                                         static_cast<unsigned*>(nullptr));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -669,7 +666,6 @@ int teeny_tp_destroy(void* ctx) {
     if (c->peer_ok && q != c->rank && c->peer[q]) cudaIpcCloseMemHandle(c->peer[q]);
   if (c->local) cudaFree(c->local);
   if (c->recv_tab) cudaFree(c->recv_tab);
-  if (c->flag_tab) cudaFree(c->flag_tab);
   const bool ok = g_nccl.CommDestroy(c->comm) == ncclSuccess;
   delete c;
   return ok ? 0 : TEENY_ERR_NCCL;
