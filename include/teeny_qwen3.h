@@ -81,7 +81,8 @@ void* teeny_qwen3_buffer(teeny_qwen3* model, int which);
 /* Tensor-parallel plumbing over NCCL (loaded at run time; the process's already-loaded libnccl is reused).
  * Rank 0 calls teeny_tp_unique_id and ships the 128 bytes to the other ranks by any host channel.  teeny_tp_init
  * allocates the small host-side context; teeny_qwen3_create may add a peer-mapped device buffer of
- * 2 * tp_size * max_batch * hidden floats to it (the one device allocation this library makes, at set-up). */
+ * 2 * tp_size * max_batch * hidden (value, stamp) pairs to it (the one device allocation this library makes, at
+ * set-up). */
 int teeny_tp_unique_id(void* out128);
 int teeny_tp_init(const void* id128, int rank, int world, void** comm_out);
 int teeny_tp_destroy(void* comm);
