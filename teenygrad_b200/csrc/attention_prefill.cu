@@ -119,11 +119,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       constexpr uint32_t idesc_qk = make_idesc_bf16(kQT, kKT, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(kQT, kHD, false, true);
       bool ok = mbar_wait(bar(Q_FULL), 0, err, DEVERR_ATTN_MMA);
+      // development builds: cycles this thread spends waiting for K, a free S buffer, V and P (summed over the tiles)
+      TRACE_ONLY(long long w_k = 0, w_se = 0, w_v = 0, w_p = 0, c0; const long long c_begin = clock64();)
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        TRACE_ONLY(c0 = clock64();)
         if (!mbar_wait(bar(K_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        TRACE_ONLY(w_k += clock64() - c0; c0 = clock64();)
         if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_MMA)) return false;
+        TRACE_ONLY(w_se += clock64() - c0;)
         tc_fence_after();
         const uint32_t qb = base + kSmemQ, kb = base + kSmemK + st * kTileBytes;
 #pragma unroll
@@ -139,8 +144,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       auto issue_pv = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        TRACE_ONLY(c0 = clock64();)
         if (!mbar_wait(bar(V_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
         if (!mbar_wait(bar(P_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        TRACE_ONLY(w_p += clock64() - c0;)
         tc_fence_after();
         const uint32_t pb = base + kSmemP + st * kTileBytes, vb = base + kSmemV + st * kTileBytes;
 #pragma unroll
@@ -160,6 +168,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (j + 1 < n_tiles) ok = issue_qk(j + 1);
         if (ok) ok = issue_pv(j);
       }
+      TRACE_VALUE(0, true, n_tiles);
+      TRACE_VALUE(1, true, clock64() - c_begin);
+      TRACE_VALUE(2, true, w_k);
+      TRACE_VALUE(3, true, w_se);
+      TRACE_VALUE(4, true, w_v);
+      TRACE_VALUE(5, true, w_p);
     }
   } else if (warp >= 4) {
     const int quarter = warp & 3;
@@ -168,10 +182,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
+    // development builds: cycles of thread 128 per phase (wait for S, TMEM load, maximum, wait for the P buffer, exp + store)
+    TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, c0; const long long c_begin = clock64();)
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
+      TRACE_ONLY(c0 = clock64();)
       if (!mbar_wait(bar(S_FULL + st), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+      TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
       tc_fence_after();
       float s[128];
 #pragma unroll
@@ -180,10 +198,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tmem_ld_32x32(tmem_s0 + lane_addr + st * 128 + c * 32, t);
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]) * args.scale_log2;
+        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);  // raw scores: the scale is folded into the exponent
       }
       tc_fence_before();
       mbar_arrive(bar(S_EMPTY + st));  // S is in registers: the buffer can take QK^T of tile j+2
+      TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
 
       const int k0 = j * kKT;
       const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
@@ -193,9 +212,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int e = 0; e < 128; ++e)
           if (k0 + e > limit) s[e] = -INFINITY;
       }
-      float tmax = s[0];
+      // four independent chains (a single running max is 128 dependent operations per tile)
+      float tm[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-      for (int e = 1; e < 128; ++e) tmax = fmaxf(tmax, s[e]);
+      for (int e = 4; e < 128; e += 4) {
+        tm[0] = fmaxf(tm[0], s[e]);
+        tm[1] = fmaxf(tm[1], s[e + 1]);
+        tm[2] = fmaxf(tm[2], s[e + 2]);
+        tm[3] = fmaxf(tm[3], s[e + 3]);
+      }
+      const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * args.scale_log2;  // log2 domain (scale > 0)
       const float m_new = fmaxf(m, tmax);
       if (j == 0) {
         m = m_new;  // key 0 is visible to every row, so m is finite from here on
@@ -221,19 +247,22 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           tc_fence_before();
         }
       }
+      TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
       // the P buffer was last read by P V of tile j-2
       if (j >= 2) {
         if (!mbar_wait(bar(PV_DONE + st), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       }
+      TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
       uint8_t* prow = gen + kSmemP + st * kTileBytes + r * 128;
-      float lsum = 0.0f;
+      float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const float neg_m = -m;
 #pragma unroll
       for (int ch = 0; ch < 16; ++ch) {  // 8 keys = one 16-byte chunk; chunk position XOR-swizzled by row & 7
         float p[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          p[e] = fast_exp2(s[ch * 8 + e] - m);
-          lsum += p[e];
+          p[e] = fast_exp2(fmaf(s[ch * 8 + e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
+          ls[e & 3] += p[e];
         }
         uint4 pk;
         pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
@@ -241,10 +270,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         const int box = ch >> 3, cib = ch & 7;
         *reinterpret_cast<uint4*>(prow + box * kBoxBytes + ((cib ^ (r & 7)) << 4)) = pk;
       }
-      l += lsum;
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       fence_proxy_async_smem();
       mbar_arrive(bar(P_FULL + st));
+      TRACE_ONLY(t_exp += clock64() - c0;)
     }
+    TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
+    TRACE_VALUE(7, threadIdx.x == 128, w_s);
+    TRACE_VALUE(8, threadIdx.x == 128, t_ld);
+    TRACE_VALUE(9, threadIdx.x == 128, t_max);
+    TRACE_VALUE(10, threadIdx.x == 128, w_pv);
+    TRACE_VALUE(11, threadIdx.x == 128, t_exp);
     if (ok) ok = mbar_wait(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
     if (ok) {
       tc_fence_after();

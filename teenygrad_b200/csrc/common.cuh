@@ -71,6 +71,8 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define TRACE_END() do {} while (0)
 #define TRACE_MARK(id, cond) do {} while (0)
+#define TRACE_VALUE(id, cond, value) do {} while (0)
+#define TRACE_ONLY(...)
 #else
 // ------------------------------------------------------------------------------------------------
 // Kernel timeline (development builds only: make EXTRA=-DTEENY_TRACE).  Thread 0 of every CTA records the global
@@ -106,6 +108,9 @@ __device__ __forceinline__ void pdl_wait_traced(int line) {
   do { if (threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0) trace_put(0, global_timer_ns(), __LINE__); } while (0)
 // intermediate record by the one thread for which `cond` holds (t0 = id, 1..15)
 #define TRACE_MARK(id, cond) do { if (cond) trace_put(id, global_timer_ns(), __LINE__); } while (0)
+// a measured quantity (e.g. cycles spent in a phase, summed by the caller) instead of a time (t0 = 16 + id, id 0..15)
+#define TRACE_VALUE(id, cond, value) do { if (cond) trace_put(16 + (id), static_cast<unsigned long long>(value), __LINE__); } while (0)
+#define TRACE_ONLY(...) __VA_ARGS__
 typedef int (*teeny_trace_dump_fn)(unsigned long long* out, unsigned cap, int reset);
 extern "C" void teeny_trace_register(const char* tu, teeny_trace_dump_fn fn);
 namespace {

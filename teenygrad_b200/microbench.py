@@ -249,6 +249,32 @@ def trace(n_layers, first=0, count=48):
         print()
 
 
+def tracecase(which):
+    """Runs ``case`` and prints, per source line and id, count / mean / sum of the TRACE_VALUE records (and the mean
+    dependency-wait interval per kernel).  Needs a -DTEENY_TRACE build."""
+    import ctypes
+    from collections import defaultdict
+
+    import numpy as np
+    lib = ops.lib
+    if not hasattr(lib, "teeny_trace_count"):
+        raise SystemExit("library was built without -DTEENY_TRACE")
+    lib.teeny_trace_name.restype = ctypes.c_char_p
+    lib.teeny_trace_name.argtypes = [ctypes.c_int]
+    lib.teeny_trace_dump.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint, ctypes.c_int]
+    case(which)
+    acc = defaultdict(list)
+    for i in range(lib.teeny_trace_count()):
+        name = lib.teeny_trace_name(i).decode().split("/")[-1]
+        buf = np.zeros((1 << 18, 4), dtype=np.uint64)
+        n = lib.teeny_trace_dump(i, buf.ctypes.data, 1 << 18, 1)
+        b = buf[:n]
+        for r in b[(b[:, 0] >= 16) & (b[:, 0] < 32)]:
+            acc[(name, int(r[2]) & 0xFFFFFFFF, int(r[0]) - 16)].append(int(r[1]))
+    for (name, line, vid), vals in sorted(acc.items()):
+        print(f"{name}:{line} value {vid:2d}: n {len(vals):6d} mean {sum(vals) / len(vals):12.1f} sum {sum(vals):14d}")
+
+
 def main(argv):
     import os
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -259,6 +285,8 @@ def main(argv):
             {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode}[name]()
     elif mode == "case":
         case(argv[1])
+    elif mode == "tracecase":
+        tracecase(argv[1])
     elif mode == "layers":
         layers(int(argv[1]) if len(argv) > 1 else 6)
     elif mode == "trace":
