@@ -6,7 +6,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def library_path():
-    return os.path.join(_HERE, "libteeny_b200.so")
+    """The library the package loads: TEENY_B200_LIB if set (e.g. a -DTEENY_TRACE build made beside the default one),
+    else the in-tree default build."""
+    return os.environ.get("TEENY_B200_LIB") or os.path.join(_HERE, "libteeny_b200.so")
 
 
 def build(force=False, jobs=8, verbose=False):

@@ -47,6 +47,9 @@ int* device_error_word() {
   return g_error_ptr[d];
 }
 
+namespace { thread_local int t_sm_limit = 0; }
+void set_sm_limit(int n) { t_sm_limit = n > 0 ? n : 0; }
+
 int sm_count() {
   const int d = current_device();
   std::lock_guard<std::mutex> lock(g_mutex);
@@ -55,7 +58,8 @@ int sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
     g_sm_count[d] = n;
   }
-  return g_sm_count[d];
+  const int n = g_sm_count[d];
+  return (t_sm_limit > 0 && t_sm_limit < n) ? t_sm_limit : n;
 }
 
 int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,

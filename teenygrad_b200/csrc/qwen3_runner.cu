@@ -31,6 +31,7 @@
 #include "../../include/teeny_qwen3.h"
 #include "common.cuh"
 #include "kernels.h"
+#include <cstdio>
 
 namespace teeny {
 
@@ -213,6 +214,11 @@ struct teeny_qwen3 {
   unsigned pending_round = 0;
   cudaGraphExec_t graph_exec = nullptr;
   cudaStream_t capture_stream = nullptr;
+  // tensor-parallel prefill in two half-batches: the all-reduce of one half runs on comm_stream while the other
+  // half computes (ev_ready: projection written; ev_done[half]: its all-reduce finished)
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_ready = nullptr, ev_done[2] = {nullptr, nullptr};
+  bool overlap_prefill = false;
   int graph_batch = 0;
   int batch = 0;  // batch of the running generation (set by prefill)
   bool tables_ready = false;
@@ -389,6 +395,98 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
   return 0;
 }
 
+// Tensor-parallel prefill with communication hidden behind compute.  The batch is cut into two halves of whole
+// sequences; on the one compute stream the halves alternate block by block (attention block of A, of B, MLP block of
+// A, of B, ...), and each row-parallel projection's all-reduce is issued on the communicator's own stream, so it runs
+// while the other half's next block computes.  The persistent GEMMs leave comm_sms() SMs to the collective's CTAs for
+// the duration (otherwise the collective cannot start until a GEMM ends, or holds back part of the next GEMM's grid).
+int comm_sms() {  // TEENY_TP_COMM_SMS overrides (0 = the GEMMs keep every SM)
+  static const int n = [] {
+    const char* e = getenv("TEENY_TP_COMM_SMS");
+    const int v = e ? atoi(e) : 8;
+    return v < 0 ? 0 : (v > 64 ? 64 : v);
+  }();
+  return n;
+}
+
+int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
+  const teeny_qwen3_config& c = m->cfg;
+  const int Bh = B / 2, Th = Bh * S, H = c.hidden, D = c.head_dim, Hq = m->Hq, Hkv = m->Hkv, I = m->I;
+  const int qkv_n = (Hq + 2 * Hkv) * D;
+  void* gs = m->at<void>(m->off.gemm_scratch);
+  const size_t gsb = m->off.gemm_scratch_bytes;
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  cudaStream_t sc = m->comm_stream;
+  struct SmLimit {
+    explicit SmLimit(int n) { set_sm_limit(n); }
+    ~SmLimit() { set_sm_limit(0); }
+  } limit(sm_count() - comm_sms());
+
+  auto half_ptrs = [&](int hf, bf16*& h, bf16*& y, bf16*& qkv, bf16*& attn, bf16*& delta, bf16*& act) {
+    const size_t r = static_cast<size_t>(hf) * Th;
+    h = m->at<bf16>(m->off.h) + r * H;
+    y = m->at<bf16>(m->off.y) + r * H;
+    qkv = m->at<bf16>(m->off.qkv) + r * qkv_n;
+    attn = m->at<bf16>(m->off.attn) + r * Hq * D;
+    delta = m->at<bf16>(m->off.delta) + r * H;
+    act = m->at<bf16>(m->off.act) + r * I;
+  };
+  // all-reduce `delta` of one half on the communicator's stream, behind everything issued on st so far
+  auto reduce_async = [&](bf16* delta, int hf) -> int {
+    if (cudaEventRecord(m->ev_ready, st) != cudaSuccess) return TEENY_ERR_NCCL;
+    if (cudaStreamWaitEvent(sc, m->ev_ready, 0) != cudaSuccess) return TEENY_ERR_NCCL;
+    TEENY_TRY(all_reduce(m, delta, static_cast<size_t>(Th) * H, sc));
+    return cudaEventRecord(m->ev_done[hf], sc) == cudaSuccess ? 0 : TEENY_ERR_NCCL;
+  };
+  auto wait_reduced = [&](int hf) -> int {
+    return cudaStreamWaitEvent(st, m->ev_done[hf], 0) == cudaSuccess ? 0 : TEENY_ERR_NCCL;
+  };
+
+  for (int l = 0; l < c.num_layers; ++l) {
+    const LayerWeights& w = m->layers[l];
+    bf16* kc = m->at<bf16>(m->off.kcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
+    bf16* vc = m->at<bf16>(m->off.vcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
+    const size_t cache_half = static_cast<size_t>(Bh) * Hkv * c.max_len * D;
+    for (int hf = 0; hf < 2; ++hf) {  // attention blocks
+      bf16 *h, *y, *qkv, *attn, *delta, *act;
+      half_ptrs(hf, h, y, qkv, attn, delta, act);
+      if (l == 0) {
+        TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, Th, H, c.eps, st));
+      } else {
+        TEENY_TRY(wait_reduced(hf));  // down projection of the layer before
+        TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.input_ln, Th, H, c.eps, st));
+      }
+      TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, Th, qkv_n, H, gs, gsb, st));
+      TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                                     kc + hf * cache_half, vc + hf * cache_half, Th, S, Hq, Hkv, D, c.max_len, 0, nullptr,
+                                     c.eps, st));
+      AttnShape a{};
+      a.B = Bh; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.scale = scale;
+      a.q_sb = static_cast<long long>(S) * qkv_n; a.q_sh = D; a.q_ss = qkv_n;
+      a.k_sb = static_cast<long long>(Hkv) * c.max_len * D; a.k_sh = static_cast<long long>(c.max_len) * D; a.k_ss = D;
+      a.v_sb = a.k_sb; a.v_sh = a.k_sh; a.v_ss = D;
+      a.o_sb = static_cast<long long>(S) * Hq * D; a.o_sh = D; a.o_ss = static_cast<long long>(Hq) * D;
+      a.Sq = S; a.Skv = S; a.causal = 1;
+      TEENY_TRY(attention_prefill_bf16(qkv, kc + hf * cache_half, vc + hf * cache_half, attn, nullptr, a, st));
+      TEENY_TRY(gemm_bf16(attn, Hq * D, w.o, Hq * D, false, nullptr, delta, H, Th, H, Hq * D, gs, gsb, st));
+      TEENY_TRY(reduce_async(delta, hf));
+    }
+    for (int hf = 0; hf < 2; ++hf) {  // MLP blocks
+      bf16 *h, *y, *qkv, *attn, *delta, *act;
+      half_ptrs(hf, h, y, qkv, attn, delta, act);
+      TEENY_TRY(wait_reduced(hf));  // O projection
+      TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.post_ln, Th, H, c.eps, st));
+      TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, act, I, Th, 2 * I, H, gs, gsb, st, /*swiglu=*/true));
+      TEENY_TRY(gemm_bf16(act, I, w.down, I, false, nullptr, delta, H, Th, H, I, gs, gsb, st));
+      TEENY_TRY(reduce_async(delta, hf));
+    }
+  }
+  // the head reads both halves' last down projection
+  TEENY_TRY(wait_reduced(0));
+  TEENY_TRY(wait_reduced(1));
+  return 0;
+}
+
 // Final norm on the last token of each sequence, LM head, greedy pick.  Leaves next ids in off.next_ids.
 int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
   const teeny_qwen3_config& c = m->cfg;
@@ -488,6 +586,17 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
     delete m;
     return prc;
   }
+  // Prefill with the all-reduces on their own stream: opt-in (TEENY_TP_OVERLAP=1).  Measured on 2 GPUs it does not
+  // pay (465 ms in line, 473 ms overlapped with no SMs reserved, 482 ms with 8 reserved: the exposed communication is
+  // only ~40 ms there and the collective's CTAs slow the GEMMs they share SMs with).
+  const char* ov_env = getenv("TEENY_TP_OVERLAP");
+  if (m->tp && cfg->tp_size > 1 && ov_env && ov_env[0] == '1') {
+    bool ok = cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&m->ev_ready, cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&m->ev_done[0], cudaEventDisableTiming) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&m->ev_done[1], cudaEventDisableTiming) == cudaSuccess;
+    m->overlap_prefill = ok;
+  }
   // decode-time peer buffers (collective: every rank creates its runner at the same point)
   const char* peer_env = getenv("TEENY_TP_PEER");  // "0" keeps decode on NCCL all-reduce (for A/B measurements)
   // (two pushes per layer, each with its own round number below 1023)
@@ -514,6 +623,10 @@ void teeny_qwen3_destroy(teeny_qwen3* m) {
   if (!m) return;
   if (m->graph_exec) cudaGraphExecDestroy(m->graph_exec);
   if (m->capture_stream) cudaStreamDestroy(m->capture_stream);
+  if (m->comm_stream) cudaStreamDestroy(m->comm_stream);
+  if (m->ev_ready) cudaEventDestroy(m->ev_ready);
+  for (cudaEvent_t ev : m->ev_done)
+    if (ev) cudaEventDestroy(ev);
   delete m;
 }
 
@@ -569,7 +682,10 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
   m->batch = B;
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(ids, m->embed, m->at<bf16>(m->off.h), B * S, c.hidden, c.vocab, st));
-  TEENY_TRY(run_layers(m, B, S, 0, nullptr, nullptr, false, st));
+  if (m->overlap_prefill && B % 2 == 0 && B * S >= 512)  // small prefills have nothing to hide
+    TEENY_TRY(run_layers_prefill_overlap(m, B, S, st));
+  else
+    TEENY_TRY(run_layers(m, B, S, 0, nullptr, nullptr, false, st));
   TEENY_TRY(run_head(m, B, S, st));
   // generation state: next position S, live length during the next step S + 1, no tokens recorded yet
   launch_kernel(set_state_kernel, dim3(1), dim3(1), 0, st, 1, state, S - 1, S, 0);
@@ -648,6 +764,13 @@ int teeny_tp_init(const void* id128, int rank, int world, void** comm_out) {
   ncclUniqueId id;
   std::memcpy(&id, id128, sizeof(id));
   ncclComm_t comm = nullptr;
+  // The prefill overlaps its all-reduces with GEMMs that leave comm_sms() SMs free: keep the collective within them
+  // (a caller's own setting wins).
+  {
+    char buf[16];
+    snprintf(buf, sizeof(buf), "%d", comm_sms() > 0 ? comm_sms() : 16);
+    setenv("NCCL_MAX_CTAS", buf, 0);
+  }
   if (g_nccl.CommInitRank(&comm, world, id, rank) != ncclSuccess) return TEENY_ERR_NCCL;
   TpContext* c = new (std::nothrow) TpContext();
   if (!c) return TEENY_ERR_BAD_ARG;

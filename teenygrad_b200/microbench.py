@@ -4,12 +4,14 @@
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
     python -m teenygrad_b200.microbench trace [N [first [count]]]                 # timeline of one graph-replayed decode step
+    python -m teenygrad_b200.microbench tracecase gemm|skinny|prefill|decode      # phase counters of one kernel
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
 one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
 microseconds, are captured in a CUDA graph over rotating copies of their inputs (larger than L2 together) so neither
 host launch overhead nor a warm L2 enters the number.  ``case`` and ``layers`` exist to be run under ``ncu``.
-``trace`` needs a library built with ``make -C teenygrad_b200/csrc EXTRA=-DTEENY_TRACE`` (per-CTA timer records).
+``trace`` and ``tracecase`` need a library with per-CTA timer records: ``make -C teenygrad_b200/csrc OBJDIR=_obj_trace
+OUT=../libteeny_b200_trace.so EXTRA=-DTEENY_TRACE`` and ``TEENY_B200_LIB=teenygrad_b200/libteeny_b200_trace.so``.
 """
 import sys
 

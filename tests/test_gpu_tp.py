@@ -18,6 +18,7 @@ def test_tensor_parallel_matches_oracle(world):
     port = 29500 + world
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    # also exercise the opt-in prefill that overlaps its all-reduces with the other half-batch's compute
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, TEENY_TP_OVERLAP="1"))
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    assert f"TP{world} OK" in res.stdout
+    assert f"TP{world} B4 S128 OK" in res.stdout and f"TP{world} B3 S40 OK" in res.stdout

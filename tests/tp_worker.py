@@ -21,9 +21,17 @@ def main():
     layers, hidden, hq, hkv, inter, vocab = 3, 512, 8, 8, 1024, 4096
     ocfg = oq.OracleQwen3Config(layers, hidden, hq, hkv, 128, inter, vocab, tied=False)
     sd = oq.make_weights(ocfg, 21)
-    B, S, steps = 3, 40, 12
-    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(22))
     cfg = qwen3.Qwen3Config(layers, hidden, hq, hkv, 128, inter, vocab, tied=False)
+    # even batch of 512 tokens: prefill in two halves with the all-reduces on the communicator's stream; odd batch:
+    # prefill all-reduces in line.  (Largest batch first: the context's peer buffers are sized by the first runner.)
+    for (B, S, steps) in ((4, 128, 6), (3, 40, 12)):
+        check(qwen3, oq, comm, cfg, ocfg, sd, rank, world, B, S, steps, vocab)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def check(qwen3, oq, comm, cfg, ocfg, sd, rank, world, B, S, steps, vocab):
+    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(22 + B))
     results, logit_runs = [], []
     for graph in (False, True):
         r = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + steps, max_new_tokens=steps, tp_rank=rank, tp_size=world,
@@ -69,10 +77,8 @@ def main():
                 gap = float(want_logits[b, t_div].max() - want_logits[b, t_div, got[b, t_div]]) / scale
                 assert gap < 2e-2, f"row {b} step {t_div}: picked a token {gap} below the oracle's best (not a near-tie)"
             assert t_div >= 1, "first generated token (prefill) must match"
-        print(f"TP{world} OK (decode reduction: {'peer-push' if peer else 'nccl'}; near-tie flips in {flips} of {B} rows)",
-              flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+        print(f"TP{world} B{B} S{S} OK (decode reduction: {'peer-push' if peer else 'nccl'}; near-tie flips in {flips} of "
+              f"{B} rows)", flush=True)
 
 
 if __name__ == "__main__":
