@@ -378,29 +378,30 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ uint4 head_norm_rope(const uint4 raw, const uint4 wraw, const uint4 craw, const uint4 sraw,
                                                 int sub, float eps) {
   const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-  float x[8];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) { x[2 * e] = bf16_lo(rw[e]); x[2 * e + 1] = bf16_hi(rw[e]); }
   float sq = 0.0f;
 #pragma unroll
-  for (int e = 0; e < 8; ++e) sq += x[e] * x[e];
+  for (int e = 0; e < 4; ++e) {
+    sq += bf16_lo(rw[e]) * bf16_lo(rw[e]);
+    sq += bf16_hi(rw[e]) * bf16_hi(rw[e]);
+  }
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);  // stays inside the half-warp
   const float rr = 1.0f / sqrtf(sq * (1.0f / 128.0f) + eps);
   const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w},
                  sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
-  float r[8];
+  const float sign = (sub < 8) ? -1.0f : 1.0f;  // rotate_half: the first half gets -x[d + 64]
+  uint32_t out[4];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float wv = (e & 1) ? bf16_hi(ww[e >> 1]) : bf16_lo(ww[e >> 1]);
-    const float cv = (e & 1) ? bf16_hi(cw[e >> 1]) : bf16_lo(cw[e >> 1]);
-    const float sv = (e & 1) ? bf16_hi(sw[e >> 1]) : bf16_lo(sw[e >> 1]);
-    const float n = bf16_round(bf16_round(x[e] * rr) * wv);  // normed head, a bf16 tensor in the traced graph
-    const float partner = __shfl_xor_sync(0xffffffffu, n, 8);
-    const float rot = (sub < 8) ? -partner : partner;         // rotate_half: first half gets -x[d + 64]
-    r[e] = bf16_round(n * cv) + bf16_round(rot * sv);         // rounded to bf16 by the pack below
+  for (int e = 0; e < 4; ++e) {  // two elements at a time: every rounding is one packed conversion
+    const uint32_t xn = pack_bf16x2(bf16_lo(rw[e]) * rr, bf16_hi(rw[e]) * rr);
+    // normed head, a bf16 tensor in the traced graph
+    const uint32_t n = pack_bf16x2(bf16_lo(xn) * bf16_lo(ww[e]), bf16_hi(xn) * bf16_hi(ww[e]));
+    const uint32_t partner = __shfl_xor_sync(0xffffffffu, n, 8);
+    const uint32_t nc = pack_bf16x2(bf16_lo(n) * bf16_lo(cw[e]), bf16_hi(n) * bf16_hi(cw[e]));
+    const uint32_t rs = pack_bf16x2(sign * bf16_lo(partner) * bf16_lo(sw[e]), sign * bf16_hi(partner) * bf16_hi(sw[e]));
+    out[e] = pack_bf16x2(bf16_lo(nc) + bf16_lo(rs), bf16_hi(nc) + bf16_hi(rs));
   }
-  return make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]), pack_bf16x2(r[6], r[7]));
+  return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

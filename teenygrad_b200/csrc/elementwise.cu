@@ -439,7 +439,11 @@ __global__ void rope_table_kernel(const float* __restrict__ inv_freq, bf16* __re
 
 // ---- per-head RMSNorm + RoPE + KV-cache append; D == 128, one half-warp per (token, head) ----
 // Lane s (0..15) of the half-warp holds elements [8s, 8s+8) as one 16-byte vector; its rotate-half partner elements
-// (d +- 64) live in lane s ^ 8.  V heads are copied into the cache unchanged.
+// (d +- 64) live in lane s ^ 8.  V heads are copied into the cache unchanged.  A half-warp takes kRopeUnits
+// consecutive (token, head) units and issues all their loads before it computes, so a short-lived CTA still keeps
+// enough bytes in flight.
+constexpr int kRopeUnits = 4;
+
 __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, const bf16* __restrict__ q_w,
                                        const bf16* __restrict__ k_w, const bf16* __restrict__ cos_t,
                                        const bf16* __restrict__ sin_t, bf16* __restrict__ k_cache,
@@ -448,33 +452,56 @@ __global__ void qk_norm_rope_kv_kernel(bf16* __restrict__ qkv, long long ld, con
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
   const long long total = static_cast<long long>(T) * heads;
-  const long long unit_raw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
-  const bool valid = unit_raw < total;
-  const long long unit = valid ? unit_raw : total - 1;  // inactive half-warps shadow the last unit (no stores)
+  const long long unit0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4) * kRopeUnits;
   const int sub = threadIdx.x & 15;
-  const int t = static_cast<int>(unit / heads);
-  const int h = static_cast<int>(unit - static_cast<long long>(t) * heads);
-  const int b = t / S;
   // head-norm weights are constants: fetched ahead of the wait for the projection
-  const uint4 wraw = __ldg(reinterpret_cast<const uint4*>((h < Hq ? q_w : k_w) + sub * 8));
+  const uint4 wq = __ldg(reinterpret_cast<const uint4*>(q_w + sub * 8));
+  const uint4 wk = __ldg(reinterpret_cast<const uint4*>(k_w + sub * 8));
   pdl_wait();
   pdl_trigger();
-  const int pos = (pos0_dev ? *pos0_dev : pos0) + (t - b * S);
-  bf16* src = qkv + static_cast<size_t>(t) * ld + static_cast<size_t>(h) * D + sub * 8;
-  const uint4 raw = *reinterpret_cast<const uint4*>(src);
-  const bool is_v = h >= Hq + Hkv, is_q = h < Hq;
-  const int tp = pos < max_len ? pos : max_len - 1;  // table has max_len rows
-  const uint4 craw = *reinterpret_cast<const uint4*>(cos_t + static_cast<size_t>(tp) * D + sub * 8);
-  const uint4 sraw = *reinterpret_cast<const uint4*>(sin_t + static_cast<size_t>(tp) * D + sub * 8);
-  const uint4 outv = head_norm_rope(raw, wraw, craw, sraw, sub, eps);
-  if (!valid) return;
-  if (is_q) {
-    *reinterpret_cast<uint4*>(src) = outv;
-  } else if (pos < max_len) {
-    bf16* cache = is_v ? v_cache : k_cache;
-    const int hh = is_v ? h - Hq - Hkv : h - Hq;
-    bf16* dst = cache + ((static_cast<size_t>(b) * Hkv + hh) * max_len + pos) * D + sub * 8;
-    *reinterpret_cast<uint4*>(dst) = is_v ? raw : outv;
+  const int base_pos = pos0_dev ? *pos0_dev : pos0;
+  uint4 raw[kRopeUnits], craw[kRopeUnits], sraw[kRopeUnits];
+  int tok[kRopeUnits], head[kRopeUnits], pos[kRopeUnits], bidx[kRopeUnits];
+  bool valid[kRopeUnits];
+  // one division for the first unit; the following units step through heads and tokens
+  const long long first = unit0 < total ? unit0 : total - 1;  // units past the end shadow the last one (no stores)
+  int t_cur = static_cast<int>(first / heads);
+  int h_cur = static_cast<int>(first - static_cast<long long>(t_cur) * heads);
+  int b_cur = t_cur / S;
+  int s_cur = t_cur - b_cur * S;
+#pragma unroll
+  for (int u = 0; u < kRopeUnits; ++u) {
+    valid[u] = unit0 + u < total;
+    tok[u] = t_cur;
+    head[u] = h_cur;
+    bidx[u] = b_cur;
+    pos[u] = base_pos + s_cur;
+    const int tp = pos[u] < max_len ? pos[u] : max_len - 1;  // table has max_len rows
+    raw[u] = *reinterpret_cast<const uint4*>(qkv + static_cast<size_t>(t_cur) * ld + static_cast<size_t>(h_cur) * D + sub * 8);
+    craw[u] = __ldg(reinterpret_cast<const uint4*>(cos_t + static_cast<size_t>(tp) * D + sub * 8));
+    sraw[u] = __ldg(reinterpret_cast<const uint4*>(sin_t + static_cast<size_t>(tp) * D + sub * 8));
+    if (unit0 + u + 1 < total) {  // advance (stays on the last unit at the end)
+      if (++h_cur == heads) {
+        h_cur = 0;
+        ++t_cur;
+        if (++s_cur == S) { s_cur = 0; ++b_cur; }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kRopeUnits; ++u) {
+    const int h = head[u];
+    const bool is_v = h >= Hq + Hkv, is_q = h < Hq;
+    const uint4 outv = head_norm_rope(raw[u], is_q ? wq : wk, craw[u], sraw[u], sub, eps);
+    if (!valid[u]) continue;
+    if (is_q) {
+      *reinterpret_cast<uint4*>(qkv + static_cast<size_t>(tok[u]) * ld + static_cast<size_t>(h) * D + sub * 8) = outv;
+    } else if (pos[u] < max_len) {
+      bf16* cache = is_v ? v_cache : k_cache;
+      const int hh = is_v ? h - Hq - Hkv : h - Hq;
+      bf16* dst = cache + ((static_cast<size_t>(bidx[u]) * Hkv + hh) * max_len + pos[u]) * D + sub * 8;
+      *reinterpret_cast<uint4*>(dst) = is_v ? raw[u] : outv;
+    }
   }
 }
 
@@ -658,8 +685,8 @@ int qk_norm_rope_kv_bf16(bf16* qkv, long long ld, const bf16* q_w, const bf16* k
       (reinterpret_cast<uintptr_t>(k_w) & 15))
     return TEENY_ERR_ALIGNMENT;
   if (T == 0) return TEENY_OK;
-  const long long units = static_cast<long long>(T) * (Hq + 2 * Hkv);  // one half-warp each
-  const long long blocks = (units + 15) / 16;
+  const long long units = static_cast<long long>(T) * (Hq + 2 * Hkv);  // kRopeUnits per half-warp, 16 half-warps per CTA
+  const long long blocks = (units + 16 * kRopeUnits - 1) / (16 * kRopeUnits);
   if (blocks > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
   launch_kernel(qk_norm_rope_kv_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, st, 1, qkv, ld, q_w, k_w, cos_t, sin_t, k_cache, v_cache,
                                                                    T, S, Hq, Hkv, max_len, pos0, pos0_dev, eps);

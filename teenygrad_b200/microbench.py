@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks and profiler cases for libteeny_b200.so.
 
-    python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode]   # CUDA-event timings
+    python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode] [elementwise]   # CUDA-event timings
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
     python -m teenygrad_b200.microbench trace [N [first [count]]]                 # timeline of one graph-replayed decode step
@@ -115,6 +115,24 @@ def time_decode():
         t = _graph_time([(lambda k=k, v=v: ops.flash_attn_decode(q, k, v, L, D ** -0.5, out=o, scratch=sc)) for k, v in kv])
         by = 2 * B * HKV * L * D * 2
         print(f"flash-attn decode B{B} L{L}: {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s", flush=True)
+
+
+def time_elementwise():
+    """The two bandwidth-bound prefill passes at the bench's size (32 x 2048 tokens of Qwen3-8B)."""
+    T, S, H = 65536, 2048, 4096
+    qkv = _rand(T, (HQ + 2 * HKV) * D)
+    qw, kw = torch.ones(D, device="cuda").bfloat16(), torch.ones(D, device="cuda").bfloat16()
+    inv = (1e6 ** (-torch.arange(0, D, 2, dtype=torch.float32) / D)).cuda()
+    cos, sin = ops.rope_table(inv, S)
+    kc = torch.empty(T // S, HKV, S, D, dtype=torch.bfloat16, device="cuda")
+    vc = torch.empty_like(kc)
+    t = _flushed_time(lambda: ops.qk_norm_rope_kv(qkv, qw, kw, cos, sin, kc, vc, S, HQ, HKV, 0, 1e-6))
+    by = 2 * (qkv.numel() + T * HQ * D + 2 * kc.numel())
+    print(f"qk_norm_rope_kv {T} tokens: {t * 1e3:.0f} us {by / t / 1e6:.0f} GB/s", flush=True)
+    x, res, w = _rand(T, H), _rand(T, H), torch.ones(H, device="cuda").bfloat16()
+    t = _flushed_time(lambda: ops.add_rms_norm(x, res, w, 1e-6))
+    by = 2 * 4 * x.numel()
+    print(f"add_rms_norm {T}x{H}: {t * 1e3:.0f} us {by / t / 1e6:.0f} GB/s (includes the output allocation)", flush=True)
 
 
 def case(which):
@@ -282,9 +300,10 @@ def main(argv):
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     mode = argv[0] if argv else "time"
     if mode == "time":
-        what = argv[1:] or ["gemm", "skinny", "prefill", "decode"]
+        what = argv[1:] or ["gemm", "skinny", "prefill", "decode", "elementwise"]
         for name in what:
-            {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode}[name]()
+            {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode,
+             "elementwise": time_elementwise}[name]()
     elif mode == "case":
         case(argv[1])
     elif mode == "tracecase":
