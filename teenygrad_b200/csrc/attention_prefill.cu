@@ -1,15 +1,20 @@
 // Causal grouped-query flash-attention forward for sm_100a, head_dim 128, bf16 in/out, f32 softmax.
 //
 // One CTA per (128-query tile, query head, batch); keys/values stream through in tiles of 128.
-//   warp 0      TMA producer: Q once, then K and V tiles into two-stage rings (128-byte swizzle, separate barriers
-//               for K and V so QK^T can start before V lands);
+//   warps 0, 3  TMA producers: warp 0 loads Q once and then the K tiles, warp 3 the V tiles, each into a two-stage ring
+//               (128-byte swizzle) with its own barriers;
 //   warp 1      MMA issuer: S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of two S buffers in
 //               TMEM, and O += P V (P K-major from shared memory, V MN-major straight from its [key][d] tile);
-//               QK^T of tile j+1 is issued before P V of tile j so the tensor pipe works while softmax runs;
+//               QK^T is issued two tiles ahead of P V so the tensor pipe works while the softmax groups run;
 //   warp 2      allocates / frees tensor memory;
-//   warps 4-7   softmax: thread = query row; tcgen05.ld the S row, scale into the log2 domain, causal / tail mask,
-//               running max with lazy rescale (O in TMEM is only rescaled when the max grows by more than 2^8),
-//               P = exp2(s - m) as bf16 into shared memory in the swizzled K-major layout, row sums in f32.
+//   warps 4-7, 8-11   two softmax warpgroups, thread = query row in both; warpgroup w takes the key tiles j = w mod 2
+//               (S buffer w, P buffer w), so one group's exponentials run while the other loads and scans its next
+//               tile.  Per tile: tcgen05.ld the S row in 32-column pieces for the row maximum (causal / tail mask);
+//               (registers re-divided with setmaxnreg: 224 per softmax thread, 56 per service thread);
+//               agree on the running maximum with the other group (it lives in shared memory; a tile's decision
+//               waits for the previous tile's, a few instructions); lazy rescale (O in TMEM is only rescaled when
+//               the maximum grows by more than 2^8); P = exp2(s * scale - m) as bf16
+//               into shared memory in the swizzled K-major layout, row sums in f32 per group.
 // Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
 #include "common.cuh"
 #include "kernels.h"
@@ -21,7 +26,7 @@ namespace {
 constexpr int kQT = 128;
 constexpr int kKT = 128;
 constexpr int kHD = 128;
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;  // TMA, MMA, TMEM, idle + two softmax warpgroups
 constexpr int kTileBytes = kKT * kHD * 2;       // 32 KB: two 16 KB boxes of [128 rows][64 d]
 constexpr int kBoxBytes = 128 * 64 * 2;         // 16 KB
 constexpr int kSmemQ = 0;
@@ -29,7 +34,9 @@ constexpr int kSmemK = kSmemQ + kTileBytes;     // 2 stages
 constexpr int kSmemV = kSmemK + 2 * kTileBytes; // 2 stages
 constexpr int kSmemP = kSmemV + 2 * kTileBytes; // 2 buffers
 constexpr int kSmemBar = kSmemP + 2 * kTileBytes;
-constexpr int kSmemTotal = kSmemBar + 256 + 1024;
+constexpr int kSmemXch = kSmemBar + 256;        // running maximum per row (128 floats), row sums of both groups (256)
+constexpr int kSmemTotal = kSmemXch + 384 * 4 + 1024;
+static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 
 struct PrefillArgs {
@@ -56,11 +63,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar0 = base + kSmemBar;
   // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty |
-  //           13,14 p_full | 15,16 pv_done ; then the TMEM base address
+  //           13,14 p_full | 15,16 pv_done | 17,18 m_ready ; then the TMEM base address
   auto bar = [&](int i) { return bar0 + 8u * i; };
   constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
-                PV_DONE = 15;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * 17);
+                PV_DONE = 15, M_READY = 17;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * 19);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* err = args.err;
@@ -79,14 +86,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
-    for (int i = 0; i < 17; ++i) {
-      const bool softmax_arrives = (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1);
+    for (int i = 0; i < 19; ++i) {
+      const bool softmax_arrives = (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1 || i >= M_READY);
       mbar_init(bar(i), softmax_arrives ? 128 : 1);
     }
     mbar_fence_init();
   }
   if (warp == 2) {
-    tmem_alloc(base + kSmemBar + 8 * 17, 512);
+    tmem_alloc(base + kSmemBar + 8 * 19, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -96,8 +103,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
   pdl_wait();
 
+  // The two softmax warpgroups hold a 128-value score row per thread; the four service warps need few registers:
+  // each side re-sizes its register file share at the top of its own branch.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0) {  // Q once, then the K tiles
       mbar_expect_tx(bar(Q_FULL), kTileBytes);
       tma_load_4d(base + kSmemQ, &tmap_q, bar(Q_FULL), 0, q0, h, b);
       tma_load_4d(base + kSmemQ + kBoxBytes, &tmap_q, bar(Q_FULL), 64, q0, h, b);
@@ -108,6 +119,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         mbar_expect_tx(bar(K_FULL + st), kTileBytes);
         tma_load_4d(base + kSmemK + st * kTileBytes, &tmap_k, bar(K_FULL + st), 0, j * kKT, hk, b);
         tma_load_4d(base + kSmemK + st * kTileBytes + kBoxBytes, &tmap_k, bar(K_FULL + st), 64, j * kKT, hk, b);
+      }
+    }
+  } else if (warp == 3) {
+    if (lane == 0) {  // the V tiles, from a thread of their own: K runs two tiles ahead of V and must not queue behind it
+      for (int j = 0; j < n_tiles; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
         mbar_expect_tx(bar(V_FULL + st), kTileBytes);
         tma_load_4d(base + kSmemV + st * kTileBytes, &tmap_v, bar(V_FULL + st), 0, j * kKT, hk, b);
@@ -163,9 +181,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         umma_commit(bar(PV_DONE + st));
         return true;
       };
+      // QK^T runs two tiles ahead of P V: an S buffer is free again as soon as its softmax group has the row in
+      // registers, and this thread must not sit in the wait for P of tile j while S of tile j+2 could be computed
       if (ok) ok = issue_qk(0);
+      if (ok && n_tiles > 1) ok = issue_qk(1);
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) ok = issue_qk(j + 1);
+        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
         if (ok) ok = issue_pv(j);
       }
       TRACE_VALUE(0, true, n_tiles);
@@ -175,35 +196,39 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       TRACE_VALUE(4, true, w_v);
       TRACE_VALUE(5, true, w_p);
     }
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int quarter = warp & 3;
+    const int wg = (warp - 4) >> 2;     // softmax warpgroup: key tiles j = wg, wg + 2, ...; S and P buffer wg
     const int r = quarter * 32 + lane;  // query row in the tile == TMEM lane
     const int qi = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    float m = -INFINITY, l = 0.0f;
+    const uint32_t s_addr = tmem_s0 + lane_addr + wg * 128;
+    float* m_sh = reinterpret_cast<float*>(gen + kSmemXch);  // [128] running maximum, log2 domain
+    float* l_sh = m_sh + 128;                                // [2 groups][128] row sums
+    float m_used = -INFINITY, l = 0.0f;                      // the maximum this group's sums are relative to
     bool ok = true;
-    // development builds: cycles of thread 128 per phase (wait for S, TMEM load, maximum, wait for the P buffer, exp + store)
+    // development builds: cycles of thread 128 per phase (wait for S, scan, decision, wait for the P buffer, exp + store)
     TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, c0; const long long c_begin = clock64();)
-    for (int j = 0; j < n_tiles; ++j) {
-      const int st = j & 1;
+    for (int j = wg; j < n_tiles; j += 2) {
       const uint32_t ph = (j >> 1) & 1;
       TRACE_ONLY(c0 = clock64();)
-      if (!mbar_wait(bar(S_FULL + st), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+      if (!mbar_wait(bar(S_FULL + wg), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
       tc_fence_after();
+      // the S row into registers (raw scores: the scale is folded into the exponent), then the buffer is free
       float s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32(tmem_s0 + lane_addr + st * 128 + c * 32, t);
+        tmem_ld_32x32(s_addr + c * 32, t);
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);  // raw scores: the scale is folded into the exponent
+        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
       }
       tc_fence_before();
-      mbar_arrive(bar(S_EMPTY + st));  // S is in registers: the buffer can take QK^T of tile j+2
-      TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
-
+      mbar_arrive(bar(S_EMPTY + wg));  // the buffer can take QK^T of tile j+2
       const int k0 = j * kKT;
       const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
       if (need_mask) {
@@ -212,7 +237,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int e = 0; e < 128; ++e)
           if (k0 + e > limit) s[e] = -INFINITY;
       }
-      // four independent chains (a single running max is 128 dependent operations per tile)
+      // row maximum: four independent chains
       float tm[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
       for (int e = 4; e < 128; e += 4) {
@@ -222,17 +247,21 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tm[3] = fmaxf(tm[3], s[e + 3]);
       }
       const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * args.scale_log2;  // log2 domain (scale > 0)
-      const float m_new = fmaxf(m, tmax);
+      TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
+      // ---- the running maximum: tile j's decision follows tile j-1's (made by the other group) ----
+      float m;
       if (j == 0) {
-        m = m_new;  // key 0 is visible to every row, so m is finite from here on
+        m = tmax;  // key 0 is visible to every row, so m is finite from here on
       } else {
+        if (!mbar_wait(bar(M_READY + (wg ^ 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+        m = m_sh[r];
+        const float m_new = fmaxf(m, tmax);
         const bool grow = m_new > m + kRescaleThreshold;
         if (__any_sync(0xffffffffu, grow)) {
           // O must be final for tile j-1 before it is rescaled
           if (!mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
           const float alpha = fast_exp2(m - m_new);
-          l *= alpha;
           m = m_new;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -247,13 +276,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           tc_fence_before();
         }
       }
+      m_sh[r] = m;
+      mbar_arrive(bar(M_READY + wg));  // tile j + 1 may decide (and rescale O) now
+      if (m_used != m) {                // this group's sums follow the maximum (no-op while l == 0)
+        l *= fast_exp2(m_used - m);
+        m_used = m;
+      }
       TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
       // the P buffer was last read by P V of tile j-2
       if (j >= 2) {
-        if (!mbar_wait(bar(PV_DONE + st), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+        if (!mbar_wait(bar(PV_DONE + wg), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       }
       TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
-      uint8_t* prow = gen + kSmemP + st * kTileBytes + r * 128;
+      uint8_t* prow = gen + kSmemP + wg * kTileBytes + r * 128;
       float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const float neg_m = -m;
 #pragma unroll
@@ -272,7 +307,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       }
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       fence_proxy_async_smem();
-      mbar_arrive(bar(P_FULL + st));
+      mbar_arrive(bar(P_FULL + wg));
       TRACE_ONLY(t_exp += clock64() - c0;)
     }
     TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
@@ -281,16 +316,25 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     TRACE_VALUE(9, threadIdx.x == 128, t_max);
     TRACE_VALUE(10, threadIdx.x == 128, w_pv);
     TRACE_VALUE(11, threadIdx.x == 128, t_exp);
-    if (ok) ok = mbar_wait(bar(PV_DONE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+    // ---- both groups: final maximum, total row sum, then half of the output columns each ----
+    const int last = n_tiles - 1;
+    if (ok) ok = mbar_wait(bar(M_READY + (last & 1)), (last >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+    const float m_fin = m_sh[r];
+    if (m_used != m_fin) l *= fast_exp2(m_used - m_fin);  // a group without tiles has l = 0 and m_used = -inf
+    l_sh[wg * 128 + r] = l;
+    named_barrier_sync(1, 256);  // every softmax thread gets here, also after a failed wait
+    l = l_sh[r] + l_sh[128 + r];
+    if (ok) ok = mbar_wait(bar(PV_DONE + (last & 1)), (last >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
       const bool valid = qi < args.Sq;
-      bf16* dst = args.o + b * args.o_sb + h * args.o_sh + static_cast<long long>(qi) * args.o_ss;
+      const int col0 = wg * 64;
+      bf16* dst = args.o + b * args.o_sb + h * args.o_sh + static_cast<long long>(qi) * args.o_ss + col0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+        tmem_ld_32x32(tmem_o + lane_addr + col0 + c * 32, t);
         tmem_wait_ld();
         if (valid) {
 #pragma unroll
@@ -304,8 +348,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           }
         }
       }
-      if (valid && args.lse)
-        args.lse[(static_cast<long long>(b) * args.Hq + h) * args.Sq + qi] = 0.6931471805599453f * (m + log2f(l));
+      if (valid && args.lse && wg == 0)
+        args.lse[(static_cast<long long>(b) * args.Hq + h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
     }
   }
 
