@@ -4,7 +4,7 @@
 //   warps 0, 3  TMA producers: warp 0 loads Q once and then the K tiles, warp 3 the V tiles, each into a two-stage ring
 //               (128-byte swizzle) with its own barriers;
 //   warp 1      MMA issuer: S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of two S buffers in
-//               TMEM, and O += P V (P K-major from shared memory, V MN-major straight from its [key][d] tile);
+//               TMEM, and O += P V (P from tensor memory, V MN-major straight from its [key][d] tile);
 //               QK^T is issued two tiles ahead of P V so the tensor pipe works while the softmax groups run;
 //   warp 2      allocates / frees tensor memory;
 //   warps 4-7, 8-11   two softmax warpgroups, thread = query row in both; warpgroup w takes the key tiles j = w mod 2
@@ -14,7 +14,7 @@
 //               agree on the running maximum with the other group (it lives in shared memory; a tile's decision
 //               waits for the previous tile's, a few instructions); lazy rescale (O in TMEM is only rescaled when
 //               the maximum grows by more than 2^8); P = exp2(s * scale - m) as bf16
-//               into shared memory in the swizzled K-major layout, row sums in f32 per group.
+//               pairs into tensor memory, row sums in f32 per group.
 // Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
 #include "common.cuh"
 #include "kernels.h"
@@ -32,8 +32,7 @@ constexpr int kBoxBytes = 128 * 64 * 2;         // 16 KB
 constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + kTileBytes;     // 2 stages
 constexpr int kSmemV = kSmemK + 2 * kTileBytes; // 2 stages
-constexpr int kSmemP = kSmemV + 2 * kTileBytes; // 2 buffers
-constexpr int kSmemBar = kSmemP + 2 * kTileBytes;
+constexpr int kSmemBar = kSmemV + 2 * kTileBytes;
 constexpr int kSmemXch = kSmemBar + 256;        // running maximum per row (128 floats), row sums of both groups (256)
 constexpr int kSmemTotal = kSmemXch + 384 * 4 + 1024;
 static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
@@ -100,7 +99,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
+  // tensor memory columns: S0 0-127, S1 128-255 (f32 scores), O 256-383 (f32), P0 384-447, P1 448-511 (bf16 pairs)
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256, tmem_p = tmem + 384;
   pdl_wait();
 
   // The two softmax warpgroups hold a 128-value score row per thread; the four service warps need few registers:
@@ -168,14 +168,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (!mbar_wait(bar(P_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
         TRACE_ONLY(w_p += clock64() - c0;)
         tc_fence_after();
-        const uint32_t pb = base + kSmemP + st * kTileBytes, vb = base + kSmemV + st * kTileBytes;
+        const uint32_t vb = base + kSmemV + st * kTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step
-          const uint64_t pd = make_smem_desc_sw128(pb + (ks >> 2) * kBoxBytes + (ks & 3) * 32, 16, 1024);
+        for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory
           // V tile: rows = keys (128 B = 64 d each), two boxes = two 64-wide d chunks (leading offset 16 KB),
           // 8-key groups 1 KB apart; 16 keys = 2 KB per step.
           const uint64_t vd = make_smem_desc_sw128(vb + ks * 2048, kBoxBytes, 1024);
-          umma_bf16_ss(tmem_o, pd, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem_o, tmem_p + st * 64 + ks * 8, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(bar(V_EMPTY + st));
         umma_commit(bar(PV_DONE + st));
@@ -288,25 +287,25 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         if (!mbar_wait(bar(PV_DONE + wg), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       }
       TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
-      uint8_t* prow = gen + kSmemP + wg * kTileBytes + r * 128;
+      // probabilities as bf16 pairs straight into tensor memory (the A operand of P V): no shared-memory round trip
       float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const float neg_m = -m;
 #pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {  // 8 keys = one 16-byte chunk; chunk position XOR-swizzled by row & 7
-        float p[8];
+      for (int hc = 0; hc < 2; ++hc) {  // 64 keys = 32 packed columns per store
+        uint32_t pk[32];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          p[e] = fast_exp2(fmaf(s[ch * 8 + e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
-          ls[e & 3] += p[e];
+        for (int e = 0; e < 32; ++e) {
+          const float p0 = fast_exp2(fmaf(s[hc * 64 + 2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
+          const float p1 = fast_exp2(fmaf(s[hc * 64 + 2 * e + 1], args.scale_log2, neg_m));
+          ls[(2 * e) & 3] += p0;
+          ls[(2 * e + 1) & 3] += p1;
+          pk[e] = pack_bf16x2(p0, p1);
         }
-        uint4 pk;
-        pk.x = pack_bf16x2(p[0], p[1]); pk.y = pack_bf16x2(p[2], p[3]);
-        pk.z = pack_bf16x2(p[4], p[5]); pk.w = pack_bf16x2(p[6], p[7]);
-        const int box = ch >> 3, cib = ch & 7;
-        *reinterpret_cast<uint4*>(prow + box * kBoxBytes + ((cib ^ (r & 7)) << 4)) = pk;
+        tmem_st_32x32(tmem_p + lane_addr + wg * 64 + hc * 32, pk);
       }
+      tmem_wait_st();
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      fence_proxy_async_smem();
+      tc_fence_before();
       mbar_arrive(bar(P_FULL + wg));
       TRACE_ONLY(t_exp += clock64() - c0;)
     }
