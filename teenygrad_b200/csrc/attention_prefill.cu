@@ -31,8 +31,9 @@ constexpr int kTileBytes = kKT * kHD * 2;       // 32 KB: two 16 KB boxes of [12
 constexpr int kBoxBytes = 128 * 64 * 2;         // 16 KB
 constexpr int kSmemQ = 0;
 constexpr int kSmemK = kSmemQ + kTileBytes;     // 2 stages
-constexpr int kSmemV = kSmemK + 2 * kTileBytes; // 2 stages
-constexpr int kSmemBar = kSmemV + 2 * kTileBytes;
+constexpr int kKV = 2;                          // stages of the K ring and of the V ring (three measured no faster)
+constexpr int kSmemV = kSmemK + kKV * kTileBytes;
+constexpr int kSmemBar = kSmemV + kKV * kTileBytes;
 constexpr int kSmemXch = kSmemBar + 256;        // running maximum per row (128 floats), row sums of both groups (256)
 constexpr int kSmemTotal = kSmemXch + 384 * 4 + 1024;
 static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
@@ -61,12 +62,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar0 = base + kSmemBar;
-  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 s_empty |
-  //           13,14 p_full | 15,16 pv_done | 17,18 m_ready ; then the TMEM base address
+  // barriers: 0 q_full | 1-3 k_full | 4-6 k_empty | 7-9 v_full | 10-12 v_empty | 13,14 s_full | 15,16 s_empty |
+  //           17,18 p_full | 19,20 pv_done | 21,22 m_ready ; then the TMEM base address
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_FULL = 13,
-                PV_DONE = 15, M_READY = 17;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * 19);
+  constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
+                S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 2,
+                M_READY = PV_DONE + 2, kNumBars = M_READY + 2;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* err = args.err;
@@ -85,14 +87,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
-    for (int i = 0; i < 19; ++i) {
+    for (int i = 0; i < kNumBars; ++i) {
       const bool softmax_arrives = (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1 || i >= M_READY);
       mbar_init(bar(i), softmax_arrives ? 128 : 1);
     }
     mbar_fence_init();
   }
   if (warp == 2) {
-    tmem_alloc(base + kSmemBar + 8 * 19, 512);
+    tmem_alloc(base + kSmemBar + 8 * kNumBars, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -113,8 +115,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       tma_load_4d(base + kSmemQ, &tmap_q, bar(Q_FULL), 0, q0, h, b);
       tma_load_4d(base + kSmemQ + kBoxBytes, &tmap_q, bar(Q_FULL), 64, q0, h, b);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j % kKV;
+        const uint32_t ph = (j / kKV) & 1;
         if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
         mbar_expect_tx(bar(K_FULL + st), kTileBytes);
         tma_load_4d(base + kSmemK + st * kTileBytes, &tmap_k, bar(K_FULL + st), 0, j * kKT, hk, b);
@@ -124,8 +126,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   } else if (warp == 3) {
     if (lane == 0) {  // the V tiles, from a thread of their own: K runs two tiles ahead of V and must not queue behind it
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j % kKV;
+        const uint32_t ph = (j / kKV) & 1;
         if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
         mbar_expect_tx(bar(V_FULL + st), kTileBytes);
         tma_load_4d(base + kSmemV + st * kTileBytes, &tmap_v, bar(V_FULL + st), 0, j * kKT, hk, b);
@@ -140,35 +142,35 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       // development builds: cycles this thread spends waiting for K, a free S buffer, V and P (summed over the tiles)
       TRACE_ONLY(long long w_k = 0, w_se = 0, w_v = 0, w_p = 0, c0; const long long c_begin = clock64();)
       auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j & 1, kst = j % kKV;  // S buffer / K ring stage
+        const uint32_t ph = (j >> 1) & 1, kph = (j / kKV) & 1;
         TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(K_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        if (!mbar_wait(bar(K_FULL + kst), kph, err, DEVERR_ATTN_MMA)) return false;
         TRACE_ONLY(w_k += clock64() - c0; c0 = clock64();)
         if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_MMA)) return false;
         TRACE_ONLY(w_se += clock64() - c0;)
         tc_fence_after();
-        const uint32_t qb = base + kSmemQ, kb = base + kSmemK + st * kTileBytes;
+        const uint32_t qb = base + kSmemQ, kb = base + kSmemK + kst * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {  // 16 d per step; 4 steps per 64-wide box
           const uint32_t o = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
           umma_bf16_ss(tmem_s0 + st * 128, make_smem_desc_sw128(qb + o, 16, 1024),
                        make_smem_desc_sw128(kb + o, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
         }
-        umma_commit(bar(K_EMPTY + st));
+        umma_commit(bar(K_EMPTY + kst));
         umma_commit(bar(S_FULL + st));
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int st = j & 1, vst = j % kKV;  // P buffer / V ring stage
+        const uint32_t ph = (j >> 1) & 1, vph = (j / kKV) & 1;
         TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(V_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
+        if (!mbar_wait(bar(V_FULL + vst), vph, err, DEVERR_ATTN_MMA)) return false;
         TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
         if (!mbar_wait(bar(P_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
         TRACE_ONLY(w_p += clock64() - c0;)
         tc_fence_after();
-        const uint32_t vb = base + kSmemV + st * kTileBytes;
+        const uint32_t vb = base + kSmemV + vst * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory
           // V tile: rows = keys (128 B = 64 d each), two boxes = two 64-wide d chunks (leading offset 16 KB),
@@ -176,7 +178,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
           const uint64_t vd = make_smem_desc_sw128(vb + ks * 2048, kBoxBytes, 1024);
           umma_bf16_ts(tmem_o, tmem_p + st * 64 + ks * 8, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(bar(V_EMPTY + st));
+        umma_commit(bar(V_EMPTY + vst));
         umma_commit(bar(PV_DONE + st));
         return true;
       };
