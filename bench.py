@@ -293,7 +293,7 @@ def main():
     T = B * S
     shapes = [(T, (32 + 16) * 128 // world, 4096), (T, 4096, 4096 // world),
               (T, 2 * 12288 // world, 4096), (T, 4096, 12288 // world)]
-    flops = gemm_ms = 0.0
+    flops = gemm_ms = gemm_bytes = 0.0
     x = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev).normal_(0, 0.05)
     wbuf = torch.empty(2 * 12288 * 4096 // world + 4096 * 6144, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
     ybuf = torch.empty(T * max(2 * 12288 // world, 4096 + 2048), dtype=torch.bfloat16, device=dev)
@@ -309,6 +309,7 @@ def main():
         torch.cuda.synchronize()
         gemm_ms += a.elapsed_time(b) / 3
         flops += 2.0 * m * n * k
+        gemm_bytes += 2.0 * (m * k + n * k + m * n)
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     del x, wbuf, ybuf
 
@@ -342,11 +343,13 @@ def main():
                 "h2d_bytes_per_step": prompts_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4},
         "gpu_launches": (launches_prefill + launches_decode * (NEW - 1)) * steps,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "gemm_bf16_kernel (prefill QKV/O/gate-up/down shapes of this run)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_bf16_2cta_kernel (prefill QKV/O/gate-up/down shapes of this run)",
                      "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": achieved / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
                      "peak_source": peaks["source"] + " (sustained cuBLAS bf16: the kernel runs inside a long step)",
-                     "traffic": None},
+                     # DRAM bytes of the four launches together: ncu measured 0.99 x the algorithmic 2(MK + NK + MN) bytes
+                     # on a 4096 x 12288 x 4096 launch of this kernel (operands read once); scaled here by algorithmic bytes
+                     "traffic": 0.99 * gemm_bytes, "traffic_unit": "bytes per set of four launches, scaled from an ncu capture"},
     }
     if not args.no_cpu_baseline and world == 1:
         v, desc, threads = cpu_generation_rate(cfg_kwargs, **CPU_SAMPLE)
