@@ -185,6 +185,17 @@ int teeny_argmax_bf16(const teeny_bf16* logits, long long ld, float* best_val, i
 /* Merge `parts` candidates per row (vals / idx laid out [parts, rows]) into out_idx[rows]. */
 int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows,
                          teeny_stream_t stream);
+/* Sampling behind the LM head: temperature, top-k (1..1024) and top-p over each row of bf16 logits [rows, cols]
+ * (row stride ld).  Candidates are the top_k entries by (logit descending, index ascending); e_i = exp((l_i - l_0) /
+ * temperature) in f32, summed sequentially in that order; the nucleus is the shortest prefix whose mass reaches
+ * top_p of the total; out_idx[r] is the first candidate whose running mass exceeds u[r] times the nucleus mass
+ * (u[r] in [0, 1) is the caller's random number, so the call is deterministic); out_prob (optional) receives the
+ * sampled token's probability within the nucleus.  The reference has only the row softmax next to the logits
+ * (kernels/teeny-kernels/src/nn/activation/softmax.rs:39-69; Op::TopK is not lowered,
+ * kernels/teeny-kernels/src/graph/mod.rs:2784). */
+int teeny_sample_top_k_top_p_bf16(const teeny_bf16* logits, long long ld, int rows, int cols, float temperature,
+                                  int top_k, float top_p, const float* u, int* out_idx, float* out_prob,
+                                  teeny_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -56,6 +56,7 @@ SIGNATURES = {
     "teeny_embedding_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "teeny_argmax_bf16": (i32, [vp, i64, vp, vp, i32, i32, i32, vp]),
     "teeny_argmax_combine": (i32, [vp, vp, vp, i32, i32, vp]),
+    "teeny_sample_top_k_top_p_bf16": (i32, [vp, i64, i32, i32, f32, i32, f32, vp, vp, vp, vp]),
 }
 
 

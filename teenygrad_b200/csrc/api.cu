@@ -298,6 +298,11 @@ int teeny_argmax_bf16(const teeny_bf16* logits, long long ld, float* bv, int* bi
 int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, teeny_stream_t s) {
   return argmax_combine(vals, idx, out_idx, parts, rows, S(s));
 }
+int teeny_sample_top_k_top_p_bf16(const teeny_bf16* logits, long long ld, int rows, int cols, float temperature,
+                                  int top_k, float top_p, const float* u, int* out_idx, float* out_prob,
+                                  teeny_stream_t s) {
+  return sample_top_k_top_p_bf16(B(logits), ld, rows, cols, temperature, top_k, top_p, u, out_idx, out_prob, S(s));
+}
 
 }  // extern "C"
 

@@ -134,5 +134,9 @@ int argmax_bf16(const bf16* logits, long long ld, float* best_val, int* best_idx
                 cudaStream_t st);
 // Combine `parts` candidate (value, index) pairs per row: vals/idx [parts, rows] -> out_idx [rows].
 int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, int rows, cudaStream_t st);
+// Temperature / top-k / top-p sampling, one row of bf16 logits per CTA (csrc/sampling.cu): out_idx[r] = sampled column,
+// out_prob[r] (optional) = its probability inside the nucleus.  u[r] in [0, 1) is the caller's random number.
+int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols, float temperature, int top_k,
+                            float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st);
 
 }  // namespace teeny

@@ -1,0 +1,161 @@
+// Token sampling after the LM head: temperature, top-k and top-p (nucleus) over one row of bf16 logits per CTA.
+//
+// The reference ships only the row softmax next to the logits (kernels/teeny-kernels/src/nn/activation/softmax.rs:39;
+// Op::TopK is unlowered, kernels/teeny-kernels/src/graph/mod.rs:2784); this is the step a serving loop needs behind
+// it.  Definition (oracle/sampling.py restates it on the CPU):
+//   1. candidates = the top_k entries of the row by (logit descending, index ascending);
+//   2. e_i = exp((l_i - l_0) / temperature) in f32 over the candidates in that order, c_i = e_0 + ... + e_i summed
+//      sequentially in f32;
+//   3. nucleus = the shortest prefix with c_{n-1} >= top_p * c_last (at least one candidate);
+//   4. the sample is the first candidate i < n with c_i > u * c_{n-1}, u in [0, 1) given per row by the caller.
+// bf16 logits have 65536 possible values, so the k-th largest value is found exactly with two 256-bin histograms
+// (high byte, then low byte inside the deciding bin); ties at the threshold are resolved in index order by a third,
+// ordered pass.  The <= 1024 candidates are sorted in shared memory (bitonic), exponentials are computed in parallel
+// and one thread does the sequential sums so the result does not depend on a reduction tree.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace teeny {
+
+namespace {
+
+constexpr int kSampleThreads = 1024;
+constexpr int kMaxTopK = 1024;
+
+// bf16 bit pattern -> 16-bit key whose unsigned order is the float order (NaNs sort above +inf; not expected here)
+__device__ __forceinline__ unsigned sort_key(unsigned short bits) {
+  return (bits & 0x8000u) ? (~static_cast<unsigned>(bits) & 0xFFFFu) : (static_cast<unsigned>(bits) | 0x8000u);
+}
+__device__ __forceinline__ float key_to_float(unsigned key) {
+  const unsigned bits = (key & 0x8000u) ? (key & 0x7FFFu) : (~key & 0xFFFFu);
+  return __uint_as_float(bits << 16);
+}
+
+// Largest bin b with (number of entries in bins above b) < want <= (number in bins >= b); `above` gets the former.
+__device__ void pick_bin(const unsigned* hist, unsigned want, unsigned* bin_out, unsigned* above_out) {
+  unsigned above = 0;
+  int b = 255;
+  for (; b > 0; --b) {
+    if (above + hist[b] >= want) break;
+    above += hist[b];
+  }
+  *bin_out = static_cast<unsigned>(b);
+  *above_out = above;
+}
+
+__global__ void __launch_bounds__(kSampleThreads, 1)
+sample_top_k_top_p_kernel(const bf16* __restrict__ logits, long long ld, int cols, float inv_temperature, int top_k,
+                          float top_p, const float* __restrict__ u, int* __restrict__ out_idx,
+                          float* __restrict__ out_prob) {
+  pdl_wait();
+  __shared__ unsigned hist[256];
+  __shared__ unsigned long long cand[kMaxTopK];  // (key << 32) | (0xFFFFFFFF - index): descending = value desc, index asc
+  __shared__ float expv[kMaxTopK];
+  __shared__ unsigned s_bin, s_above, s_count, s_eq_base;
+  __shared__ unsigned warp_tot[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned short* row = reinterpret_cast<const unsigned short*>(logits) + static_cast<size_t>(blockIdx.x) * ld;
+  const unsigned K = static_cast<unsigned>(min(top_k, cols));
+
+  // ---- pass 1: histogram of the key's high byte ----
+  if (tid < 256) hist[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < cols; i += kSampleThreads) atomicAdd(&hist[sort_key(row[i]) >> 8], 1u);
+  __syncthreads();
+  if (tid == 0) pick_bin(hist, K, &s_bin, &s_above);
+  __syncthreads();
+  const unsigned hi_bin = s_bin, above_hi = s_above;
+  __syncthreads();
+  // ---- pass 2: histogram of the low byte inside that bin ----
+  if (tid < 256) hist[tid] = 0;
+  __syncthreads();
+  for (int i = tid; i < cols; i += kSampleThreads) {
+    const unsigned k = sort_key(row[i]);
+    if ((k >> 8) == hi_bin) atomicAdd(&hist[k & 255u], 1u);
+  }
+  __syncthreads();
+  if (tid == 0) pick_bin(hist, K - above_hi, &s_bin, &s_above);
+  __syncthreads();
+  const unsigned thresh = (hi_bin << 8) | s_bin;            // the K-th largest key
+  const unsigned need_eq = K - (above_hi + s_above);        // how many entries equal to it are taken (>= 1)
+  if (tid == 0) { s_count = 0; s_eq_base = 0; }
+  for (int i = tid; i < kMaxTopK; i += kSampleThreads) cand[i] = 0ull;
+  __syncthreads();
+  // ---- pass 3, in index order: everything above the threshold, and the first need_eq entries equal to it ----
+  for (int base = 0; base < cols; base += kSampleThreads) {
+    const int i = base + tid;
+    const unsigned k = i < cols ? sort_key(row[i]) : 0u;
+    const bool gt = i < cols && k > thresh, eq = i < cols && k == thresh;
+    // rank of this thread's tie among the ties of the tile (block-wide exclusive count in index order)
+    const unsigned eq_mask = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) warp_tot[warp] = __popc(eq_mask);
+    __syncthreads();
+    unsigned before = s_eq_base;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    before += __popc(eq_mask & ((1u << lane) - 1u));
+    if (gt || (eq && before < need_eq)) {
+      const unsigned slot = atomicAdd(&s_count, 1u);
+      if (slot < static_cast<unsigned>(kMaxTopK))
+        cand[slot] = (static_cast<unsigned long long>(k) << 32) | (0xFFFFFFFFu - static_cast<unsigned>(i));
+    }
+    __syncthreads();
+    if (tid == 0) {
+      unsigned t = 0;
+      for (int w = 0; w < 32; ++w) t += warp_tot[w];
+      s_eq_base += t;
+    }
+    __syncthreads();
+  }
+  // ---- bitonic sort of the 1024 slots, descending (empty slots are zero and end up last) ----
+  for (unsigned size = 2; size <= static_cast<unsigned>(kMaxTopK); size <<= 1) {
+    for (unsigned stride = size >> 1; stride > 0; stride >>= 1) {
+      const unsigned partner = tid ^ stride;
+      if (partner > static_cast<unsigned>(tid)) {
+        const bool descending = (tid & size) == 0;
+        const unsigned long long a = cand[tid], b = cand[partner];
+        if ((a < b) == descending) { cand[tid] = b; cand[partner] = a; }
+      }
+      __syncthreads();
+    }
+  }
+  // ---- exponentials in parallel, sums by one thread in candidate order ----
+  const float l0 = key_to_float(static_cast<unsigned>(cand[0] >> 32));
+  if (static_cast<unsigned>(tid) < K) expv[tid] = expf((key_to_float(static_cast<unsigned>(cand[tid] >> 32)) - l0) * inv_temperature);
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.0f;
+    for (unsigned i = 0; i < K; ++i) total += expv[i];
+    // nucleus: shortest prefix whose mass reaches top_p of the total
+    const float want = top_p * total;
+    float c = 0.0f;
+    unsigned n = 0;
+    while (n < K) {
+      c += expv[n];
+      ++n;
+      if (c >= want) break;
+    }
+    const float target = u[blockIdx.x] * c;  // c = mass of the nucleus
+    float run = 0.0f;
+    unsigned pick = n - 1;
+    for (unsigned i = 0; i < n; ++i) {
+      run += expv[i];
+      if (run > target) { pick = i; break; }
+    }
+    out_idx[blockIdx.x] = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned>(cand[pick] & 0xFFFFFFFFull));
+    if (out_prob) out_prob[blockIdx.x] = expv[pick] / c;
+  }
+}
+
+}  // namespace
+
+int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols, float temperature, int top_k,
+                            float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st) {
+  if (!logits || !u || !out_idx || rows < 0 || cols <= 0 || ld < cols) return TEENY_ERR_BAD_ARG;
+  if (!(temperature > 0.0f) || top_k < 1 || top_k > kMaxTopK || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  launch_kernel(sample_top_k_top_p_kernel, dim3(rows), dim3(kSampleThreads), 0, st, 1, logits, ld, cols,
+                1.0f / temperature, top_k, top_p, u, out_idx, out_prob);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace teeny

@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks and profiler cases for libteeny_b200.so.
 
-    python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode] [elementwise]   # CUDA-event timings
+    python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode] [elementwise] [sampling]   # CUDA-event timings
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
     python -m teenygrad_b200.microbench trace [N [first [count]]]                 # timeline of one graph-replayed decode step
@@ -133,6 +133,14 @@ def time_elementwise():
     t = _flushed_time(lambda: ops.add_rms_norm(x, res, w, 1e-6))
     by = 2 * 4 * x.numel()
     print(f"add_rms_norm {T}x{H}: {t * 1e3:.0f} us {by / t / 1e6:.0f} GB/s (includes the output allocation)", flush=True)
+
+
+def time_sampling():
+    logits = (torch.randn(32, 151936, device="cuda") * 3).bfloat16()
+    u = torch.rand(32, device="cuda")
+    for k in (50, 1024):
+        t = _flushed_time(lambda: ops.sample_top_k_top_p(logits, 0.8, k, 0.9, u))
+        print(f"sample_top_k_top_p 32 x 151936, top_k {k}: {t * 1e3:.0f} us (three passes over 9.7 MB of logits)", flush=True)
 
 
 def case(which):
@@ -300,10 +308,10 @@ def main(argv):
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     mode = argv[0] if argv else "time"
     if mode == "time":
-        what = argv[1:] or ["gemm", "skinny", "prefill", "decode", "elementwise"]
+        what = argv[1:] or ["gemm", "skinny", "prefill", "decode", "elementwise", "sampling"]
         for name in what:
             {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode,
-             "elementwise": time_elementwise}[name]()
+             "elementwise": time_elementwise, "sampling": time_sampling}[name]()
     elif mode == "case":
         case(argv[1])
     elif mode == "tracecase":

@@ -258,3 +258,17 @@ def argmax_combine(vals, idx):
     out = torch.empty(rows, dtype=torch.int32, device=vals.device)
     check(lib.teeny_argmax_combine(_ptr(vals), _ptr(idx), _ptr(out), parts, rows, _stream()), "argmax_combine")
     return out
+
+
+def sample_top_k_top_p(logits, temperature, top_k, top_p, u, want_prob=False):
+    """Temperature / top-k / top-p sampling of one token per row of bf16 logits [rows, cols]; ``u`` f32 [rows] in
+    [0, 1) supplies the randomness (the call itself is deterministic).  Returns indices int32 [rows] (and the sampled
+    tokens' probabilities inside the nucleus when asked)."""
+    _req(logits, _BF16, "logits"); _req(u, _F32, "u")
+    rows, cols = logits.shape
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    prob = torch.empty(rows, dtype=_F32, device=logits.device) if want_prob else None
+    check(lib.teeny_sample_top_k_top_p_bf16(_ptr(logits), logits.stride(0), rows, cols, float(temperature), int(top_k),
+                                            float(top_p), _ptr(u), _ptr(idx), _ptr(prob), _stream()),
+          "sample_top_k_top_p")
+    return (idx, prob) if want_prob else idx

@@ -329,3 +329,41 @@ def test_rope_table_and_qk_norm_rope_kv(ops):
     assert rel(kc[:, :, pos0:pos0 + S].cpu(), ek.transpose(1, 2)) < BF16_TOL
     assert torch.equal(vc[:, :, pos0:pos0 + S].cpu(), v.transpose(1, 2))
     assert float(kc[:, :, :pos0].abs().sum()) == 0 and float(kc[:, :, pos0 + S:].abs().sum()) == 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# sampling behind the LM head
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols,temperature,top_k,top_p", [
+    (4, 1000, 1.0, 1, 1.0),          # top-k 1 = argmax
+    (8, 151936, 0.8, 50, 0.9),       # Qwen3 vocabulary, usual serving settings
+    (3, 151936, 1.5, 1024, 0.95),    # widest candidate list
+    (5, 777, 0.3, 1024, 1.0),        # fewer columns than top_k, odd row length
+    (6, 32000, 1.0, 40, 0.5),
+])
+def test_sample_top_k_top_p_matches_oracle(ops, rows, cols, temperature, top_k, top_p):
+    from oracle import sampling as osamp
+    g = torch.Generator().manual_seed(rows * 131 + cols)
+    logits = (torch.randn(rows, cols, generator=g) * 3).bfloat16()
+    if top_k == 1:
+        logits[0, [5, 9, 700]] = 20.0  # ties at the top: the lowest index must win
+    u = torch.rand(rows, generator=g)
+    got, prob = ops.sample_top_k_top_p(logits.cuda(), temperature, top_k, top_p, u.cuda(), want_prob=True)
+    got, prob = got.cpu().numpy(), prob.cpu().numpy()
+    lf = logits.float().numpy()
+    for r in range(rows):
+        want, wprob, c, n, cand = osamp.sample_row(lf[r], temperature, top_k, top_p, float(u[r]))
+        if got[r] == want:
+            assert abs(prob[r] - wprob) <= 1e-4 * max(1.0, wprob)
+            continue
+        # exp() differs by a few ulp between the GPU and numpy, so at a boundary of the CDF the neighbour may be
+        # picked: accept only a candidate of the nucleus (or the first one past it) whose CDF interval lies within
+        # 1e-5 (relative) of u
+        cl = list(cand)
+        assert got[r] in cl[:n + 1], f"row {r}: {got[r]} is not a nucleus candidate"
+        i = cl.index(got[r])
+        lo = c[i - 1] if i > 0 else 0.0
+        target = np.float32(u[r]) * c[n - 1]
+        tol = 1e-5 * c[n - 1]
+        assert lo - tol <= target <= c[i] + tol, f"row {r}: picked {got[r]} outside its CDF interval"
+    assert ops.device_error() == 0
