@@ -69,3 +69,21 @@ def test_qwen3_0_6b_config_greedy_ids(q):
     print("min top-2 logit gap over steps:", float((top2[..., 0] - top2[..., 1]).min()), "worst rel", worst)
     assert worst < TOL
     assert torch.equal(got, want)
+
+
+def test_weights_from_a_sharded_safetensors_checkpoint(q, tmp_path):
+    """The same model loaded from HF-named safetensors shards generates the same ids as from the in-memory dict."""
+    from oracle import qwen3 as oq
+    from teenygrad_b200 import safetensors as st
+    ocfg = oq.OracleQwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
+    sd = oq.make_weights(ocfg, 9)
+    st.save_sharded(sd, tmp_path / "ckpt", max_shard_bytes=600_000)
+    ids = torch.randint(0, 1024, (2, 24), generator=torch.Generator().manual_seed(1))
+    cfg = q.Qwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
+    outs = []
+    for weights in (sd, st.SafeTensors(tmp_path / "ckpt")):
+        r = q.Qwen3Runner(cfg, max_batch=2, max_len=40, max_new_tokens=8)
+        r.load_state_dict(weights)
+        outs.append(r.generate(ids, 8).cpu())
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0].long(), oq.OracleQwen3(ocfg, sd).generate(ids, 8))
