@@ -38,3 +38,14 @@ def sample_row(row_f32, temperature, top_k, top_p, u):
 def sample(logits_f32, temperature, top_k, top_p, u):
     return np.array([sample_row(logits_f32[r], temperature, top_k, top_p, u[r])[0] for r in range(logits_f32.shape[0])],
                     dtype=np.int32)
+
+
+def uniform(seed, step, row):
+    """u in [0, 1) for token `step` of a generation and batch row `row`: the runner's stateless hash
+    (teenygrad_b200/csrc/sampling.cu, sampling_uniform_kernel), restated on Python integers."""
+    m = (1 << 64) - 1
+    x = (seed ^ (step * 0x9E3779B97F4A7C15) ^ (row * 0xBF58476D1CE4E5B9)) & m
+    x ^= x >> 30; x = (x * 0xBF58476D1CE4E5B9) & m
+    x ^= x >> 27; x = (x * 0x94D049BB133111EB) & m
+    x ^= x >> 31
+    return np.float32(x >> 40) * np.float32(1.0 / 16777216.0)

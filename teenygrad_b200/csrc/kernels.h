@@ -138,5 +138,7 @@ int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, i
 // out_prob[r] (optional) = its probability inside the nucleus.  u[r] in [0, 1) is the caller's random number.
 int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols, float temperature, int top_k,
                             float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st);
+// u[row] = uniform in [0, 1) from (seed, step, row) by a stateless hash; step from *step_dev when given.
+int sampling_uniform(unsigned long long seed, int step, const int* step_dev, float* u, int rows, cudaStream_t st);
 
 }  // namespace teeny

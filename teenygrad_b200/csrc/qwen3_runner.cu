@@ -189,7 +189,7 @@ struct LayerWeights {
 
 struct Workspace {
   // offsets into the caller's workspace
-  size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters;
+  size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters, sample_u;
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
   size_t gemm_scratch_bytes, attn_scratch_bytes, attn_counter_bytes, cache_layer_elems;
 };
@@ -219,6 +219,10 @@ struct teeny_qwen3 {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_ready = nullptr, ev_done[2] = {nullptr, nullptr};
   bool overlap_prefill = false;
+  // token selection: greedy unless a temperature > 0 was set (single GPU only)
+  float sample_temperature = 0.0f, sample_top_p = 1.0f;
+  int sample_top_k = 1;
+  unsigned long long sample_seed = 0;
   int graph_batch = 0;
   int batch = 0;  // batch of the running generation (set by prefill)
   bool tables_ready = false;
@@ -279,6 +283,7 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.attn_scratch = take(w.attn_scratch_bytes);
   w.attn_counter_bytes = Bm * static_cast<size_t>(c.num_kv_heads) * 4;  // arrival counters of the split-sequence merge
   w.attn_counters = take(w.attn_counter_bytes);
+  w.sample_u = take(Bm * 4);
   w.cand_val = take(Bm * 4);
   w.cand_idx = take(Bm * 4);
   w.gather_val = take(Bm * 4 * tp);
@@ -488,7 +493,7 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
 }
 
 // Final norm on the last token of each sequence, LM head, greedy pick.  Leaves next ids in off.next_ids.
-int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
+int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st, const int* step_dev = nullptr) {
   const teeny_qwen3_config& c = m->cfg;
   const int H = c.hidden, Vl = m->Vl;
   bf16 *h = m->at<bf16>(m->off.h), *y = m->at<bf16>(m->off.y), *delta = m->at<bf16>(m->off.delta);
@@ -503,6 +508,14 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st) {
   int* ci = m->at<int>(m->off.cand_idx);
   int* next = m->at<int>(m->off.next_ids);
   if (c.tp_size == 1) {
+    if (m->sample_temperature > 0.0f) {
+      // token t of a generation draws u from (seed, t, row): t = 0 at prefill, the running count in decode
+      float* u = m->at<float>(m->off.sample_u);
+      TEENY_TRY(sampling_uniform(m->sample_seed, 0, S > 1 || !step_dev ? nullptr : step_dev, u, B, st));
+      TEENY_TRY(sample_top_k_top_p_bf16(logits, Vl, B, Vl, m->sample_temperature, m->sample_top_k, m->sample_top_p, u, next,
+                                        nullptr, st));
+      return 0;
+    }
     TEENY_TRY(argmax_bf16(logits, Vl, cv, next, B, Vl, 0, st));
     return 0;
   }
@@ -536,7 +549,7 @@ int decode_body(teeny_qwen3* m, int B, cudaStream_t st) {
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(m->at<int>(m->off.cur_ids), m->embed, m->at<bf16>(m->off.h), B, c.hidden, c.vocab, st));
   TEENY_TRY(run_layers(m, B, 1, 0, state + 0, state + 1, true, st));
-  TEENY_TRY(run_head(m, B, 1, st));
+  TEENY_TRY(run_head(m, B, 1, st, state + 2));
   unsigned* tp_epoch = (m->tp && m->tp->peer_ok) ? m->tp->epoch() : nullptr;
   launch_kernel(finish_step_kernel, dim3(1), dim3(1024), 0, st, 1, m->at<int>(m->off.next_ids), m->at<int>(m->off.cur_ids),
                                          m->at<int>(m->off.history), state, B, c.max_new_tokens, tp_epoch);
@@ -698,6 +711,21 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
 int teeny_qwen3_decode(teeny_qwen3* m, teeny_stream_t stream) {
   if (!m || m->batch <= 0) return TEENY_ERR_BAD_ARG;
   return decode_body(m, m->batch, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int teeny_qwen3_set_sampling(teeny_qwen3* m, float temperature, int top_k, float top_p, unsigned long long seed) {
+  if (!m) return TEENY_ERR_BAD_ARG;
+  if (temperature > 0.0f) {
+    if (m->cfg.tp_size != 1 || top_k < 1 || top_k > 1024 || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
+    m->sample_temperature = temperature; m->sample_top_k = top_k; m->sample_top_p = top_p; m->sample_seed = seed;
+  } else {
+    m->sample_temperature = 0.0f;
+  }
+  if (m->graph_exec) {  // the captured step has the old selection baked in
+    cudaGraphExecDestroy(m->graph_exec);
+    m->graph_exec = nullptr;
+  }
+  return TEENY_OK;
 }
 
 int teeny_qwen3_capture_decode(teeny_qwen3* m, teeny_stream_t stream) {

@@ -146,7 +146,29 @@ sample_top_k_top_p_kernel(const bf16* __restrict__ logits, long long ld, int col
   }
 }
 
+// u[row] in [0, 1) as a pure function of (seed, step, row): a splitmix64 finaliser over the three, top 24 bits.
+// (oracle/sampling.py restates it, so a generation can be replayed on the CPU.)
+__global__ void sampling_uniform_kernel(unsigned long long seed, int step, const int* __restrict__ step_dev,
+                                        float* __restrict__ u, int rows) {
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const unsigned long long t = static_cast<unsigned long long>(step_dev ? *step_dev : step);
+  unsigned long long x = seed ^ (t * 0x9E3779B97F4A7C15ull) ^ (static_cast<unsigned long long>(r) * 0xBF58476D1CE4E5B9ull);
+  x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+  x ^= x >> 27; x *= 0x94D049BB133111EBull;
+  x ^= x >> 31;
+  u[r] = static_cast<float>(x >> 40) * (1.0f / 16777216.0f);
+}
+
 }  // namespace
+
+int sampling_uniform(unsigned long long seed, int step, const int* step_dev, float* u, int rows, cudaStream_t st) {
+  if (!u || rows < 0) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  launch_kernel(sampling_uniform_kernel, dim3((rows + 127) / 128), dim3(128), 0, st, 1, seed, step, step_dev, u, rows);
+  return static_cast<int>(cudaGetLastError());
+}
 
 int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols, float temperature, int top_k,
                             float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st) {

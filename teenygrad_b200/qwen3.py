@@ -30,6 +30,7 @@ SIGNATURES = {
     "teeny_qwen3_set_weight": (i32, [vp, i32, i32, vp]),
     "teeny_qwen3_prefill": (i32, [vp, vp, i32, i32, vp]),
     "teeny_qwen3_decode": (i32, [vp, vp]),
+    "teeny_qwen3_set_sampling": (i32, [vp, f32, i32, f32, C.c_ulonglong]),
     "teeny_qwen3_capture_decode": (i32, [vp, vp]),
     "teeny_qwen3_decode_replay": (i32, [vp, vp]),
     "teeny_qwen3_buffer": (vp, [vp, i32]),
@@ -160,6 +161,13 @@ class Qwen3Runner:
         self.batch = B
         self._captured = False
         check(lib.teeny_qwen3_prefill(self._h, C.c_void_p(ids.data_ptr()), B, S, _stream()), "teeny_qwen3_prefill")
+
+    def set_sampling(self, temperature, top_k=50, top_p=1.0, seed=0):
+        """Token selection for the following generations: ``temperature <= 0`` is greedy; otherwise temperature /
+        top-k / top-p sampling with u for token t and row r a stateless hash of (seed, t, r) (single GPU only)."""
+        check(lib.teeny_qwen3_set_sampling(self._h, float(temperature), int(top_k), float(top_p), int(seed)),
+              "teeny_qwen3_set_sampling")
+        self._captured = False
 
     def decode_step(self, graph=False):
         if graph:

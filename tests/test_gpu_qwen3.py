@@ -87,3 +87,44 @@ def test_weights_from_a_sharded_safetensors_checkpoint(q, tmp_path):
         outs.append(r.generate(ids, 8).cpu())
     assert torch.equal(outs[0], outs[1])
     assert torch.equal(outs[0].long(), oq.OracleQwen3(ocfg, sd).generate(ids, 8))
+
+
+def test_sampling_in_the_runner(q):
+    """top-k 1 sampling equals greedy; with a temperature every chosen token is the oracle sampler's pick for the
+    runner's own logits of that step and the hashed u of (seed, step, row), eager and graph-replayed alike."""
+    import numpy as np
+    from oracle import qwen3 as oq
+    from oracle import sampling as osamp
+    ocfg = oq.OracleQwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
+    sd = oq.make_weights(ocfg, 13)
+    ids = torch.randint(0, 1024, (3, 20), generator=torch.Generator().manual_seed(2))
+    cfg = q.Qwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
+    r = q.Qwen3Runner(cfg, max_batch=3, max_len=40, max_new_tokens=10)
+    r.load_state_dict(sd)
+    greedy = r.generate(ids, 10).cpu().clone()
+    r.set_sampling(0.7, top_k=1, top_p=1.0, seed=5)
+    assert torch.equal(r.generate(ids, 10).cpu(), greedy)
+    runs = []
+    for graph in (False, True):
+        r.set_sampling(0.9, top_k=40, top_p=0.9, seed=1234)
+        r.prefill(ids)
+        logits = [r.logits().float().cpu().numpy()]
+        for _ in range(9):
+            r.decode_step(graph=graph)
+            logits.append(r.logits().float().cpu().numpy())
+        got = r.history()[:10].t().cpu().numpy()
+        runs.append(got)
+        for t in range(10):
+            for row in range(3):
+                u = osamp.uniform(1234, t, row)
+                want, _, c, n, cand = osamp.sample_row(logits[t][row], 0.9, 40, 0.9, float(u))
+                if got[row, t] != want:  # only a CDF boundary within float noise may differ
+                    cl = list(cand)
+                    i = cl.index(got[row, t])
+                    lo = c[i - 1] if i > 0 else 0.0
+                    assert lo - 1e-5 * c[n - 1] <= u * c[n - 1] <= c[i] + 1e-5 * c[n - 1]
+    assert np.array_equal(runs[0], runs[1])
+    assert not np.array_equal(runs[0], greedy.numpy()), "sampling at temperature 0.9 reproduced the greedy ids"
+    r.set_sampling(0.0)
+    assert torch.equal(r.generate(ids, 10).cpu(), greedy)
+    assert q.lib.teeny_device_error(1) == 0
