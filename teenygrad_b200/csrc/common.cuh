@@ -370,6 +370,17 @@ __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(_
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // Per-head RMSNorm followed by rotate-half RoPE for one 128-wide head spread over a half-warp: lane `sub` (0..15)
 // holds elements [8 sub, 8 sub + 8) of the head (raw), of the norm weight (wraw) and of the position's cos / sin rows
 // (craw, sraw); the rotate-half partner elements (d +- 64) live in lane sub ^ 8.  Every lane of the warp must call
@@ -389,17 +400,17 @@ __device__ __forceinline__ uint4 head_norm_rope(const uint4 raw, const uint4 wra
   const float rr = 1.0f / sqrtf(sq * (1.0f / 128.0f) + eps);
   const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w}, cw[4] = {craw.x, craw.y, craw.z, craw.w},
                  sw[4] = {sraw.x, sraw.y, sraw.z, sraw.w};
-  const float sign = (sub < 8) ? -1.0f : 1.0f;  // rotate_half: the first half gets -x[d + 64]
+  const uint32_t flip = (sub < 8) ? 0x80008000u : 0u;  // rotate_half: the first half gets -x[d + 64]
   uint32_t out[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {  // two elements at a time: every rounding is one packed conversion
+  for (int e = 0; e < 4; ++e) {
+    // Two elements at a time.  A product of two bf16 values is exact in f32, and so is their sum unless it is far
+    // below the result's rounding step, so the packed bf16 multiply / add (one rounding) equal the f32 operation
+    // followed by a rounding to bf16.
     const uint32_t xn = pack_bf16x2(bf16_lo(rw[e]) * rr, bf16_hi(rw[e]) * rr);
-    // normed head, a bf16 tensor in the traced graph
-    const uint32_t n = pack_bf16x2(bf16_lo(xn) * bf16_lo(ww[e]), bf16_hi(xn) * bf16_hi(ww[e]));
-    const uint32_t partner = __shfl_xor_sync(0xffffffffu, n, 8);
-    const uint32_t nc = pack_bf16x2(bf16_lo(n) * bf16_lo(cw[e]), bf16_hi(n) * bf16_hi(cw[e]));
-    const uint32_t rs = pack_bf16x2(sign * bf16_lo(partner) * bf16_lo(sw[e]), sign * bf16_hi(partner) * bf16_hi(sw[e]));
-    out[e] = pack_bf16x2(bf16_lo(nc) + bf16_lo(rs), bf16_hi(nc) + bf16_hi(rs));
+    const uint32_t n = bf16x2_mul(xn, ww[e]);  // normed head, a bf16 tensor in the traced graph
+    const uint32_t partner = __shfl_xor_sync(0xffffffffu, n, 8) ^ flip;
+    out[e] = bf16x2_add(bf16x2_mul(n, cw[e]), bf16x2_mul(partner, sw[e]));
   }
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
