@@ -35,6 +35,8 @@ METRIC = "qwen3_8b_tokens_per_s"
 UNIT = "tok/s"
 # bounded CPU sample of the workload (sized for roughly 10-30 s of host work on a 16-thread box)
 CPU_SAMPLE = dict(sample_layers=4, batch=16, prefill=2048, new_tokens=16)
+# per-step sample of the --impl reference arm: a quarter of that, so warm-up + steps stay within a few minutes
+REF_SAMPLE = dict(sample_layers=2, batch=8, prefill=2048, new_tokens=8)
 
 
 def parse_args():
@@ -167,11 +169,11 @@ def reference_arm(args, cfg_kwargs):
     vals = []
     desc, threads = "", 1
     for i in range(args.warmup + args.steps):
-        v, desc, threads = cpu_generation_rate(cfg_kwargs, **CPU_SAMPLE)
+        v, desc, threads = cpu_generation_rate(cfg_kwargs, **REF_SAMPLE)
         if i >= args.warmup:
             vals.append(v)
     value = sum(vals) / len(vals)
-    tokens = CPU_SAMPLE['batch'] * (CPU_SAMPLE['prefill'] + CPU_SAMPLE['new_tokens'])
+    tokens = REF_SAMPLE['batch'] * (REF_SAMPLE['prefill'] + REF_SAMPLE['new_tokens'])
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * tokens / value,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
