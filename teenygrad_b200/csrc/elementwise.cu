@@ -363,6 +363,130 @@ __global__ void gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_
   }
 }
 
+// ---- the same epilogue in two hops, for wider tensor parallelism ----
+// Pushing every rank's partial rows to every rank costs world x the tensor per rank.  Here token row r has one owner
+// (rank r / owner_rows): the GEMMs push row r only to its owner; the owner's CTA sums the world partials, adds the
+// residual, normalises, keeps the new residual and the normed row and stores both, stamped, into every other rank's
+// broadcast buffer; every other rank's CTA for row r waits for that row and unpacks it.  Traffic per rank is about
+// twice the tensor instead of world times it, for one more NVLink latency.
+// bcast[p]: rank p's broadcast buffer (this rank's own entry = local); a row is N / 2 lines of
+// {residual pair, stamp, normed pair, stamp}.
+template <int VPT>
+__global__ void gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world, int rank,
+                                                 int owner_rows, uint4* const* __restrict__ bcast,
+                                                 const unsigned* __restrict__ epoch, unsigned round,
+                                                 bf16* __restrict__ res, long long ldr, bf16* __restrict__ y,
+                                                 long long ldy, const bf16* __restrict__ w, int N, float eps, int* err) {
+  const int nv = N >> 3;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 g[VPT];  // norm weights: constant, fetched ahead of the wait
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    g[i] = idx < nv ? __ldg(wr + idx) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float red[32];
+  const unsigned stamp = __ldcg(epoch) * 1024u + round + 1u;
+  const int row = blockIdx.x;
+  const int owner = row / owner_rows;
+  uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
+  uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
+  const size_t brow = static_cast<size_t>(row) * (N >> 1);  // lines per row in a broadcast buffer
+  uint64_t t0 = 0;
+  bool live = true;
+  auto poll4 = [&](const uint4* src, uint4 (&q)[4]) {  // four 16-byte lines, each half carrying its own stamp
+    for (uint32_t it = 0;; ++it) {
+      bool all = true;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        q[k] = ld_volatile_u4(src + k);
+        all = all && (q[k].y == stamp) && (q[k].w == stamp);
+      }
+      if (all || !live) break;
+      if ((it & 0x3f) == 0x3f) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); live = false; }
+      }
+    }
+  };
+  if (owner != rank) {
+    // this row is reduced elsewhere: take the finished residual and normed row from the owner's broadcast
+    const uint4* src = bcast[rank] + brow;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nv) {
+        uint4 q[4];
+        poll4(src + 4 * idx, q);
+        rr4[idx] = make_uint4(q[0].x, q[1].x, q[2].x, q[3].x);
+        yr[idx] = make_uint4(q[0].z, q[1].z, q[2].z, q[3].z);
+      }
+    }
+    return;
+  }
+  float v[VPT][8];
+  float sq = 0.0f;
+  uint32_t hp[VPT][4];
+  uint4 hb[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    hb[i] = idx < nv ? rr4[idx] : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < world; ++p) {  // rank order: the one owner's result is what every rank gets
+        const uint4* src = reinterpret_cast<const uint4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 4 * idx;
+        uint4 q[4];
+        poll4(src, q);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          sum[2 * k] += __uint_as_float(q[k].x);
+          sum[2 * k + 1] += __uint_as_float(q[k].z);
+        }
+      }
+      const uint32_t hw[4] = {hb[i].x, hb[i].y, hb[i].z, hb[i].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float lo = bf16_round(bf16_lo(hw[e]) + bf16_round(sum[2 * e]));      // projection is a bf16 tensor
+        const float hi = bf16_round(bf16_hi(hw[e]) + bf16_round(sum[2 * e + 1]));
+        v[i][2 * e] = lo;
+        v[i][2 * e + 1] = hi;
+        hp[i][e] = pack_bf16x2(lo, hi);
+      }
+      rr4[idx] = make_uint4(hp[i][0], hp[i][1], hp[i][2], hp[i][3]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
+    }
+  }
+  sq = block_sum(sq, red);
+  const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      const uint32_t gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        ow[e] = pack_bf16x2(bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]), bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]));
+      yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      for (int p = 0; p < world; ++p) {  // NVLink stores to the other ranks
+        if (p == rank) continue;
+        uint4* dst = bcast[p] + brow + 4 * idx;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(hp[i][e], stamp, ow[e], stamp);
+      }
+    }
+  }
+}
+
 // ---- SiLU(gate) * up on the fused [T, 2*inter] projection ----
 __global__ void silu_mul_bf16_kernel(const bf16* __restrict__ gu, long long ld, bf16* __restrict__ out, int T,
                                      int inter) {
@@ -622,6 +746,27 @@ int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, co
 #define TEENY_GATHER_CASE(V)                                                                                       \
   launch_kernel(gather_add_rms_norm_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, epoch, round, \
                 residual, ldr, y, ldy, w, N, eps, err)
+  if (vpt <= 1) TEENY_GATHER_CASE(1);
+  else if (vpt <= 2) TEENY_GATHER_CASE(2);
+  else TEENY_GATHER_CASE(4);
+#undef TEENY_GATHER_CASE
+  return static_cast<int>(cudaGetLastError());
+}
+int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int world, int rank, int owner_rows,
+                                   uint4* const* bcast, const unsigned* epoch, unsigned round, bf16* residual,
+                                   long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N, float eps,
+                                   cudaStream_t st) {
+  if (!recv || !bcast || !epoch || !residual || !y || !w || world < 2 || rank < 0 || rank >= world || owner_rows <= 0 ||
+      M <= 0 || M > owner_rows * world || N <= 0 || round >= 1023)
+    return TEENY_ERR_BAD_ARG;
+  if (N % 8 || ldr % 8 || ldy % 8 || N > 8 * 4 * 512) return TEENY_ERR_BAD_ARG;
+  if (!aligned16(recv) || !aligned16(residual) || !aligned16(y) || !aligned16(w) || (slot_elems % 2)) return TEENY_ERR_ALIGNMENT;
+  const int nv = N / 8;
+  const int threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32, vpt = (nv + threads - 1) / threads;
+  int* err = device_error_word();
+#define TEENY_GATHER_CASE(V)                                                                                          \
+  launch_kernel(gather_add_rms_norm_owner_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, rank, \
+                owner_rows, bcast, epoch, round, residual, ldr, y, ldy, w, N, eps, err)
   if (vpt <= 1) TEENY_GATHER_CASE(1);
   else if (vpt <= 2) TEENY_GATHER_CASE(2);
   else TEENY_GATHER_CASE(4);

@@ -53,6 +53,7 @@ struct GemmArgs {
   const unsigned* push_epoch; // stamp of the pushed {value, stamp} pairs = *push_epoch * 1024 + push_round + 1
   unsigned push_round;
   int push_world;
+  int push_owner_rows;        // > 0: token row c goes only to rank c / push_owner_rows (which reduces it); 0: to every rank
   int* err;
 };
 
@@ -484,7 +485,9 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                 const float v = __uint_as_float(r[e]) + bias;
                 if (args.push_recv) {
                   const size_t off = static_cast<size_t>(c) * args.N + n;
-                  for (int p = 0; p < args.push_world; ++p)  // NVLink stores
+                  const int p0 = args.push_owner_rows > 0 ? c / args.push_owner_rows : 0;
+                  const int p1 = args.push_owner_rows > 0 ? p0 + 1 : args.push_world;
+                  for (int p = p0; p < p1; ++p)  // NVLink stores
                     args.push_recv[p][off] = make_uint2(__float_as_uint(v), stamp);
                 } else {
                   args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(v);
@@ -571,7 +574,9 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           }
           if (args.push_recv) {
             const size_t off = static_cast<size_t>(c) * args.N + n;
-            for (int p = 0; p < args.push_world; ++p) {  // NVLink stores: two 16-byte {v, stamp, v, stamp} lines
+            const int p0 = args.push_owner_rows > 0 ? c / args.push_owner_rows : 0;
+            const int p1 = args.push_owner_rows > 0 ? p0 + 1 : args.push_world;
+            for (int p = p0; p < p1; ++p) {  // NVLink stores: two 16-byte {v, stamp, v, stamp} lines
               if (vec_ok) {
                 uint4* dst = reinterpret_cast<uint4*>(args.push_recv[p] + off);
                 dst[0] = make_uint4(__float_as_uint(o[0]), stamp, __float_as_uint(o[1]), stamp);
@@ -703,6 +708,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
     a.push_epoch = push->epoch;
     a.push_round = push->round;
     a.push_world = push->world;
+    a.push_owner_rows = push->owner_rows;
   }
   a.err = device_error_word();
   const int sms = sm_count();

@@ -31,6 +31,7 @@ struct GemmPush {
   int world;
   const unsigned* epoch;  // device word, constant while the kernel runs
   unsigned round;         // < 1023
+  int owner_rows;         // 0: every rank receives every row; > 0: row r goes only to rank r / owner_rows, which sums it
 };
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
               int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false,
@@ -42,6 +43,13 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
 int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
                              bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,
                              float eps, cudaStream_t st);
+// The same in two hops: row r is summed and normalised only by rank r / owner_rows (the GEMMs pushed it only there,
+// GemmPush::owner_rows), which then stores the new residual row and the normed row, stamped, into every other rank's
+// broadcast buffer bcast[p] (device array [world], own entry unused); the other ranks' CTAs wait for their copy.
+int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int world, int rank, int owner_rows,
+                                   uint4* const* bcast, const unsigned* epoch, unsigned round, bf16* residual,
+                                   long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N, float eps,
+                                   cudaStream_t st);
 // Large-M path on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); same contract as gemm_bf16 without the options.
 int gemm_bf16_2cta_prepare();
 int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* bias, bf16* y, int ldy, int M, int N,

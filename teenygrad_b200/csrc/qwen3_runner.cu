@@ -78,6 +78,11 @@ struct TpContext {
   uint8_t* local = nullptr;    // [2 parities][world][rows][cols] {f32 value, u32 stamp} pairs, then the epoch word
   void* peer[8] = {};          // the same buffer of every rank (own entry = local)
   uint2** recv_tab = nullptr;  // device [2][world]: where this rank writes inside rank q's buffer
+  // Two-hop mode (row owners reduce, then broadcast the finished rows): per parity a [rows][cols / 2] array of
+  // 16-byte lines behind the epoch word in every rank's buffer; bcast_tab is device [2][world].
+  bool two_hop = false;
+  size_t bcast_off = 0;
+  uint4** bcast_tab = nullptr;
   const uint2* local_recv(int parity) const {
     return reinterpret_cast<const uint2*>(local) + static_cast<size_t>(parity) * world * slot_elems;
   }
@@ -95,8 +100,16 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   int ok = 1;
   cudaIpcMemHandle_t mine;
   uint8_t* xbuf = nullptr;
-  if (cudaMalloc(&c->local, c->data_bytes + 256) != cudaSuccess) ok = 0;
-  if (ok && cudaMemsetAsync(c->local, 0, c->data_bytes + 256, st) != cudaSuccess) ok = 0;
+  c->bcast_off = c->data_bytes + 256;
+  const size_t bcast_bytes = 2 * c->slot_elems * 8;  // 2 parities x rows x cols / 2 lines of 16 bytes
+  const size_t total_bytes = c->bcast_off + bcast_bytes;
+  {
+    // one hop (every rank gets every partial) costs world x the tensor per rank: from 4 ranks on, two hops win
+    const char* e = getenv("TEENY_TP_HOPS");
+    c->two_hop = e ? (e[0] == '2') : (c->world >= 4);
+  }
+  if (cudaMalloc(&c->local, total_bytes) != cudaSuccess) ok = 0;
+  if (ok && cudaMemsetAsync(c->local, 0, total_bytes, st) != cudaSuccess) ok = 0;
   if (ok && cudaIpcGetMemHandle(&mine, c->local) != cudaSuccess) ok = 0;
   const size_t rec = sizeof(mine) + 8;
   if (cudaMalloc(&xbuf, rec * c->world) != cudaSuccess) return TEENY_ERR_BAD_ARG;
@@ -145,6 +158,13 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
           reinterpret_cast<uint2*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
   if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(uint2*)) != cudaSuccess) return 0;
   cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(uint2*), cudaMemcpyHostToDevice);
+  std::vector<uint4*> bt(2 * c->world);
+  for (int par = 0; par < 2; ++par)
+    for (int q = 0; q < c->world; ++q)
+      bt[par * c->world + q] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(c->peer[q]) + c->bcast_off) +
+                               static_cast<size_t>(par) * (c->slot_elems / 2);
+  if (cudaMalloc(&c->bcast_tab, bt.size() * sizeof(uint4*)) != cudaSuccess) return 0;
+  cudaMemcpy(c->bcast_tab, bt.data(), bt.size() * sizeof(uint4*), cudaMemcpyHostToDevice);
   c->peer_ok = true;
   return 0;
 }
@@ -318,7 +338,9 @@ int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const bf16* w, bf16* de
   TpContext* tp = m->tp;
   if (decode && tp && tp->peer_ok && T <= static_cast<int>(tp->rows) && N == static_cast<int>(tp->cols)) {
     const int parity = m->push_round & 1;
-    GemmPush push{tp->recv_tab + parity * tp->world, tp->world, tp->epoch(), static_cast<unsigned>(m->push_round)};
+    const int owner_rows = tp->two_hop ? (T + tp->world - 1) / tp->world : 0;
+    GemmPush push{tp->recv_tab + parity * tp->world, tp->world, tp->epoch(), static_cast<unsigned>(m->push_round),
+                  owner_rows};
     TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st, false, &push));
     m->pending_gather = true;
     m->pending_parity = parity;
@@ -336,6 +358,10 @@ int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, c
   if (m->pending_gather) {
     m->pending_gather = false;
     TpContext* tp = m->tp;
+    if (tp->two_hop)
+      return gather_add_rms_norm_owner_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world, tp->rank,
+                                            (M + tp->world - 1) / tp->world, tp->bcast_tab + m->pending_parity * tp->world,
+                                            tp->epoch(), m->pending_round, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
     return gather_add_rms_norm_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world, tp->epoch(),
                                     m->pending_round, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
   }
@@ -817,6 +843,7 @@ int teeny_tp_destroy(void* ctx) {
     if (c->peer_ok && q != c->rank && c->peer[q]) cudaIpcCloseMemHandle(c->peer[q]);
   if (c->local) cudaFree(c->local);
   if (c->recv_tab) cudaFree(c->recv_tab);
+  if (c->bcast_tab) cudaFree(c->bcast_tab);
   const bool ok = g_nccl.CommDestroy(c->comm) == ncclSuccess;
   delete c;
   return ok ? 0 : TEENY_ERR_NCCL;

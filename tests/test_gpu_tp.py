@@ -18,7 +18,13 @@ def test_tensor_parallel_matches_oracle(world):
     port = 29500 + world
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
-    # also exercise the opt-in prefill that overlaps its all-reduces with the other half-batch's compute
-    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, TEENY_TP_OVERLAP="1"))
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    assert f"TP{world} B4 S128 OK" in res.stdout and f"TP{world} B3 S40 OK" in res.stdout
+    # Also exercise the opt-in prefill that overlaps its all-reduces with the other half-batch's compute.  The decode
+    # reduction has two forms (every rank gets every partial / row owners reduce and broadcast; the default switches
+    # at 4 ranks): two ranks run both, wider runs their default.
+    for hops in (("1", "2") if world == 2 else ("",)):
+        env = dict(os.environ, TEENY_TP_OVERLAP="1")
+        if hops:
+            env["TEENY_TP_HOPS"] = hops
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+        assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+        assert f"TP{world} B4 S128 OK" in res.stdout and f"TP{world} B3 S40 OK" in res.stdout
