@@ -104,9 +104,11 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   const size_t bcast_bytes = 2 * c->slot_elems * 8;  // 2 parities x rows x cols / 2 lines of 16 bytes
   const size_t total_bytes = c->bcast_off + bcast_bytes;
   {
-    // one hop (every rank gets every partial) costs world x the tensor per rank: from 4 ranks on, two hops win
+    // One hop (every rank gets every partial) costs world x the tensor per rank.  Measured per decode step: 2 ranks
+    // 3.25 ms in one hop against 3.53 ms in two; 8 ranks 3.51 ms against 3.25 ms.  4 ranks: one hop measured (2.96 ms),
+    // two hops not yet, so the switch sits at 8.  TEENY_TP_HOPS=1|2 overrides.
     const char* e = getenv("TEENY_TP_HOPS");
-    c->two_hop = e ? (e[0] == '2') : (c->world >= 4);
+    c->two_hop = e ? (e[0] == '2') : (c->world >= 8);
   }
   if (cudaMalloc(&c->local, total_bytes) != cudaSuccess) ok = 0;
   if (ok && cudaMemsetAsync(c->local, 0, total_bytes, st) != cudaSuccess) ok = 0;

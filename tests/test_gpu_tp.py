@@ -20,8 +20,8 @@ def test_tensor_parallel_matches_oracle(world):
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "tp_worker.py")]
     # Also exercise the opt-in prefill that overlaps its all-reduces with the other half-batch's compute.  The decode
     # reduction has two forms (every rank gets every partial / row owners reduce and broadcast; the default switches
-    # at 4 ranks): two ranks run both, wider runs their default.
-    for hops in (("1", "2") if world == 2 else ("",)):
+    # at 8 ranks): two ranks run both, four run the two-hop form too, eight their default.
+    for hops in {2: ("1", "2"), 4: ("", "2")}.get(world, ("",)):
         env = dict(os.environ, TEENY_TP_OVERLAP="1")
         if hops:
             env["TEENY_TP_HOPS"] = hops
