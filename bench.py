@@ -322,6 +322,8 @@ def main():
         return
 
     steps = args.steps
+    ov = os.environ.get("TEENY_TP_OVERLAP")  # the library's default: overlapped from 8 ranks on
+    prefill_overlap = world > 1 and ((ov == "1") if ov else world >= 8)
     value = tokens_per_step * steps / (total_ms * 1e-3)
     decode_ms = total_ms - prefill_ms
     L = cfg.num_layers
@@ -336,7 +338,8 @@ def main():
         "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {**workload_config(args, world), "tp_decode_reduction": tp_mode, "tp_prefill_reduction":
-                   "none" if world == 1 else "nccl-allreduce"},
+                   "none" if world == 1 else ("nccl-allreduce, overlapped with the other half-batch's compute"
+                                              if prefill_overlap else "nccl-allreduce")},
         "phases": {"prefill_ms": prefill_ms / steps, "decode_ms": decode_ms / steps,
                    "prefill_tok_s": B * S * steps / (prefill_ms * 1e-3),
                    "decode_tok_s": B * (NEW - 1) * steps / (decode_ms * 1e-3),

@@ -436,7 +436,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
 int comm_sms() {  // TEENY_TP_COMM_SMS overrides (0 = the GEMMs keep every SM)
   static const int n = [] {
     const char* e = getenv("TEENY_TP_COMM_SMS");
-    const int v = e ? atoi(e) : 8;
+    const int v = e ? atoi(e) : 0;
     return v < 0 ? 0 : (v > 64 ? 64 : v);
   }();
   return n;
@@ -627,11 +627,14 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
     delete m;
     return prc;
   }
-  // Prefill with the all-reduces on their own stream: opt-in (TEENY_TP_OVERLAP=1).  Measured on 2 GPUs it does not
-  // pay (465 ms in line, 473 ms overlapped with no SMs reserved, 482 ms with 8 reserved: the exposed communication is
-  // only ~40 ms there and the collective's CTAs slow the GEMMs they share SMs with).
+  // Prefill with the all-reduces on their own stream.  Measured (prefill of 32 x 2048 tokens): 8 GPUs 186 ms against
+  // 210 ms in line, so it is the default from 8 ranks on; 2 GPUs 473 ms against 465 ms (only ~40 ms of communication
+  // are exposed there and the collective's CTAs slow the GEMMs they share SMs with), so it stays off below 8 (4 GPUs
+  // not measured).  Reserving SMs for the collective never paid (TEENY_TP_COMM_SMS, default 0).
+  // TEENY_TP_OVERLAP=0|1 overrides.
   const char* ov_env = getenv("TEENY_TP_OVERLAP");
-  if (m->tp && cfg->tp_size > 1 && ov_env && ov_env[0] == '1') {
+  const bool want_overlap = ov_env ? (ov_env[0] == '1') : (cfg->tp_size >= 8);
+  if (m->tp && cfg->tp_size > 1 && want_overlap) {
     bool ok = cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&m->ev_ready, cudaEventDisableTiming) == cudaSuccess;
     ok = ok && cudaEventCreateWithFlags(&m->ev_done[0], cudaEventDisableTiming) == cudaSuccess;
