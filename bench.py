@@ -1,21 +1,24 @@
 #!/usr/bin/env python
-"""Headline benchmark: Qwen3-8B-shaped greedy generation (batch 32, prefill 2048, 256 new tokens), bf16,
-tensor-parallel over N GPUs of one node; value = tokens (prompt + generated) per second over the whole job.
+"""Benchmarks of the GEMM / flash-attention / Qwen3-forward path, one JSON line per run.
 
-    python bench.py --gpus 1 --steps 3 --warmup 3
+    python bench.py --gpus 1 --steps 3 --warmup 3                # headline: BASELINE config 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench.py --gpus N --steps K --warmup W
-    python bench.py --impl reference ...      # CPU arm: the Qwen3 forward the reference runs (PyTorch CPU)
+    python bench.py --config 1|2|3|4                             # the other BASELINE configs (one GPU)
+    python bench.py --impl reference ...                         # CPU arm: what the reference runs for the path
 
-A "step" is one full generation: prefill of 32 x 2048 prompt tokens, then 255 CUDA-graph decode steps (the first
-new token comes out of the prefill).  Weights are seeded random-init tensors of the Qwen3-8B shapes and prompts are
-uniform random ids (no checkpoints or datasets on this machine): `data` says synthetic.
+Config 5 (default) and 4: Qwen3-8B / Qwen3-0.6B shaped greedy generation; a "step" is one full generation (prefill,
+then CUDA-graph decode steps; the first new token comes out of the prefill); value = tokens (prompt + generated) per
+second over the whole job, tensor-parallel over N GPUs for config 5.  Configs 1-3: one kernel (fp32 GEMM 512^3, the
+bf16 GEMM sweep, causal GQA flash attention with its decode variant); a step is one launch with an L2 flush before it.
+Weights and inputs are seeded random tensors of the configs' shapes (no checkpoints or datasets on this machine).
 
-One JSON line on stdout (rank 0).  `value` is timed with CUDA events with everything already on the device; `e2e`
-is the same job through the public API (`Qwen3Runner.generate`) with the prompt ids in pinned host memory and the
-generated ids copied back, host<->device copies inside the timed region.  `roofline` is for the dominant kernel,
-the tcgen05 GEMM, timed live on this run's four prefill GEMM shapes.  `cpu_baseline` is the CPU port of the path
-(oracle/qwen3.py, PyTorch CPU threads) timed on a bounded sample.
+`value` is timed with CUDA events with everything already on the device; `e2e` is the same work through the public
+API with inputs in pinned host memory and results copied back, copies inside the timed region.  `roofline` is the
+dominant kernel timed live; for the generation configs `roofline_prefill` and `roofline_decode` add the whole-phase
+figures.  `cpu_baseline` is the CPU port of the path timed on a bounded sample on the host cores.  `parity_check`
+(generation configs) compares sequence 0's first-token logits with the CPU oracle run at full depth on the same
+weights, after the timed region, so a wrong answer at the benchmark's size cannot print a throughput unnoticed.
 """
 import argparse
 import json
@@ -24,6 +27,7 @@ import subprocess
 import sys
 import threading
 import time
+import zlib
 
 _JSON_OUT = None  # duplicate of the original stdout, opened in main()
 
@@ -31,12 +35,21 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-METRIC = "qwen3_8b_tokens_per_s"
-UNIT = "tok/s"
-# bounded CPU sample of the workload (sized for roughly 10-30 s of host work on a 16-thread box)
-CPU_SAMPLE = dict(sample_layers=4, batch=16, prefill=2048, new_tokens=16)
-# per-step sample of the --impl reference arm: a quarter of that, so warm-up + steps stay within a few minutes
-REF_SAMPLE = dict(sample_layers=2, batch=8, prefill=2048, new_tokens=8)
+# bounded CPU samples of the generation workloads (roughly 10-30 s of host work on a 16-thread box for cpu_baseline;
+# a quarter of that per step for the --impl reference arm, so warm-up + steps stay within a few minutes)
+CPU_SAMPLE = {5: dict(sample_layers=4, batch=16, prefill=2048, new_tokens=16),
+              4: dict(sample_layers=28, batch=1, prefill=512, new_tokens=32)}
+REF_SAMPLE = {5: dict(sample_layers=2, batch=8, prefill=2048, new_tokens=8),
+              4: dict(sample_layers=28, batch=1, prefill=512, new_tokens=16)}
+MODEL = {5: dict(num_layers=36, hidden=4096, num_q_heads=32, num_kv_heads=8, head_dim=128, intermediate=12288,
+                 vocab=151936, eps=1e-6, rope_theta=1e6, tied=False),
+         4: dict(num_layers=28, hidden=1024, num_q_heads=16, num_kv_heads=8, head_dim=128, intermediate=3072,
+                 vocab=151936, eps=1e-6, rope_theta=1e6, tied=True)}
+WORKLOAD = {5: dict(batch=32, prefill=2048, new_tokens=256, seed=4, name="Qwen3-8B"),
+            4: dict(batch=1, prefill=512, new_tokens=128, seed=3, name="Qwen3-0.6B")}
+METRIC = {1: ("gemm_f32_512_tflops", "TFLOP/s"), 2: ("gemm_bf16_4096x12288x4096_tflops", "TFLOP/s"),
+          3: ("flash_attn_causal_b4_h32_s4096_tflops", "TFLOP/s"), 4: ("qwen3_0_6b_tokens_per_s", "tok/s"),
+          5: ("qwen3_8b_tokens_per_s", "tok/s")}
 
 
 def parse_args():
@@ -45,13 +58,28 @@ def parse_args():
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    # workload knobs (defaults = BASELINE config 5); smaller values are for debugging only and are echoed in `config`
-    p.add_argument("--layers", type=int, default=36)
-    p.add_argument("--batch", type=int, default=32)
-    p.add_argument("--prefill", type=int, default=2048)
-    p.add_argument("--new-tokens", type=int, default=256)
+    p.add_argument("--config", type=int, default=5, choices=[1, 2, 3, 4, 5], help="BASELINE.json config (default 5)")
+    # workload knobs for debugging only (defaults = the BASELINE config); echoed in `config`
+    p.add_argument("--layers", type=int, default=None)
+    p.add_argument("--batch", type=int, default=None)
+    p.add_argument("--prefill", type=int, default=None)
+    p.add_argument("--new-tokens", type=int, default=None)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-verify", action="store_true", help="skip the CPU-oracle check of sequence 0 after the timing")
     return p.parse_args()
+
+
+def host_threads():
+    """Host cores this process may use (torch.distributed.run exports OMP_NUM_THREADS=1, which is not a property of the
+    machine: the CPU legs set their thread count from this instead)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def emit(line):
+    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
 
 
 # ------------------------------------------------------------------------------------------------ peaks / clocks
@@ -59,7 +87,7 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         d = json.load(open(path))
-        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained"),
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d.get("bf16_tflops_sustained") or d["bf16_tflops"],
                 "hbm_gbs": d["hbm_gbs"], "source": "measured"}
     return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
@@ -98,16 +126,16 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
-# ------------------------------------------------------------------------------------------------ CPU arm
-def cpu_generation_rate(cfg_kwargs, sample_layers, batch, prefill, new_tokens, threads=None):
+# ------------------------------------------------------------------------------------------------ CPU legs
+def cpu_generation_rate(cfg_kwargs, sample_layers, batch, prefill, new_tokens):
     """Times the CPU port of the path (oracle.qwen3.OracleQwen3 -- the op sequence HF transformers runs for the
     reference's Qwen3 script, on PyTorch CPU) on `sample_layers` layers of the real shapes and scales the layer time
-    to the full depth.  Returns (tok/s for the full-depth model on the sample's batch/prompt, description)."""
+    to the full depth.  Returns (tok/s for the full-depth model on the sample's batch / prompt, description, threads)."""
     import torch
     from oracle import qwen3 as oq
-    if threads:
-        torch.set_num_threads(threads)
+    torch.set_num_threads(host_threads())
     full_layers = cfg_kwargs["num_layers"]
+    sample_layers = min(sample_layers, full_layers)
     kw = dict(cfg_kwargs)
     kw["num_layers"] = sample_layers
     cfg = oq.OracleQwen3Config(**kw)
@@ -159,54 +187,271 @@ def cpu_generation_rate(cfg_kwargs, sample_layers, batch, prefill, new_tokens, t
     return tokens / t_full, desc, torch.get_num_threads()
 
 
-def reference_arm(args, cfg_kwargs):
-    """The reference's CPU execution of the path (its Qwen3 script runs the traced PyTorch graph on the CPU,
-    support/teeny-torch/python/teenygrad/atlas/module.py:42-45).  The Rust crates cannot be built here (no cargo,
-    no teenyc), so this times the CPU port of that op sequence on a bounded sample per step."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def cpu_kernel_rate(config):
+    """CPU leg of the single-kernel configs: (value in the config's unit, description, threads, seconds per sample)."""
+    import numpy as np
+    import torch
+    import torch.nn.functional as F
+    torch.set_num_threads(host_threads())
+    if config == 1:
+        # the reference's own CPU matmul for this workload is the test-side triple loop
+        # (kernels/teeny-kernels/tests/test_gemm.rs:183-196), restated in C in oracle/teeny_oracle.c: one thread
+        from oracle import cpu as oc
+        g = torch.Generator().manual_seed(0)
+        a, b = torch.randn(512, 512, generator=g).numpy(), torch.randn(512, 512, generator=g).numpy()
+        oc.matmul_f32(a, b)
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            oc.matmul_f32(a, b)
+        dt = (time.perf_counter() - t0) / reps
+        ta, tb = torch.from_numpy(a), torch.from_numpy(b)
+        torch.matmul(ta, tb)
+        t0 = time.perf_counter()
+        for _ in range(50):
+            torch.matmul(ta, tb)
+        dt2 = (time.perf_counter() - t0) / 50
+        fl = 2 * 512 ** 3
+        return fl / dt / 1e12, (f"sequential f32 triple loop (the reference's test-side matmul_reference restated in C), "
+                                f"512^3, {reps} runs; torch.matmul f32 on {torch.get_num_threads()} threads for comparison: "
+                                f"{fl / dt2 / 1e12:.4f} TFLOP/s"), 1, dt
+    if config == 2:
+        M, N, K = 4096, 12288, 4096
+        g = torch.Generator().manual_seed(1)
+        x = ((torch.rand(M // 4, K, generator=g) * 2 - 1) * 0.05).bfloat16()
+        w = ((torch.rand(N, K, generator=g) * 2 - 1) * 0.05).bfloat16()
+        F.linear(x.float(), w.float())
+        t0 = time.perf_counter()
+        F.linear(x.float(), w.float()).bfloat16()
+        dt = time.perf_counter() - t0
+        return 2.0 * (M // 4) * N * K / dt / 1e12, (f"F.linear on bf16 inputs up-cast to f32, a quarter of the rows "
+                                                     f"({M // 4} x {N} x {K}), {torch.get_num_threads()} threads"), torch.get_num_threads(), dt
+    if config == 3:
+        B, Hq, Hkv, S, D = 1, 32, 8, 4096, 128
+        g = torch.Generator().manual_seed(2)
+        q = torch.randn(B, Hq, S, D, generator=g).bfloat16()
+        k = torch.randn(B, Hkv, S, D, generator=g).bfloat16()
+        v = torch.randn(B, Hkv, S, D, generator=g).bfloat16()
+        rep = Hq // Hkv
+        t0 = time.perf_counter()
+        F.scaled_dot_product_attention(q.float(), k.float().repeat_interleave(rep, 1), v.float().repeat_interleave(rep, 1),
+                                       is_causal=True, scale=D ** -0.5).bfloat16()
+        dt = time.perf_counter() - t0
+        return 0.5 * 4 * B * Hq * S * S * D / dt / 1e12, (f"F.scaled_dot_product_attention (causal, KV heads repeated, f32) on "
+                                                          f"batch 1 of 4, {torch.get_num_threads()} threads; causal FLOP count"), torch.get_num_threads(), dt
+    raise ValueError(config)
+
+
+def reference_arm(args):
+    """The reference's CPU execution of the path.  Its Qwen3 script runs the traced PyTorch graph on the CPU
+    (support/teeny-torch/python/teenygrad/atlas/module.py:42-45) and its only CPU matmul is the test-side triple loop;
+    the Rust crates cannot be built here (no cargo, no teenyc), so this times the CPU port of those on a bounded sample
+    per step, on every host core.  Under torch.distributed.run only rank 0 works."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    vals = []
-    desc, threads = "", 1
+    cfgn = args.config
+    vals, desc, threads = [], "", 1
     for i in range(args.warmup + args.steps):
-        v, desc, threads = cpu_generation_rate(cfg_kwargs, **REF_SAMPLE)
+        if cfgn in (4, 5):
+            v, desc, threads = cpu_generation_rate(model_kwargs(args), **REF_SAMPLE[cfgn])
+        else:
+            v, desc, threads, sample_s = cpu_kernel_rate(cfgn)
         if i >= args.warmup:
             vals.append(v)
     value = sum(vals) / len(vals)
-    tokens = REF_SAMPLE['batch'] * (REF_SAMPLE['prefill'] + REF_SAMPLE['new_tokens'])
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * tokens / value,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+    metric, unit = METRIC[cfgn]
+    if cfgn in (4, 5):
+        s = REF_SAMPLE[cfgn]
+        ms = 1000.0 * s["batch"] * (s["prefill"] + s["new_tokens"]) / value
+    else:
+        ms = 1000.0 * sample_s
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32" if cfgn == 1 else "bf16", "data": "synthetic",
             "config": workload_config(args, args.gpus),
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
+            "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    emit(line)
+
+
+def model_kwargs(args):
+    kw = dict(MODEL[args.config])
+    if args.layers is not None:
+        kw["num_layers"] = args.layers
+    return kw
+
+
+def workload_of(args):
+    w = dict(WORKLOAD[args.config])
+    for k, a in (("batch", args.batch), ("prefill", args.prefill), ("new_tokens", args.new_tokens)):
+        if a is not None:
+            w[k] = a
+    return w
 
 
 def workload_config(args, n):
-    return {"workload": f"Qwen3-8B-shaped decoder ({args.layers} layers, hidden 4096, 32 q / 8 kv heads, head_dim 128, "
-                        f"intermediate 12288, vocab 151936, untied head), random-init bf16 seed 4; batch {args.batch}, "
-                        f"prefill {args.prefill} uniform-random ids, {args.new_tokens} greedy tokens",
-            "global_batch": args.batch, "seq_len": args.prefill, "new_tokens": args.new_tokens,
-            "parallelism": f"tp{n}", "l2": "inputs larger than L2 (16 GB of weights + KV cache stream every step)"}
+    c = args.config
+    if c in (4, 5):
+        kw, w = model_kwargs(args), workload_of(args)
+        return {"workload": f"{w['name']}-shaped decoder ({kw['num_layers']} layers, hidden {kw['hidden']}, {kw['num_q_heads']} q / "
+                            f"{kw['num_kv_heads']} kv heads, head_dim 128, intermediate {kw['intermediate']}, vocab {kw['vocab']}, "
+                            f"{'tied' if kw['tied'] else 'untied'} head), random-init bf16 seed {w['seed']}; batch {w['batch']}, "
+                            f"prefill {w['prefill']} uniform-random ids, {w['new_tokens']} greedy tokens",
+                "baseline_config": c, "global_batch": w["batch"], "seq_len": w["prefill"], "new_tokens": w["new_tokens"],
+                "parallelism": f"tp{n}", "l2": "inputs larger than L2 (weights + KV cache stream every step)"
+                if c == 5 else "L2 flushed between generations is not needed: 1.2 GB of weights stream every decode step"}
+    text = {1: "fp32 GEMM C = A B, A and B 512 x 512 row-major, N(0,1) seed 0",
+            2: "bf16 GEMM sweep, fp32 accumulate: N = K = 4096 with M in {1, 16, 128, 4096}, and M = 4096, N = 12288, K = 4096; "
+               "U(-1,1) * 0.05 seed 1, row-major A, K-major B; value = the M = 4096, N = 12288 shape",
+            3: "causal GQA flash-attention forward, bf16, batch 4, 32 / 8 heads, head_dim 128, sequence 4096, N(0,1) seed 2; "
+               "plus the decode variant (1 query token against 4096 cached)"}[c]
+    return {"workload": text, "baseline_config": c, "parallelism": "1 GPU",
+            "l2": "L2 flushed (256 MB write) before every timed launch"}
 
 
-# ------------------------------------------------------------------------------------------------ GPU arm
-def main():
-    args = parse_args()
-    # Keep stdout to the one JSON line: libraries write there at the file-descriptor level (NCCL prints its version
-    # banner to fd 1 at NCCL_DEBUG=VERSION and WARN), so fd 1 is pointed at stderr for the whole run and the line goes
-    # to a private duplicate of the original stdout.
-    global _JSON_OUT
-    sys.stdout.flush()
-    _JSON_OUT = os.fdopen(os.dup(1), "w")
-    os.dup2(2, 1)
-    cfg_kwargs = dict(num_layers=args.layers, hidden=4096, num_q_heads=32, num_kv_heads=8, head_dim=128,
-                      intermediate=12288, vocab=151936, eps=1e-6, rope_theta=1e6, tied=False)
-    if args.impl == "reference":
-        reference_arm(args, cfg_kwargs)
-        return
+# ------------------------------------------------------------------------------------------------ single-kernel configs
+def kernel_config(args):
+    import torch
+    from teenygrad_b200 import ops
+    from teenygrad_b200._lib import lib
+    if args.gpus != 1:
+        raise SystemExit("configs 1-3 are single-GPU kernels")
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    warm = max(args.warmup, 3)
 
+    def timed(fn, steps=args.steps):
+        for _ in range(warm):
+            fn()
+        ts = []
+        for _ in range(steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sum(ts) / len(ts)
+
+    def e2e_timed(host_inputs, run, out_dev_to_host):
+        """inputs from pinned host memory, result read back, all inside the timed region (wall clock around a sync)."""
+        def once():
+            devs = [h.to("cuda", non_blocking=True) for h in host_inputs]
+            out_dev_to_host(run(*devs))
+            torch.cuda.current_stream().synchronize()
+        for _ in range(2):
+            once()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            once()
+        return (time.perf_counter() - t0) / args.steps * 1e3
+
+    metric, unit = METRIC[args.config]
+    sampler = ClockSampler(0)
+    sampler.start()
+    lib.teeny_launch_count(1)
+    extra = {}
+    if args.config == 1:
+        g = torch.Generator().manual_seed(0)
+        ah, bh = torch.randn(512, 512, generator=g).pin_memory(), torch.randn(512, 512, generator=g).pin_memory()
+        a, b = ah.cuda(), bh.cuda()
+        c = torch.empty(512, 512, device="cuda")
+        ms = timed(lambda: ops.matmul_forward(a, b, out=c), steps=max(args.steps, 20))
+        ms_t = timed(lambda: torch.matmul(a, b, out=c), steps=max(args.steps, 20))
+        fl = 2.0 * 512 ** 3
+        value = fl / ms / 1e9
+        ch = torch.empty(512, 512).pin_memory()
+        e2e_ms = e2e_timed([ah, bh], lambda x, y: ops.matmul_forward(x, y), lambda o: ch.copy_(o, non_blocking=True))
+        h2d, d2h = 2 * 512 * 512 * 4, 512 * 512 * 4
+        # f32 products at f32 accuracy: the bound is the FP32 FMA pipe, 148 SMs x 128 lanes x 2 FLOP x max clock
+        peak = 148 * 128 * 2 * 1.965e9 / 1e12
+        roof = {"bound": "tensor", "kernel": "f32 GEMM 512^3 (latency-dominated: 2.7e8 FLOP)", "achieved": value, "peak": peak,
+                "unit": "TFLOP/s", "frac": value / peak, "peak_source": "nominal FP32 FMA rate (no measured f32 peak on file)",
+                "traffic": None}
+        extra["torch_matmul_f32_tflops"] = fl / ms_t / 1e9
+        dtype = "f32"
+    elif args.config == 2:
+        sweep = []
+        for (M, N, K) in [(1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (4096, 4096, 4096), (4096, 12288, 4096)]:
+            g = torch.Generator(device="cuda").manual_seed(1)
+            x = ((torch.rand(M, K, generator=g, device="cuda") * 2 - 1) * 0.05).bfloat16()
+            w = ((torch.rand(N, K, generator=g, device="cuda") * 2 - 1) * 0.05).bfloat16()
+            y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            ms = timed(lambda: ops.linear_forward(x, w, out=y), steps=max(args.steps, 10))
+            ms_t = timed(lambda: torch.matmul(x, w.t(), out=y), steps=max(args.steps, 10))
+            fl, by = 2.0 * M * N * K, 2.0 * (M * K + N * K + M * N)
+            hbm_bound = M <= 16
+            ach = by / ms / 1e6 if hbm_bound else fl / ms / 1e9
+            pk = peaks["hbm_gbs"] if hbm_bound else peaks["bf16_tflops"]
+            sweep.append({"M": M, "N": N, "K": K, "us": ms * 1e3, "bound": "hbm" if hbm_bound else "tensor",
+                          "achieved": ach, "unit": "GB/s" if hbm_bound else "TFLOP/s", "frac": ach / pk,
+                          "cublas_us": ms_t * 1e3})
+        head = sweep[-1]
+        value, ms = head["achieved"], head["us"] / 1e3
+        M, N, K = 4096, 12288, 4096
+        xh = torch.empty(M, K, dtype=torch.bfloat16).pin_memory()
+        yh = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+        e2e_ms = e2e_timed([xh], lambda xd: ops.linear_forward(xd, w), lambda o: yh.copy_(o, non_blocking=True))
+        h2d, d2h = M * K * 2, M * N * 2
+        roof = {"bound": "tensor", "kernel": "gemm_bf16_2cta_kernel 4096 x 12288 x 4096", "achieved": value,
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / peaks["bf16_tflops"],
+                "peak_source": peaks["source"] + " (burst cuBLAS bf16: kernel timed alone)",
+                "traffic": 0.99 * 2.0 * (M * K + N * K + M * N),
+                "traffic_unit": "bytes per launch (ncu: 231.6 MB on this shape)"}
+        extra["sweep"] = sweep
+        dtype = "bf16"
+    else:
+        B, Hq, Hkv, S, D = 4, 32, 8, 4096, 128
+        g = torch.Generator(device="cuda").manual_seed(2)
+        q = torch.randn(B, Hq, S, D, generator=g, device="cuda").bfloat16()
+        k = torch.randn(B, Hkv, S, D, generator=g, device="cuda").bfloat16()
+        v = torch.randn(B, Hkv, S, D, generator=g, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        ms = timed(lambda: ops.flash_attn_fwd(q, k, v, D ** -0.5, causal=True, out=o), steps=max(args.steps, 10))
+        ms_t = timed(lambda: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True),
+                     steps=max(args.steps, 10))
+        fl = 0.5 * 4 * B * Hq * S * S * D
+        value = fl / ms / 1e9
+        q1 = torch.randn(B, Hq, 1, D, generator=g, device="cuda").bfloat16()
+        o1 = torch.empty_like(q1)
+        sc = torch.empty(lib.teeny_attn_decode_scratch_bytes(B, Hq, D, S), dtype=torch.uint8, device="cuda")
+        ms_d = timed(lambda: ops.flash_attn_decode(q1, k, v, S, D ** -0.5, out=o1, scratch=sc), steps=max(args.steps, 20))
+        by_d = 2.0 * B * Hkv * S * D * 2
+        qh, kh, vh = (t.cpu().pin_memory() for t in (q, k, v))
+        oh = torch.empty(B, Hq, S, D, dtype=torch.bfloat16).pin_memory()
+        e2e_ms = e2e_timed([qh, kh, vh], lambda a, b, c: ops.flash_attn_fwd(a, b, c, D ** -0.5, causal=True),
+                           lambda r: oh.copy_(r, non_blocking=True))
+        h2d, d2h = (q.numel() + k.numel() + v.numel()) * 2, q.numel() * 2
+        roof = {"bound": "tensor", "kernel": "attention_prefill_kernel B4 H32/8 S4096 causal", "achieved": value,
+                "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": value / peaks["bf16_tflops"],
+                "peak_source": peaks["source"] + " (burst cuBLAS bf16: kernel timed alone)",
+                "traffic": 301.8e6, "traffic_unit": "bytes per launch (ncu on this shape; 268 MB algorithmic)"}
+        extra["torch_sdpa_tflops"] = fl / ms_t / 1e9
+        extra["decode_variant"] = {"us": ms_d * 1e3, "achieved": by_d / ms_d / 1e6, "unit": "GB/s", "bound": "hbm",
+                                   "frac": by_d / ms_d / 1e6 / peaks["hbm_gbs"], "bytes": by_d}
+        dtype = "bf16"
+    launches = int(lib.teeny_launch_count(1))
+    clocks = sampler.stop()
+    err = lib.teeny_device_error(1)
+    if err != 0:
+        raise SystemExit(f"device error word {err:#x}")
+    line = {"metric": metric, "value": value, "unit": unit, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "warmup_run": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": dtype, "data": "synthetic", "config": workload_config(args, 1),
+            "e2e": {"value": value * ms / e2e_ms, "unit": unit, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roof, **extra}
+    if not args.no_cpu_baseline:
+        v, desc, threads, _ = cpu_kernel_rate(args.config)
+        line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": desc}
+    emit(line)
+
+
+# ------------------------------------------------------------------------------------------------ generation configs
+def generation_config(args):
     import torch
     import torch.distributed as dist
     from teenygrad_b200 import ops, qwen3, tp
@@ -229,13 +474,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    B, S, NEW = args.batch, args.prefill, args.new_tokens
+    cfg_kwargs, wl = model_kwargs(args), workload_of(args)
+    B, S, NEW, seed = wl["batch"], wl["prefill"], wl["new_tokens"], wl["seed"]
     cfg = qwen3.Qwen3Config(**cfg_kwargs)
     runner = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + NEW, max_tokens=B * S, max_new_tokens=NEW,
                                tp_rank=rank, tp_size=world, comm=comm)
-    qwen3.load_random_weights(runner, seed=4)
+    qwen3.load_random_weights(runner, seed=seed)
     tp_mode = "none" if world == 1 else ("peer-push" if lib.teeny_tp_peer_enabled(comm) else "nccl-allreduce")
-    g = torch.Generator().manual_seed(4)
+    g = torch.Generator().manual_seed(seed)
     prompts_host = torch.randint(0, cfg.vocab, (B, S), generator=g, dtype=torch.int32).pin_memory()
     prompts_dev = prompts_host.to(dev)
     out_host = torch.empty(B, NEW, dtype=torch.int32).pin_memory()
@@ -250,7 +496,8 @@ def main():
         out_host.copy_(out, non_blocking=True)                # D2H of the step's result
         torch.cuda.current_stream().synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)  # timing rule: at least three warm-up generations, whatever was asked
+    for _ in range(warm):
         one_generation_device()
     barrier()
 
@@ -261,6 +508,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     pre = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
+    lib.teeny_launch_count(1)
     e0.record()
     for i in range(args.steps):
         pre[i][0].record()
@@ -270,6 +518,7 @@ def main():
             runner.decode_step(graph=True)
     e1.record()
     barrier()
+    launches = int(lib.teeny_launch_count(1))
     clocks = sampler.stop() if rank == 0 else None
     ms = torch.tensor([e0.elapsed_time(e1), sum(a.elapsed_time(b) for a, b in pre)], device=dev, dtype=torch.float64)
     if world > 1:
@@ -278,6 +527,8 @@ def main():
     err = lib.teeny_device_error(1)
     if err != 0:
         raise SystemExit(f"device error word {err:#x} after the timed region")
+    ids_crc = zlib.crc32(runner.history()[:NEW].t().contiguous().cpu().numpy().tobytes())
+    first_crc = zlib.crc32(runner.history()[0].contiguous().cpu().numpy().tobytes())
 
     # ---- end to end through the public API, host buffers ----
     one_generation_e2e()
@@ -290,15 +541,15 @@ def main():
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
 
-    # ---- dominant kernel: the tcgen05 GEMM on this run's prefill shapes (per rank), CUDA events ----
+    # ---- dominant kernel: the tcgen05 GEMM on this run's prefill shapes (per rank), CUDA events, timed alone ----
     peaks = measured_peaks()
-    T = B * S
-    shapes = [(T, (32 + 16) * 128 // world, 4096), (T, 4096, 4096 // world),
-              (T, 2 * 12288 // world, 4096), (T, 4096, 12288 // world)]
+    T, H, I = B * S, cfg.hidden, cfg.intermediate
+    qkv_n = (cfg.num_q_heads + 2 * cfg.num_kv_heads) * 128
+    shapes = [(T, qkv_n // world, H), (T, H, cfg.num_q_heads * 128 // world), (T, 2 * I // world, H), (T, H, I // world)]
     flops = gemm_ms = gemm_bytes = 0.0
-    x = torch.empty(T, 12288, dtype=torch.bfloat16, device=dev).normal_(0, 0.05)
-    wbuf = torch.empty(2 * 12288 * 4096 // world + 4096 * 6144, dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
-    ybuf = torch.empty(T * max(2 * 12288 // world, 4096 + 2048), dtype=torch.bfloat16, device=dev)
+    x = torch.empty(T, max(I // world, H), dtype=torch.bfloat16, device=dev).normal_(0, 0.05)
+    wbuf = torch.empty(max(2 * I * H // world, H * qkv_n), dtype=torch.bfloat16, device=dev).normal_(0, 0.02)
+    ybuf = torch.empty(T * max(2 * I // world, qkv_n), dtype=torch.bfloat16, device=dev)
     for (m, n, k) in shapes:
         xv, wv, yv = x[:, :k], wbuf[:n * k].view(n, k), ybuf[:m * n].view(m, n)
         for _ in range(2):
@@ -315,6 +566,33 @@ def main():
     achieved = flops / (gemm_ms * 1e-3) / 1e12
     del x, wbuf, ybuf
 
+    # ---- parity: sequence 0's first-token logits against the CPU oracle at full depth, same weights ----
+    parity = None
+    if not args.no_verify:
+        runner.prefill(prompts_dev)
+        row = runner.logits()[0].clone()
+        if world > 1:
+            parts = [torch.empty_like(row) for _ in range(world)]
+            dist.all_gather(parts, row)
+            row = torch.cat(parts)
+        torch.cuda.synchronize()
+        if rank == 0:
+            from oracle import qwen3 as oq
+            torch.set_num_threads(host_threads())
+            t0 = time.perf_counter()
+            sd = {name: t.cpu() for name, t in qwen3.random_weights_device(cfg, seed, dev)}
+            oracle = oq.OracleQwen3(oq.OracleQwen3Config(**cfg_kwargs), sd)
+            want = oracle.forward(prompts_host[:1].long())[0].float()
+            got = row.float().cpu()
+            rel = float((got - want).abs().max() / want.abs().max())
+            gi, wi = int(torch.argmax(got)), int(torch.argmax(want))
+            gap = float(want.max() - want[gi]) / float(want.abs().max())
+            parity = {"what": "sequence 0 of the batch, first generated token, all layers, against oracle/qwen3.py on the host",
+                      "logits_rel_err": rel, "bar": 2e-2, "token": gi, "oracle_token": wi,
+                      "token_ok": gi == wi or gap < 2e-2, "ok": rel < 2e-2 and (gi == wi or gap < 2e-2),
+                      "seconds": time.perf_counter() - t0}
+            del sd, oracle
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -326,43 +604,80 @@ def main():
     prefill_overlap = world > 1 and ((ov == "1") if ov else world >= 8)
     value = tokens_per_step * steps / (total_ms * 1e-3)
     decode_ms = total_ms - prefill_ms
-    L = cfg.num_layers
-    # this library's kernels only (NCCL's are not counted).  Prefill: embedding; per layer norm, QKV GEMM,
-    # norm+RoPE+cache, attention, O GEMM, add+norm, gate/up GEMM with SwiGLU epilogue, down GEMM; final add+norm, LM head,
-    # argmax (+ merge when tp > 1), generation-state kernels.  Decode: the attention kernel also does the head norms,
-    # RoPE, cache append and the merge of split sequences, so a layer is seven launches.
-    launches_prefill = 1 + L * 8 + 3 + 2 + (1 if world > 1 else 0)
-    launches_decode = 1 + L * 7 + 3 + 1 + (1 if world > 1 else 0)
+    step_ms = decode_ms / steps / max(NEW - 1, 1)
+    L, D = cfg.num_layers, 128
+    # algorithmic work per GPU: matmul parameters (2 FLOP / 2 bytes each), causal attention, KV-cache read at the mean length
+    layer_params = H * qkv_n + cfg.num_q_heads * D * H + 3 * I * H
+    head_params = cfg.vocab * H
+    prefill_flop = (2.0 * L * layer_params * T + 2.0 * head_params * B + L * 2.0 * B * cfg.num_q_heads * S * S * D) / world
+    mean_len = S + (NEW - 1) / 2.0 + 0.5
+    decode_bytes = (2.0 * (L * layer_params + head_params) + L * 2.0 * B * cfg.num_kv_heads * D * 2.0 * mean_len) / world
+    metric, unit = METRIC[args.config]
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": args.warmup,
+        "warmup_run": warm, "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {**workload_config(args, world), "tp_decode_reduction": tp_mode, "tp_prefill_reduction":
                    "none" if world == 1 else ("nccl-allreduce, overlapped with the other half-batch's compute"
                                               if prefill_overlap else "nccl-allreduce")},
         "phases": {"prefill_ms": prefill_ms / steps, "decode_ms": decode_ms / steps,
                    "prefill_tok_s": B * S * steps / (prefill_ms * 1e-3),
-                   "decode_tok_s": B * (NEW - 1) * steps / (decode_ms * 1e-3),
-                   "decode_ms_per_token_step": decode_ms / steps / (NEW - 1)},
-        "e2e": {"value": tokens_per_step * steps / float(e2e_s[0]), "unit": UNIT,
+                   "decode_tok_s": B * (NEW - 1) * steps / max(decode_ms * 1e-3, 1e-9),
+                   "decode_ms_per_token_step": step_ms},
+        "e2e": {"value": tokens_per_step * steps / float(e2e_s[0]), "unit": unit,
                 "h2d_bytes_per_step": prompts_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 4},
-        "gpu_launches": (launches_prefill + launches_decode * (NEW - 1)) * steps,
+        # counted by the library's launch wrapper on rank 0 inside the timed region (graph replays add the recorded
+        # step's kernel count); NCCL's kernels are not this library's and are not counted
+        "gpu_launches": launches,
         "clocks": clocks,
-        "roofline": {"bound": "tensor", "kernel": "gemm_bf16_2cta_kernel (prefill QKV/O/gate-up/down shapes of this run)",
-                     "achieved": achieved, "peak": peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"],
-                     "unit": "TFLOP/s", "frac": achieved / (peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]),
-                     "peak_source": peaks["source"] + " (sustained cuBLAS bf16: the kernel runs inside a long step)",
+        "roofline": {"bound": "tensor", "kernel": "the tcgen05 GEMM on this run's prefill QKV / O / gate-up / down shapes "
+                                                  "(gemm_bf16_2cta_kernel at config 5), timed alone after the generation",
+                     "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["bf16_tflops"],
+                     "peak_source": peaks["source"] + " (burst cuBLAS bf16: the kernel is timed alone, a few launches)",
                      # DRAM bytes of the four launches together: ncu measured 0.99 x the algorithmic 2(MK + NK + MN) bytes
                      # on a 4096 x 12288 x 4096 launch of this kernel (operands read once); scaled here by algorithmic bytes
                      "traffic": 0.99 * gemm_bytes, "traffic_unit": "bytes per set of four launches, scaled from an ncu capture"},
+        "roofline_prefill": {"bound": "tensor", "what": "whole prefill phase inside the step (all kernels, per GPU)",
+                             "achieved": prefill_flop / (prefill_ms / steps * 1e-3) / 1e12,
+                             "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                             "frac": prefill_flop / (prefill_ms / steps * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                             "peak_source": peaks["source"] + " (sustained cuBLAS bf16: measured inside a long step)",
+                             "flop_per_gpu": prefill_flop},
+        "roofline_decode": {"bound": "hbm", "what": "one decode step (all kernels, per GPU): weights + KV cache at the mean length",
+                            "achieved": decode_bytes / (step_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": decode_bytes / (step_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                            "peak_source": peaks["source"] + " (copy bandwidth)", "bytes_per_gpu": decode_bytes},
+        "ids_crc32": {"all": ids_crc, "first_token": first_crc},
     }
+    if parity is not None:
+        line["parity_check"] = parity
     if not args.no_cpu_baseline and world == 1:
-        v, desc, threads = cpu_generation_rate(cfg_kwargs, **CPU_SAMPLE)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc}
-    print(json.dumps(line), file=_JSON_OUT or sys.stdout, flush=True)
+        v, desc, threads = cpu_generation_rate(cfg_kwargs, **CPU_SAMPLE[args.config])
+        line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": desc}
+    emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
+
+
+def main():
+    args = parse_args()
+    # Keep stdout to the one JSON line: libraries write there at the file-descriptor level (NCCL prints its version
+    # banner to fd 1 at NCCL_DEBUG=VERSION and WARN), so fd 1 is pointed at stderr for the whole run and the line goes
+    # to a private duplicate of the original stdout.
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    if args.impl == "reference":
+        reference_arm(args)
+    elif args.config in (4, 5):
+        generation_config(args)
+    else:
+        kernel_config(args)
 
 
 if __name__ == "__main__":

@@ -43,6 +43,11 @@ const char* teeny_status_string(int status);
  * (0 = none).  clear != 0 resets it.  The reference surfaces device faults by cuCtxSynchronize after each launch
  * (drivers/teeny-cuda/src/device/mod.rs:369-381); here launches stay asynchronous and this is the explicit check. */
 int teeny_device_error(int clear);
+/* Kernels this library has launched in this process so far (a kernel recorded into a CUDA graph counts when it is
+ * recorded and again on every replay by teeny_qwen3_decode_replay); reset != 0 returns the count and zeroes it.
+ * Library kernels of others (NCCL) are not counted.  For callers that want to see that the CUDA path ran, as the
+ * reference's launcher can by counting its cuLaunchKernel calls (drivers/teeny-cuda/src/device/mod.rs:315-388). */
+unsigned long long teeny_launch_count(int reset);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * GEMM

@@ -54,7 +54,14 @@ enum {
   TEENY_QWEN3_BUF_STATE,      /* int32 [3]: next position, live KV length of the coming step, tokens generated */
   TEENY_QWEN3_BUF_HIDDEN,     /* bf16 [batch, hidden]: final-norm output of the last step */
   TEENY_QWEN3_BUF_K_CACHE,    /* bf16 [layers, max_batch, Hkv/tp, max_len, 128] */
-  TEENY_QWEN3_BUF_V_CACHE
+  TEENY_QWEN3_BUF_V_CACHE,
+  /* For layer-level checks (the reference reads intermediate tensors the same way, TensorRef outputs of
+   * LoadedModel::forward, drivers/teeny-cuda/src/model/mod.rs:524): after a call, RESIDUAL holds the residual stream
+   * before the last layer's MLP output was added and LAST_DELTA that (summed over ranks) output, both bf16
+   * [tokens, hidden], so residual + delta is the hidden state the final norm sees.  Rows of each sequence's last
+   * position already have the sum in RESIDUAL (the head adds it in place). */
+  TEENY_QWEN3_BUF_RESIDUAL,
+  TEENY_QWEN3_BUF_LAST_DELTA
 };
 
 /* Bytes of workspace (activations, KV cache, RoPE tables, scratch, generation state) for this configuration;
@@ -71,7 +78,9 @@ int teeny_qwen3_set_weight(teeny_qwen3* model, int layer, int which, const void*
 int teeny_qwen3_prefill(teeny_qwen3* model, const int* ids, int B, int S, teeny_stream_t stream);
 /* One greedy decode step for the batch of the last prefill: consumes NEXT_IDS, appends to the cache, produces the
  * next token.  teeny_qwen3_decode launches the kernels directly; capture_decode records one step into a CUDA graph
- * (position and length live in device memory, so one graph serves every step) and decode_replay launches it. */
+ * (position and length live in device memory, so one graph serves every step) and decode_replay launches it.
+ * A generation holds at most max_len cache rows: once prefill length + decode steps reaches max_len, decode and
+ * decode_replay return TEENY_ERR_BAD_ARG and launch nothing. */
 int teeny_qwen3_decode(teeny_qwen3* model, teeny_stream_t stream);
 /* Token selection.  temperature <= 0 (the default): greedy argmax, lowest index on ties.  temperature > 0: the
  * temperature / top-k (1..1024) / top-p sampler of teeny_sample_top_k_top_p_bf16, with u for token t of a generation

@@ -150,6 +150,7 @@ class OracleQwen3:
             m = F.silu(F.linear(y, sd[p + "mlp.gate_proj.weight"])) * F.linear(y, sd[p + "mlp.up_proj.weight"])
             x = x + F.linear(m, sd[p + "mlp.down_proj.weight"])
         self.pos = L
+        self.last_residual = x  # bf16 [B, s, hidden]: the residual stream after the last layer (layer-level checks)
         h = _rms(x, sd["model.norm.weight"], cfg.eps)
         head = sd["model.embed_tokens.weight"] if cfg.tied else sd["lm_head.weight"]
         logits = F.linear(h[:, -1, :], head)

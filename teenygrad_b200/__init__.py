@@ -2,8 +2,8 @@
 
 The compute lives in ``libteeny_b200.so`` (hand-written CUDA behind the C ABI declared in
 ``include/teeny_b200.h``).  This package is the host side: a ctypes binding (``_lib``), thin operator
-wrappers over torch device tensors (``ops``), a mirror of teeny-core's Device/Buffer traits (``device``) and
-the Qwen3 runner (``qwen3``).  There is no CPU fallback: importing ``_lib`` fails when the library has not
+wrappers over torch device tensors (``ops``), tensor-parallel sharding (``tp``), a safetensors reader
+(``safetensors``) and the Qwen3 runner (``qwen3``).  There is no CPU fallback: importing ``_lib`` fails when the library has not
 been built, and every operator raises when the C ABI returns a non-zero status.
 """
 from .build import build, library_path  # noqa: F401

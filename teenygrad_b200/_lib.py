@@ -26,6 +26,7 @@ SIGNATURES = {
     "teeny_version": (i32, []),
     "teeny_status_string": (C.c_char_p, [i32]),
     "teeny_device_error": (i32, [i32]),
+    "teeny_launch_count": (C.c_ulonglong, [i32]),
     "matmul_forward_entry_point_f32": (i32, [vp, vp, vp, i32, i32, i32, vp, sz, vp]),
     "matmul_forward_entry_point_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp, sz, vp]),
     "linear_forward_entry_point_f32": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp, sz, vp]),

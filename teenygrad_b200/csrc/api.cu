@@ -1,5 +1,6 @@
 // C ABI (include/teeny_b200.h): argument checks, dtype / layout dispatch, and the few process-wide helpers
 // (tensor-map encoding through the driver entry point, per-device error word, SM count).
+#include <atomic>
 #include <mutex>
 
 #include "../../include/teeny_b200.h"
@@ -46,6 +47,10 @@ int* device_error_word() {
   }
   return g_error_ptr[d];
 }
+
+namespace { std::atomic<unsigned long long> g_launches{0}; }
+void count_launches(unsigned long long n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+unsigned long long launches_so_far() { return g_launches.load(std::memory_order_relaxed); }
 
 namespace { thread_local int t_sm_limit = 0; }
 void set_sm_limit(int n) { t_sm_limit = n > 0 ? n : 0; }
@@ -143,6 +148,10 @@ const char* teeny_status_string(int status) {
     case TEENY_ERR_STATIC_LIMIT: return "shape needs more scratch than the no-allocation entry point has built in";
     default: return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
   }
+}
+
+unsigned long long teeny_launch_count(int reset) {
+  return reset ? g_launches.exchange(0, std::memory_order_relaxed) : g_launches.load(std::memory_order_relaxed);
 }
 
 int teeny_device_error(int clear) {

@@ -10,6 +10,8 @@
 // 2. attention_generic<T>: any head_dim <= 256, f32 or bf16, one warp per query row, sequential online softmax --
 //    the reference kernel's own recurrence; used for the f32 entry point and for shapes the tcgen05 kernel
 //    does not cover.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -465,16 +467,16 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
 
 // Raises the decode kernel's dynamic shared-memory limit once per device.
 int attention_decode_prepare() {
-  static unsigned long long done = 0;
+  static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
   cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
   if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
   if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
   if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_decode_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, dec_smem_bytes(kDecStagesAlone));
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 64) done |= 1ull << dev;
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
 }
 
@@ -542,6 +544,7 @@ int attention_decode_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o, 
   }
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;  // kernels report expired waits through this word: no launch without it
   // Split the sequence only as far as needed to fill the GPU.  With B * Hkv at (or near) two CTAs per SM, each CTA
   // walks its whole sequence behind a three-stage ring and writes the output itself.  With fewer, the grid is sized
   // to at most one CTA per SM and each CTA gets the whole shared memory as a six-stage ring (the same bytes in flight

@@ -16,6 +16,8 @@
 //               the maximum grows by more than 2^8); P = exp2(s * scale - m) as bf16
 //               pairs into tensor memory, row sums in f32 per group.
 // Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -377,13 +379,13 @@ int make_map(CUtensorMap* m, const bf16* p, int S, int H, int B, long long ss, l
 }  // namespace
 
 int attention_prefill_prepare() {
-  static unsigned long long done = 0;
+  static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
   cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 64) done |= 1ull << dev;
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
 }
 
@@ -413,6 +415,7 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.causal = s.causal;
   a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;  // kernels report expired waits through this word: no launch without it
 
   {
     const int prc = attention_prefill_prepare();

@@ -133,6 +133,10 @@ struct TraceReg { TraceReg() { teeny_trace_register(__BASE_FILE__, trace_dump_tu
 bool pdl_enabled();
 void pdl_set_enabled(bool on);
 
+// Kernel launches issued by this library since the last reset (process-wide; teeny_launch_count in the C ABI).  A
+// launch recorded into a CUDA graph counts once when it is recorded; the runner adds a graph's kernel count per replay.
+void count_launches(unsigned long long n);
+
 // Launch through cudaLaunchKernelEx so the attribute can be attached; `cluster` > 1 also sets the cluster width.
 template <typename... KArgs, typename... Args>
 inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
@@ -158,6 +162,7 @@ inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
+  count_launches(1);
   return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 

@@ -743,6 +743,7 @@ int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, co
   const int nv = N / 8;
   const int threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32, vpt = (nv + threads - 1) / threads;
   int* err = device_error_word();
+  if (!err) return TEENY_ERR_DRIVER;
 #define TEENY_GATHER_CASE(V)                                                                                       \
   launch_kernel(gather_add_rms_norm_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, epoch, round, \
                 residual, ldr, y, ldy, w, N, eps, err)
@@ -764,6 +765,7 @@ int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int wor
   const int nv = N / 8;
   const int threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32, vpt = (nv + threads - 1) / threads;
   int* err = device_error_word();
+  if (!err) return TEENY_ERR_DRIVER;
 #define TEENY_GATHER_CASE(V)                                                                                          \
   launch_kernel(gather_add_rms_norm_owner_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, rank, \
                 owner_rows, bcast, epoch, round, residual, ldr, y, ldy, w, N, eps, err)

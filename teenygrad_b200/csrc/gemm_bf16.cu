@@ -23,6 +23,8 @@
 // in its own shared memory, and after a cluster barrier the CTAs sum the partials through distributed shared
 // memory -- each CTA reduces its own slice of the token columns, in cluster-rank order, so the result is
 // bit-reproducible.  No global scratch, no atomics.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -621,27 +623,27 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 // Raises the kernel's dynamic shared-memory limit once per device (bit d of `done` = device d prepared).
 template <int BN, bool SWAP, bool Q_MN>
 int prepare_variant() {
-  static unsigned long long done = 0;
+  static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, SWAP, Q_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        GemmCfg<BN>::kSmemBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 64) done |= 1ull << dev;
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
 }
 
 template <int BN>
 int prepare_skinny() {
-  static unsigned long long done = 0;
+  static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        SkinnyCfg<BN>::kSmemBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 64) done |= 1ull << dev;
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
 }
 
@@ -711,6 +713,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
     a.push_owner_rows = push->owner_rows;
   }
   a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;  // kernels report expired waits through this word: no launch without it
   const int sms = sm_count();
 
   CUtensorMap tmx, tmw;

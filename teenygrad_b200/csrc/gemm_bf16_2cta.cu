@@ -15,6 +15,8 @@
 //   warps 2-5 epilogue (both CTAs): tcgen05.ld the CTA's 128 x 256 f32 half, bf16, 16-byte stores; then arrive on
 //            the leader's `acc_empty` (the peer does so through a cluster-mapped address).
 // Two accumulators in tensor memory (2 x 256 columns) let the epilogue of tile t overlap the main loop of tile t+1.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -309,13 +311,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 }  // namespace
 
 int gemm_bf16_2cta_prepare() {
-  static unsigned long long done = 0;
+  static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 64 && (done >> dev) & 1ull) return 0;
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
   cudaError_t e = cudaFuncSetAttribute(gemm_bf16_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
-  if (dev < 64) done |= 1ull << dev;
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
 }
 
@@ -345,6 +347,7 @@ int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* b
   a.group = 16;  // 16 x 256 rows of X share each 256-row block of W before moving on (best of 4/8/16/32 measured)
   a.swiglu = swiglu ? 1 : 0;
   a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;  // kernels report expired waits through this word: no launch without it
   const int tiles = a.tiles_m * a.tiles_n;
   int pairs = sm_count() / 2;
   if (pairs > tiles) pairs = tiles;

@@ -11,6 +11,8 @@ namespace teeny {
 
 typedef __nv_bfloat16 bf16;
 
+unsigned long long launches_so_far();  // see count_launches (common.cuh)
+
 // ---- GEMM --------------------------------------------------------------------------------------
 constexpr int kGemmMaxSplitK = 16;     // most k-splits per output tile
 constexpr int kGemmMaxWorkPerSm = 8;   // split-K is only used while tiles*splits <= this * SM count

@@ -93,13 +93,13 @@ struct TpContext {
 
 // Collective over the communicator: allocate the receive buffer, exchange IPC handles, map the peers.  Leaves
 // peer_ok false (on every rank alike) if any rank could not set it up; the runner then all-reduces through NCCL.
+// Every local failure (an allocation, a handle, a mapping, a table upload) is folded into the one `ok` byte that the
+// ranks exchange, and no rank returns between the collectives, so the ranks cannot end up on different reduction paths
+// or in a collective that others skipped.
 int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   if (c->peer_ok || c->world < 2 || c->world > 8) return 0;
   c->rows = rows; c->cols = cols; c->slot_elems = rows * cols;
   c->data_bytes = 2 * static_cast<size_t>(c->world) * c->slot_elems * sizeof(uint2);
-  int ok = 1;
-  cudaIpcMemHandle_t mine;
-  uint8_t* xbuf = nullptr;
   c->bcast_off = c->data_bytes + 256;
   const size_t bcast_bytes = 2 * c->slot_elems * 8;  // 2 parities x rows x cols / 2 lines of 16 bytes
   const size_t total_bytes = c->bcast_off + bcast_bytes;
@@ -110,26 +110,42 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
     const char* e = getenv("TEENY_TP_HOPS");
     c->two_hop = e ? (e[0] == '2') : (c->world >= 8);
   }
-  if (cudaMalloc(&c->local, total_bytes) != cudaSuccess) ok = 0;
+  cudaIpcMemHandle_t mine;
+  std::memset(&mine, 0, sizeof(mine));
+  const size_t rec = sizeof(mine) + 8;
+  uint8_t* xbuf = nullptr;  // exchange buffer: [world] records of [handle | ok], reused for the later one-byte rounds
+  int ok = 1;
+  bool nccl_failed = false;
+  if (cudaMalloc(&c->local, total_bytes) != cudaSuccess) { c->local = nullptr; ok = 0; }
   if (ok && cudaMemsetAsync(c->local, 0, total_bytes, st) != cudaSuccess) ok = 0;
   if (ok && cudaIpcGetMemHandle(&mine, c->local) != cudaSuccess) ok = 0;
-  const size_t rec = sizeof(mine) + 8;
-  if (cudaMalloc(&xbuf, rec * c->world) != cudaSuccess) return TEENY_ERR_BAD_ARG;
-  // exchange [handle | ok] records
+  if (cudaMalloc(&xbuf, rec * c->world) != cudaSuccess) {
+    // without the exchange buffer this rank cannot even say "no": the communicator is unusable for set-up
+    if (c->local) { cudaFree(c->local); c->local = nullptr; }
+    cudaGetLastError();
+    return TEENY_ERR_NCCL;
+  }
   std::vector<uint8_t> host(rec * c->world, 0);
-  if (ok) std::memcpy(host.data() + rec * c->rank, &mine, sizeof(mine));
+  // all ranks: ok &= (every rank's ok); one byte per rank through the communicator
+  auto agree = [&]() {
+    host[0] = static_cast<uint8_t>(ok);
+    cudaMemcpyAsync(xbuf + c->rank, host.data(), 1, cudaMemcpyHostToDevice, st);
+    if (g_nccl.AllGather(xbuf + c->rank, xbuf, 1, ncclChar, c->comm, st) != ncclSuccess) nccl_failed = true;
+    cudaMemcpyAsync(host.data(), xbuf, c->world, cudaMemcpyDeviceToHost, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess) nccl_failed = true;
+    for (int q = 0; q < c->world; ++q) ok &= host[q];
+    if (nccl_failed) ok = 0;
+  };
+  // round 1: [handle | ok] records
+  std::memcpy(host.data() + rec * c->rank, &mine, sizeof(mine));
   host[rec * c->rank + sizeof(mine)] = static_cast<uint8_t>(ok);
   cudaMemcpyAsync(xbuf + rec * c->rank, host.data() + rec * c->rank, rec, cudaMemcpyHostToDevice, st);
-  if (g_nccl.AllGather(xbuf + rec * c->rank, xbuf, rec, ncclChar, c->comm, st) != ncclSuccess) {
-    cudaFree(xbuf);
-    return TEENY_ERR_NCCL;
-  }
+  if (g_nccl.AllGather(xbuf + rec * c->rank, xbuf, rec, ncclChar, c->comm, st) != ncclSuccess) nccl_failed = true;
   cudaMemcpyAsync(host.data(), xbuf, rec * c->world, cudaMemcpyDeviceToHost, st);
-  if (cudaStreamSynchronize(st) != cudaSuccess) {
-    cudaFree(xbuf);
-    return TEENY_ERR_NCCL;
-  }
+  if (cudaStreamSynchronize(st) != cudaSuccess) nccl_failed = true;
+  if (nccl_failed) ok = 0;
   for (int q = 0; q < c->world; ++q) ok &= host[rec * q + sizeof(mine)];
+  bool mapped[8] = {};
   if (ok) {
     for (int q = 0; q < c->world && ok; ++q) {
       if (q == c->rank) { c->peer[q] = c->local; continue; }
@@ -137,36 +153,42 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
       std::memcpy(&h, host.data() + rec * q, sizeof(h));
       if (cudaIpcOpenMemHandle(&c->peer[q], h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
         ok = 0;
+        c->peer[q] = nullptr;
         cudaGetLastError();
+      } else {
+        mapped[q] = true;
       }
     }
   }
-  // second round: did every rank map every peer?
-  host[0] = static_cast<uint8_t>(ok);
-  cudaMemcpyAsync(xbuf + c->rank, host.data(), 1, cudaMemcpyHostToDevice, st);
-  if (g_nccl.AllGather(xbuf + c->rank, xbuf, 1, ncclChar, c->comm, st) != ncclSuccess) {
-    cudaFree(xbuf);
-    return TEENY_ERR_NCCL;
+  // round 2: did every rank map every peer?
+  if (!nccl_failed) agree();
+  if (ok) {
+    std::vector<uint2*> rt(2 * c->world);
+    std::vector<uint4*> bt(2 * c->world);
+    for (int par = 0; par < 2; ++par)
+      for (int q = 0; q < c->world; ++q) {
+        rt[par * c->world + q] =
+            reinterpret_cast<uint2*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
+        bt[par * c->world + q] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(c->peer[q]) + c->bcast_off) +
+                                 static_cast<size_t>(par) * (c->slot_elems / 2);
+      }
+    if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(uint2*)) != cudaSuccess) { c->recv_tab = nullptr; ok = 0; }
+    if (ok && cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(uint2*), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
+    if (ok && cudaMalloc(&c->bcast_tab, bt.size() * sizeof(uint4*)) != cudaSuccess) { c->bcast_tab = nullptr; ok = 0; }
+    if (ok && cudaMemcpy(c->bcast_tab, bt.data(), bt.size() * sizeof(uint4*), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
   }
-  cudaMemcpyAsync(host.data(), xbuf, c->world, cudaMemcpyDeviceToHost, st);
-  cudaStreamSynchronize(st);
-  for (int q = 0; q < c->world; ++q) ok &= host[q];
+  // round 3: does every rank hold its tables?  Only then do all ranks switch to the peer path together.
+  if (!nccl_failed) agree();
   cudaFree(xbuf);
-  if (!ok) return 0;  // stay on the NCCL path
-  std::vector<uint2*> rt(2 * c->world);
-  for (int par = 0; par < 2; ++par)
+  if (!ok) {
     for (int q = 0; q < c->world; ++q)
-      rt[par * c->world + q] =
-          reinterpret_cast<uint2*>(c->peer[q]) + (static_cast<size_t>(par) * c->world + c->rank) * c->slot_elems;
-  if (cudaMalloc(&c->recv_tab, rt.size() * sizeof(uint2*)) != cudaSuccess) return 0;
-  cudaMemcpy(c->recv_tab, rt.data(), rt.size() * sizeof(uint2*), cudaMemcpyHostToDevice);
-  std::vector<uint4*> bt(2 * c->world);
-  for (int par = 0; par < 2; ++par)
-    for (int q = 0; q < c->world; ++q)
-      bt[par * c->world + q] = reinterpret_cast<uint4*>(static_cast<uint8_t*>(c->peer[q]) + c->bcast_off) +
-                               static_cast<size_t>(par) * (c->slot_elems / 2);
-  if (cudaMalloc(&c->bcast_tab, bt.size() * sizeof(uint4*)) != cudaSuccess) return 0;
-  cudaMemcpy(c->bcast_tab, bt.data(), bt.size() * sizeof(uint4*), cudaMemcpyHostToDevice);
+      if (mapped[q]) { cudaIpcCloseMemHandle(c->peer[q]); c->peer[q] = nullptr; }
+    if (c->recv_tab) { cudaFree(c->recv_tab); c->recv_tab = nullptr; }
+    if (c->bcast_tab) { cudaFree(c->bcast_tab); c->bcast_tab = nullptr; }
+    if (c->local) { cudaFree(c->local); c->local = nullptr; }
+    cudaGetLastError();
+    return nccl_failed ? TEENY_ERR_NCCL : 0;  // 0: stay on the NCCL path
+  }
   c->peer_ok = true;
   return 0;
 }
@@ -246,7 +268,9 @@ struct teeny_qwen3 {
   int sample_top_k = 1;
   unsigned long long sample_seed = 0;
   int graph_batch = 0;
+  unsigned long long graph_kernels = 0;  // kernels recorded in graph_exec (launch accounting)
   int batch = 0;  // batch of the running generation (set by prefill)
+  int next_pos = 0;  // host mirror of state[0]: cache position the next decode step appends at (prefill sets it to S)
   bool tables_ready = false;
 
   template <typename T> T* at(size_t o) const { return reinterpret_cast<T*>(ws + o); }
@@ -327,7 +351,6 @@ Workspace plan(const teeny_qwen3_config& c) {
 int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
   if (m->cfg.tp_size == 1) return 0;
   if (!m->comm) return TEENY_ERR_NCCL;
-  // chunked so each message stays within NCCL's comfortable size and later chunks can start while earlier ones drain
   return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, m->comm, st) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
 }
 
@@ -724,6 +747,10 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
   TEENY_TRY(check_ready(m, st));
   PdlScope pdl;
   m->batch = B;
+  m->next_pos = S;
+  // a decode step that failed half-way may have left a push waiting for its norm: a new generation starts clean
+  m->pending_gather = false;
+  m->push_round = 0;
   int* state = m->at<int>(m->off.state);
   TEENY_TRY(embedding_bf16(ids, m->embed, m->at<bf16>(m->off.h), B * S, c.hidden, c.vocab, st));
   if (m->overlap_prefill && B % 2 == 0 && B * S >= 512)  // small prefills have nothing to hide
@@ -741,7 +768,12 @@ int teeny_qwen3_prefill(teeny_qwen3* m, const int* ids, int B, int S, teeny_stre
 
 int teeny_qwen3_decode(teeny_qwen3* m, teeny_stream_t stream) {
   if (!m || m->batch <= 0) return TEENY_ERR_BAD_ARG;
-  return decode_body(m, m->batch, reinterpret_cast<cudaStream_t>(stream));
+  // A step appends at cache row next_pos.  Past the capacity the append would be skipped while the live length kept
+  // growing, and the tokens would be silently wrong: refuse instead.
+  if (m->next_pos >= m->cfg.max_len) return TEENY_ERR_BAD_ARG;
+  const int rc = decode_body(m, m->batch, reinterpret_cast<cudaStream_t>(stream));
+  if (rc == 0) ++m->next_pos;
+  return rc;
 }
 
 int teeny_qwen3_set_sampling(teeny_qwen3* m, float temperature, int top_k, float top_p, unsigned long long seed) {
@@ -772,7 +804,9 @@ int teeny_qwen3_capture_decode(teeny_qwen3* m, teeny_stream_t stream) {
   cudaStream_t st = m->capture_stream;
   e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
   if (e != cudaSuccess) return static_cast<int>(e);
+  const unsigned long long launches_before = launches_so_far();
   const int rc = decode_body(m, m->batch, st);
+  m->graph_kernels = launches_so_far() - launches_before;
   cudaGraph_t graph = nullptr;
   e = cudaStreamEndCapture(st, &graph);
   if (rc != 0) {
@@ -789,7 +823,13 @@ int teeny_qwen3_capture_decode(teeny_qwen3* m, teeny_stream_t stream) {
 
 int teeny_qwen3_decode_replay(teeny_qwen3* m, teeny_stream_t stream) {
   if (!m || !m->graph_exec || m->graph_batch != m->batch) return TEENY_ERR_BAD_ARG;
-  return static_cast<int>(cudaGraphLaunch(m->graph_exec, reinterpret_cast<cudaStream_t>(stream)));
+  if (m->next_pos >= m->cfg.max_len) return TEENY_ERR_BAD_ARG;  // cache full (see teeny_qwen3_decode)
+  const int rc = static_cast<int>(cudaGraphLaunch(m->graph_exec, reinterpret_cast<cudaStream_t>(stream)));
+  if (rc == 0) {
+    ++m->next_pos;
+    count_launches(m->graph_kernels);
+  }
+  return rc;
 }
 
 void* teeny_qwen3_buffer(teeny_qwen3* m, int which) {
@@ -802,6 +842,8 @@ void* teeny_qwen3_buffer(teeny_qwen3* m, int which) {
     case TEENY_QWEN3_BUF_HIDDEN: return m->ws + m->off.y;
     case TEENY_QWEN3_BUF_K_CACHE: return m->ws + m->off.kcache;
     case TEENY_QWEN3_BUF_V_CACHE: return m->ws + m->off.vcache;
+    case TEENY_QWEN3_BUF_RESIDUAL: return m->ws + m->off.h;
+    case TEENY_QWEN3_BUF_LAST_DELTA: return m->ws + m->off.delta;
     default: return nullptr;
   }
 }

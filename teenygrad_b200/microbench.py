@@ -3,7 +3,7 @@
     python -m teenygrad_b200.microbench time [gemm] [skinny] [prefill] [decode] [elementwise] [sampling]   # CUDA-event timings
     python -m teenygrad_b200.microbench case gemm|skinny|prefill|decode           # a few launches of one kernel
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
-    python -m teenygrad_b200.microbench trace [N [first [count]]]                 # timeline of one graph-replayed decode step
+    python -m teenygrad_b200.microbench trace [N [first [count [shard]]]]         # timeline of one graph-replayed decode step
     python -m teenygrad_b200.microbench tracecase gemm|skinny|prefill|decode      # phase counters of one kernel
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
@@ -192,12 +192,14 @@ def layers(n_layers):
     torch.cuda.synchronize()
 
 
-def trace(n_layers, first=0, count=48):
+def trace(n_layers, first=0, count=48, shard=1):
     """Prints, for every kernel launch of one graph-replayed decode step (batch 32, cache length ~2050) of an
     n-layer Qwen3-8B-shaped model: CTAs, first/last CTA resident, first/last CTA released by its dependency wait,
     first/last CTA finished (where the kernel records it), in microseconds from the start of the step.  Prints
     ``count`` launches starting at launch number ``first`` (under tensor parallelism the first layer absorbs the
-    ranks' start skew, so look further in)."""
+    ranks' start skew, so look further in).  ``shard`` > 1 on one GPU runs one rank's shard of a ``shard``-way
+    tensor-parallel split (heads, intermediate and vocabulary divided, no exchange): the per-layer time a rank would
+    have if the cross-rank reductions were free."""
     import ctypes
     from collections import defaultdict
 
@@ -230,7 +232,7 @@ def trace(n_layers, first=0, count=48):
         from . import tp
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
         comm = tp.init_comm(rank, world)
-    cfg = qwen3.Qwen3Config(n_layers, 4096, 32, 8, 128, 12288, 151936, tied=False)
+    cfg = qwen3.Qwen3Config(n_layers, 4096, 32 // shard, 8 // shard, 128, 12288 // shard, 151936 // shard, tied=False)
     r = qwen3.Qwen3Runner(cfg, max_batch=32, max_len=2304, max_tokens=32 * 2048, max_new_tokens=16,
                           tp_rank=rank, tp_size=world, comm=comm)
     qwen3.load_random_weights(r, 4)
@@ -319,7 +321,7 @@ def main(argv):
     elif mode == "layers":
         layers(int(argv[1]) if len(argv) > 1 else 6)
     elif mode == "trace":
-        trace(*(int(v) for v in argv[1:4])) if len(argv) > 1 else trace(8)
+        trace(*(int(v) for v in argv[1:5])) if len(argv) > 1 else trace(8)
     else:
         raise SystemExit(__doc__)
     print("device error word:", ops.device_error())

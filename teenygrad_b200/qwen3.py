@@ -44,7 +44,7 @@ _lib.bind(SIGNATURES)
 
 W_QKV, W_O, W_GATE_UP, W_DOWN, W_INPUT_LN, W_POST_LN, W_Q_NORM, W_K_NORM = range(8)
 W_EMBED, W_FINAL_NORM, W_LM_HEAD, W_INV_FREQ = 100, 101, 102, 103
-BUF_LOGITS, BUF_NEXT_IDS, BUF_HISTORY, BUF_STATE, BUF_HIDDEN, BUF_K_CACHE, BUF_V_CACHE = range(7)
+BUF_LOGITS, BUF_NEXT_IDS, BUF_HISTORY, BUF_STATE, BUF_HIDDEN, BUF_K_CACHE, BUF_V_CACHE, BUF_RESIDUAL, BUF_LAST_DELTA = range(9)
 _LAYER_SLOTS = {"qkv": W_QKV, "o": W_O, "gate_up": W_GATE_UP, "down": W_DOWN, "input_ln": W_INPUT_LN,
                 "post_ln": W_POST_LN, "q_norm": W_Q_NORM, "k_norm": W_K_NORM}
 
@@ -76,6 +76,17 @@ def _stream():
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def check_generation_fits(prompt_len, max_new_tokens, max_len, history_capacity):
+    """Raises unless a generation of ``max_new_tokens`` after a prompt of ``prompt_len`` fits the runner: the first
+    token comes out of the prefill, each later one appends one cache row, so rows 0 .. prompt_len + max_new_tokens - 2
+    must exist.  (The C side refuses the step that would overflow as well; this fails before any launch.)"""
+    if max_new_tokens > history_capacity:
+        raise ValueError("max_new_tokens exceeds the runner's history capacity")
+    if prompt_len + max_new_tokens - 1 > max_len:
+        raise ValueError(f"prompt of {prompt_len} + {max_new_tokens} new tokens needs {prompt_len + max_new_tokens - 1} "
+                         f"cache rows; the runner was created with max_len={max_len}")
+
+
 class Qwen3Runner:
     """Greedy Qwen3 decoding on one GPU (or one tensor-parallel rank)."""
 
@@ -92,6 +103,7 @@ class Qwen3Runner:
         c.max_new_tokens, c.tp_rank, c.tp_size = max_new_tokens, tp_rank, tp_size
         self._c = c
         self.tp_rank, self.tp_size, self.max_batch, self.max_new_tokens = tp_rank, tp_size, max_batch, max_new_tokens
+        self.max_len = max_len
         nbytes = lib.teeny_qwen3_workspace_bytes(C.byref(c))
         if nbytes == 0:
             raise ValueError("unsupported Qwen3 configuration for this backend")
@@ -153,13 +165,20 @@ class Qwen3Runner:
     def state(self):
         return self._view(BUF_STATE, (3,), torch.int32)
 
+    def residual_stream(self, tokens):
+        """(residual, last_delta), bf16 [tokens, hidden] each: their sum is the hidden state after the last layer
+        (rows of each sequence's last position already hold the sum in ``residual``)."""
+        return (self._view(BUF_RESIDUAL, (tokens, self.cfg.hidden), _BF16),
+                self._view(BUF_LAST_DELTA, (tokens, self.cfg.hidden), _BF16))
+
     # ---- execution ----
     def prefill(self, ids):
         """ids: int [B, S] (any device).  Runs the prompt, records the first generated token."""
         ids = ids.to(self.device, dtype=torch.int32).contiguous()
         B, S = ids.shape
+        if B != self.batch:
+            self._captured = False  # the recorded decode step has the batch baked in; everything else is a fixed address
         self.batch = B
-        self._captured = False
         check(lib.teeny_qwen3_prefill(self._h, C.c_void_p(ids.data_ptr()), B, S, _stream()), "teeny_qwen3_prefill")
 
     def set_sampling(self, temperature, top_k=50, top_p=1.0, seed=0):
@@ -180,8 +199,7 @@ class Qwen3Runner:
 
     def generate(self, prompt_ids, max_new_tokens, use_graph=True):
         """Greedy decode; returns int32 [B, max_new_tokens] on the device (no host sync inside)."""
-        if max_new_tokens > self.max_new_tokens:
-            raise ValueError("max_new_tokens exceeds the runner's history capacity")
+        check_generation_fits(prompt_ids.shape[1], max_new_tokens, self.max_len, self.max_new_tokens)
         self.prefill(prompt_ids)
         for _ in range(max_new_tokens - 1):
             self.decode_step(graph=use_graph)
@@ -231,18 +249,3 @@ def load_random_weights(runner, seed):
             head[name] = t
     runner.load_head_shards(tpmod.shard_head(head, cfg, runner.tp_rank, runner.tp_size))
 
-
-def smoke():
-    """Tiny Qwen3-shaped model: prefill + 4 greedy steps on cuda:0, token ids checked against the CPU oracle."""
-    from oracle import qwen3 as oq
-    ocfg = oq.OracleQwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
-    sd = oq.make_weights(ocfg, 3)
-    ids = torch.randint(0, ocfg.vocab, (2, 24), generator=torch.Generator().manual_seed(0))
-    want = oq.OracleQwen3(ocfg, sd).generate(ids, 4)
-    cfg = Qwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
-    r = Qwen3Runner(cfg, max_batch=2, max_len=64, max_new_tokens=8)
-    r.load_state_dict(sd)
-    got = r.generate(ids, 4, use_graph=True).cpu().long()
-    assert lib.teeny_device_error(1) == 0
-    assert torch.equal(got, want), (got, want)
-    print("smoke ok: qwen3 greedy ids match the oracle", got.tolist())

@@ -128,3 +128,24 @@ def test_sampling_in_the_runner(q):
     r.set_sampling(0.0)
     assert torch.equal(r.generate(ids, 10).cpu(), greedy)
     assert q.lib.teeny_device_error(1) == 0
+
+
+def test_decode_past_cache_capacity_is_refused(q):
+    """A step that would append beyond max_len returns an error instead of silently attending over a stale cache."""
+    from oracle import qwen3 as oq
+    ocfg = oq.OracleQwen3Config(1, 256, 4, 2, 128, 512, 512, tied=True)
+    sd = oq.make_weights(ocfg, 2)
+    cfg = q.Qwen3Config(1, 256, 4, 2, 128, 512, 512, tied=True)
+    r = q.Qwen3Runner(cfg, max_batch=1, max_len=10, max_new_tokens=8)
+    r.load_state_dict(sd)
+    ids = torch.randint(0, 512, (1, 8), generator=torch.Generator().manual_seed(0))
+    with pytest.raises(ValueError):
+        r.generate(ids, 4)          # rows 8, 9, 10 would be needed
+    got = r.generate(ids, 3)        # rows 8 and 9: fits exactly
+    assert torch.equal(got.cpu().long(), oq.OracleQwen3(ocfg, sd).generate(ids, 3))
+    for graph in (False, True):
+        with pytest.raises(q._lib.TeenyError):
+            r.decode_step(graph=graph)
+    assert q.lib.teeny_device_error(1) == 0
+    r.prefill(ids)                  # a new generation starts from an empty cache again
+    r.decode_step(graph=True)
