@@ -102,8 +102,11 @@ def _rotate_half(x):
 class OracleQwen3:
     """Greedy decoder over an HF-named bf16 state dict with a growing KV cache."""
 
-    def __init__(self, cfg, state_dict):
-        self.cfg, self.sd = cfg, state_dict
+    def __init__(self, cfg, state_dict, f32_twin=False):
+        """f32_twin: evaluate the same graph with every projection and the attention computed on operands up-cast to
+        f32 and the result rounded to bf16 once -- the same rounding points, another summation order.  The distance
+        between the two evaluations is the noise floor a deep bf16 model has between any two correct implementations."""
+        self.cfg, self.sd, self.f32_twin = cfg, state_dict, f32_twin
         self.k_cache = [None] * cfg.num_layers
         self.v_cache = [None] * cfg.num_layers
         self.pos = 0
@@ -112,6 +115,11 @@ class OracleQwen3:
         self.k_cache = [None] * self.cfg.num_layers
         self.v_cache = [None] * self.cfg.num_layers
         self.pos = 0
+
+    def _linear(self, x, w):
+        if self.f32_twin:
+            return F.linear(x.float(), w.float()).to(torch.bfloat16)
+        return F.linear(x, w)
 
     @torch.no_grad()
     def forward(self, ids, return_hidden=False):
@@ -128,9 +136,9 @@ class OracleQwen3:
         for i in range(cfg.num_layers):
             p = f"model.layers.{i}."
             y = _rms(x, sd[p + "input_layernorm.weight"], cfg.eps)
-            q = F.linear(y, sd[p + "self_attn.q_proj.weight"]).view(B, s, Hq, D)
-            k = F.linear(y, sd[p + "self_attn.k_proj.weight"]).view(B, s, Hkv, D)
-            v = F.linear(y, sd[p + "self_attn.v_proj.weight"]).view(B, s, Hkv, D).transpose(1, 2)
+            q = self._linear(y, sd[p + "self_attn.q_proj.weight"]).view(B, s, Hq, D)
+            k = self._linear(y, sd[p + "self_attn.k_proj.weight"]).view(B, s, Hkv, D)
+            v = self._linear(y, sd[p + "self_attn.v_proj.weight"]).view(B, s, Hkv, D).transpose(1, 2)
             q = _rms(q, sd[p + "self_attn.q_norm.weight"], cfg.eps).transpose(1, 2)
             k = _rms(k, sd[p + "self_attn.k_norm.weight"], cfg.eps).transpose(1, 2)
             q = q * cos + _rotate_half(q) * sin
@@ -142,18 +150,22 @@ class OracleQwen3:
             g = Hq // Hkv
             ke = k[:, :, None].expand(B, Hkv, g, L, D).reshape(B, Hq, L, D)
             ve = v[:, :, None].expand(B, Hkv, g, L, D).reshape(B, Hq, L, D)
-            a = F.scaled_dot_product_attention(q, ke, ve, attn_mask=mask, dropout_p=0.0,
-                                               scale=D ** -0.5, is_causal=False)
+            if self.f32_twin:
+                a = F.scaled_dot_product_attention(q.float(), ke.float(), ve.float(), attn_mask=mask, dropout_p=0.0,
+                                                   scale=D ** -0.5, is_causal=False).to(torch.bfloat16)
+            else:
+                a = F.scaled_dot_product_attention(q, ke, ve, attn_mask=mask, dropout_p=0.0,
+                                                   scale=D ** -0.5, is_causal=False)
             a = a.transpose(1, 2).reshape(B, s, Hq * D)
-            x = x + F.linear(a, sd[p + "self_attn.o_proj.weight"])
+            x = x + self._linear(a, sd[p + "self_attn.o_proj.weight"])
             y = _rms(x, sd[p + "post_attention_layernorm.weight"], cfg.eps)
-            m = F.silu(F.linear(y, sd[p + "mlp.gate_proj.weight"])) * F.linear(y, sd[p + "mlp.up_proj.weight"])
-            x = x + F.linear(m, sd[p + "mlp.down_proj.weight"])
+            m = F.silu(self._linear(y, sd[p + "mlp.gate_proj.weight"])) * self._linear(y, sd[p + "mlp.up_proj.weight"])
+            x = x + self._linear(m, sd[p + "mlp.down_proj.weight"])
         self.pos = L
         self.last_residual = x  # bf16 [B, s, hidden]: the residual stream after the last layer (layer-level checks)
         h = _rms(x, sd["model.norm.weight"], cfg.eps)
         head = sd["model.embed_tokens.weight"] if cfg.tied else sd["lm_head.weight"]
-        logits = F.linear(h[:, -1, :], head)
+        logits = self._linear(h[:, -1, :], head)
         return (logits, h) if return_hidden else logits
 
     @torch.no_grad()
