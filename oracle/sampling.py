@@ -8,8 +8,12 @@ logits-processor definitions, pinned here so the CUDA kernel has something exact
   2. e_i = exp((l_i - l_0) / temperature) in float32, c_i = e_0 + ... + e_i summed sequentially in float32;
   3. nucleus = the shortest prefix with c_{n-1} >= top_p * c_last (at least one candidate);
   4. sample = the first candidate i < n with c_i > u * c_{n-1}.
-Parity unpinned against the reference (it has no sampler); the softmax part is pinned by the reference's own
-softmax fixture through oracle/cpu.py.
+The reference has no sampler to pin this against; it is pinned instead to the logits processors of ``transformers``
+(the package the reference's Qwen3 script generates with, support/teeny-torch/python/tests/test_qwen3.py:18):
+tests/test_oracle_sampling.py checks that the candidate set equals TopKLogitsWarper's kept set, the nucleus equals what
+TopPLogitsWarper keeps after it, and the in-nucleus probabilities equal the softmax of the surviving scores (one
+stated difference: on a tie at the k-th value the warper keeps every tied entry, this keeps exactly k, lowest indices
+first).  The softmax part is also pinned by the reference's own softmax fixture through oracle/cpu.py.
 """
 import numpy as np
 

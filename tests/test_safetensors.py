@@ -80,3 +80,40 @@ def test_sharded_qwen3_checkpoint_gives_the_same_rank_shards(tmp_path):
             want, got = tp.shard_head(sd, cfg, rank, world), tp.shard_head(ckpt, cfg, rank, world)
             for k in want:
                 assert torch.equal(want[k], got[k]), (world, rank, k)
+
+
+def test_interchange_with_the_safetensors_package(tmp_path):
+    """Files written by the ``safetensors`` package (the format's own implementation, which the reference's crate
+    follows) read back bit-exact through this reader, and files written here read back bit-exact through the package,
+    for every dtype the reader maps, a zero-dimensional tensor, an empty tensor and the metadata block."""
+    safetensors_torch = pytest.importorskip("safetensors.torch")
+    from safetensors import safe_open
+    from teenygrad_b200 import safetensors as st
+    g = torch.Generator().manual_seed(3)
+    tensors = {
+        "model.layers.0.self_attn.q_proj.weight": torch.randn(48, 32, generator=g).bfloat16(),
+        "model.norm.weight": torch.randn(32, generator=g).half(),
+        "f32": torch.randn(3, 5, 7, generator=g),
+        "f64": torch.randn(4, generator=g, dtype=torch.float64),
+        "i64": torch.randint(-5, 5, (6,), generator=g),
+        "i32": torch.randint(-5, 5, (2, 3), generator=g, dtype=torch.int32),
+        "u8": torch.randint(0, 255, (9,), generator=g, dtype=torch.uint8),
+        "flag": torch.tensor([True, False, True]),
+        "scalar": torch.tensor(2.5),
+        "empty": torch.zeros(0, 4),
+    }
+    theirs = tmp_path / "theirs.safetensors"
+    safetensors_torch.save_file(tensors, str(theirs), metadata={"format": "pt"})
+    mine = st.SafeTensors(theirs)
+    assert sorted(mine) == sorted(tensors)
+    for k, v in tensors.items():
+        assert mine[k].dtype == v.dtype and tuple(mine[k].shape) == tuple(v.shape), k
+        assert torch.equal(mine[k], v), k
+    ours = tmp_path / "ours.safetensors"
+    st.save_file(tensors, ours, metadata={"format": "pt"})
+    back = safetensors_torch.load_file(str(ours))
+    assert sorted(back) == sorted(tensors)
+    for k, v in tensors.items():
+        assert back[k].dtype == v.dtype and torch.equal(back[k], v), k
+    with safe_open(str(ours), framework="pt") as f:
+        assert f.metadata() == {"format": "pt"}
