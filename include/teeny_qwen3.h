@@ -98,6 +98,11 @@ void* teeny_qwen3_buffer(teeny_qwen3* model, int which);
  * 2 * tp_size * max_batch * hidden (value, stamp) pairs to it (the one device allocation this library makes, at
  * set-up). */
 int teeny_tp_unique_id(void* out128);
+/* Collective over all `world` ranks.  The rendezvous cannot hang on a rank that never arrives: it is made with a
+ * non-blocking guard communicator that is polled against a host timeout (TEENY_TP_INIT_TIMEOUT_MS in the environment,
+ * default 300000; 0 = plain blocking ncclCommInitRank) and aborted with ncclCommAbort when the timeout expires, in
+ * which case TEENY_ERR_NCCL is returned and nothing is left behind.  TEENY_NCCL_LIB names the NCCL library to load
+ * (default libnccl.so.2). */
 int teeny_tp_init(const void* id128, int rank, int world, void** comm_out);
 int teeny_tp_destroy(void* comm);
 int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_stream_t stream);

@@ -22,9 +22,11 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <thread>
 #include <vector>
 
 #include "../../include/teeny_b200.h"
@@ -47,13 +49,20 @@ struct NcclApi {
   ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
+  // optional (NCCL >= 2.14): what the guarded set-up needs
+  ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*Broadcast)(const void*, void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
   bool ok = false;
 };
 NcclApi g_nccl;
 
 bool load_nccl() {
   if (g_nccl.ok) return true;
-  if (!g_nccl.handle) g_nccl.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  // TEENY_NCCL_LIB names another library with the NCCL entry points (the host-side tests put a stand-in there)
+  const char* name = getenv("TEENY_NCCL_LIB");
+  if (!g_nccl.handle) g_nccl.handle = dlopen(name && name[0] ? name : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
   if (!g_nccl.handle) return false;
   auto sym = [&](const char* n) { return dlsym(g_nccl.handle, n); };
   g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(sym("ncclGetUniqueId"));
@@ -63,9 +72,73 @@ bool load_nccl() {
   g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(sym("ncclAllGather"));
   g_nccl.GroupStart = reinterpret_cast<decltype(g_nccl.GroupStart)>(sym("ncclGroupStart"));
   g_nccl.GroupEnd = reinterpret_cast<decltype(g_nccl.GroupEnd)>(sym("ncclGroupEnd"));
+  g_nccl.CommInitRankConfig = reinterpret_cast<decltype(g_nccl.CommInitRankConfig)>(sym("ncclCommInitRankConfig"));
+  g_nccl.CommGetAsyncError = reinterpret_cast<decltype(g_nccl.CommGetAsyncError)>(sym("ncclCommGetAsyncError"));
+  g_nccl.CommAbort = reinterpret_cast<decltype(g_nccl.CommAbort)>(sym("ncclCommAbort"));
+  g_nccl.Broadcast = reinterpret_cast<decltype(g_nccl.Broadcast)>(sym("ncclBroadcast"));
   g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.CommDestroy && g_nccl.AllReduce &&
               g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd;
   return g_nccl.ok;
+}
+
+// Polls a non-blocking communicator until its pending operation has finished, failed, or `deadline` (steady clock)
+// has passed.  Returns ncclSuccess, the error, or ncclInProgress for "still pending at the deadline".
+ncclResult_t nccl_wait(ncclComm_t comm, ncclResult_t first, std::chrono::steady_clock::time_point deadline) {
+  ncclResult_t state = first;
+  while (state == ncclInProgress) {
+    if (std::chrono::steady_clock::now() >= deadline) return ncclInProgress;
+    std::this_thread::sleep_for(std::chrono::milliseconds(2));
+    if (g_nccl.CommGetAsyncError(comm, &state) != ncclSuccess) return ncclInternalError;
+  }
+  return state;
+}
+
+// Communicator set-up that cannot hang on a rank that never arrives.  ncclCommInitRank blocks for ever in that case
+// and a blocking communicator under construction cannot be aborted, so the rendezvous is first made with a
+// NON-blocking "guard" communicator: init, poll with a host timeout, ncclCommAbort when the timeout expires.  Once the
+// guard is up every rank is known to be alive; rank 0 then broadcasts a second unique id over it and all ranks create
+// the blocking communicator the runner uses (its collectives are recorded into CUDA graphs, which a non-blocking
+// communicator's helper-thread launches do not allow), and the guard is aborted.  Returns 0, or TEENY_ERR_NCCL with
+// nothing left behind.
+int guarded_comm_init(const ncclUniqueId& id, int rank, int world, long timeout_ms, ncclComm_t* out) {
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+  config.blocking = 0;
+  ncclComm_t guard = nullptr;
+  ncclResult_t r = g_nccl.CommInitRankConfig(&guard, world, id, rank, &config);
+  if (r != ncclSuccess && r != ncclInProgress) return TEENY_ERR_NCCL;
+  r = nccl_wait(guard, r, deadline);
+  if (r != ncclSuccess) {  // a rank did not arrive in time (or the bootstrap failed): give everything back
+    if (guard) g_nccl.CommAbort(guard);
+    return TEENY_ERR_NCCL;
+  }
+  // second id over the guard
+  ncclUniqueId id2;
+  std::memset(&id2, 0, sizeof(id2));
+  int rc = 0;
+  void* dbuf = nullptr;
+  if (rank == 0 && g_nccl.GetUniqueId(&id2) != ncclSuccess) rc = TEENY_ERR_NCCL;
+  if (cudaMalloc(&dbuf, sizeof(id2)) != cudaSuccess) { dbuf = nullptr; rc = TEENY_ERR_NCCL; }
+  if (!rc && cudaMemcpy(dbuf, &id2, sizeof(id2), cudaMemcpyHostToDevice) != cudaSuccess) rc = TEENY_ERR_NCCL;
+  if (!rc) {
+    r = nccl_wait(guard, g_nccl.Broadcast(dbuf, dbuf, sizeof(id2), ncclChar, 0, guard, nullptr), deadline);
+    if (r != ncclSuccess) rc = TEENY_ERR_NCCL;
+  }
+  if (!rc) {
+    // the broadcast runs on the legacy default stream; bound the wait for it as well
+    cudaError_t q;
+    while ((q = cudaStreamQuery(nullptr)) == cudaErrorNotReady) {
+      if (std::chrono::steady_clock::now() >= deadline) { rc = TEENY_ERR_NCCL; break; }
+      std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+    if (!rc && q != cudaSuccess) rc = TEENY_ERR_NCCL;
+  }
+  if (!rc && cudaMemcpy(&id2, dbuf, sizeof(id2), cudaMemcpyDeviceToHost) != cudaSuccess) rc = TEENY_ERR_NCCL;
+  if (!rc && g_nccl.CommInitRank(out, world, id2, rank) != ncclSuccess) rc = TEENY_ERR_NCCL;
+  g_nccl.CommAbort(guard);
+  if (dbuf) cudaFree(dbuf);
+  if (rc) cudaGetLastError();
+  return rc;
 }
 
 // Tensor-parallel context: the NCCL communicator plus, for decode, peer-mapped receive buffers through which the
@@ -865,14 +938,24 @@ int teeny_tp_init(const void* id128, int rank, int world, void** comm_out) {
   ncclUniqueId id;
   std::memcpy(&id, id128, sizeof(id));
   ncclComm_t comm = nullptr;
-  // The prefill overlaps its all-reduces with GEMMs that leave comm_sms() SMs free: keep the collective within them
-  // (a caller's own setting wins).
-  {
+  // Only when the caller reserved SMs for the collective (TEENY_TP_COMM_SMS) is NCCL told to stay within them; otherwise
+  // NCCL's own choice of CTAs stands (a caller's NCCL_MAX_CTAS always wins).
+  if (comm_sms() > 0) {
     char buf[16];
-    snprintf(buf, sizeof(buf), "%d", comm_sms() > 0 ? comm_sms() : 16);
+    snprintf(buf, sizeof(buf), "%d", comm_sms());
     setenv("NCCL_MAX_CTAS", buf, 0);
   }
-  if (g_nccl.CommInitRank(&comm, world, id, rank) != ncclSuccess) return TEENY_ERR_NCCL;
+  // TEENY_TP_INIT_TIMEOUT_MS: how long the rendezvous may take before it is abandoned (default 5 minutes; 0 = plain
+  // blocking ncclCommInitRank, which waits for ever for a rank that never comes).
+  long timeout_ms = 300000;
+  if (const char* e = getenv("TEENY_TP_INIT_TIMEOUT_MS")) timeout_ms = atol(e);
+  const bool can_guard = g_nccl.CommInitRankConfig && g_nccl.CommGetAsyncError && g_nccl.CommAbort && g_nccl.Broadcast;
+  if (timeout_ms > 0 && can_guard) {
+    const int rc = guarded_comm_init(id, rank, world, timeout_ms, &comm);
+    if (rc != 0) return rc;
+  } else if (g_nccl.CommInitRank(&comm, world, id, rank) != ncclSuccess) {
+    return TEENY_ERR_NCCL;
+  }
   TpContext* c = new (std::nothrow) TpContext();
   if (!c) return TEENY_ERR_BAD_ARG;
   c->comm = comm;

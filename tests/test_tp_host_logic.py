@@ -100,3 +100,77 @@ def test_shard_shapes_8b_tp8():
     sh = tp.shard_layer(sd, cfg, 0, 3, 8)
     assert sh["qkv"].shape == (768, 4096) and sh["o"].shape == (4096, 512)
     assert sh["gate_up"].shape == (3072, 4096) and sh["down"].shape == (4096, 1536)
+
+
+_FAKE_NCCL = r"""
+/* Stand-in for libnccl.so.2 on a machine without GPUs: a communicator whose rendezvous never completes (the other
+ * rank never arrives).  Records what the library under test does with it. */
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+typedef struct { char internal[128]; } ncclUniqueId;
+typedef void* ncclComm_t;
+typedef int ncclResult_t;
+enum { ncclSuccess = 0, ncclInProgress = 7 };
+static int polls = 0;
+static void note(const char* what) {
+  const char* path = getenv("FAKE_NCCL_LOG");
+  if (!path) return;
+  FILE* f = fopen(path, "a");
+  if (f) { fprintf(f, "%s polls=%d\n", what, polls); fclose(f); }
+}
+ncclResult_t ncclGetUniqueId(ncclUniqueId* id) { memset(id, 7, sizeof(*id)); return ncclSuccess; }
+ncclResult_t ncclCommInitRankConfig(ncclComm_t* comm, int n, ncclUniqueId id, int rank, void* config) {
+  (void)n; (void)id; (void)rank;
+  /* the blocking flag is the int behind size, magic and version in ncclConfig_t */
+  note(((int*)((char*)config + sizeof(size_t)))[2] == 0 ? "init nonblocking" : "init blocking");
+  *comm = (ncclComm_t)0x1234;
+  return ncclInProgress;
+}
+ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* state) { (void)comm; ++polls; *state = ncclInProgress; return ncclSuccess; }
+ncclResult_t ncclCommAbort(ncclComm_t comm) { note(comm == (ncclComm_t)0x1234 ? "abort guard" : "abort other"); return ncclSuccess; }
+ncclResult_t ncclCommInitRank(ncclComm_t* c, int n, ncclUniqueId id, int r) { (void)c; (void)n; (void)id; (void)r; note("blocking init"); return 1; }
+ncclResult_t ncclCommDestroy(ncclComm_t c) { (void)c; return ncclSuccess; }
+ncclResult_t ncclAllReduce(void) { return 1; }
+ncclResult_t ncclAllGather(void) { return 1; }
+ncclResult_t ncclBroadcast(void) { note("broadcast"); return 1; }
+ncclResult_t ncclGroupStart(void) { return ncclSuccess; }
+ncclResult_t ncclGroupEnd(void) { return ncclSuccess; }
+"""
+
+
+def test_rendezvous_with_a_rank_that_never_arrives_times_out_and_aborts(tmp_path):
+    """teeny_tp_init against a stand-in NCCL whose communicator never finishes its rendezvous (the peer rank exited
+    before joining): the call must come back with TEENY_ERR_NCCL after the host timeout, having aborted the guard
+    communicator, and must not have fallen into the blocking initialisation."""
+    import shutil
+    import subprocess
+    import sys
+    import time
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler for the NCCL stand-in")
+    src, so, log = tmp_path / "fake_nccl.c", tmp_path / "libfake_nccl.so", tmp_path / "calls.log"
+    src.write_text(_FAKE_NCCL)
+    subprocess.check_call(["gcc", "-shared", "-fPIC", "-O1", "-o", str(so), str(src)])
+    code = (
+        "import ctypes, sys, time\n"
+        "from teenygrad_b200 import qwen3\n"
+        "buf = (ctypes.c_ubyte * 128)()\n"
+        "assert qwen3.lib.teeny_tp_unique_id(buf) == 0\n"
+        "comm = ctypes.c_void_p()\n"
+        "t0 = time.time()\n"
+        "rc = qwen3.lib.teeny_tp_init(bytes(buf), 0, 2, ctypes.byref(comm))\n"
+        "print('rc', rc, 'seconds', round(time.time() - t0, 2), 'comm', comm.value)\n"
+    )
+    env = dict(os.environ, TEENY_NCCL_LIB=str(so), TEENY_TP_INIT_TIMEOUT_MS="400", FAKE_NCCL_LOG=str(log),
+               PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    t0 = time.time()
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "rc -6 " in res.stdout and "comm None" in res.stdout, res.stdout   # TEENY_ERR_NCCL, no context handed out
+    seconds = float(res.stdout.split("seconds")[1].split()[0])
+    assert 0.3 <= seconds < 5.0, res.stdout                                     # the timeout, not a hang and not at once
+    calls = log.read_text().splitlines()
+    assert calls[0].startswith("init nonblocking")
+    assert calls[-1].startswith("abort guard") and "polls=0" not in calls[-1]   # polled, then aborted
+    assert not any(c.startswith(("blocking init", "broadcast")) for c in calls)
