@@ -110,6 +110,17 @@ int teeny_tp_all_reduce_bf16(void* comm, teeny_bf16* buf, size_t count, teeny_st
  * teeny_qwen3_create when tp_size > 1 and max_batch <= 128; needs CUDA IPC between the ranks' processes), 0 when it
  * all-reduces through NCCL instead. */
 int teeny_tp_peer_enabled(void* comm);
+/* The receiving half of the decode-time row-parallel reduction, for hosts that run their own layer loop (the runner
+ * uses the same kernel).  recv holds `world` copies of the projection, slot_elems elements apart, each element one
+ * 64-bit word {f32 value, 32-bit stamp} that the ranks' GEMM epilogues stored over NVLink; an element has arrived when
+ * its stamp equals *epoch * 1024 + round + 1.  The kernel waits per element, sums the copies in rank order in f32,
+ * rounds the sum to bf16, adds it into residual [M, N] and writes y = rms_norm(residual) * weight.  No wait is
+ * unbounded: after wait_limit_ns nanoseconds without progress (0 = the library's 2 s) the kernel stores 0x301 in the
+ * device error word (teeny_device_error) and returns, leaving the context usable.  The reference has no multi-GPU
+ * path and no counterpart. */
+int teeny_tp_gather_add_rms_norm_bf16(const void* recv, size_t slot_elems, int world, const uint32_t* epoch,
+                                      uint32_t round, teeny_bf16* residual, teeny_bf16* y, const teeny_bf16* weight,
+                                      int M, int N, float eps, unsigned long long wait_limit_ns, teeny_stream_t stream);
 
 #ifdef __cplusplus
 }

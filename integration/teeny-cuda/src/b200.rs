@@ -153,6 +153,7 @@ extern "C" {
     pub fn teeny_tp_destroy(comm: *mut c_void) -> c_int;
     pub fn teeny_tp_all_reduce_bf16(comm: *mut c_void, buf: *mut u16, count: usize, stream: CUstream) -> c_int;
     pub fn teeny_tp_peer_enabled(comm: *mut c_void) -> c_int;
+    pub fn teeny_tp_gather_add_rms_norm_bf16(recv: *const c_void, slot_elems: usize, world: c_int, epoch: *const u32, round: u32, residual: *mut u16, y: *mut u16, weight: *const u16, m: c_int, n: c_int, eps: f32, wait_limit_ns: c_ulonglong, stream: CUstream) -> c_int;
 }
 // ---- generated from include/*.h: end ----
 

@@ -1,21 +1,38 @@
-// Causal grouped-query flash-attention forward for sm_100a, head_dim 128, bf16 in/out, f32 softmax.
+// Causal grouped-query flash-attention forward for sm_100a, head_dim 128, bf16 in/out, f32 softmax, on CTA pairs.
 //
-// One CTA per (128-query tile, query head, batch); keys/values stream through in tiles of 128.
-//   warps 0, 3  TMA producers: warp 0 loads Q once and then the K tiles, warp 3 the V tiles, each into a two-stage ring
-//               (128-byte swizzle) with its own barriers;
-//   warp 1      MMA issuer: S = Q K^T (tcgen05.mma 128x128x16, both operands K-major) into one of two S buffers in
-//               TMEM, and O += P V (P from tensor memory, V MN-major straight from its [key][d] tile);
-//               QK^T is issued two tiles ahead of P V so the tensor pipe works while the softmax groups run;
-//   warp 2      allocates / frees tensor memory;
-//   warps 4-7, 8-11   two softmax warpgroups, thread = query row in both; warpgroup w takes the key tiles j = w mod 2
-//               (S buffer w, P buffer w), so one group's exponentials run while the other loads and scans its next
-//               tile.  Per tile: tcgen05.ld the S row in 32-column pieces for the row maximum (causal / tail mask);
-//               (registers re-divided with setmaxnreg: 224 per softmax thread, 56 per service thread);
-//               agree on the running maximum with the other group (it lives in shared memory; a tile's decision
-//               waits for the previous tile's, a few instructions); lazy rescale (O in TMEM is only rescaled when
-//               the maximum grows by more than 2^8); P = exp2(s * scale - m) as bf16
-//               pairs into tensor memory, row sums in f32 per group.
+// A cluster of two CTAs (two neighbouring SMs) takes 256 queries of one (head, batch): CTA r owns query rows
+// [q0 + 128 r, q0 + 128 r + 128).  Keys / values stream through in tiles of 128 keys.  Every tcgen05.mma is issued by
+// the leader CTA for the pair (cta_group::2, M = 256): the instruction takes rows 0-127 of its A operand and output
+// from the leader's tensor memory and rows 128-255 from the peer's, and HALF of its B operand from each CTA's shared
+// memory.  So each SM loads and re-reads only half of every K and V tile, and neither Q nor P is read from shared
+// memory at all (both are A operands in tensor memory): per key tile an SM's shared memory sees 32 KB of TMA writes
+// and 32 KB of operand reads for 1024 tensor-pipe cycles, where a lone 128 x 128 tile with Q in shared memory needs
+// 64 KB + 96 KB -- more than the port delivers in that time, which is what held a single-CTA version of this kernel at
+// 43 % tensor-pipe activity.  No multicast loads: each CTA's TMA fetches its own half; only completions
+// (tcgen05.commit) are delivered to both CTAs.
+//
+//   warp 0       K producer (both CTAs): its 64 keys x 128 d of each key tile (two 8 KB boxes), ring of kKV stages;
+//                transaction bytes of both CTAs are credited to the leader's barrier.
+//   warp 3       V producer (both CTAs): all 128 keys x its 64 d columns (one 16 KB box), ring of its own: K runs two
+//                tiles ahead of V and must not queue behind it.
+//   warps 1, 2   MMA issuers (leader only), one thread each.  Warp 1: S = Q K^T (A = Q from tensor memory, B = K,
+//                K-major) into one of two S buffers, as far ahead of P V as the buffers allow (an S buffer is free
+//                again as soon as its softmax group of both CTAs has the rows in registers), so the tensor pipe works
+//                while the softmax groups run.  Warp 2: O += P V (A = P from tensor memory, B = V MN-major straight
+//                from its [key][d] tile).  Two threads because a lone thread cannot issue these 64-cycle instructions
+//                fast enough, and so that neither stream waits behind the other's barriers.
+//   warp 2       also allocates / frees tensor memory (cta_group::2, both CTAs).
+//   warps 4-7, 8-11   two softmax warpgroups per CTA, thread = query row in both; warpgroup w takes the key tiles
+//                j = w mod 2 (S buffer w), so one group's exponentials run while the other scans its next tile.
+//                Before the loop the groups copy the CTA's Q rows from global memory into tensor memory.  Per tile:
+//                tcgen05.ld the S row in 32-column pieces, row maximum (causal / tail mask), agreement on the running
+//                maximum with the other group (shared memory; a tile's decision waits for the previous tile's), lazy
+//                rescale (O in tensor memory is only rescaled when the maximum grows by more than 2^8),
+//                P = exp2(s * scale - m) as bf16 pairs into the one P buffer in tensor memory (free once P V of the
+//                previous tile has completed), row sums in f32 per group.
+//                (Registers re-divided with setmaxnreg: 224 per softmax thread, 56 per service thread.)
 // Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
+// Tensor memory columns per CTA: S0 0-127, S1 128-255 (f32 scores), O 256-383 (f32), Q 384-447, P 448-511 (bf16 pairs).
 #include <atomic>
 
 #include "common.cuh"
@@ -25,26 +42,28 @@ namespace teeny {
 
 namespace {
 
-constexpr int kQT = 128;
-constexpr int kKT = 128;
+constexpr int kQT = 128;                        // query rows per CTA (pair: 256)
+constexpr int kKT = 128;                        // keys per tile
 constexpr int kHD = 128;
-constexpr int kThreads = 384;  // TMA, MMA, TMEM, idle + two softmax warpgroups
-constexpr int kTileBytes = kKT * kHD * 2;       // 32 KB: two 16 KB boxes of [128 rows][64 d]
-constexpr int kBoxBytes = 128 * 64 * 2;         // 16 KB
-constexpr int kSmemQ = 0;
-constexpr int kSmemK = kSmemQ + kTileBytes;     // 2 stages
-constexpr int kKV = 2;                          // stages of the K ring and of the V ring (three measured no faster)
-constexpr int kSmemV = kSmemK + kKV * kTileBytes;
-constexpr int kSmemBar = kSmemV + kKV * kTileBytes;
+constexpr int kThreads = 384;                   // TMA K, MMA QK, MMA PV + TMEM, TMA V; two softmax warpgroups
+constexpr int kHalfBytes = 64 * kHD * 2;        // 16 KB: this CTA's half of a K tile (64 keys) or of a V tile (64 d)
+constexpr int kKBoxBytes = 64 * 64 * 2;         // 8 KB: [64 keys][64 d]
+constexpr int kKV = 4;                          // stages of the K ring and of the V ring
+constexpr int kSmemK = 0;
+constexpr int kSmemV = kSmemK + kKV * kHalfBytes;
+constexpr int kSmemBar = kSmemV + kKV * kHalfBytes;
 constexpr int kSmemXch = kSmemBar + 256;        // running maximum per row (128 floats), row sums of both groups (256)
 constexpr int kSmemTotal = kSmemXch + 384 * 4 + 1024;
 static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address -> leader
 
 struct PrefillArgs {
+  const bf16* q;
   bf16* o;
   float* lse;
   int B, Hq, Hkv, Sq, Skv;
+  long long q_sb, q_sh, q_ss;
   long long o_sb, o_sh, o_ss;
   float scale_log2;
   int causal;
@@ -56,55 +75,116 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ uint32_t pair_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void pair_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_leader(uint32_t local_addr) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(0u));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// This CTA's half tile; completion bytes are credited to the LEADER's barrier at the same offset.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+// The eight K-steps of one 128-deep product for the pair, D[tmem] (+)= A[tmem] * B[smem] (rows 0-127 in the leader,
+// 128-255 in the peer), as one block of straight-line code: A advances eight tensor-memory columns per step, the
+// address field of the B descriptor by the compile-time offsets O1..O7 (16-byte units).  One thread issues a
+// tcgen05.mma only every ~100 cycles when address arithmetic sits between them (a lone lane runs a dependent
+// instruction every few cycles), which is more than the 64 cycles the tensor pipe needs for one of these steps.
+template <int O1, int O2, int O3, int O4, int O5, int O6, int O7>
+__device__ __forceinline__ void umma_bf16_ts_pair_x8(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                     uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 a, %1, 8;\n\t add.u64 b, %2, %5;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 16;\n\t add.u64 b, %2, %6;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 24;\n\t add.u64 b, %2, %7;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 32;\n\t add.u64 b, %2, %8;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 40;\n\t add.u64 b, %2, %9;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 48;\n\t add.u64 b, %2, %10;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 56;\n\t add.u64 b, %2, %11;\n\t tcgen05.mma.cta_group::2.kind::f16 [%0], [a], b, %3, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "n"(O1), "n"(O2), "n"(O3), "n"(O4), "n"(O5),
+        "n"(O6), "n"(O7)
+      : "memory");
+}
+// Arrives on the barrier at this offset in BOTH CTAs of the pair once all MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(static_cast<uint16_t>(3))
+      : "memory");
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
-attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                         const __grid_constant__ CUtensorMap tmap_v, const PrefillArgs args) {
+attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                         const PrefillArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bar0 = base + kSmemBar;
-  // barriers: 0 q_full | 1-3 k_full | 4-6 k_empty | 7-9 v_full | 10-12 v_empty | 13,14 s_full | 15,16 s_empty |
-  //           17,18 p_full | 19,20 pv_done | 21,22 m_ready ; then the TMEM base address
   auto bar = [&](int i) { return bar0 + 8u * i; };
-  constexpr int Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
-                S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 2,
+  // K_FULL / V_FULL / S_EMPTY / P_FULL / Q_READY are used in the leader's copy only (the peer's producers and softmax
+  // threads signal them across the pair); the others exist and are used in both CTAs
+  constexpr int Q_READY = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
+                S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 1,
                 M_READY = PV_DONE + 2, kNumBars = M_READY + 2;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
+  static_assert(8 * kNumBars + 8 <= 256, "barrier block");
+  const uint32_t tmem_slot = bar0 + 8u * kNumBars;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = pair_rank();
+  const bool leader = rank == 0;
   int* err = args.err;
 
   // heavier (later) query tiles first: with causal masking they have the most key tiles
-  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int n_pair_tiles = gridDim.x >> 1;
+  const int pt = n_pair_tiles - 1 - static_cast<int>(blockIdx.x >> 1);
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (args.Hq / args.Hkv);
-  const int q0 = qt * kQT;
-  const int off = args.Skv - args.Sq;  // causal: query i sees keys <= i + off
+  const int q0 = pt * 2 * kQT + static_cast<int>(rank) * kQT;   // this CTA's first query row
+  const int off = args.Skv - args.Sq;                           // causal: query i sees keys <= i + off
   int kv_end = args.Skv;
-  if (args.causal) kv_end = min(args.Skv, q0 + kQT + off);
+  if (args.causal) kv_end = min(args.Skv, pt * 2 * kQT + 2 * kQT + off);   // of the pair's last row
   const int n_tiles = (kv_end + kKT - 1) / kKT;  // >= 1 (host guarantees Skv >= Sq >= 1 when causal)
 
   if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     for (int i = 0; i < kNumBars; ++i) {
-      const bool softmax_arrives = (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL || i == P_FULL + 1 || i >= M_READY);
-      mbar_init(bar(i), softmax_arrives ? 128 : 1);
+      uint32_t count = 1;
+      if (i == Q_READY) count = 512;                        // both softmax groups of both CTAs
+      else if (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) count = 256;  // one softmax group of each CTA
+      else if (i >= M_READY) count = 128;
+      mbar_init(bar(i), count);
     }
     mbar_fence_init();
   }
   if (warp == 2) {
-    tmem_alloc(base + kSmemBar + 8 * kNumBars, 512);
-    tmem_relinquish();
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
+  pair_sync();  // both CTAs' barriers exist before either CTA can signal the other
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  // tensor memory columns: S0 0-127, S1 128-255 (f32 scores), O 256-383 (f32), P0 384-447, P1 448-511 (bf16 pairs)
-  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256, tmem_p = tmem + 384;
+  const uint32_t tmem = *tmem_slot_ptr;
+  const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256, tmem_q = tmem + 384, tmem_p = tmem + 448;
   pdl_wait();
 
   // The two softmax warpgroups hold a 128-value score row per thread; the four service warps need few registers:
@@ -112,90 +192,86 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   if (warp < 4) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
-    if (lane == 0) {  // Q once, then the K tiles
-      mbar_expect_tx(bar(Q_FULL), kTileBytes);
-      tma_load_4d(base + kSmemQ, &tmap_q, bar(Q_FULL), 0, q0, h, b);
-      tma_load_4d(base + kSmemQ + kBoxBytes, &tmap_q, bar(Q_FULL), 64, q0, h, b);
+    if (lane == 0) {  // this CTA's 64 keys of every K tile
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j % kKV;
         const uint32_t ph = (j / kKV) & 1;
         if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
-        mbar_expect_tx(bar(K_FULL + st), kTileBytes);
-        tma_load_4d(base + kSmemK + st * kTileBytes, &tmap_k, bar(K_FULL + st), 0, j * kKT, hk, b);
-        tma_load_4d(base + kSmemK + st * kTileBytes + kBoxBytes, &tmap_k, bar(K_FULL + st), 64, j * kKT, hk, b);
+        if (leader) mbar_expect_tx(bar(K_FULL + st), 2 * kHalfBytes);  // both CTAs' halves
+        const uint32_t dst = base + kSmemK + st * kHalfBytes;
+        const int key0 = j * kKT + static_cast<int>(rank) * 64;
+        tma_load_4d_pair(dst, &tmap_k, bar(K_FULL + st), 0, key0, hk, b);
+        tma_load_4d_pair(dst + kKBoxBytes, &tmap_k, bar(K_FULL + st), 64, key0, hk, b);
       }
     }
   } else if (warp == 3) {
-    if (lane == 0) {  // the V tiles, from a thread of their own: K runs two tiles ahead of V and must not queue behind it
+    if (lane == 0) {  // this CTA's 64 d columns of every V tile
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j % kKV;
         const uint32_t ph = (j / kKV) & 1;
         if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
-        mbar_expect_tx(bar(V_FULL + st), kTileBytes);
-        tma_load_4d(base + kSmemV + st * kTileBytes, &tmap_v, bar(V_FULL + st), 0, j * kKT, hk, b);
-        tma_load_4d(base + kSmemV + st * kTileBytes + kBoxBytes, &tmap_v, bar(V_FULL + st), 64, j * kKT, hk, b);
+        if (leader) mbar_expect_tx(bar(V_FULL + st), 2 * kHalfBytes);
+        tma_load_4d_pair(base + kSmemV + st * kHalfBytes, &tmap_v, bar(V_FULL + st), static_cast<int>(rank) * 64, j * kKT, hk, b);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(kQT, kKT, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(kQT, kHD, false, true);
-      bool ok = mbar_wait(bar(Q_FULL), 0, err, DEVERR_ATTN_MMA);
-      // development builds: cycles this thread spends waiting for K, a free S buffer, V and P (summed over the tiles)
-      TRACE_ONLY(long long w_k = 0, w_se = 0, w_v = 0, w_p = 0, c0; const long long c_begin = clock64();)
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1, kst = j % kKV;  // S buffer / K ring stage
+    // ---------------- QK^T issuer (leader only) ----------------
+    // Two issuing threads, this one and warp 2's: their instruction streams are independent (S buffers here, O there),
+    // neither waits for the other's barriers, and together they keep the tensor pipe fed.
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(2 * kQT, kKT, false, false);
+      bool ok = mbar_wait(bar(Q_READY), 0, err, DEVERR_ATTN_MMA);
+      // K-major B: 8-row groups 1 KB apart; ring stage s is kHalfBytes further on
+      const uint64_t kdesc0 = make_smem_desc_sw128(base + kSmemK, 16, 1024);
+      // development builds: cycles this thread spends waiting for K and for a free S buffer (summed over the tiles)
+      TRACE_ONLY(long long w_k = 0, w_se = 0, c0; const long long c_begin = clock64();)
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int sb = j & 1, kst = j % kKV;  // S buffer / K ring stage
         const uint32_t ph = (j >> 1) & 1, kph = (j / kKV) & 1;
         TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(K_FULL + kst), kph, err, DEVERR_ATTN_MMA)) return false;
+        if (!mbar_wait(bar(K_FULL + kst), kph, err, DEVERR_ATTN_MMA)) break;
         TRACE_ONLY(w_k += clock64() - c0; c0 = clock64();)
-        if (!mbar_wait(bar(S_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_MMA)) return false;
+        // an S buffer is free again as soon as its softmax groups (of both CTAs) have the rows in registers
+        if (!mbar_wait(bar(S_EMPTY + sb), ph ^ 1, err, DEVERR_ATTN_MMA)) break;
         TRACE_ONLY(w_se += clock64() - c0;)
         tc_fence_after();
-        const uint32_t qb = base + kSmemQ, kb = base + kSmemK + kst * kTileBytes;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 d per step; 4 steps per 64-wide box
-          const uint32_t o = (ks >> 2) * kBoxBytes + (ks & 3) * 32;
-          umma_bf16_ss(tmem_s0 + st * 128, make_smem_desc_sw128(qb + o, 16, 1024),
-                       make_smem_desc_sw128(kb + o, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(bar(K_EMPTY + kst));
-        umma_commit(bar(S_FULL + st));
-        return true;
-      };
-      auto issue_pv = [&](int j) -> bool {
-        const int st = j & 1, vst = j % kKV;  // P buffer / V ring stage
-        const uint32_t ph = (j >> 1) & 1, vph = (j / kKV) & 1;
-        TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(V_FULL + vst), vph, err, DEVERR_ATTN_MMA)) return false;
-        TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
-        if (!mbar_wait(bar(P_FULL + st), ph, err, DEVERR_ATTN_MMA)) return false;
-        TRACE_ONLY(w_p += clock64() - c0;)
-        tc_fence_after();
-        const uint32_t vb = base + kSmemV + vst * kTileBytes;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {  // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory
-          // V tile: rows = keys (128 B = 64 d each), two boxes = two 64-wide d chunks (leading offset 16 KB),
-          // 8-key groups 1 KB apart; 16 keys = 2 KB per step.
-          const uint64_t vd = make_smem_desc_sw128(vb + ks * 2048, kBoxBytes, 1024);
-          umma_bf16_ts(tmem_o, tmem_p + st * 64 + ks * 8, vd, idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(bar(V_EMPTY + vst));
-        umma_commit(bar(PV_DONE + st));
-        return true;
-      };
-      // QK^T runs two tiles ahead of P V: an S buffer is free again as soon as its softmax group has the row in
-      // registers, and this thread must not sit in the wait for P of tile j while S of tile j+2 could be computed
-      if (ok) ok = issue_qk(0);
-      if (ok && n_tiles > 1) ok = issue_qk(1);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 2 < n_tiles) ok = issue_qk(j + 2);
-        if (ok) ok = issue_pv(j);
+        // 16 d per step: 8 tensor-memory columns of Q; 32 bytes along a K box row, the second box 8 KB further on
+        constexpr int B2 = kKBoxBytes >> 4;
+        umma_bf16_ts_pair_x8<2, 4, 6, B2, B2 + 2, B2 + 4, B2 + 6>(tmem_s0 + sb * 128, tmem_q,
+                                                                   kdesc0 + static_cast<uint64_t>(kst * (kHalfBytes >> 4)),
+                                                                   idesc_qk, 0u);
+        umma_commit_pair(bar(K_EMPTY + kst));
+        umma_commit_pair(bar(S_FULL + sb));
       }
       TRACE_VALUE(0, true, n_tiles);
       TRACE_VALUE(1, true, clock64() - c_begin);
       TRACE_VALUE(2, true, w_k);
       TRACE_VALUE(3, true, w_se);
+    }
+  } else {
+    // ---------------- P V issuer (warp 2, leader only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc_pv = make_idesc_bf16(2 * kQT, kHD, false, true);
+      // MN-major B, this CTA's V half: rows = keys (128 B = its 64 d each), 8-key groups 1 KB apart; 16 keys = 2 KB per step
+      const uint64_t vdesc0 = make_smem_desc_sw128(base + kSmemV, kHalfBytes, 1024);
+      TRACE_ONLY(long long w_v = 0, w_p = 0, c0; const long long c_begin = clock64();)
+      for (int j = 0; j < n_tiles; ++j) {
+        const int sb = j & 1, vst = j % kKV;  // tile parity / V ring stage
+        const uint32_t vph = (j / kKV) & 1;
+        TRACE_ONLY(c0 = clock64();)
+        if (!mbar_wait(bar(V_FULL + vst), vph, err, DEVERR_ATTN_MMA)) break;
+        TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
+        if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(j & 1), err, DEVERR_ATTN_MMA)) break;  // one phase per tile
+        TRACE_ONLY(w_p += clock64() - c0;)
+        tc_fence_after();
+        // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory, 2 KB of the V tile
+        umma_bf16_ts_pair_x8<128, 256, 384, 512, 640, 768, 896>(tmem_o, tmem_p,
+                                                                vdesc0 + static_cast<uint64_t>(vst * (kHalfBytes >> 4)),
+                                                                idesc_pv, j > 0 ? 1u : 0u);
+        umma_commit_pair(bar(V_EMPTY + vst));
+        umma_commit_pair(bar(PV_DONE + sb));
+      }
+      TRACE_VALUE(12, true, clock64() - c_begin);
       TRACE_VALUE(4, true, w_v);
       TRACE_VALUE(5, true, w_p);
     }
@@ -203,16 +279,39 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     const int quarter = warp & 3;
-    const int wg = (warp - 4) >> 2;     // softmax warpgroup: key tiles j = wg, wg + 2, ...; S and P buffer wg
-    const int r = quarter * 32 + lane;  // query row in the tile == TMEM lane
+    const int wg = (warp - 4) >> 2;     // softmax warpgroup: key tiles j = wg, wg + 2, ...; S buffer wg
+    const int r = quarter * 32 + lane;  // query row in this CTA's tile == TMEM lane
     const int qi = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_s0 + lane_addr + wg * 128;
+    const uint32_t p_full_leader = map_to_leader(bar(P_FULL)), s_empty_leader = map_to_leader(bar(S_EMPTY + wg));
     float* m_sh = reinterpret_cast<float*>(gen + kSmemXch);  // [128] running maximum, log2 domain
     float* l_sh = m_sh + 128;                                // [2 groups][128] row sums
     float m_used = -INFINITY, l = 0.0f;                      // the maximum this group's sums are relative to
     bool ok = true;
-    // development builds: cycles of thread 128 per phase (wait for S, scan, decision, wait for the P buffer, exp + store)
+
+    // ---- Q rows into tensor memory: group w copies d columns [64 w, 64 w + 64) of its thread's row ----
+    {
+      uint32_t qw[32];
+      if (qi < args.Sq) {
+        const uint4* src = reinterpret_cast<const uint4*>(args.q + b * args.q_sb + h * args.q_sh +
+                                                          static_cast<long long>(qi) * args.q_ss + wg * 64);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const uint4 t = __ldg(src + v);
+          qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < 32; ++v) qw[v] = 0u;
+      }
+      tmem_st_32x32(tmem_q + lane_addr + wg * 32, qw);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_cluster(map_to_leader(bar(Q_READY)));
+    }
+
+    // development builds: cycles of thread 128 per phase (wait for S, load + scan, decision, exp, wait for the P buffer)
     TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, c0; const long long c_begin = clock64();)
     for (int j = wg; j < n_tiles; j += 2) {
       const uint32_t ph = (j >> 1) & 1;
@@ -220,7 +319,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       if (!mbar_wait(bar(S_FULL + wg), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
       TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
       tc_fence_after();
-      // the S row into registers (raw scores: the scale is folded into the exponent), then the buffer is free
+      // the S row into registers (raw scores: the scale is folded into the exponent)
       float s[128];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -231,7 +330,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
       }
       tc_fence_before();
-      mbar_arrive(bar(S_EMPTY + wg));  // the buffer can take QK^T of tile j+2
+      mbar_arrive_cluster(s_empty_leader);  // the buffer can take QK^T of tile j+2 (once the peer's group is here too)
       const int k0 = j * kKT;
       const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
       if (need_mask) {
@@ -286,32 +385,37 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         m_used = m;
       }
       TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
-      // the P buffer was last read by P V of tile j-2
-      if (j >= 2) {
-        if (!mbar_wait(bar(PV_DONE + wg), ((j - 2) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
-      }
-      TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
-      // probabilities as bf16 pairs straight into tensor memory (the A operand of P V): no shared-memory round trip
+      // probabilities as bf16 pairs (the A operand of P V), into registers first: the one P buffer in tensor memory is
+      // free only when P V of the previous tile (the other group's) has completed, and that must not hold up the
+      // exponentials
       float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const float neg_m = -m;
+      uint32_t pk[64];
+#pragma unroll
+      for (int e = 0; e < 64; ++e) {
+        const float p0 = fast_exp2(fmaf(s[2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
+        const float p1 = fast_exp2(fmaf(s[2 * e + 1], args.scale_log2, neg_m));
+        ls[(2 * e) & 3] += p0;
+        ls[(2 * e + 1) & 3] += p1;
+        pk[e] = pack_bf16x2(p0, p1);
+      }
+      TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
+      if (j >= 1) {
+        if (!mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+        tc_fence_after();
+      }
+      TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {  // 64 keys = 32 packed columns per store
-        uint32_t pk[32];
+        uint32_t part[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float p0 = fast_exp2(fmaf(s[hc * 64 + 2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
-          const float p1 = fast_exp2(fmaf(s[hc * 64 + 2 * e + 1], args.scale_log2, neg_m));
-          ls[(2 * e) & 3] += p0;
-          ls[(2 * e + 1) & 3] += p1;
-          pk[e] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x32(tmem_p + lane_addr + wg * 64 + hc * 32, pk);
+        for (int e = 0; e < 32; ++e) part[e] = pk[hc * 32 + e];
+        tmem_st_32x32(tmem_p + lane_addr + hc * 32, part);
       }
       tmem_wait_st();
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tc_fence_before();
-      mbar_arrive(bar(P_FULL + wg));
-      TRACE_ONLY(t_exp += clock64() - c0;)
+      mbar_arrive_cluster(p_full_leader);
     }
     TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
     TRACE_VALUE(7, threadIdx.x == 128, w_s);
@@ -358,21 +462,22 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
   tc_fence_before();
   __syncthreads();
+  pair_sync();  // the peer may still be signalling this CTA's barriers or waiting on a commit from the leader
   if (warp == 2) {
     if (*reinterpret_cast<volatile int*>(err) != 0) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
   }
 }
 
-int make_map(CUtensorMap* m, const bf16* p, int S, int H, int B, long long ss, long long sh, long long sb) {
+int make_map(CUtensorMap* m, const bf16* p, int S, int H, int B, long long ss, long long sh, long long sb, int box_rows) {
   const uint64_t dims[4] = {kHD, static_cast<uint64_t>(S), static_cast<uint64_t>(H), static_cast<uint64_t>(B)};
   const uint64_t strides[3] = {static_cast<uint64_t>(ss) * 2, static_cast<uint64_t>(sh) * 2,
                                static_cast<uint64_t>(sb) * 2};
-  const uint32_t box[4] = {64, 128, 1, 1};
+  const uint32_t box[4] = {64, static_cast<uint32_t>(box_rows), 1, 1};
   return encode_tensor_map_bf16(m, p, 4, dims, strides, box);
 }
 
@@ -401,16 +506,16 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
        reinterpret_cast<uintptr_t>(o)) & 15)
     return TEENY_ERR_ALIGNMENT;
   if (s.Hq > 65535 || s.B > 65535) return TEENY_ERR_BAD_ARG;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mk, mv;
   int rc;
   // a dimension of extent 1 still needs a legal (multiple-of-16-byte, non-zero) stride
   auto fix = [](long long st, long long fallback) { return st > 0 ? st : fallback; };
-  if ((rc = make_map(&mq, q, s.Sq, s.Hq, s.B, s.q_ss, fix(s.q_sh, s.q_ss), fix(s.q_sb, s.q_ss)))) return rc;
-  if ((rc = make_map(&mk, k, s.Skv, s.Hkv, s.B, s.k_ss, fix(s.k_sh, s.k_ss), fix(s.k_sb, s.k_ss)))) return rc;
-  if ((rc = make_map(&mv, v, s.Skv, s.Hkv, s.B, s.v_ss, fix(s.v_sh, s.v_ss), fix(s.v_sb, s.v_ss)))) return rc;
+  if ((rc = make_map(&mk, k, s.Skv, s.Hkv, s.B, s.k_ss, fix(s.k_sh, s.k_ss), fix(s.k_sb, s.k_ss), 64))) return rc;
+  if ((rc = make_map(&mv, v, s.Skv, s.Hkv, s.B, s.v_ss, fix(s.v_sh, s.v_ss), fix(s.v_sb, s.v_ss), 128))) return rc;
 
   PrefillArgs a{};
-  a.o = o; a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
+  a.q = q; a.o = o; a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
+  a.q_sb = s.q_sb; a.q_sh = s.q_sh; a.q_ss = s.q_ss;
   a.o_sb = s.o_sb; a.o_sh = s.o_sh; a.o_ss = s.o_ss;
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.causal = s.causal;
@@ -421,8 +526,9 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
     const int prc = attention_prefill_prepare();
     if (prc) return prc;
   }
-  dim3 grid((s.Sq + kQT - 1) / kQT, s.Hq, s.B);
-  launch_kernel(attention_prefill_kernel, dim3(grid), dim3(kThreads), kSmemTotal, stream, 1, mq, mk, mv, a);
+  const int pair_tiles = (s.Sq + 2 * kQT - 1) / (2 * kQT);
+  dim3 grid(2 * pair_tiles, s.Hq, s.B);
+  launch_kernel(attention_prefill_kernel, dim3(grid), dim3(kThreads), kSmemTotal, stream, 2, mk, mv, a);
   return static_cast<int>(cudaGetLastError());
 }
 

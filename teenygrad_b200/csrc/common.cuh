@@ -337,6 +337,16 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
       : "memory");
 }
 
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15])
+      : "memory");
+}
+
 // Shared-memory matrix descriptor for a tile written by TMA with the 128-byte swizzle.
 //   K-major operand  ([rows][64] bf16, one 128-byte row per matrix row; 8-row groups 1024 B apart):
 //       leading byte offset unused (1), stride byte offset 1024.
@@ -418,6 +428,29 @@ __device__ __forceinline__ uint4 head_norm_rope(const uint4 raw, const uint4 wra
     out[e] = bf16x2_add(bf16x2_mul(n, cw[e]), bf16x2_mul(partner, sw[e]));
   }
   return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// A {32-bit payload, 32-bit stamp} pair as ONE 64-bit word in (possibly another GPU's) global memory: a 64-bit scalar
+// access is single-copy atomic, so a reader that sees the stamp sees the payload written with it.  (A 16-byte vector
+// store of two pairs carries no such guarantee between its halves, let alone inside one.)  Layout = uint2{payload, stamp}.
+__device__ __forceinline__ void st_stamped(uint2* dst, uint32_t payload, uint32_t stamp) {
+  const unsigned long long word = (static_cast<unsigned long long>(stamp) << 32) | payload;
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(word) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_stamped(const uint2* src) {
+  unsigned long long word;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(src) : "memory");
+  return word;
+}
+// Two neighbouring pairs in one 16-byte access (dst / src 16-byte aligned).  A vector access counts as one access per
+// element, so each 64-bit pair is still single-copy atomic on its own, and the access keeps the width that NVLink
+// packets and the memory system like.
+__device__ __forceinline__ void st_stamped_x2(uint2* dst, uint32_t payload0, uint32_t payload1, uint32_t stamp) {
+  const unsigned long long hi = static_cast<unsigned long long>(stamp) << 32;
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(hi | payload0), "l"(hi | payload1) : "memory");
+}
+__device__ __forceinline__ void ld_stamped_x2(const uint2* src, unsigned long long& w0, unsigned long long& w1) {
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -265,18 +265,77 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
 // ---- tensor-parallel row-parallel epilogue: take every rank's pushed partial rows as they arrive, sum, add, normalise ----
 // One CTA per token row (decode batches: a few dozen rows).  recv holds `world` copies of the projection as
 // {f32 value, stamp} pairs, slot_elems elements apart; an element has arrived when its stamp equals this round's.
-// A 16-byte load holds two elements and may tear between them, so each carries its own stamp.
-__device__ __forceinline__ uint4 ld_volatile_u4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
+// A pair is one 64-bit word, written with one 64-bit store and read with one 64-bit load (st_stamped / ld_stamped,
+// common.cuh): single-copy atomic, so a reader never sees a new stamp beside an old value.
+
+// Bounded polling state of one thread: gives up `limit_ns` after its first unsuccessful poll, or as soon as another
+// thread has reported an error.
+struct PollState {
+  uint64_t t0 = 0, limit_ns;
+  int* err;
+  bool live = true;
+  __device__ PollState(int* e, uint64_t limit) : limit_ns(limit), err(e) {}
+  __device__ __forceinline__ void tick(uint32_t it) {
+    if ((it & 0x3f) != 0x3f) return;
+    if (*reinterpret_cast<volatile int*>(err) != 0) { live = false; return; }
+    const uint64_t now = global_timer_ns();
+    if (t0 == 0) t0 = now;
+    else if (now - t0 > limit_ns) { atomicCAS(err, 0, DEVERR_TP_GATHER); live = false; }
+  }
+};
+
+// Eight consecutive stamped words from each of `nr` <= NR sources (src[r] + k), every request in flight together;
+// words that do not carry `stamp` yet are asked for again until they do (or the poll state gives up).
+template <int NR>
+__device__ __forceinline__ void poll_words(const uint2* const (&src)[NR], int nr, unsigned stamp, unsigned long long (&q)[NR][8],
+                                           PollState& ps) {
+#pragma unroll
+  for (int r = 0; r < NR; ++r)
+#pragma unroll
+    for (int k = 0; k < 8; k += 2) {  // 16-byte accesses, each 64-bit word of which is atomic on its own
+      if (r < nr) ld_stamped_x2(src[r] + k, q[r][k], q[r][k + 1]);
+      else q[r][k] = q[r][k + 1] = static_cast<unsigned long long>(stamp) << 32;
+    }
+  for (uint32_t it = 0;; ++it) {
+    bool all = true;
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+      for (int k = 0; k < 8; k += 2)
+        if (static_cast<unsigned>(q[r][k] >> 32) != stamp || static_cast<unsigned>(q[r][k + 1] >> 32) != stamp) {
+          ld_stamped_x2(src[r] + k, q[r][k], q[r][k + 1]);
+          all = false;
+        }
+    if (all || !ps.live) break;
+    ps.tick(it);
+  }
+}
+
+// sum[e] += the `world` ranks' values of this thread's eight columns, in rank order (every rank adds in the same order,
+// so all ranks hold identical results), four ranks' requests in flight at a time
+__device__ __forceinline__ void gather_sum8(const uint2* recv, size_t slot_elems, int world, size_t elem, unsigned stamp,
+                                            float (&sum)[8], PollState& ps) {
+  for (int p0 = 0; p0 < world; p0 += 4) {
+    const int nr = min(4, world - p0);
+    const uint2* src[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) src[r] = recv + static_cast<size_t>(p0 + (r < nr ? r : 0)) * slot_elems + elem;
+    unsigned long long q[4][8];
+    poll_words<4>(src, nr, stamp, q, ps);
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+      if (r < nr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum[k] += __uint_as_float(static_cast<unsigned>(q[r][k]));
+      }
+  }
 }
 
 template <int VPT>
-__global__ void gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world,
+__global__ void __launch_bounds__(512) gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world,
                                            const unsigned* __restrict__ epoch, unsigned round,
                                            bf16* __restrict__ res, long long ldr, bf16* __restrict__ y, long long ldy,
-                                           const bf16* __restrict__ w, int N, float eps, int* err) {
+                                           const bf16* __restrict__ w, int N, float eps, int* err, uint64_t limit_ns) {
   const int nv = N >> 3;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
   uint4 g[VPT];  // norm weights: constant, fetched ahead of the wait
@@ -300,37 +359,13 @@ __global__ void gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_
     const int idx = threadIdx.x + i * blockDim.x;
     hb[i] = idx < nv ? rr4[idx] : make_uint4(0u, 0u, 0u, 0u);
   }
-  uint64_t t0 = 0;
-  bool live = true;
+  PollState ps(err, limit_ns);
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int p = 0; p < world; ++p) {  // rank order: every rank adds in the same order -> identical results
-        // eight elements = four 16-byte {v, stamp, v, stamp} lines
-        const uint4* src = reinterpret_cast<const uint4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 4 * idx;
-        uint4 q[4];
-        for (uint32_t it = 0;; ++it) {
-          bool all = true;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            q[k] = ld_volatile_u4(src + k);
-            all = all && (q[k].y == stamp) && (q[k].w == stamp);
-          }
-          if (all || !live) break;
-          if ((it & 0x3f) == 0x3f) {
-            const uint64_t now = global_timer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); live = false; }
-          }
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          sum[2 * k] += __uint_as_float(q[k].x);
-          sum[2 * k + 1] += __uint_as_float(q[k].z);
-        }
-      }
+      gather_sum8(recv, slot_elems, world, static_cast<size_t>(row) * N + 8 * static_cast<size_t>(idx), stamp, sum, ps);
       const uint32_t hw[4] = {hb[i].x, hb[i].y, hb[i].z, hb[i].w};
       uint32_t ow[4];
 #pragma unroll
@@ -369,14 +404,15 @@ __global__ void gather_add_rms_norm_kernel(const uint2* __restrict__ recv, size_
 // residual, normalises, keeps the new residual and the normed row and stores both, stamped, into every other rank's
 // broadcast buffer; every other rank's CTA for row r waits for that row and unpacks it.  Traffic per rank is about
 // twice the tensor instead of world times it, for one more NVLink latency.
-// bcast[p]: rank p's broadcast buffer (this rank's own entry = local); a row is N / 2 lines of
-// {residual pair, stamp, normed pair, stamp}.
+// bcast[p]: rank p's broadcast buffer (this rank's own entry = local); a row is N words of
+// {bf16 pair, stamp}: per two columns one word with the residual pair, then one with the normed pair.
 template <int VPT>
-__global__ void gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world, int rank,
+__global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv, size_t slot_elems, int world, int rank,
                                                  int owner_rows, uint4* const* __restrict__ bcast,
                                                  const unsigned* __restrict__ epoch, unsigned round,
                                                  bf16* __restrict__ res, long long ldr, bf16* __restrict__ y,
-                                                 long long ldy, const bf16* __restrict__ w, int N, float eps, int* err) {
+                                                 long long ldy, const bf16* __restrict__ w, int N, float eps, int* err,
+                                                 uint64_t limit_ns) {
   const int nv = N >> 3;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
   uint4 g[VPT];  // norm weights: constant, fetched ahead of the wait
@@ -393,36 +429,22 @@ __global__ void gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv,
   const int owner = row / owner_rows;
   uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
-  const size_t brow = static_cast<size_t>(row) * (N >> 1);  // lines per row in a broadcast buffer
-  uint64_t t0 = 0;
-  bool live = true;
-  auto poll4 = [&](const uint4* src, uint4 (&q)[4]) {  // four 16-byte lines, each half carrying its own stamp
-    for (uint32_t it = 0;; ++it) {
-      bool all = true;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        q[k] = ld_volatile_u4(src + k);
-        all = all && (q[k].y == stamp) && (q[k].w == stamp);
-      }
-      if (all || !live) break;
-      if ((it & 0x3f) == 0x3f) {
-        const uint64_t now = global_timer_ns();
-        if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitLimitNs) { atomicCAS(err, 0, DEVERR_TP_GATHER); live = false; }
-      }
-    }
-  };
+  const size_t brow = static_cast<size_t>(row) * (N >> 1);  // 16-byte lines per row in a broadcast buffer
+  PollState ps(err, limit_ns);
   if (owner != rank) {
     // this row is reduced elsewhere: take the finished residual and normed row from the owner's broadcast
-    const uint4* src = bcast[rank] + brow;
+    const uint2* src0 = reinterpret_cast<const uint2*>(bcast[rank] + brow);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
       if (idx < nv) {
-        uint4 q[4];
-        poll4(src + 4 * idx, q);
-        rr4[idx] = make_uint4(q[0].x, q[1].x, q[2].x, q[3].x);
-        yr[idx] = make_uint4(q[0].z, q[1].z, q[2].z, q[3].z);
+        const uint2* src[1] = {src0 + 8 * idx};
+        unsigned long long q[1][8];
+        poll_words<1>(src, 1, stamp, q, ps);
+        rr4[idx] = make_uint4(static_cast<unsigned>(q[0][0]), static_cast<unsigned>(q[0][2]), static_cast<unsigned>(q[0][4]),
+                              static_cast<unsigned>(q[0][6]));
+        yr[idx] = make_uint4(static_cast<unsigned>(q[0][1]), static_cast<unsigned>(q[0][3]), static_cast<unsigned>(q[0][5]),
+                             static_cast<unsigned>(q[0][7]));
       }
     }
     return;
@@ -441,16 +463,8 @@ __global__ void gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv,
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int p = 0; p < world; ++p) {  // rank order: the one owner's result is what every rank gets
-        const uint4* src = reinterpret_cast<const uint4*>(recv + p * slot_elems + static_cast<size_t>(row) * N) + 4 * idx;
-        uint4 q[4];
-        poll4(src, q);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          sum[2 * k] += __uint_as_float(q[k].x);
-          sum[2 * k + 1] += __uint_as_float(q[k].z);
-        }
-      }
+      // rank order: the one owner's result is what every rank gets
+      gather_sum8(recv, slot_elems, world, static_cast<size_t>(row) * N + 8 * static_cast<size_t>(idx), stamp, sum, ps);
       const uint32_t hw[4] = {hb[i].x, hb[i].y, hb[i].z, hb[i].w};
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -477,11 +491,11 @@ __global__ void gather_add_rms_norm_owner_kernel(const uint2* __restrict__ recv,
       for (int e = 0; e < 4; ++e)
         ow[e] = pack_bf16x2(bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]), bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]));
       yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-      for (int p = 0; p < world; ++p) {  // NVLink stores to the other ranks
+      for (int p = 0; p < world; ++p) {  // NVLink stores to the other ranks: 16 bytes = {residual pair, stamp}, {normed pair, stamp}
         if (p == rank) continue;
-        uint4* dst = bcast[p] + brow + 4 * idx;
+        uint2* dst = reinterpret_cast<uint2*>(bcast[p] + brow) + 8 * idx;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dst[e] = make_uint4(hp[i][e], stamp, ow[e], stamp);
+        for (int e = 0; e < 4; ++e) st_stamped_x2(dst + 2 * e, hp[i][e], ow[e], stamp);
       }
     }
   }
@@ -736,7 +750,8 @@ int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ld
 }
 int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
                              bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,
-                             float eps, cudaStream_t st) {
+                             float eps, cudaStream_t st, unsigned long long wait_limit_ns) {
+  const uint64_t limit = wait_limit_ns ? wait_limit_ns : kWaitLimitNs;
   if (!recv || !epoch || !residual || !y || !w || world < 2 || M <= 0 || N <= 0 || round >= 1023) return TEENY_ERR_BAD_ARG;
   if (N % 8 || ldr % 8 || ldy % 8 || N > 8 * 4 * 512) return TEENY_ERR_BAD_ARG;
   if (!aligned16(recv) || !aligned16(residual) || !aligned16(y) || !aligned16(w) || (slot_elems % 2)) return TEENY_ERR_ALIGNMENT;
@@ -746,7 +761,7 @@ int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, co
   if (!err) return TEENY_ERR_DRIVER;
 #define TEENY_GATHER_CASE(V)                                                                                       \
   launch_kernel(gather_add_rms_norm_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, epoch, round, \
-                residual, ldr, y, ldy, w, N, eps, err)
+                residual, ldr, y, ldy, w, N, eps, err, limit)
   if (vpt <= 1) TEENY_GATHER_CASE(1);
   else if (vpt <= 2) TEENY_GATHER_CASE(2);
   else TEENY_GATHER_CASE(4);
@@ -756,7 +771,8 @@ int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, co
 int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int world, int rank, int owner_rows,
                                    uint4* const* bcast, const unsigned* epoch, unsigned round, bf16* residual,
                                    long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N, float eps,
-                                   cudaStream_t st) {
+                                   cudaStream_t st, unsigned long long wait_limit_ns) {
+  const uint64_t limit = wait_limit_ns ? wait_limit_ns : kWaitLimitNs;
   if (!recv || !bcast || !epoch || !residual || !y || !w || world < 2 || rank < 0 || rank >= world || owner_rows <= 0 ||
       M <= 0 || M > owner_rows * world || N <= 0 || round >= 1023)
     return TEENY_ERR_BAD_ARG;
@@ -768,7 +784,7 @@ int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int wor
   if (!err) return TEENY_ERR_DRIVER;
 #define TEENY_GATHER_CASE(V)                                                                                          \
   launch_kernel(gather_add_rms_norm_owner_kernel<V>, dim3(M), dim3(threads), 0, st, 1, recv, slot_elems, world, rank, \
-                owner_rows, bcast, epoch, round, residual, ldr, y, ldy, w, N, eps, err)
+                owner_rows, bcast, epoch, round, residual, ldr, y, ldy, w, N, eps, err, limit)
   if (vpt <= 1) TEENY_GATHER_CASE(1);
   else if (vpt <= 2) TEENY_GATHER_CASE(2);
   else TEENY_GATHER_CASE(4);

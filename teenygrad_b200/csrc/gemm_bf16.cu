@@ -489,8 +489,8 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
                   const size_t off = static_cast<size_t>(c) * args.N + n;
                   const int p0 = args.push_owner_rows > 0 ? c / args.push_owner_rows : 0;
                   const int p1 = args.push_owner_rows > 0 ? p0 + 1 : args.push_world;
-                  for (int p = p0; p < p1; ++p)  // NVLink stores
-                    args.push_recv[p][off] = make_uint2(__float_as_uint(v), stamp);
+                  for (int p = p0; p < p1; ++p)  // NVLink stores, one 64-bit word per {value, stamp}
+                    st_stamped(args.push_recv[p] + off, __float_as_uint(v), stamp);
                 } else {
                   args.y[static_cast<size_t>(c) * args.ldy + n] = __float2bfloat16_rn(v);
                 }
@@ -578,14 +578,14 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             const size_t off = static_cast<size_t>(c) * args.N + n;
             const int p0 = args.push_owner_rows > 0 ? c / args.push_owner_rows : 0;
             const int p1 = args.push_owner_rows > 0 ? p0 + 1 : args.push_world;
-            for (int p = p0; p < p1; ++p) {  // NVLink stores: two 16-byte {v, stamp, v, stamp} lines
+            for (int p = p0; p < p1; ++p) {  // NVLink stores: 16 bytes = two {value, stamp} words, each atomic on its own
               if (vec_ok) {
-                uint4* dst = reinterpret_cast<uint4*>(args.push_recv[p] + off);
-                dst[0] = make_uint4(__float_as_uint(o[0]), stamp, __float_as_uint(o[1]), stamp);
-                dst[1] = make_uint4(__float_as_uint(o[2]), stamp, __float_as_uint(o[3]), stamp);
+                st_stamped_x2(args.push_recv[p] + off, __float_as_uint(o[0]), __float_as_uint(o[1]), stamp);
+                st_stamped_x2(args.push_recv[p] + off + 2, __float_as_uint(o[2]), __float_as_uint(o[3]), stamp);
               } else {
+#pragma unroll
                 for (int e = 0; e < 4; ++e)
-                  if (n + e < args.N) args.push_recv[p][off + e] = make_uint2(__float_as_uint(o[e]), stamp);
+                  if (n + e < args.N) st_stamped(args.push_recv[p] + off + e, __float_as_uint(o[e]), stamp);
               }
             }
           } else {
@@ -686,6 +686,10 @@ int gemm_bf16_prepare() {
   return prepare_skinny<128>();
 }
 
+bool gemm_bf16_uses_2cta(int M, int N) {
+  return M > kSwapMaxM && static_cast<long long>(ceil_div(M, 256)) * ceil_div(N, 256) >= sm_count() / 2;
+}
+
 // The GEMM keeps its split-K partials in distributed shared memory: no global scratch at any shape.
 size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
@@ -781,7 +785,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   }
 
   // Enough 256 x 256 tiles to occupy every SM pair: the CTA-pair kernel (about a fifth faster at these sizes).
-  if (!w_is_kn && static_cast<long long>(ceil_div(M, 256)) * ceil_div(N, 256) >= sms / 2)
+  if (!w_is_kn && gemm_bf16_uses_2cta(M, N))
     return gemm_bf16_2cta(x, ldx, w, ldw, bias, y, ldy, M, N, K, stream, swiglu);
   a.tiles_p = ceil_div(M, kBM);
   a.tiles_q = ceil_div(N, bn);

@@ -44,6 +44,8 @@ struct Args2 {
   int k_blocks;
   int group;
   int swiglu;             // W rows interleave 64 gate / 64 up channels; Y[M, N/2] = silu(gate) * up
+  int qkv;                // the fused QKV projection with head norms, rotary embedding and cache fill in the epilogue
+  QkvEpilogue f;
   int* err;
 };
 
@@ -212,11 +214,96 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       tile_coords2(t, args.tiles_m, args.tiles_n, args.group, tm, tn);
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      const int row = tm * 256 + static_cast<int>(rank) * kBM + row_in_half;
+      // fused QKV epilogue: the token's rotary rows are requested before the wait for the accumulator, so their latency
+      // is gone by the time they are used.  cos[d + 64] == cos[d] (the angles are cat(freqs, freqs)): 64 values each.
+      uint4 rope_c[8], rope_s[8];
+      if (args.qkv && row < args.M) {
+        const int pos = args.f.pos0 + row % args.f.S;
+        const uint4* c4 = reinterpret_cast<const uint4*>(args.f.cos_t + static_cast<size_t>(pos) * 128);
+        const uint4* s4 = reinterpret_cast<const uint4*>(args.f.sin_t + static_cast<size_t>(pos) * 128);
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          rope_c[v] = __ldg(c4 + v);
+          rope_s[v] = __ldg(s4 + v);
+        }
+      }
       if (!mbar_wait(acc_full_bar(buf), acc_phase, err, DEVERR_GEMM_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBN;
-      const int row = tm * 256 + static_cast<int>(rank) * kBM + row_in_half;
-      if (args.swiglu) {
+      if (args.qkv) {
+        // Each 128-column half of the tile is one head of the fused [q | k | v] projection and a thread holds the whole
+        // head of its token: per-head RMSNorm (q, k), rotate-half rotary embedding at the token's position (q, k), then
+        // q goes back into the projection buffer and k / v straight into the caches -- the rounding points are those of
+        // the separate kernel (head_norm_rope, common.cuh): the projection, the normed head, each product and the sum
+        // are bf16 tensors.
+        const QkvEpilogue& f = args.f;
+        const int seq = row / f.S, pos = f.pos0 + row % f.S;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          const int head = tn * 2 + hh;
+          if (head >= f.Hq + 2 * f.Hkv) break;  // uniform over the CTA
+          uint32_t xp[64];                      // the head as bf16 pairs (the projection is a bf16 tensor)
+          float sq4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_addr + hh * 128 + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const uint32_t pr = pack_bf16x2(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+              xp[c * 16 + e] = pr;
+              sq4[e & 3] = fmaf(bf16_lo(pr), bf16_lo(pr), fmaf(bf16_hi(pr), bf16_hi(pr), sq4[e & 3]));
+            }
+          }
+          const float sq = (sq4[0] + sq4[1]) + (sq4[2] + sq4[3]);
+          if (row >= args.M) continue;
+          bf16* dst;
+          if (head < f.Hq) {
+            dst = args.y + static_cast<size_t>(row) * args.ldy + static_cast<size_t>(head) * 128;
+          } else {
+            const bool is_k = head < f.Hq + f.Hkv;
+            const int hk = head - f.Hq - (is_k ? 0 : f.Hkv);
+            dst = (is_k ? f.k_cache : f.v_cache) +
+                  ((static_cast<size_t>(seq) * f.Hkv + hk) * f.max_len + pos) * 128;
+          }
+          uint4* dst4 = reinterpret_cast<uint4*>(dst);
+          if (head >= f.Hq + f.Hkv) {  // v: no norm, no rotation
+#pragma unroll
+            for (int v = 0; v < 16; ++v) dst4[v] = make_uint4(xp[4 * v], xp[4 * v + 1], xp[4 * v + 2], xp[4 * v + 3]);
+            continue;
+          }
+          const float rr = 1.0f / sqrtf(sq * (1.0f / 128.0f) + f.eps);
+          const uint4* w4 = reinterpret_cast<const uint4*>(head < f.Hq ? f.q_w : f.k_w);
+          // normed head n = bf16(bf16(x * rr) * w), pairs 0..31 = d 0..63, pairs 32..63 = d 64..127
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            const uint4 wv = __ldg(w4 + v);
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t pr = xp[4 * v + e];
+              xp[4 * v + e] = bf16x2_mul(pack_bf16x2(bf16_lo(pr) * rr, bf16_hi(pr) * rr), ww[e]);
+            }
+          }
+          // out[d] = n[d] cos[d] - n[d + 64] sin[d];  out[d + 64] = n[d + 64] cos[d + 64] + n[d] sin[d + 64]
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint32_t cw[4] = {rope_c[v].x, rope_c[v].y, rope_c[v].z, rope_c[v].w};
+            const uint32_t sw[4] = {rope_s[v].x, rope_s[v].y, rope_s[v].z, rope_s[v].w};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t n_lo = xp[4 * v + e], n_hi = xp[32 + 4 * v + e];
+              lo[e] = bf16x2_add(bf16x2_mul(n_lo, cw[e]), bf16x2_mul(n_hi ^ 0x80008000u, sw[e]));
+              hi[e] = bf16x2_add(bf16x2_mul(n_hi, cw[e]), bf16x2_mul(n_lo, sw[e]));
+            }
+            dst4[v] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            dst4[8 + v] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          }
+        }
+      } else if (args.swiglu) {
         // columns come in groups of 128 weight rows = 64 gate + 64 up channels: 64 outputs per group
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN; c0 += 128) {
@@ -323,9 +410,20 @@ int gemm_bf16_2cta_prepare() {
 
 // Y[M, N] = X[M, K] W[N, K]^T (+ bias) for large M and N; caller has checked pointers / alignment.
 int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* bias, bf16* y, int ldy, int M, int N,
-                   int K, cudaStream_t stream, bool swiglu) {
+                   int K, cudaStream_t stream, bool swiglu, const QkvEpilogue* qkv) {
   int rc = gemm_bf16_2cta_prepare();
   if (rc) return rc;
+  if (qkv) {
+    if (swiglu || bias || !qkv->q_w || !qkv->k_w || !qkv->cos_t || !qkv->sin_t || !qkv->k_cache || !qkv->v_cache ||
+        qkv->S <= 0 || qkv->Hq <= 0 || qkv->Hkv <= 0 || N != (qkv->Hq + 2 * qkv->Hkv) * 128 || M % qkv->S != 0 ||
+        qkv->pos0 < 0 || qkv->pos0 + qkv->S > qkv->max_len || (ldy & 7))
+      return TEENY_ERR_BAD_ARG;
+    const uintptr_t al = reinterpret_cast<uintptr_t>(qkv->q_w) | reinterpret_cast<uintptr_t>(qkv->k_w) |
+                         reinterpret_cast<uintptr_t>(qkv->cos_t) | reinterpret_cast<uintptr_t>(qkv->sin_t) |
+                         reinterpret_cast<uintptr_t>(qkv->k_cache) | reinterpret_cast<uintptr_t>(qkv->v_cache) |
+                         reinterpret_cast<uintptr_t>(y);
+    if (al & 15) return TEENY_ERR_ALIGNMENT;
+  }
   CUtensorMap tmx, tmw;
   {
     const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
@@ -346,6 +444,10 @@ int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* b
   a.k_blocks = (K + kBK - 1) / kBK;
   a.group = 16;  // 16 x 256 rows of X share each 256-row block of W before moving on (best of 4/8/16/32 measured)
   a.swiglu = swiglu ? 1 : 0;
+  if (qkv) {
+    a.qkv = 1;
+    a.f = *qkv;
+  }
   a.err = device_error_word();
   if (!a.err) return TEENY_ERR_DRIVER;  // kernels report expired waits through this word: no launch without it
   const int tiles = a.tiles_m * a.tiles_n;

@@ -41,21 +41,38 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
 // Row-parallel epilogue of tensor parallelism: sums the `world` f32 partial rows [M][N] that the ranks' GEMMs pushed
 // as {value, stamp} pairs (slot_elems elements between ranks), waiting for each element until it carries the stamp
 // *epoch * 1024 + round + 1; rounds the sum to bf16 (the all-reduced projection), adds it into the bf16 residual and
-// RMS-normalises it: residual <- residual + sum; y <- norm(residual).  Waits are bounded (device error word).
+// RMS-normalises it: residual <- residual + sum; y <- norm(residual).  Waits are bounded (device error word;
+// wait_limit_ns = 0 means the library's 2 s limit).
 int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
                              bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,
-                             float eps, cudaStream_t st);
+                             float eps, cudaStream_t st, unsigned long long wait_limit_ns = 0);
 // The same in two hops: row r is summed and normalised only by rank r / owner_rows (the GEMMs pushed it only there,
 // GemmPush::owner_rows), which then stores the new residual row and the normed row, stamped, into every other rank's
 // broadcast buffer bcast[p] (device array [world], own entry unused); the other ranks' CTAs wait for their copy.
 int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int world, int rank, int owner_rows,
                                    uint4* const* bcast, const unsigned* epoch, unsigned round, bf16* residual,
                                    long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N, float eps,
-                                   cudaStream_t st);
+                                   cudaStream_t st, unsigned long long wait_limit_ns = 0);
 // Large-M path on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); same contract as gemm_bf16 without the options.
+// With `qkv` the GEMM is the fused [q | k | v] projection of a prefill (N = (Hq + 2 Hkv) * 128, token t = sequence
+// t / S at position pos0 + t % S) and its epilogue does what qk_norm_rope_kv_bf16 does in a pass of its own: per-head
+// RMSNorm of q and k, rotary embedding, q written to y (k / v columns of y are NOT written), k and v rows appended
+// to the caches [B, Hkv, max_len, 128].
+struct QkvEpilogue {
+  const bf16* q_w;     // [128] head-norm weights
+  const bf16* k_w;
+  const bf16* cos_t;   // [max_len, 128] tables
+  const bf16* sin_t;
+  bf16* k_cache;
+  bf16* v_cache;
+  int S, Hq, Hkv, max_len, pos0;
+  float eps;
+};
 int gemm_bf16_2cta_prepare();
 int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* bias, bf16* y, int ldy, int M, int N,
-                   int K, cudaStream_t stream, bool swiglu = false);
+                   int K, cudaStream_t stream, bool swiglu = false, const QkvEpilogue* qkv = nullptr);
+// Whether gemm_bf16 hands an [M, N] problem to the CTA-pair kernel (enough 256 x 256 tiles for every SM pair).
+bool gemm_bf16_uses_2cta(int M, int N);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
 int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
              const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);

@@ -466,6 +466,12 @@ int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, c
   return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
 }
 
+// TEENY_QKV_FUSE=0 keeps head norms / RoPE / cache fill in their own kernel behind the QKV projection (for A/B timing).
+bool qkv_fuse_enabled() {
+  static const bool on = [] { const char* e = getenv("TEENY_QKV_FUSE"); return !(e && e[0] == '0'); }();
+  return on;
+}
+
 // The shared layer loop.  T tokens arranged [B, S]; pos0 is the position of the first token of every sequence
 // (device value when pos_dev != null).  decode selects the split-KV attention kernel (S == 1).
 int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const int* len_dev, bool decode,
@@ -486,12 +492,19 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     bf16* vc = m->at<bf16>(m->off.vcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
     if (l == 0) TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st));
     else TEENY_TRY(residual_norm(m, delta, h, H, y, w.input_ln, T, st));
-    TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
-    // prefill: head norms, RoPE and the cache fill are one pass over the projection; in decode the attention kernel
-    // does them for its own (sequence, kv head) on the way in
-    if (!decode)
-      TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
-                                     kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
+    // Head norms, RoPE and the cache fill: in a large prefill they run in the epilogue of the QKV projection itself (k
+    // and v never pass through the projection buffer); in a small one as one pass over the projection; in decode the
+    // attention kernel does them for its own (sequence, kv head) on the way in.
+    if (!decode && !pos_dev && qkv_fuse_enabled() && gemm_bf16_uses_2cta(T, qkv_n)) {
+      const QkvEpilogue fuse{w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin), kc, vc,
+                             S, Hq, Hkv, c.max_len, pos0, c.eps};
+      TEENY_TRY(gemm_bf16_2cta(y, H, w.qkv, H, nullptr, qkv, qkv_n, T, qkv_n, H, st, false, &fuse));
+    } else {
+      TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
+      if (!decode)
+        TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                                       kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
+    }
     AttnShape a{};
     a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.scale = scale;
     a.q_sb = static_cast<long long>(S) * qkv_n; a.q_sh = D; a.q_ss = qkv_n;
@@ -585,10 +598,16 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
         TEENY_TRY(wait_reduced(hf));  // down projection of the layer before
         TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.input_ln, Th, H, c.eps, st));
       }
-      TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, Th, qkv_n, H, gs, gsb, st));
-      TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
-                                     kc + hf * cache_half, vc + hf * cache_half, Th, S, Hq, Hkv, D, c.max_len, 0, nullptr,
-                                     c.eps, st));
+      if (qkv_fuse_enabled() && gemm_bf16_uses_2cta(Th, qkv_n)) {  // head norms, RoPE and the cache fill in the projection's epilogue
+        const QkvEpilogue fuse{w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                               kc + hf * cache_half, vc + hf * cache_half, S, Hq, Hkv, c.max_len, 0, c.eps};
+        TEENY_TRY(gemm_bf16_2cta(y, H, w.qkv, H, nullptr, qkv, qkv_n, Th, qkv_n, H, st, false, &fuse));
+      } else {
+        TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, Th, qkv_n, H, gs, gsb, st));
+        TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
+                                       kc + hf * cache_half, vc + hf * cache_half, Th, S, Hq, Hkv, D, c.max_len, 0, nullptr,
+                                       c.eps, st));
+      }
       AttnShape a{};
       a.B = Bh; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.scale = scale;
       a.q_sb = static_cast<long long>(S) * qkv_n; a.q_sh = D; a.q_ss = qkv_n;
@@ -987,5 +1006,14 @@ int teeny_tp_all_reduce_bf16(void* ctx, teeny_bf16* buf, size_t count, teeny_str
 }
 
 int teeny_tp_peer_enabled(void* ctx) { return ctx && static_cast<TpContext*>(ctx)->peer_ok ? 1 : 0; }
+
+int teeny_tp_gather_add_rms_norm_bf16(const void* recv, size_t slot_elems, int world, const uint32_t* epoch,
+                                      uint32_t round, teeny_bf16* residual, teeny_bf16* y, const teeny_bf16* weight,
+                                      int M, int N, float eps, unsigned long long wait_limit_ns, teeny_stream_t stream) {
+  return gather_add_rms_norm_bf16(static_cast<const uint2*>(recv), slot_elems, world, epoch, round,
+                                  reinterpret_cast<bf16*>(residual), N, reinterpret_cast<bf16*>(y), N,
+                                  reinterpret_cast<const bf16*>(weight), M, N, eps, reinterpret_cast<cudaStream_t>(stream),
+                                  wait_limit_ns);
+}
 
 }  // extern "C"

@@ -39,6 +39,7 @@ SIGNATURES = {
     "teeny_tp_destroy": (i32, [vp]),
     "teeny_tp_all_reduce_bf16": (i32, [vp, vp, sz, vp]),
     "teeny_tp_peer_enabled": (i32, [vp]),
+    "teeny_tp_gather_add_rms_norm_bf16": (i32, [vp, sz, i32, vp, C.c_uint32, vp, vp, vp, i32, i32, f32, C.c_ulonglong, vp]),
 }
 _lib.bind(SIGNATURES)
 

@@ -371,3 +371,70 @@ def test_sample_top_k_top_p_matches_oracle(ops, rows, cols, temperature, top_k, 
         tol = 1e-5 * c[n - 1]
         assert lo - tol <= target <= c[i] + tol, f"row {r}: picked {got[r]} outside its CDF interval"
     assert ops.device_error() == 0
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# the receiving half of the tensor-parallel decode reduction, with the ranks' pushes laid out by the test
+# ---------------------------------------------------------------------------------------------------------------
+def _stamped(values_f32, stamp):
+    """[..., N] f32 -> [..., N] 64-bit words {value bits, stamp} as the GEMM push epilogue stores them."""
+    bits = values_f32.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    return bits | (int(stamp) << 32)
+
+
+@pytest.mark.parametrize("world,M,N", [(2, 5, 1024), (4, 32, 4096), (8, 32, 4096), (3, 7, 8192)])
+def test_tp_gather_add_rms_norm_sums_stamped_partials(ops, world, M, N):
+    import ctypes as C
+    from oracle import cpu as oc
+    from teenygrad_b200 import qwen3
+    g = torch.Generator().manual_seed(world * 100 + M)
+    parts = torch.randn(world, M, N, generator=g) * 0.1
+    res = torch.randn(M, N, generator=g).bfloat16()
+    w = (torch.rand(N, generator=g) + 0.5).bfloat16()
+    epoch, rnd = 37, 5
+    stamp = epoch * 1024 + rnd + 1
+    rows_cap = M + 3                      # slots are sized for the runner's max batch, not for this call
+    recv = torch.zeros(world, rows_cap, N, dtype=torch.int64)
+    recv[:, :M] = _stamped(parts, stamp)
+    recv_d, res_d = recv.cuda(), res.cuda()
+    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ep = torch.tensor([epoch], dtype=torch.int32, device="cuda")
+    vp = C.c_void_p
+    st = qwen3.lib.teeny_tp_gather_add_rms_norm_bf16(vp(recv_d.data_ptr()), rows_cap * N, world, vp(ep.data_ptr()), rnd,
+                                                     vp(res_d.data_ptr()), vp(y.data_ptr()), vp(w.cuda().data_ptr()), M, N,
+                                                     1e-6, 0, vp(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    total = parts[0].clone()
+    for p in range(1, world):             # rank order, f32
+        total += parts[p]
+    h = res + total.bfloat16()
+    assert torch.equal(res_d.cpu(), h)
+    assert rel(y, oc.rms_norm_bf16(h, w, 1e-6)) < BF16_TOL
+
+
+def test_tp_gather_wait_runs_out_and_reports_instead_of_hanging(ops):
+    """Partials that never arrive (a peer stopped pushing): with a 2 ms limit the kernel must give up, leave 0x301 in
+    the device error word, and the device must keep answering."""
+    import ctypes as C
+    import time
+    from oracle import cpu as oc
+    from teenygrad_b200 import qwen3
+    world, M, N = 2, 4, 1024
+    recv = torch.zeros(world, M, N, dtype=torch.int64, device="cuda")   # stamp 0 everywhere: never this round's
+    recv[0] = _stamped(torch.ones(M, N), 1).cuda()                        # rank 0 pushed, rank 1 never does
+    res = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    y = torch.empty_like(res)
+    w = torch.ones(N, dtype=torch.bfloat16, device="cuda")
+    ep = torch.zeros(1, dtype=torch.int32, device="cuda")
+    vp = C.c_void_p
+    t0 = time.time()
+    st = qwen3.lib.teeny_tp_gather_add_rms_norm_bf16(vp(recv.data_ptr()), M * N, world, vp(ep.data_ptr()), 0,
+                                                     vp(res.data_ptr()), vp(y.data_ptr()), vp(w.data_ptr()), M, N, 1e-6,
+                                                     2_000_000, vp(torch.cuda.current_stream().cuda_stream))
+    assert st == 0
+    assert ops.device_error(clear=True) == 0x301
+    assert time.time() - t0 < 1.0, "the bounded wait took far longer than its limit"
+    # the context is intact: an ordinary kernel still runs and is right
+    x, wt = _gemm_inputs(64, 128, 256)
+    assert rel(ops.linear_forward(x.cuda(), wt.cuda()), oc.linear_bf16(x, wt)) < BF16_TOL
+    assert ops.device_error(clear=True) == 0
