@@ -201,6 +201,16 @@ int teeny_argmax_combine(const float* vals, const int* idx, int* out_idx, int pa
 int teeny_sample_top_k_top_p_bf16(const teeny_bf16* logits, long long ld, int rows, int cols, float temperature,
                                   int top_k, float top_p, const float* u, int* out_idx, float* out_prob,
                                   teeny_stream_t stream);
+/* The same sampler over a vocabulary that is split in shards (vocabulary-parallel LM head).  Per shard,
+ * teeny_sample_candidates_bf16 writes the shard's top_k candidates of every row, sorted, as 64-bit words
+ * (order key << 32 | 0xFFFFFFFF - (index + idx_offset); zero = empty slot) to cand_out[row * top_k + i].
+ * teeny_sample_merge takes `parts` such lists per row (shard p's at lists + p * list_stride words: the layout an
+ * all-gather of the shards' outputs has), finds the top_k of their union and finishes as the unsharded call does: given
+ * the same u it returns the token teeny_sample_top_k_top_p_bf16 returns on the concatenated row.  parts <= 8. */
+int teeny_sample_candidates_bf16(const teeny_bf16* logits, long long ld, int rows, int cols, int top_k, int idx_offset,
+                                 unsigned long long* cand_out, teeny_stream_t stream);
+int teeny_sample_merge(const unsigned long long* lists, int parts, size_t list_stride, int rows, float temperature,
+                       int top_k, float top_p, const float* u, int* out_idx, float* out_prob, teeny_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -85,7 +85,9 @@ int teeny_qwen3_decode(teeny_qwen3* model, teeny_stream_t stream);
 /* Token selection.  temperature <= 0 (the default): greedy argmax, lowest index on ties.  temperature > 0: the
  * temperature / top-k (1..1024) / top-p sampler of teeny_sample_top_k_top_p_bf16, with u for token t of a generation
  * and batch row r drawn by a stateless hash of (seed, t, r), so a generation is reproducible and replayable on the
- * CPU.  Single GPU only (tp_size == 1).  Drops a captured decode graph: capture again afterwards. */
+ * CPU.  Under tensor parallelism every rank sends the top-k candidates of its vocabulary shard to all ranks and all
+ * make the same pick (teeny_sample_candidates_bf16 / teeny_sample_merge).  Drops a captured decode graph: capture
+ * again afterwards. */
 int teeny_qwen3_set_sampling(teeny_qwen3* model, float temperature, int top_k, float top_p, unsigned long long seed);
 int teeny_qwen3_capture_decode(teeny_qwen3* model, teeny_stream_t stream);
 int teeny_qwen3_decode_replay(teeny_qwen3* model, teeny_stream_t stream);

@@ -138,6 +138,8 @@ extern "C" {
     pub fn teeny_argmax_bf16(logits: *const u16, ld: c_longlong, best_val: *mut f32, best_idx: *mut c_int, rows: c_int, cols: c_int, idx_offset: c_int, stream: CUstream) -> c_int;
     pub fn teeny_argmax_combine(vals: *const f32, idx: *const c_int, out_idx: *mut c_int, parts: c_int, rows: c_int, stream: CUstream) -> c_int;
     pub fn teeny_sample_top_k_top_p_bf16(logits: *const u16, ld: c_longlong, rows: c_int, cols: c_int, temperature: f32, top_k: c_int, top_p: f32, u: *const f32, out_idx: *mut c_int, out_prob: *mut f32, stream: CUstream) -> c_int;
+    pub fn teeny_sample_candidates_bf16(logits: *const u16, ld: c_longlong, rows: c_int, cols: c_int, top_k: c_int, idx_offset: c_int, cand_out: *mut c_ulonglong, stream: CUstream) -> c_int;
+    pub fn teeny_sample_merge(lists: *const c_ulonglong, parts: c_int, list_stride: usize, rows: c_int, temperature: f32, top_k: c_int, top_p: f32, u: *const f32, out_idx: *mut c_int, out_prob: *mut f32, stream: CUstream) -> c_int;
     pub fn teeny_qwen3_workspace_bytes(cfg: *const TeenyQwen3Config) -> usize;
     pub fn teeny_qwen3_create(cfg: *const TeenyQwen3Config, workspace: *mut c_void, workspace_bytes: usize, tp_comm: *mut c_void, stream: CUstream, out: *mut *mut TeenyQwen3) -> c_int;
     pub fn teeny_qwen3_destroy(model: *mut TeenyQwen3);

@@ -58,6 +58,8 @@ SIGNATURES = {
     "teeny_argmax_bf16": (i32, [vp, i64, vp, vp, i32, i32, i32, vp]),
     "teeny_argmax_combine": (i32, [vp, vp, vp, i32, i32, vp]),
     "teeny_sample_top_k_top_p_bf16": (i32, [vp, i64, i32, i32, f32, i32, f32, vp, vp, vp, vp]),
+    "teeny_sample_candidates_bf16": (i32, [vp, i64, i32, i32, i32, i32, vp, vp]),
+    "teeny_sample_merge": (i32, [vp, i32, sz, i32, f32, i32, f32, vp, vp, vp, vp]),
 }
 
 

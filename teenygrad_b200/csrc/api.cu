@@ -312,6 +312,14 @@ int teeny_sample_top_k_top_p_bf16(const teeny_bf16* logits, long long ld, int ro
                                   teeny_stream_t s) {
   return sample_top_k_top_p_bf16(B(logits), ld, rows, cols, temperature, top_k, top_p, u, out_idx, out_prob, S(s));
 }
+int teeny_sample_candidates_bf16(const teeny_bf16* logits, long long ld, int rows, int cols, int top_k, int idx_offset,
+                                 unsigned long long* cand_out, teeny_stream_t stream) {
+  return sample_candidates_bf16(B(logits), ld, rows, cols, top_k, idx_offset, cand_out, S(stream));
+}
+int teeny_sample_merge(const unsigned long long* lists, int parts, size_t list_stride, int rows, float temperature,
+                       int top_k, float top_p, const float* u, int* out_idx, float* out_prob, teeny_stream_t stream) {
+  return sample_merge(lists, parts, list_stride, rows, temperature, top_k, top_p, u, out_idx, out_prob, S(stream));
+}
 
 }  // extern "C"
 

@@ -165,6 +165,15 @@ int argmax_combine(const float* vals, const int* idx, int* out_idx, int parts, i
 // out_prob[r] (optional) = its probability inside the nucleus.  u[r] in [0, 1) is the caller's random number.
 int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols, float temperature, int top_k,
                             float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st);
+// The same sampler over a vocabulary split in `parts` shards (tensor parallelism): sample_candidates_bf16 writes a
+// shard's top_k candidates per row, sorted, as 64-bit words (order key << 32 | 0xFFFFFFFF - global index, zero = empty) to
+// cand_out[row * top_k + i]; sample_merge takes the shards' lists (lists + p * list_stride, e.g. straight out of an
+// all-gather) and finishes: same token as the unsharded call on the concatenated row, on every rank.
+int sample_candidates_bf16(const bf16* logits, long long ld, int rows, int cols, int top_k, int idx_offset,
+                           unsigned long long* cand_out, cudaStream_t st);
+int sample_merge_prepare();
+int sample_merge(const unsigned long long* lists, int parts, size_t list_stride, int rows, float temperature, int top_k,
+                 float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st);
 // u[row] = uniform in [0, 1) from (seed, step, row) by a stateless hash; step from *step_dev when given.
 int sampling_uniform(unsigned long long seed, int step, const int* step_dev, float* u, int rows, cudaStream_t st);
 

@@ -307,6 +307,7 @@ struct LayerWeights {
 struct Workspace {
   // offsets into the caller's workspace
   size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters, sample_u;
+  size_t sample_cand, sample_gather;  // tensor-parallel sampling: this rank's candidate lists, all ranks' lists
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
   size_t gemm_scratch_bytes, attn_scratch_bytes, attn_counter_bytes, cache_layer_elems;
 };
@@ -336,7 +337,7 @@ struct teeny_qwen3 {
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_ready = nullptr, ev_done[2] = {nullptr, nullptr};
   bool overlap_prefill = false;
-  // token selection: greedy unless a temperature > 0 was set (single GPU only)
+  // token selection: greedy unless a temperature > 0 was set
   float sample_temperature = 0.0f, sample_top_p = 1.0f;
   int sample_top_k = 1;
   unsigned long long sample_seed = 0;
@@ -403,6 +404,8 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.attn_counter_bytes = Bm * static_cast<size_t>(c.num_kv_heads) * 4;  // arrival counters of the split-sequence merge
   w.attn_counters = take(w.attn_counter_bytes);
   w.sample_u = take(Bm * 4);
+  w.sample_cand = take(tp > 1 ? Bm * 1024 * 8 : 0);
+  w.sample_gather = take(tp > 1 ? Bm * 1024 * 8 * tp : 0);
   w.cand_val = take(Bm * 4);
   w.cand_idx = take(Bm * 4);
   w.gather_val = take(Bm * 4 * tp);
@@ -662,8 +665,22 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st, const int* step_dev 
     TEENY_TRY(argmax_bf16(logits, Vl, cv, next, B, Vl, 0, st));
     return 0;
   }
-  TEENY_TRY(argmax_bf16(logits, Vl, cv, ci, B, Vl, c.tp_rank * Vl, st));
   if (!m->comm) return TEENY_ERR_NCCL;
+  if (m->sample_temperature > 0.0f) {
+    // every rank: the top-k candidates of its vocabulary shard, all-gathered; then the same merge + pick on every rank
+    // (same u, same lists -> same token)
+    float* u = m->at<float>(m->off.sample_u);
+    unsigned long long* mine = m->at<unsigned long long>(m->off.sample_cand);
+    unsigned long long* all = m->at<unsigned long long>(m->off.sample_gather);
+    const size_t words = static_cast<size_t>(B) * m->sample_top_k;
+    TEENY_TRY(sampling_uniform(m->sample_seed, 0, S > 1 || !step_dev ? nullptr : step_dev, u, B, st));
+    TEENY_TRY(sample_candidates_bf16(logits, Vl, B, Vl, m->sample_top_k, c.tp_rank * Vl, mine, st));
+    if (g_nccl.AllGather(mine, all, words, ncclUint64, m->comm, st) != ncclSuccess) return TEENY_ERR_NCCL;
+    TEENY_TRY(sample_merge(all, c.tp_size, words, B, m->sample_temperature, m->sample_top_k, m->sample_top_p, u, next,
+                           nullptr, st));
+    return 0;
+  }
+  TEENY_TRY(argmax_bf16(logits, Vl, cv, ci, B, Vl, c.tp_rank * Vl, st));
   float* gv = m->at<float>(m->off.gather_val);
   int* gi = m->at<int>(m->off.gather_idx);
   // gathered layout [rank][max_batch]; only the first B of each rank's slot are meaningful
@@ -738,6 +755,7 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
   if (prc == 0) prc = gemm_bf16_2cta_prepare();
   if (prc == 0) prc = attention_prefill_prepare();
   if (prc == 0) prc = attention_decode_prepare();
+  if (prc == 0 && cfg->tp_size > 1) prc = sample_merge_prepare();
   if (prc != 0) {
     delete m;
     return prc;
@@ -871,7 +889,7 @@ int teeny_qwen3_decode(teeny_qwen3* m, teeny_stream_t stream) {
 int teeny_qwen3_set_sampling(teeny_qwen3* m, float temperature, int top_k, float top_p, unsigned long long seed) {
   if (!m) return TEENY_ERR_BAD_ARG;
   if (temperature > 0.0f) {
-    if (m->cfg.tp_size != 1 || top_k < 1 || top_k > 1024 || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
+    if (top_k < 1 || top_k > 1024 || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
     m->sample_temperature = temperature; m->sample_top_k = top_k; m->sample_top_p = top_p; m->sample_seed = seed;
   } else {
     m->sample_temperature = 0.0f;

@@ -12,6 +12,8 @@
 // (high byte, then low byte inside the deciding bin); ties at the threshold are resolved in index order by a third,
 // ordered pass.  The <= 1024 candidates are sorted in shared memory (bitonic), exponentials are computed in parallel
 // and one thread does the sequential sums so the result does not depend on a reduction tree.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -43,10 +45,46 @@ __device__ void pick_bin(const unsigned* hist, unsigned want, unsigned* bin_out,
   *above_out = above;
 }
 
+// Steps 2-4 of the definition over the K sorted candidates in cand[]: exponentials in parallel, sums by one thread in
+// candidate order.  A candidate is (key << 32) | (0xFFFFFFFF - index).
+__device__ __forceinline__ void pick_from_sorted(const unsigned long long* cand, float* expv, unsigned K, float inv_temperature,
+                                                 float top_p, float u, int* out_idx, float* out_prob) {
+  const int tid = threadIdx.x;
+  const float l0 = key_to_float(static_cast<unsigned>(cand[0] >> 32));
+  if (static_cast<unsigned>(tid) < K) expv[tid] = expf((key_to_float(static_cast<unsigned>(cand[tid] >> 32)) - l0) * inv_temperature);
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.0f;
+    for (unsigned i = 0; i < K; ++i) total += expv[i];
+    // nucleus: shortest prefix whose mass reaches top_p of the total
+    const float want = top_p * total;
+    float c = 0.0f;
+    unsigned n = 0;
+    while (n < K) {
+      c += expv[n];
+      ++n;
+      if (c >= want) break;
+    }
+    const float target = u * c;  // c = mass of the nucleus
+    float run = 0.0f;
+    unsigned pick = n - 1;
+    for (unsigned i = 0; i < n; ++i) {
+      run += expv[i];
+      if (run > target) { pick = i; break; }
+    }
+    *out_idx = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned>(cand[pick] & 0xFFFFFFFFull));
+    if (out_prob) *out_prob = expv[pick] / c;
+  }
+}
+
+// cand_out != null: stop after step 1 and write the K sorted candidates of the row, indices shifted by idx_offset, to
+// cand_out[row * cand_stride ...] (a vocabulary shard's contribution under tensor parallelism; sample_merge_kernel
+// finishes the job over all shards' lists).
 __global__ void __launch_bounds__(kSampleThreads, 1)
 sample_top_k_top_p_kernel(const bf16* __restrict__ logits, long long ld, int cols, float inv_temperature, int top_k,
                           float top_p, const float* __restrict__ u, int* __restrict__ out_idx,
-                          float* __restrict__ out_prob) {
+                          float* __restrict__ out_prob, unsigned long long* __restrict__ cand_out, int cand_stride,
+                          int idx_offset) {
   pdl_wait();
   __shared__ unsigned hist[256];
   __shared__ unsigned long long cand[kMaxTopK];  // (key << 32) | (0xFFFFFFFF - index): descending = value desc, index asc
@@ -118,32 +156,64 @@ sample_top_k_top_p_kernel(const bf16* __restrict__ logits, long long ld, int col
       __syncthreads();
     }
   }
-  // ---- exponentials in parallel, sums by one thread in candidate order ----
-  const float l0 = key_to_float(static_cast<unsigned>(cand[0] >> 32));
-  if (static_cast<unsigned>(tid) < K) expv[tid] = expf((key_to_float(static_cast<unsigned>(cand[tid] >> 32)) - l0) * inv_temperature);
-  __syncthreads();
-  if (tid == 0) {
-    float total = 0.0f;
-    for (unsigned i = 0; i < K; ++i) total += expv[i];
-    // nucleus: shortest prefix whose mass reaches top_p of the total
-    const float want = top_p * total;
-    float c = 0.0f;
-    unsigned n = 0;
-    while (n < K) {
-      c += expv[n];
-      ++n;
-      if (c >= want) break;
+  if (cand_out) {
+    // entries past K are zero (smaller than any real candidate); the shift keeps (value desc, index asc) order
+    if (tid < cand_stride) {
+      const unsigned long long c = cand[tid];
+      cand_out[static_cast<size_t>(blockIdx.x) * cand_stride + tid] =
+          static_cast<unsigned>(tid) < K ? ((c & 0xFFFFFFFF00000000ull) | ((c & 0xFFFFFFFFull) - static_cast<unsigned>(idx_offset))) : 0ull;
     }
-    const float target = u[blockIdx.x] * c;  // c = mass of the nucleus
-    float run = 0.0f;
-    unsigned pick = n - 1;
-    for (unsigned i = 0; i < n; ++i) {
-      run += expv[i];
-      if (run > target) { pick = i; break; }
-    }
-    out_idx[blockIdx.x] = static_cast<int>(0xFFFFFFFFu - static_cast<unsigned>(cand[pick] & 0xFFFFFFFFull));
-    if (out_prob) out_prob[blockIdx.x] = expv[pick] / c;
+    return;
   }
+  pick_from_sorted(cand, expv, K, inv_temperature, top_p, u[blockIdx.x], out_idx + blockIdx.x,
+                   out_prob ? out_prob + blockIdx.x : nullptr);
+}
+
+// Tensor-parallel finish: lists[p * list_stride + row * K + i] is candidate i (sorted descending) of vocabulary shard p
+// for this row; the top K of their union are found by rank counting -- a candidate's place in the union is the number
+// of candidates above it, a binary search per list, and the keys are distinct -- and steps 2-4 follow as on one GPU,
+// so every rank, given the same u, picks the same token as the unsharded kernel would.
+__global__ void __launch_bounds__(kSampleThreads, 1)
+sample_merge_kernel(const unsigned long long* __restrict__ lists, int parts, size_t list_stride, int K_list, int top_k,
+                    float inv_temperature, float top_p, const float* __restrict__ u, int* __restrict__ out_idx,
+                    float* __restrict__ out_prob) {
+  pdl_wait();
+  extern __shared__ unsigned long long all[];      // [parts][K_list]
+  __shared__ unsigned long long cand[kMaxTopK];
+  __shared__ float expv[kMaxTopK];
+  const int tid = threadIdx.x;
+  const int total = parts * K_list;
+  for (int i = tid; i < total; i += kSampleThreads) {
+    const int p = i / K_list, e = i - p * K_list;
+    all[i] = lists[static_cast<size_t>(p) * list_stride + static_cast<size_t>(blockIdx.x) * K_list + e];
+  }
+  for (int i = tid; i < kMaxTopK; i += kSampleThreads) cand[i] = 0ull;
+  __syncthreads();
+  unsigned live = 0;  // real candidates in the union (empty slots are zero)
+  for (int i = tid; i < total; i += kSampleThreads) {
+    const unsigned long long c = all[i];
+    if (c == 0ull) continue;
+    unsigned above = 0;
+    for (int p = 0; p < parts; ++p) {  // entries of list p greater than c: lists are sorted descending
+      const unsigned long long* lp = all + p * K_list;
+      int lo = 0, hi = K_list;
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (lp[mid] > c) lo = mid + 1; else hi = mid;
+      }
+      above += static_cast<unsigned>(lo);
+    }
+    if (above < static_cast<unsigned>(kMaxTopK)) cand[above] = c;
+    ++live;
+  }
+  __shared__ unsigned s_live;
+  if (tid == 0) s_live = 0;
+  __syncthreads();
+  if (live) atomicAdd(&s_live, live);
+  __syncthreads();
+  const unsigned K = min(static_cast<unsigned>(top_k), s_live);
+  pick_from_sorted(cand, expv, K, inv_temperature, top_p, u[blockIdx.x], out_idx + blockIdx.x,
+                   out_prob ? out_prob + blockIdx.x : nullptr);
 }
 
 // u[row] in [0, 1) as a pure function of (seed, step, row): a splitmix64 finaliser over the three, top 24 bits.
@@ -176,7 +246,42 @@ int sample_top_k_top_p_bf16(const bf16* logits, long long ld, int rows, int cols
   if (!(temperature > 0.0f) || top_k < 1 || top_k > kMaxTopK || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
   if (rows == 0) return TEENY_OK;
   launch_kernel(sample_top_k_top_p_kernel, dim3(rows), dim3(kSampleThreads), 0, st, 1, logits, ld, cols,
-                1.0f / temperature, top_k, top_p, u, out_idx, out_prob);
+                1.0f / temperature, top_k, top_p, u, out_idx, out_prob, static_cast<unsigned long long*>(nullptr), 0, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int sample_candidates_bf16(const bf16* logits, long long ld, int rows, int cols, int top_k, int idx_offset,
+                           unsigned long long* cand_out, cudaStream_t st) {
+  if (!logits || !cand_out || rows < 0 || cols <= 0 || ld < cols || top_k < 1 || top_k > kMaxTopK || idx_offset < 0)
+    return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  launch_kernel(sample_top_k_top_p_kernel, dim3(rows), dim3(kSampleThreads), 0, st, 1, logits, ld, cols, 1.0f, top_k, 1.0f,
+                static_cast<const float*>(nullptr), static_cast<int*>(nullptr), static_cast<float*>(nullptr), cand_out,
+                top_k, idx_offset);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int sample_merge_prepare() {
+  static std::atomic<unsigned long long> done{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
+  cudaError_t e = cudaFuncSetAttribute(sample_merge_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * kMaxTopK * 8);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
+  return 0;
+}
+
+int sample_merge(const unsigned long long* lists, int parts, size_t list_stride, int rows, float temperature, int top_k,
+                 float top_p, const float* u, int* out_idx, float* out_prob, cudaStream_t st) {
+  if (!lists || !u || !out_idx || parts < 1 || parts > 8 || rows < 0 || list_stride < static_cast<size_t>(rows) * top_k)
+    return TEENY_ERR_BAD_ARG;
+  if (!(temperature > 0.0f) || top_k < 1 || top_k > kMaxTopK || !(top_p > 0.0f) || top_p > 1.0f) return TEENY_ERR_BAD_ARG;
+  if (rows == 0) return TEENY_OK;
+  const int prc = sample_merge_prepare();
+  if (prc) return prc;
+  launch_kernel(sample_merge_kernel, dim3(rows), dim3(kSampleThreads), static_cast<size_t>(parts) * top_k * 8, st, 1, lists,
+                parts, list_stride, top_k, top_k, 1.0f / temperature, top_p, u, out_idx, out_prob);
   return static_cast<int>(cudaGetLastError());
 }
 

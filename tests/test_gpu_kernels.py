@@ -438,3 +438,33 @@ def test_tp_gather_wait_runs_out_and_reports_instead_of_hanging(ops):
     x, wt = _gemm_inputs(64, 128, 256)
     assert rel(ops.linear_forward(x.cuda(), wt.cuda()), oc.linear_bf16(x, wt)) < BF16_TOL
     assert ops.device_error(clear=True) == 0
+
+
+@pytest.mark.parametrize("rows,cols,parts,temperature,top_k,top_p", [
+    (8, 151936, 8, 0.8, 50, 0.9), (3, 151936, 2, 1.5, 1024, 0.95), (5, 4096, 4, 0.6, 64, 1.0), (4, 1024, 8, 1.0, 1024, 0.7),
+])
+def test_sampling_over_vocabulary_shards_equals_the_unsharded_sampler(ops, rows, cols, parts, temperature, top_k, top_p):
+    """Per-shard candidate lists + merge (what the vocabulary-parallel LM head does across ranks) must pick exactly the
+    token the one-kernel sampler picks on the whole row: same candidates, same order, same sums, same u."""
+    import ctypes as C
+    g = torch.Generator().manual_seed(rows * 7 + parts)
+    logits = (torch.randn(rows, cols, generator=g) * 3).bfloat16()
+    logits[0, [1, cols // parts, cols - 1]] = 30.0   # ties across shards: lowest global index first
+    u = torch.rand(rows, generator=g)
+    want, wprob = ops.sample_top_k_top_p(logits.cuda(), temperature, top_k, top_p, u.cuda(), want_prob=True)
+    vl = cols // parts
+    lists = torch.zeros(parts, rows, top_k, dtype=torch.int64, device="cuda")
+    vp = C.c_void_p
+    st = vp(torch.cuda.current_stream().cuda_stream)
+    for p in range(parts):
+        shard = logits[:, p * vl:(p + 1) * vl].contiguous().cuda()
+        rc = ops.lib.teeny_sample_candidates_bf16(vp(shard.data_ptr()), vl, rows, vl, top_k, p * vl, vp(lists[p].data_ptr()), st)
+        assert rc == 0
+    got = torch.empty(rows, dtype=torch.int32, device="cuda")
+    prob = torch.empty(rows, dtype=torch.float32, device="cuda")
+    uc = u.cuda()
+    rc = ops.lib.teeny_sample_merge(vp(lists.data_ptr()), parts, rows * top_k, rows, temperature, top_k, top_p,
+                                    vp(uc.data_ptr()), vp(got.data_ptr()), vp(prob.data_ptr()), st)
+    assert rc == 0
+    assert torch.equal(got.cpu(), want.cpu())
+    assert torch.allclose(prob.cpu(), wprob.cpu(), rtol=1e-6, atol=0)

@@ -28,3 +28,4 @@ def test_tensor_parallel_matches_oracle(world):
         res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
         assert f"TP{world} B4 S128 OK" in res.stdout and f"TP{world} B3 S40 OK" in res.stdout
+        assert f"TP{world} sampling OK" in res.stdout

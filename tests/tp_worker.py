@@ -26,6 +26,7 @@ def main():
     # prefill all-reduces in line.  (Largest batch first: the context's peer buffers are sized by the first runner.)
     for (B, S, steps) in ((4, 128, 6), (3, 40, 12)):
         check(qwen3, oq, comm, cfg, ocfg, sd, rank, world, B, S, steps, vocab)
+    check_sampling(qwen3, comm, cfg, sd, rank, world, vocab)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -79,6 +80,51 @@ def check(qwen3, oq, comm, cfg, ocfg, sd, rank, world, B, S, steps, vocab):
             assert t_div >= 1, "first generated token (prefill) must match"
         print(f"TP{world} B{B} S{S} OK (decode reduction: {'peer-push' if peer else 'nccl'}; near-tie flips in {flips} of "
               f"{B} rows)", flush=True)
+
+
+def check_sampling(qwen3, comm, cfg, sd, rank, world, vocab):
+    """Temperature / top-k / top-p under tensor parallelism: every rank must pick the same token, and that token must
+    be the oracle sampler's pick for the step's (gathered) logits and the hashed u of (seed, step, row)."""
+    import numpy as np
+    from oracle import sampling as osamp
+    B, S, steps, seed = 3, 24, 8, 4321
+    ids = torch.randint(0, vocab, (B, S), generator=torch.Generator().manual_seed(9))
+    runs = []
+    for graph in (False, True):
+        r = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + steps, max_new_tokens=steps, tp_rank=rank, tp_size=world, comm=comm)
+        r.load_state_dict(sd)
+        r.set_sampling(0.9, top_k=40, top_p=0.9, seed=seed)
+        r.prefill(ids)
+        step_logits = [r.logits().clone()]
+        for _ in range(steps - 1):
+            r.decode_step(graph=graph)
+            step_logits.append(r.logits().clone())
+        got = r.history()[:steps].t().contiguous()
+        torch.cuda.synchronize()
+        assert qwen3.lib.teeny_device_error(1) == 0
+        mine = torch.stack(step_logits, 1).contiguous()
+        slices = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(slices, mine)
+        gathered = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(gathered, got)
+        for g in gathered:
+            assert torch.equal(g, gathered[0]), "ranks disagree on the sampled ids"
+        runs.append(got.cpu().numpy())
+        if rank == 0:
+            logits = torch.cat(slices, dim=-1).float().cpu().numpy()  # [B, steps, vocab]
+            for t in range(steps):
+                for row in range(B):
+                    u = osamp.uniform(seed, t, row)
+                    want, _, c, n, cand = osamp.sample_row(logits[row, t], 0.9, 40, 0.9, float(u))
+                    if runs[-1][row, t] != want:  # only a CDF boundary within float noise may differ
+                        cl = list(cand)
+                        i = cl.index(runs[-1][row, t])
+                        lo = c[i - 1] if i > 0 else 0.0
+                        assert lo - 1e-5 * c[n - 1] <= u * c[n - 1] <= c[i] + 1e-5 * c[n - 1]
+        del r
+    assert np.array_equal(runs[0], runs[1]), "sampled ids differ between eager and graph replay"
+    if rank == 0:
+        print(f"TP{world} sampling OK", flush=True)
 
 
 if __name__ == "__main__":
