@@ -384,17 +384,20 @@ def kernel_config(args):
         ah, bh = torch.randn(512, 512, generator=g).pin_memory(), torch.randn(512, 512, generator=g).pin_memory()
         a, b = ah.cuda(), bh.cuda()
         c = torch.empty(512, 512, device="cuda")
-        ms = timed(lambda: ops.matmul_forward(a, b, out=c), steps=max(args.steps, 20))
+        sc = ops.matmul_f32_scratch(512, 512, 512)
+        ms = timed(lambda: ops.matmul_forward(a, b, out=c, scratch=sc), steps=max(args.steps, 20))   # tensor cores, bf16 x 3
+        ms_simt = timed(lambda: ops.matmul_forward(a, b, out=c), steps=max(args.steps, 20))          # CUDA cores
         ms_t = timed(lambda: torch.matmul(a, b, out=c), steps=max(args.steps, 20))
         fl = 2.0 * 512 ** 3
         value = fl / ms / 1e9
+        extra["cuda_core_path_tflops"] = fl / ms_simt / 1e9
         ch = torch.empty(512, 512).pin_memory()
         e2e_ms = e2e_timed([ah, bh], lambda x, y: ops.matmul_forward(x, y), lambda o: ch.copy_(o, non_blocking=True))
         h2d, d2h = 2 * 512 * 512 * 4, 512 * 512 * 4
-        # f32 products at f32 accuracy: the bound is the FP32 FMA pipe, 148 SMs x 128 lanes x 2 FLOP x max clock
-        peak = 148 * 128 * 2 * 1.965e9 / 1e12
-        roof = {"bound": "tensor", "kernel": "f32 GEMM 512^3 (latency-dominated: 2.7e8 FLOP)", "achieved": value, "peak": peak,
-                "unit": "TFLOP/s", "frac": value / peak, "peak_source": "nominal FP32 FMA rate (no measured f32 peak on file)",
+        # three bf16 tensor-core products per f32 product: the bound is a third of the bf16 peak
+        peak = peaks["bf16_tflops"] / 3.0
+        roof = {"bound": "tensor", "kernel": "f32 GEMM 512^3 on the tensor cores, operands split into bf16 terms (latency-dominated: 2.7e8 FLOP, 3 launches)", "achieved": value, "peak": peak,
+                "unit": "TFLOP/s", "frac": value / peak, "peak_source": peaks["source"] + " (burst cuBLAS bf16 / 3: three bf16 products per f32 product)",
                 "traffic": None}
         extra["torch_matmul_f32_tflops"] = fl / ms_t / 1e9
         dtype = "f32"

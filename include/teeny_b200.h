@@ -53,8 +53,11 @@ unsigned long long teeny_launch_count(int reset);
  * GEMM
  * ------------------------------------------------------------------------------------------------------------- */
 /* C[M,N] = A[M,K] @ B[K,N], all row-major.  Replaces matmul_forward, kernels/teeny-kernels/src/math/gemm.rs:44-108
- * (arguments a_ptr, b_ptr, c_ptr, M, N, K, :52-59).  f32: true f32 products and accumulation.  bf16: f32 accumulate.
- * global_scratch may be NULL. */
+ * (arguments a_ptr, b_ptr, c_ptr, M, N, K, :52-59).  bf16: f32 accumulate.  f32: f32 accuracy either way -- with
+ * global_scratch of at least teeny_matmul_f32_scratch_bytes(M, N, K) bytes (and K, N multiples of 8, 16-byte aligned
+ * pointers) on the tensor cores, every operand split into two bf16 terms and three products accumulated in f32 (the
+ * split the reference's DSL calls TF32x3, kernels/teeny-triton/src/triton/mod.rs:76-83; its kernel uses one TF32 pass,
+ * math/gemm.rs:95, which the 1e-4 bar rules out); with global_scratch NULL by f32 FMAs on the CUDA cores. */
 int matmul_forward_entry_point_f32(const float* a, const float* b, float* c, int M, int N, int K,
                                    void* global_scratch, size_t global_scratch_bytes, teeny_stream_t stream);
 int matmul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* c, int M, int N, int K,
@@ -74,6 +77,7 @@ int linear_forward_entry_point_bf16(const teeny_bf16* x, const teeny_bf16* w, co
                                     int M, int N, int K, int stride_xm, int stride_xk, int stride_wn, int stride_wk,
                                     int stride_ym, int stride_yn, void* global_scratch, size_t global_scratch_bytes,
                                     teeny_stream_t stream);
+size_t teeny_matmul_f32_scratch_bytes(int M, int N, int K);
 /* Global scratch the bf16 GEMM wants at this shape.  Always 0 (split-K is reduced on chip); kept so hosts that size
  * a scratch arena per shape, as the reference's launcher does, have one call to ask. */
 size_t teeny_gemm_scratch_bytes(int M, int N, int K);

@@ -111,6 +111,7 @@ extern "C" {
     pub fn matmul_forward_entry_point_bf16(a: *const u16, b: *const u16, c: *mut u16, m: c_int, n: c_int, k: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
     pub fn linear_forward_entry_point_f32(x: *const f32, w: *const f32, bias: *const f32, y: *mut f32, m: c_int, n: c_int, k: c_int, stride_xm: c_int, stride_xk: c_int, stride_wn: c_int, stride_wk: c_int, stride_ym: c_int, stride_yn: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
     pub fn linear_forward_entry_point_bf16(x: *const u16, w: *const u16, bias: *const u16, y: *mut u16, m: c_int, n: c_int, k: c_int, stride_xm: c_int, stride_xk: c_int, stride_wn: c_int, stride_wk: c_int, stride_ym: c_int, stride_yn: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
+    pub fn teeny_matmul_f32_scratch_bytes(m: c_int, n: c_int, k: c_int) -> usize;
     pub fn teeny_gemm_scratch_bytes(m: c_int, n: c_int, k: c_int) -> usize;
     pub fn flash_attention2_forward_entry_point_f32(q: *const f32, k: *const f32, v: *const f32, o: *mut f32, l: *mut f32, n_ctx_q: c_int, n_ctx_k: c_int, softmax_scale: f32, neg_inf: f32, bh: c_int, head_dim: c_int, stream: CUstream) -> c_int;
     pub fn flash_attention2_forward_entry_point_bf16(q: *const u16, k: *const u16, v: *const u16, o: *mut u16, l: *mut f32, n_ctx_q: c_int, n_ctx_k: c_int, softmax_scale: f32, neg_inf: f32, bh: c_int, head_dim: c_int, stream: CUstream) -> c_int;

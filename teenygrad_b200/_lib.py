@@ -32,6 +32,7 @@ SIGNATURES = {
     "linear_forward_entry_point_f32": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp, sz, vp]),
     "linear_forward_entry_point_bf16": (i32, [vp, vp, vp, vp] + [i32] * 9 + [vp, sz, vp]),
     "teeny_gemm_scratch_bytes": (sz, [i32, i32, i32]),
+    "teeny_matmul_f32_scratch_bytes": (sz, [i32, i32, i32]),
     "flash_attention2_forward_entry_point_f32": (i32, [vp, vp, vp, vp, vp, i32, i32, f32, f32, i32, i32, vp]),
     "flash_attention2_forward_entry_point_bf16": (i32, [vp, vp, vp, vp, vp, i32, i32, f32, f32, i32, i32, vp]),
     "teeny_flash_attn_fwd_bf16": (i32, [vp, vp, vp, vp, vp, C.POINTER(AttnShape), vp]),

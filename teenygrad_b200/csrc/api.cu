@@ -170,10 +170,18 @@ int teeny_device_error(int clear) {
 }
 
 // ---- GEMM ----
-int matmul_forward_entry_point_f32(const float* a, const float* b, float* c, int M, int N, int K, void*, size_t,
-                                   teeny_stream_t stream) {
+int matmul_forward_entry_point_f32(const float* a, const float* b, float* c, int M, int N, int K, void* scratch,
+                                   size_t scratch_bytes, teeny_stream_t stream) {
+  // with scratch for the split operands: the tensor-core path (bf16 x 3, f32 accuracy); else f32 FMAs on the CUDA cores
+  if (a && b && c && scratch && M > 0 && N > 0 && K > 0 && !(K & 7) && !(N & 7) &&
+      !((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+         reinterpret_cast<uintptr_t>(scratch)) & 15) &&
+      scratch_bytes >= gemm_f32_split_scratch_bytes(M, N, K))
+    return gemm_f32_split(a, b, c, M, N, K, scratch, scratch_bytes, S(stream));
   return gemm_f32(a, K, 1, b, N, 1, nullptr, c, N, 1, M, N, K, S(stream));
 }
+
+size_t teeny_matmul_f32_scratch_bytes(int M, int N, int K) { return gemm_f32_split_scratch_bytes(M, N, K); }
 
 int matmul_forward_entry_point_bf16(const teeny_bf16* a, const teeny_bf16* b, teeny_bf16* c, int M, int N, int K,
                                     void* scratch, size_t scratch_bytes, teeny_stream_t stream) {

@@ -44,6 +44,7 @@ struct GemmArgs {
   int M, N, K;            // Y[M, N] = X[M, K] * W[N, K]^T
   int ldy;                // row stride of Y in elements
   bf16* y;
+  float* y32;             // when set (persistent kernel, unswapped): the f32 accumulators are stored as they are, to y32[M, ldy]
   const bf16* bias;       // [N] or null
   int tiles_p, tiles_q;   // tiles along P rows and along Q rows
   int k_blocks;           // ceil(K / 64)
@@ -269,7 +270,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
         const int qcol0 = tq * BN + c0;  // index along Q rows
         if constexpr (!SWAP) {
           // thread owns Y[prow, qcol0 .. qcol0+kChunk)
-          if (prow < args.M) {
+          if (prow < args.M && args.y32) {
+            float* dst = args.y32 + static_cast<size_t>(prow) * args.ldy + qcol0;
+            if (((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (qcol0 + kChunk <= args.N)) {
+#pragma unroll
+              for (int v = 0; v < kChunk / 4; ++v)
+                *reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < kChunk; ++e)
+                if (qcol0 + e < args.N) dst[e] = __uint_as_float(r[e]);
+            }
+          } else if (prow < args.M) {
             bf16* dst = args.y + static_cast<size_t>(prow) * args.ldy + qcol0;
             const bool vec_ok = ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) && (qcol0 + kChunk <= args.N);
             if (vec_ok) {
@@ -706,14 +718,15 @@ size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
 // Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu, const GemmPush* push) {
-  if (!x || !w || !y || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu, const GemmPush* push, float* y32) {
+  if (!x || !w || (!y && !y32) || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  if (y32 && (!w_is_kn || swiglu || push || bias)) return TEENY_ERR_BAD_ARG;  // f32 output: the [K, N] form only
   if (swiglu && (w_is_kn || bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) || (ldx & 7) || (ldw & 7))
     return TEENY_ERR_ALIGNMENT;
 
   GemmArgs a{};
-  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
+  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.y32 = y32; a.bias = bias;
   a.k_blocks = ceil_div(K, kBK);
   a.kb_per_split = a.k_blocks;
   a.group = 8;
@@ -777,6 +790,10 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
       const int slots = sms * 2;
       int split = (slots * 85 / 100) / tiles;
       if (split > 8) split = 8;
+      {  // TEENY_SKINNY_SPLIT: fixed cluster width, for measurements
+        static const int forced = [] { const char* e = getenv("TEENY_SKINNY_SPLIT"); return e ? atoi(e) : 0; }();
+        if (forced > 0 && forced <= 8) split = forced;
+      }
       while (split > 1 && (ceil_div(a.k_blocks, split) < 4 || ceil_div(a.k_blocks, split) * (split - 1) >= a.k_blocks))
         --split;  // too thin, or a rank would be left without k-blocks
       if (split < 1) split = 1;

@@ -37,7 +37,8 @@ struct GemmPush {
 };
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
               int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false,
-              const GemmPush* push = nullptr);
+              const GemmPush* push = nullptr, float* y32 = nullptr);
+// y32 (w_is_kn only): store the f32 accumulators to y32[M, ldy] instead of rounding them to bf16 into y.
 // Row-parallel epilogue of tensor parallelism: sums the `world` f32 partial rows [M][N] that the ranks' GEMMs pushed
 // as {value, stamp} pairs (slot_elems elements between ranks), waiting for each element until it carries the stamp
 // *epoch * 1024 + round + 1; rounds the sum to bf16 (the all-reduced projection), adds it into the bf16 residual and
@@ -73,6 +74,13 @@ int gemm_bf16_2cta(const bf16* x, int ldx, const bf16* w, int ldw, const bf16* b
                    int K, cudaStream_t stream, bool swiglu = false, const QkvEpilogue* qkv = nullptr);
 // Whether gemm_bf16 hands an [M, N] problem to the CTA-pair kernel (enough 256 x 256 tiles for every SM pair).
 bool gemm_bf16_uses_2cta(int M, int N);
+// C[M, N] = A[M, K] B[K, N], all f32 row-major and contiguous, on the tensor cores at f32 accuracy: each operand is
+// split into two bf16 terms (x = hi + mid + O(2^-16 x)) and hi*hi + mid*hi + hi*mid is accumulated in f32 by ONE bf16
+// GEMM over the concatenated K (A' = [hi | mid | hi], B' = [hi ; hi ; mid]).  scratch holds A' and B':
+// gemm_f32_split_scratch_bytes(M, N, K).  Needs K and N multiples of 8 and 16-byte aligned pointers.
+size_t gemm_f32_split_scratch_bytes(int M, int N, int K);
+int gemm_f32_split(const float* a, const float* b, float* c, int M, int N, int K, void* scratch, size_t scratch_bytes,
+                   cudaStream_t stream);
 // f32 GEMM with true f32 accuracy.  b_is_nk: B given as [N, K] (linear layout) instead of [K, N].
 int gemm_f32(const float* a, long long sam, long long sak, const float* b, long long sbk, long long sbn,
              const float* bias, float* c, long long scm, long long scn, int M, int N, int K, cudaStream_t stream);

@@ -49,6 +49,12 @@ def gemm_scratch(M, N, K, device="cuda"):
     return torch.zeros(n, dtype=torch.uint8, device=device) if n else None
 
 
+def matmul_f32_scratch(M, N, K, device="cuda"):
+    """Scratch that sends the f32 matmul to the tensor cores (operands split into bf16 terms); without it the f32
+    entry point runs on the CUDA cores."""
+    return torch.empty(lib.teeny_matmul_f32_scratch_bytes(M, N, K), dtype=torch.uint8, device=device)
+
+
 def matmul_forward(a, b, out=None, scratch=None):
     """C = A @ B, row-major [M,K] x [K,N]."""
     _req(a, name="a"); _req(b, a.dtype, "b")

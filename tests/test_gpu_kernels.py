@@ -53,6 +53,33 @@ def test_matmul_f32_512_config(ops):
     assert rel(c, torch.from_numpy(oc.matmul_f32(a.numpy(), b.numpy()))) < F32_TOL
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 512), (128, 136, 72), (300, 264, 200), (1024, 2048, 512), (5, 8, 8)])
+def test_matmul_f32_on_tensor_cores_keeps_f32_accuracy(ops, M, N, K):
+    """With scratch the f32 matmul runs as one bf16 GEMM over operands split into two bf16 terms (three products): the
+    1e-4 bar must hold with a wide margin (a single reduced-precision pass would sit near 1e-3)."""
+    from oracle import cpu as oc
+    g = torch.Generator().manual_seed(M + N + K)
+    a, b = torch.randn(M, K, generator=g), torch.randn(K, N, generator=g)
+    a[0, 0], b[0, 0] = 1000.0, -1000.0   # a large product next to ordinary ones
+    e = torch.from_numpy(oc.matmul_f32(a.numpy(), b.numpy()))
+    c = ops.matmul_forward(a.cuda(), b.cuda(), scratch=ops.matmul_f32_scratch(M, N, K))
+    assert rel(c, e) < 2e-5
+    c_simt = ops.matmul_forward(a.cuda(), b.cuda())
+    assert rel(c_simt, e) < F32_TOL
+
+
+def test_matmul_f32_ramp_fixture_on_tensor_cores(ops, golden):
+    a, b = dev(golden["gemm_ramp_a"]), dev(golden["gemm_ramp_b"])
+    M, K = a.shape
+    N = b.shape[1]
+    if K % 8 or N % 8:
+        pytest.skip("fixture shape is not a multiple of 8: served by the CUDA-core kernel")
+    c = ops.matmul_forward(a, b, scratch=ops.matmul_f32_scratch(M, N, K))
+    e = torch.from_numpy(golden["gemm_ramp_expected"])
+    assert rel(c, e) < F32_TOL
+    assert torch.all((c.cpu() - e).abs() < 1e-2 + 1e-3 * e.abs())  # test_gemm.rs:41-47
+
+
 def test_linear_f32_fixture(ops, golden):
     x, w, b = dev(golden["linear_input"]), dev(golden["linear_weight"]), dev(golden["linear_bias"])
     assert rel(ops.linear_forward(x, w), torch.from_numpy(golden["linear_expected_no_bias"])) < F32_TOL
