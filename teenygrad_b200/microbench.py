@@ -5,6 +5,7 @@
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
     python -m teenygrad_b200.microbench trace [N [first [count [shard]]]]         # timeline of one graph-replayed decode step
     python -m teenygrad_b200.microbench tracecase gemm|skinny|prefill|decode      # phase counters of one kernel
+    python -m teenygrad_b200.microbench probe                                     # tcgen05.mma issue rate from one / two threads
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
 one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
@@ -305,6 +306,29 @@ def tracecase(which):
         print(f"{name}:{line} value {vid:2d}: n {len(vals):6d} mean {sum(vals) / len(vals):12.1f} sum {sum(vals):14d}")
 
 
+def probe():
+    """Cycles per tcgen05.mma when one thread (or two, in different warps) issues 4096 of them from a loop: the
+    figures behind the attention kernel's straight-line issue blocks and its two issuer threads.  Needs a
+    -DTEENY_TRACE build."""
+    import ctypes
+    lib = ops.lib
+    if not hasattr(lib, "teeny_probe_mma_issue"):
+        raise SystemExit("library was built without -DTEENY_TRACE")
+    iters = 4096
+    print("cta_group  M    N    A operand   issuers / accumulators   cycles per MMA (issue, completed)   pipe needs")
+    for pair, n, mode in [(0, 128, 0), (0, 128, 1), (0, 128, 2), (0, 128, 5), (0, 64, 1), (0, 256, 0), (0, 256, 1),
+                          (1, 128, 0), (1, 128, 1), (1, 128, 5), (1, 128, 4), (1, 256, 0), (1, 256, 4)]:
+        out = (ctypes.c_longlong * 2)()
+        rc = lib.teeny_probe_mma_issue(pair, mode, n, iters, out)
+        if rc != 0:
+            raise SystemExit(f"probe failed: {rc}")
+        m = 256 if pair else 128
+        need = m * n * 16 * 2 / 8192 / (2 if pair else 1)
+        who = "two threads" if mode & 4 else ("one thread, two accumulators" if mode & 2 else "one thread")
+        print(f"{'::2' if pair else '::1':9s} {m:4d} {n:4d}  {'tensor mem' if mode & 1 else 'shared mem':10s}  {who:28s} "
+              f"{out[0] / iters:7.1f} {out[1] / iters:7.1f}   {need:5.0f}")
+
+
 def main(argv):
     import os
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
@@ -316,6 +340,8 @@ def main(argv):
              "elementwise": time_elementwise, "sampling": time_sampling}[name]()
     elif mode == "case":
         case(argv[1])
+    elif mode == "probe":
+        probe()
     elif mode == "tracecase":
         tracecase(argv[1])
     elif mode == "layers":
