@@ -344,7 +344,12 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_kernel(const uint2* _
     const int idx = threadIdx.x + i * blockDim.x;
     g[i] = idx < nv ? __ldg(wr + idx) : make_uint4(0u, 0u, 0u, 0u);
   }
-  pdl_wait();
+  // Nothing this kernel READS comes from its immediate predecessor in the stream (the GEMM that pushes) except the
+  // pushed words themselves, and those carry their own stamps: the residual and the step counter were written by
+  // kernels older than that, which are complete when this one starts.  So the partial sums are gathered BEFORE the
+  // dependency wait -- while the GEMM's epilogue and the acknowledgement of its NVLink stores are still under way --
+  // and only the writes come after it (so a later kernel that waits for this one still finds everything before it
+  // complete).  The GEMM behind this kernel is let in at once: it fetches weights while this kernel waits for peers.
   pdl_trigger();
   __shared__ float red[32];
   const unsigned stamp = __ldcg(epoch) * 1024u + round + 1u;
@@ -352,8 +357,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_kernel(const uint2* _
   uint4* rr4 = reinterpret_cast<uint4*>(res + static_cast<size_t>(row) * ldr);
   float v[VPT][8];
   float sq = 0.0f;
-  // all loads of the residual first: the stores into it below would otherwise order every later load behind them
-  uint4 hb[VPT];
+  uint4 hb[VPT];  // the residual row as loaded; overwritten below with the new residual, stored after the wait
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
@@ -376,7 +380,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_kernel(const uint2* _
         v[i][2 * e + 1] = hi;
         ow[e] = pack_bf16x2(lo, hi);
       }
-      rr4[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      hb[i] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
     }
@@ -384,10 +388,12 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_kernel(const uint2* _
   sq = block_sum(sq, red);
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
+  pdl_wait();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
     if (idx < nv) {
+      rr4[idx] = hb[i];
       const uint32_t gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
       uint32_t ow[4];
 #pragma unroll
@@ -421,7 +427,8 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
     const int idx = threadIdx.x + i * blockDim.x;
     g[i] = idx < nv ? __ldg(wr + idx) : make_uint4(0u, 0u, 0u, 0u);
   }
-  pdl_wait();
+  // as in gather_add_rms_norm_kernel: gather (and, for a row owned elsewhere, the wait for its broadcast) before the
+  // dependency wait, local writes after it; the stores into OTHER ranks' broadcast buffers need no such order
   pdl_trigger();
   __shared__ float red[32];
   const unsigned stamp = __ldcg(epoch) * 1024u + round + 1u;
@@ -434,6 +441,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
   if (owner != rank) {
     // this row is reduced elsewhere: take the finished residual and normed row from the owner's broadcast
     const uint2* src0 = reinterpret_cast<const uint2*>(bcast[rank] + brow);
+    uint4 got_r[VPT], got_y[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int idx = threadIdx.x + i * blockDim.x;
@@ -441,10 +449,19 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
         const uint2* src[1] = {src0 + 8 * idx};
         unsigned long long q[1][8];
         poll_words<1>(src, 1, stamp, q, ps);
-        rr4[idx] = make_uint4(static_cast<unsigned>(q[0][0]), static_cast<unsigned>(q[0][2]), static_cast<unsigned>(q[0][4]),
+        got_r[i] = make_uint4(static_cast<unsigned>(q[0][0]), static_cast<unsigned>(q[0][2]), static_cast<unsigned>(q[0][4]),
                               static_cast<unsigned>(q[0][6]));
-        yr[idx] = make_uint4(static_cast<unsigned>(q[0][1]), static_cast<unsigned>(q[0][3]), static_cast<unsigned>(q[0][5]),
-                             static_cast<unsigned>(q[0][7]));
+        got_y[i] = make_uint4(static_cast<unsigned>(q[0][1]), static_cast<unsigned>(q[0][3]), static_cast<unsigned>(q[0][5]),
+                              static_cast<unsigned>(q[0][7]));
+      }
+    }
+    pdl_wait();
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nv) {
+        rr4[idx] = got_r[i];
+        yr[idx] = got_y[i];
       }
     }
     return;
@@ -474,13 +491,13 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
         v[i][2 * e + 1] = hi;
         hp[i][e] = pack_bf16x2(lo, hi);
       }
-      rr4[idx] = make_uint4(hp[i][0], hp[i][1], hp[i][2], hp[i][3]);
 #pragma unroll
       for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
     }
   }
   sq = block_sum(sq, red);
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
+  uint32_t yw[VPT][4];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
@@ -488,15 +505,25 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
       const uint32_t gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
       uint32_t ow[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
+      for (int e = 0; e < 4; ++e) {
         ow[e] = pack_bf16x2(bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]), bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]));
-      yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        yw[i][e] = ow[e];
+      }
       for (int p = 0; p < world; ++p) {  // NVLink stores to the other ranks: 16 bytes = {residual pair, stamp}, {normed pair, stamp}
         if (p == rank) continue;
         uint2* dst = reinterpret_cast<uint2*>(bcast[p] + brow) + 8 * idx;
 #pragma unroll
         for (int e = 0; e < 4; ++e) st_stamped_x2(dst + 2 * e, hp[i][e], ow[e], stamp);
       }
+    }
+  }
+  pdl_wait();
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int idx = threadIdx.x + i * blockDim.x;
+    if (idx < nv) {
+      rr4[idx] = make_uint4(hp[i][0], hp[i][1], hp[i][2], hp[i][3]);
+      yr[idx] = make_uint4(yw[i][0], yw[i][1], yw[i][2], yw[i][3]);
     }
   }
 }

@@ -718,7 +718,8 @@ size_t gemm_bf16_scratch_bytes(int, int, int) { return 0; }
 
 // Y[M,N] = X[M,K] W^T (+bias).  w_is_kn: W given as [K, N] row-major (matmul_forward's B) instead of [N, K].
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
-              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu, const GemmPush* push, float* y32) {
+              int M, int N, int K, void*, size_t, cudaStream_t stream, bool swiglu, const GemmPush* push, float* y32,
+              int l2_ahead) {
   if (!x || !w || (!y && !y32) || M <= 0 || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
   if (y32 && (!w_is_kn || swiglu || push || bias)) return TEENY_ERR_BAD_ARG;  // f32 output: the [K, N] form only
   if (swiglu && (w_is_kn || bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
@@ -733,7 +734,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   a.swiglu = swiglu ? 1 : 0;
   {
     static const int ahead = [] { const char* e = getenv("TEENY_L2_AHEAD"); return e ? atoi(e) : kL2Ahead; }();
-    a.l2_ahead = ahead < 0 ? 0 : ahead;
+    a.l2_ahead = l2_ahead >= 0 ? l2_ahead : (ahead < 0 ? 0 : ahead);
   }
   if (push) {
     if (swiglu || w_is_kn || M > kSwapMaxM || !push->recv || !push->epoch || push->world < 2 || push->round >= 1023)
@@ -798,6 +799,10 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
         --split;  // too thin, or a rank would be left without k-blocks
       if (split < 1) split = 1;
       a.kb_per_split = ceil_div(a.k_blocks, split);
+      {  // what the CTAs ask into L2 ahead of time must stay well inside it (126 MB): at most 48 MB over the grid
+        const long long per_cta = (48ll << 20) / (static_cast<long long>(kBM * kBK * 2) * split * tiles);
+        if (a.l2_ahead > per_cta) a.l2_ahead = static_cast<int>(per_cta);
+      }
       switch (bn) {
         case 16: return launch_skinny<16>(tmw, tmx, a, split, tiles, stream);
         case 32: return launch_skinny<32>(tmw, tmx, a, split, tiles, stream);

@@ -37,8 +37,11 @@ struct GemmPush {
 };
 int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, const bf16* bias, bf16* y, int ldy,
               int M, int N, int K, void* scratch, size_t scratch_bytes, cudaStream_t stream, bool swiglu = false,
-              const GemmPush* push = nullptr, float* y32 = nullptr);
+              const GemmPush* push = nullptr, float* y32 = nullptr, int l2_ahead = -1);
 // y32 (w_is_kn only): store the f32 accumulators to y32[M, ldy] instead of rounding them to bf16 into y.
+// l2_ahead (decode-shaped GEMMs, M <= 128): how many of its 16 KB weight tiles beyond the shared-memory ring each CTA
+// asks into L2 before it waits for its predecessor (-1: the library default, none).  Worth it only where the
+// predecessor leaves HBM idle, e.g. a norm kernel that waits for other ranks' partial sums.
 // Row-parallel epilogue of tensor parallelism: sums the `world` f32 partial rows [M][N] that the ranks' GEMMs pushed
 // as {value, stamp} pairs (slot_elems elements between ranks), waiting for each element until it carries the stamp
 // *epoch * 1024 + round + 1; rounds the sum to bf16 (the all-reduced projection), adds it into the bf16 residual and

@@ -488,7 +488,8 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
   void* gs = m->at<void>(m->off.gemm_scratch);
   const size_t gsb = m->off.gemm_scratch_bytes;
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
-
+  // (Asking the QKV and gate/up weights into L2 while the norm in front of them waits for the other ranks' partial sums
+  // was measured under tensor parallelism: 3.29 ms per decode step against 3.25 ms without, 2 ranks.  Not used.)
   for (int l = 0; l < c.num_layers; ++l) {
     const LayerWeights& w = m->layers[l];
     bf16* kc = m->at<bf16>(m->off.kcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
