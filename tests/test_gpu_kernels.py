@@ -140,7 +140,7 @@ def test_linear_bf16_large_m(ops, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [
     (1, 256, 512), (16, 512, 1024), (32, 4096, 4096), (1, 4096, 4096), (7, 1000, 520), (64, 2048, 2048),
-    (128, 1024, 4096), (33, 384, 2048),
+    (128, 1024, 4096), (33, 384, 2048), (5, 333, 1024), (100, 130, 4096), (3, 6, 2048), (13, 4097, 512),
     # BASELINE config 2 at its exact shapes: N = K = 4096 with M = 1, 16, 128
     (16, 4096, 4096), (128, 4096, 4096),
 ])
@@ -298,7 +298,9 @@ def test_silu_mul_bf16(ops):
 
 
 @pytest.mark.parametrize("M,I,K", [(32, 3072, 1024), (1, 128, 512), (7, 1536, 4096), (300, 1024, 512), (4096, 3072, 1024),
-                                   (128, 12288, 4096), (129, 640, 264), (8192, 3072, 512), (5000, 2496, 264)])
+                                   (128, 12288, 4096), (129, 640, 264), (8192, 3072, 512), (5000, 2496, 264),
+                                   (4, 8192, 512)])  # the last: one CTA per weight tile, no cluster
+
 def test_linear_swiglu_fused(ops, M, I, K):
     """One GEMM over interleaved gate/up rows must equal linear -> linear -> silu -> mul of the bf16 graph."""
     from oracle import cpu as oc
