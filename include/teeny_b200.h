@@ -175,6 +175,30 @@ int teeny_silu_mul_bf16(const teeny_bf16* gate_up, long long ld, teeny_bf16* out
  * of the unfused bf16 graph.  Strides in elements; unit inner strides, 16-byte aligned rows. */
 int teeny_linear_swiglu_bf16(const teeny_bf16* x, long long ldx, const teeny_bf16* w, long long ldw, teeny_bf16* y,
                              long long ldy, int M, int N, int K, teeny_stream_t stream);
+/* Weight-only FP8 linear: Y[M, N] = X[M, K] @ W^T (+ bias) with X, Y bf16 and W in the "float-quantized"
+ * compressed-tensors layout the reference's quantiser writes (utilities/teeny-quant/src/format.rs:215-240): w_fp8 holds
+ * OCP FP8 E4M3 bytes in the weight's own [N, K] shape (row stride ldw bytes, a multiple of 16) and w_scale the f32
+ * scales of `foo.weight_scale`, one per group as utilities/teeny-quant/src/quant/groups.rs:84-110 numbers them:
+ * scale_kind 0 = "tensor" (1 scale), 1 = "channel" with axis 0 (N scales), 2 = "group" with axis 1 (row-major
+ * [N][ceil(K / group_size)], group_size a multiple of 64).  An element's value is f8_to_f32(byte) * scale
+ * (utilities/teeny-quant/src/quant/fp8.rs:175-206, 262-268); the products are accumulated in f32.  The reference has
+ * no kernel that consumes these files (its Linear is f32, nn/linear.rs:226-335); this is the weight-only GEMM its
+ * quantiser feeds.  M <= 128 streams the bytes (half the traffic of bf16 weights), converts them next to the tensor
+ * core and applies kinds 0 and 1 to the f32 sums; larger M first converts W into global_scratch
+ * (teeny_linear_w8a16_scratch_bytes) as bf16(value * scale) and runs the bf16 GEMM.  swiglu != 0: rows interleaved
+ * and output as in teeny_linear_swiglu_bf16 (scales in the same interleaved row order, no bias).  The two NaN bytes
+ * (0x7f, 0xff) are not reproduced by the M <= 128 path: check a tensor once with teeny_fp8_e4m3_count_nan. */
+int teeny_linear_w8a16_forward(const teeny_bf16* x, long long ldx, const void* w_fp8, long long ldw, const float* w_scale,
+                               int scale_kind, int group_size, const teeny_bf16* bias, teeny_bf16* y, long long ldy, int M,
+                               int N, int K, int swiglu, void* global_scratch, size_t global_scratch_bytes,
+                               teeny_stream_t stream);
+size_t teeny_linear_w8a16_scratch_bytes(int M, int N, int K);
+/* out[N, K] (bf16, row stride ldo elements) = bf16(f8_to_f32(w_fp8) * scale): dequantize_fp8 of
+ * utilities/teeny-quant/src/quant/fp8.rs:262-268 with one rounding to bf16, every byte value handled (NaN included). */
+int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w_scale, int scale_kind, int group_size,
+                                teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t stream);
+/* *count (device word) <- how many of the n bytes are E4M3 NaN encodings. */
+int teeny_fp8_e4m3_count_nan(const void* bytes, size_t n, unsigned* count, teeny_stream_t stream);
 /* cos/sin tables [max_pos, D] from inv_freq[D/2] (f32 angles, one rounding to bf16). */
 int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* cos_table, teeny_bf16* sin_table, int max_pos, int D,
                           teeny_stream_t stream);

@@ -73,6 +73,17 @@ int teeny_qwen3_create(const teeny_qwen3_config* cfg, void* workspace, size_t wo
                        teeny_stream_t stream, teeny_qwen3** out);
 void teeny_qwen3_destroy(teeny_qwen3* model);
 int teeny_qwen3_set_weight(teeny_qwen3* model, int layer, int which, const void* device_ptr);
+/* The same for a projection weight (QKV, O, GATE_UP, DOWN of a layer, or LM_HEAD) given as FP8 E4M3 bytes with f32
+ * scales, the "float-quantized" tensors the reference's quantiser writes (utilities/teeny-quant/src/format.rs:215-240);
+ * shapes, fusion and row order as for the bf16 slots, scale_kind / group_size as in teeny_linear_w8a16_forward
+ * (include/teeny_b200.h), scales of fused or interleaved rows in the same row order.  Decode streams the bytes
+ * (teeny_linear_w8a16_forward's M <= 128 path); a prefill of more than 128 tokens converts one projection at a time
+ * into the scratch given by teeny_qwen3_set_fp8_scratch (teeny_qwen3_fp8_scratch_bytes for this configuration) and
+ * fails with TEENY_ERR_SCRATCH without it.  Norm weights, the embedding table and inv_freq keep their own types. */
+int teeny_qwen3_set_weight_fp8(teeny_qwen3* model, int layer, int which, const void* fp8_bytes, const float* scales,
+                               int scale_kind, int group_size);
+size_t teeny_qwen3_fp8_scratch_bytes(const teeny_qwen3_config* cfg);
+int teeny_qwen3_set_fp8_scratch(teeny_qwen3* model, void* scratch, size_t bytes);
 /* Prefill: ids int32 [B, S] on the device.  Fills the KV cache, picks the first generated token of every sequence
  * (greedy, lowest index on ties) and records it as history[0]. */
 int teeny_qwen3_prefill(teeny_qwen3* model, const int* ids, int B, int S, teeny_stream_t stream);

@@ -18,7 +18,7 @@ BEGIN, END = "// ---- generated from include/*.h: begin ----", "// ---- generate
 TYPES = {
     "void": "()", "int": "c_int", "float": "f32", "size_t": "usize", "long long": "c_longlong",
     "unsigned long long": "c_ulonglong", "teeny_stream_t": "CUstream", "uint32_t": "u32", "const uint32_t*": "*const u32",
-    "unsigned long long*": "*mut c_ulonglong", "const unsigned long long*": "*const c_ulonglong",
+    "unsigned*": "*mut c_uint", "unsigned long long*": "*mut c_ulonglong", "const unsigned long long*": "*const c_ulonglong",
     "const float*": "*const f32", "float*": "*mut f32", "const int*": "*const c_int", "int*": "*mut c_int",
     "const teeny_bf16*": "*const u16", "teeny_bf16*": "*mut u16", "const void*": "*const c_void", "void*": "*mut c_void",
     "void**": "*mut *mut c_void", "const char*": "*const c_char",
@@ -127,7 +127,8 @@ def parse_rust_extern(text):
 def main():
     text = open(RUST_FILE).read()
     a, b = text.index(BEGIN), text.index(END) + len(END)
-    open(RUST_FILE, "w").write(text[:a] + render_rust(*parse_headers()) + text[b:])
+    new = text[:a] + render_rust(*parse_headers()) + text[b:]  # rendered in full before the file is touched
+    open(RUST_FILE, "w").write(new)
 
 
 if __name__ == "__main__":

@@ -16,7 +16,7 @@
 //!
 //! `build.rs` of teeny-cuda gains: `println!("cargo:rustc-link-search=native={}", env!("TEENY_B200_LIB_DIR"));`
 
-use core::ffi::{c_char, c_int, c_longlong, c_ulonglong, c_void};
+use core::ffi::{c_char, c_int, c_longlong, c_uint, c_ulonglong, c_void};
 use std::ffi::CStr;
 
 use teeny_core::device::program::ArgVisitor;
@@ -133,6 +133,10 @@ extern "C" {
     pub fn teeny_add_rms_norm_bf16(x: *const u16, residual: *mut u16, y: *mut u16, weight: *const u16, m: c_int, n: c_int, eps: f32, stream: CUstream) -> c_int;
     pub fn teeny_silu_mul_bf16(gate_up: *const u16, ld: c_longlong, out: *mut u16, t: c_int, inter: c_int, stream: CUstream) -> c_int;
     pub fn teeny_linear_swiglu_bf16(x: *const u16, ldx: c_longlong, w: *const u16, ldw: c_longlong, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, stream: CUstream) -> c_int;
+    pub fn teeny_linear_w8a16_forward(x: *const u16, ldx: c_longlong, w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, bias: *const u16, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, swiglu: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
+    pub fn teeny_linear_w8a16_scratch_bytes(m: c_int, n: c_int, k: c_int) -> usize;
+    pub fn teeny_dequant_fp8_e4m3_bf16(w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, out: *mut u16, ldo: c_longlong, n: c_int, k: c_int, stream: CUstream) -> c_int;
+    pub fn teeny_fp8_e4m3_count_nan(bytes: *const c_void, n: usize, count: *mut c_uint, stream: CUstream) -> c_int;
     pub fn teeny_rope_table_bf16(inv_freq: *const f32, cos_table: *mut u16, sin_table: *mut u16, max_pos: c_int, d: c_int, stream: CUstream) -> c_int;
     pub fn teeny_qk_norm_rope_kv_bf16(qkv: *mut u16, ld: c_longlong, q_norm_w: *const u16, k_norm_w: *const u16, cos_table: *const u16, sin_table: *const u16, k_cache: *mut u16, v_cache: *mut u16, t: c_int, s: c_int, hq: c_int, hkv: c_int, d: c_int, max_len: c_int, pos0: c_int, pos0_dev: *const c_int, eps: f32, stream: CUstream) -> c_int;
     pub fn teeny_embedding_bf16(ids: *const c_int, table: *const u16, out: *mut u16, t: c_int, hidden: c_int, vocab: c_int, stream: CUstream) -> c_int;
@@ -145,6 +149,9 @@ extern "C" {
     pub fn teeny_qwen3_create(cfg: *const TeenyQwen3Config, workspace: *mut c_void, workspace_bytes: usize, tp_comm: *mut c_void, stream: CUstream, out: *mut *mut TeenyQwen3) -> c_int;
     pub fn teeny_qwen3_destroy(model: *mut TeenyQwen3);
     pub fn teeny_qwen3_set_weight(model: *mut TeenyQwen3, layer: c_int, which: c_int, device_ptr: *const c_void) -> c_int;
+    pub fn teeny_qwen3_set_weight_fp8(model: *mut TeenyQwen3, layer: c_int, which: c_int, fp8_bytes: *const c_void, scales: *const f32, scale_kind: c_int, group_size: c_int) -> c_int;
+    pub fn teeny_qwen3_fp8_scratch_bytes(cfg: *const TeenyQwen3Config) -> usize;
+    pub fn teeny_qwen3_set_fp8_scratch(model: *mut TeenyQwen3, scratch: *mut c_void, bytes: usize) -> c_int;
     pub fn teeny_qwen3_prefill(model: *mut TeenyQwen3, ids: *const c_int, b: c_int, s: c_int, stream: CUstream) -> c_int;
     pub fn teeny_qwen3_decode(model: *mut TeenyQwen3, stream: CUstream) -> c_int;
     pub fn teeny_qwen3_set_sampling(model: *mut TeenyQwen3, temperature: f32, top_k: c_int, top_p: f32, seed: c_ulonglong) -> c_int;

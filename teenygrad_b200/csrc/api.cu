@@ -67,8 +67,9 @@ int sm_count() {
   return (t_sm_limit > 0 && t_sm_limit < n) ? t_sm_limit : n;
 }
 
-int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                           const uint64_t* strides_bytes, const uint32_t* box) {
+namespace {
+int encode_tensor_map(CUtensorMap* out, CUtensorMapDataType type, CUtensorMapSwizzle swizzle, const void* base, int rank,
+                      const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!g_encode) {
@@ -93,11 +94,25 @@ int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const u
     gstr[i] = strides_bytes[i];
   }
   if (reinterpret_cast<uintptr_t>(base) & 15) return TEENY_ERR_ALIGNMENT;
-  const CUresult r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+  const CUresult r = g_encode(out, type, static_cast<cuuint32_t>(rank),
                               const_cast<void*>(base), gdim, gstr, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? TEENY_OK : TEENY_ERR_DRIVER;
+}
+}  // namespace
+
+int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_SWIZZLE_128B, base, rank, dims,
+                           strides_bytes, box);
+}
+
+// Bytes in the same 128-byte swizzle: the FP8 weight tiles that warps convert before the MMA reads them.
+int encode_tensor_map_u8(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_128B, base, rank, dims, strides_bytes,
+                           box);
 }
 
 }  // namespace teeny
@@ -293,6 +308,23 @@ int teeny_linear_swiglu_bf16(const teeny_bf16* x, long long ldx, const teeny_bf1
   if (ldx > 0x7fffffffLL || ldw > 0x7fffffffLL || ldy > 0x7fffffffLL || ldx < K || ldw < K) return TEENY_ERR_BAD_ARG;
   return gemm_bf16(B(x), static_cast<int>(ldx), B(w), static_cast<int>(ldw), false, nullptr, B(y),
                    static_cast<int>(ldy), M, N, K, nullptr, 0, S(s), /*swiglu=*/true);
+}
+int teeny_linear_w8a16_forward(const teeny_bf16* x, long long ldx, const void* w_fp8, long long ldw, const float* w_scale,
+                               int scale_kind, int group_size, const teeny_bf16* bias, teeny_bf16* y, long long ldy, int M,
+                               int N, int K, int swiglu, void* global_scratch, size_t global_scratch_bytes,
+                               teeny_stream_t s) {
+  if (ldx > 0x7fffffffLL || ldw > 0x7fffffffLL || ldy > 0x7fffffffLL || ldx < K || ldw < K) return TEENY_ERR_BAD_ARG;
+  return linear_w8a16(B(x), static_cast<int>(ldx), static_cast<const uint8_t*>(w_fp8), static_cast<int>(ldw), w_scale,
+                      scale_kind, group_size, B(bias), B(y), static_cast<int>(ldy), M, N, K, global_scratch,
+                      global_scratch_bytes, S(s), swiglu != 0);
+}
+size_t teeny_linear_w8a16_scratch_bytes(int M, int N, int K) { return linear_w8a16_scratch_bytes(M, N, K); }
+int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w_scale, int scale_kind, int group_size,
+                                teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t s) {
+  return dequant_e4m3_bf16(static_cast<const uint8_t*>(w_fp8), ldw, w_scale, scale_kind, group_size, B(out), ldo, N, K, S(s));
+}
+int teeny_fp8_e4m3_count_nan(const void* bytes, size_t n, unsigned* count, teeny_stream_t s) {
+  return e4m3_count_nan(static_cast<const uint8_t*>(bytes), n, count, S(s));
 }
 int teeny_rope_table_bf16(const float* inv_freq, teeny_bf16* c, teeny_bf16* sn, int max_pos, int D, teeny_stream_t s) {
   return rope_table_bf16(inv_freq, B(c), B(sn), max_pos, D, S(s));

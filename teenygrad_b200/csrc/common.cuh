@@ -478,6 +478,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // 128-byte swizzle; box[0] must be 64 elements.  Returns TEENY_OK or an error code.
 int encode_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                            const uint64_t* strides_bytes, const uint32_t* box);
+// the same for a tensor of bytes
+int encode_tensor_map_u8(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                         const uint64_t* strides_bytes, const uint32_t* box);
 
 // SMs of the current device that this thread's launches size their grids for: the device's count, or less while a
 // limit is set (set_sm_limit(n), n <= 0 clears it) to leave SMs to kernels of another stream.

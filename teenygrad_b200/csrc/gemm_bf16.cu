@@ -59,6 +59,11 @@ struct GemmArgs {
   unsigned push_round;
   int push_world;
   int push_owner_rows;        // > 0: token row c goes only to rank c / push_owner_rows (which reduces it); 0: to every rank
+  // FP8 (E4M3) weights (skinny kernel, W8 variant): W is one byte per element, value = decode(byte) * scale of its group
+  const float* w_scale;       // 1 scale (w_scale_kind 0), N scales (1: per weight row) or [N][ceil(K / group)] (2)
+  int w_scale_kind;
+  int w_group;                // w_scale_kind 2: elements of k per scale, a multiple of 64
+  unsigned w_mul16;           // the constant 16, in a register (see e4m3x4_to_bf16x4)
   int* err;
 };
 
@@ -91,20 +96,48 @@ __device__ __forceinline__ float swiglu_f(float gate_acc, float up_acc) {
   return bf16_round(g * (1.0f / (1.0f + expf(-g)))) * u;
 }
 
+// The four K=16 steps of a 64-deep product as one block of straight-line code, D[tmem] (+)= A * B with B in shared
+// memory and A in shared memory (SS) or tensor memory (TS).  Per step the address field of a K-major shared-memory
+// descriptor advances by 2 (16 k = 32 bytes inside the swizzled row), that of an MN-major one by 128 (two 8-row groups
+// of 1024 bytes), a tensor-memory A by 8 columns (16 bf16 as pairs); the steps are compile-time immediates because a
+// lone thread that computes addresses between its tcgen05.mma issues one only every ~100 cycles.
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void umma_bf16_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 a, b;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "add.u64 a, %1, %5;\n\t add.u64 b, %2, %6;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, %7;\n\t add.u64 b, %2, %8;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, %9;\n\t add.u64 b, %2, %10;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "n"(A_STEP), "n"(B_STEP), "n"(2 * A_STEP),
+        "n"(2 * B_STEP), "n"(3 * A_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
+template <int B_STEP>
+__device__ __forceinline__ void umma_bf16_ts_x4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 b;\n\t.reg .b32 a;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "add.u32 a, %1, 8;\n\t add.u64 b, %2, %5;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 16;\n\t add.u64 b, %2, %6;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, t;\n\t"
+      "add.u32 a, %1, 24;\n\t add.u64 b, %2, %7;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], [a], b, %3, t;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "n"(B_STEP), "n"(2 * B_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
+
 // One k-block of MMAs: four K=16 steps over the 64-wide stage.
 template <int BN, bool Q_MN_MAJOR>
 __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t sp, uint32_t sq, bool first) {
   constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, Q_MN_MAJOR);
   const uint64_t pdesc = make_smem_desc_sw128(sp, 16, 1024);
   const uint64_t qdesc = Q_MN_MAJOR ? make_smem_desc_sw128(sq, kBK * 128, 1024) : make_smem_desc_sw128(sq, 16, 1024);
-#pragma unroll
-  for (int k = 0; k < kBK / 16; ++k) {
-    // K-major: 16 elements along k = 32 bytes inside the swizzled row -> +2 in the address field.
-    // MN-major: 16 k = two 8-row groups of 1024 bytes -> +128.
-    const uint64_t pd = pdesc + static_cast<uint64_t>(k * 2);
-    const uint64_t qd = qdesc + static_cast<uint64_t>(Q_MN_MAJOR ? k * 128 : k * 2);
-    umma_bf16_ss(d_tmem, pd, qd, idesc, (!first || k > 0) ? 1u : 0u);
-  }
+  umma_bf16_ss_x4<2, Q_MN_MAJOR ? 128 : 2>(d_tmem, pdesc, qdesc, idesc, first ? 0u : 1u);
 }
 
 template <int BN, bool SWAP, bool Q_MN_MAJOR>
@@ -353,19 +386,67 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p, const __grid_consta
 // filling an idle bus -- so the default is none.
 constexpr int kL2Ahead = 0;
 
-template <int BN>
+// W8: the weights arrive as FP8 (E4M3) bytes.  A stage holds 16 KB of them -- 128 rows of 128 k -- next to the two
+// 64-k activation tiles that go with them.  Eight warps (the four epilogue warps, idle during the main loop otherwise,
+// and four more) turn each 64-k half of a stage into bf16 in registers and store it into TENSOR memory, from where the
+// MMA takes it as its A operand.  Converting through shared memory instead (bytes in, bf16 tile out, tile read by the
+// MMA) costs six bytes of shared-memory traffic per weight byte, more than the SM has at the rate HBM delivers the
+// bytes -- that version ran no faster than the bf16 kernel; this one reads every weight byte from shared memory once.
+template <int BN, bool W8 = false>
 struct SkinnyCfg {
-  static constexpr int kStageP = kBM * kBK * 2;
-  static constexpr int kStageQ = BN * kBK * 2;
+  static constexpr int kKB = W8 ? 2 * kBK : kBK;       // k per stage
+  static constexpr int kStageP = kBM * kBK * 2;        // 16 KB of weights either way
+  static constexpr int kStageQ = BN * kKB * 2;
   static constexpr int kStageBytes = kStageP + kStageQ;
   // As many stages as let two CTAs share an SM (about 100 KB each): what streams the weights fast is the number of
   // bytes in flight per SM, and two short-lived CTAs overlap each other's set-up and reduction.
-  static constexpr int kStages = (BN <= 32) ? 5 : (BN <= 64 ? 4 : 3);
+  static constexpr int kStages = W8 ? (BN <= 16 ? 5 : (BN <= 32 ? 4 : (BN <= 64 ? 3 : 2)))
+                                    : ((BN <= 32) ? 5 : (BN <= 64 ? 4 : 3));
   static constexpr int kPartialBytes = BN * kBM * 4;  // f32 partial tile, column-major [BN][128]; reuses the ring
   static_assert(kPartialBytes <= kStages * kStageBytes, "partial tile must fit in the stage ring");
-  static constexpr int kTmemCols = BN < 32 ? 32 : BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 128;
+  // W8: 64 k of 128 weight rows as bf16 pairs are 32 columns of tensor memory; four such tiles behind the accumulator
+  static constexpr int kABufs = W8 ? 4 : 0;
+  static constexpr int kAccCols = BN < 32 ? 32 : BN;
+  static constexpr int kTmemA = 128;                   // first column of the weight tiles
+  static constexpr int kTmemCols = W8 ? 256 : kAccCols;
+  // W8: four more warps behind the epilogue warps, all eight convert (a lone warp per scheduler cannot hide the latency
+  // of its own dependent bit operations); only the first four run the epilogue
+  static constexpr int kConvWarps = W8 ? 8 : 0;
+  // W8: one thread issues a tcgen05.mma only every ~90 cycles, and a 64-k block of FP8 weights is half the bytes of a
+  // bf16 one for the same four instructions: two issuing threads (a second MMA warp behind the converting warps), one
+  // per half of a stage, each with its own accumulator (the epilogue adds the two); BN = 128 has no columns left for a
+  // second accumulator and keeps one issuer
+  static constexpr int kIssuers = (W8 && BN <= 64) ? 2 : 1;
+  static constexpr int kAcc1 = 64;                     // first column of the second accumulator
+  static constexpr int kThreads = W8 ? 64 + 32 * kConvWarps + (kIssuers == 2 ? 32 : 0) : kNumThreads;
+  static_assert(kTmemA + kABufs * 32 <= 256 && kAccCols <= kTmemA && (kIssuers == 1 || kAcc1 + kAccCols <= kTmemA),
+                "accumulators and weight tiles share the allocation");
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kSmemBytes = kBarOffset + 1024 + 256;
 };
+
+// Four FP8 E4M3 bytes (k ascending from the low byte) -> two bf16 pairs, exactly.  A byte's seven magnitude bits,
+// placed four bits below the top of a bf16's exponent field, read as the bf16 number 2^-120 times the E4M3 value --
+// also for E4M3 subnormals, which land on bf16 subnormals -- so one multiplication by 2^120 finishes the job.  (The two
+// NaN bytes 0x7f / 0xff decode as +-480; the loader refuses tensors that contain them.)
+// The conversion is what bounds this kernel, and the integer pipe (logic, shifts, byte permutes: half the rate of the
+// FMA pipe) is what bounds the conversion.  So the placement is done by integer multiply-adds, which run on the FMA
+// pipe: with the byte in the low half of a halfword (one permute), x * 16 puts the magnitude at bits 10..4 and the sign
+// at bit 11, and adding 240 * (x & 0x80) carries the sign from bit 11 to bit 15 without touching the rest.  `mul16`
+// is the constant 16 handed in through a register, so that the compiler keeps the multiply-add instead of turning it
+// into a shift on the integer pipe.
+__device__ __forceinline__ void e4m3x4_to_bf16x4(uint32_t w, uint32_t mul16, uint32_t& lo, uint32_t& hi) {
+  const uint32_t x0 = __byte_perm(w, 0u, 0x4140), x1 = __byte_perm(w, 0u, 0x4342);
+  const uint32_t s0 = x0 & 0x00800080u, s1 = x1 & 0x00800080u;
+  uint32_t t0, t1;
+  asm("mad.lo.u32 %0, %1, %2, 0;\n\tmad.lo.u32 %0, %3, 240, %0;" : "=&r"(t0) : "r"(x0), "r"(mul16), "r"(s0));
+  asm("mad.lo.u32 %0, %1, %2, 0;\n\tmad.lo.u32 %0, %3, 240, %0;" : "=&r"(t1) : "r"(x1), "r"(mul16), "r"(s1));
+  const __nv_bfloat162 k = __halves2bfloat162(__ushort_as_bfloat16(0x7b80), __ushort_as_bfloat16(0x7b80));  // 2^120
+  const __nv_bfloat162 r0 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t0), k);
+  const __nv_bfloat162 r1 = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&t1), k);
+  lo = *reinterpret_cast<const uint32_t*>(&r0);
+  hi = *reinterpret_cast<const uint32_t*>(&r1);
+}
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -392,25 +473,27 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t
 }
 
 // grid (S, tiles): blockIdx.x = cluster rank = k-split, blockIdx.y = 128-row weight tile.
-template <int BN>
-__global__ void __launch_bounds__(kNumThreads, 2)
+template <int BN, bool W8 = false>
+__global__ void __launch_bounds__((SkinnyCfg<BN, W8>::kThreads), 2)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const GemmArgs args) {
-  using Cfg = SkinnyCfg<BN>;
+  using Cfg = SkinnyCfg<BN, W8>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // The partial tile is written after the last MMA has completed, i.e. when no stage is in use any more, so it
   // lives at the start of the ring.
   const uint32_t part_base = smem_base;
-  const uint32_t bar_base = smem_base + Cfg::kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = smem_base + Cfg::kBarOffset;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (Cfg::kStages + s); };
   const uint32_t acc_full_bar = bar_base + 8u * (2 * Cfg::kStages);
   const uint32_t tmem_slot = acc_full_bar + 8;
+  auto wfull_bar = [&](int b) { return acc_full_bar + 16u + 8u * b; };   // W8: weight tile b is in tensor memory
+  auto wempty_bar = [&](int b) { return acc_full_bar + 48u + 8u * b; };  // W8: the MMAs that read tile b are done
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   float* part_gen = reinterpret_cast<float*>(smem_gen);
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
-      smem_gen + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 1));
+      smem_gen + Cfg::kBarOffset + 8 * (2 * Cfg::kStages + 1));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* err = args.err;
@@ -418,15 +501,29 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int tile = blockIdx.y;
   const int kb0 = static_cast<int>(rank) * args.kb_per_split;
   const int kb1 = min(args.k_blocks, kb0 + args.kb_per_split);
+  // W8: what the accumulator of weight row n is multiplied by on the way out (per-group scales are already in the
+  // converted weights)
+  auto row_scale = [&](int n) -> float {
+    if constexpr (!W8) return 1.0f;
+    if (args.w_scale_kind == 0) return __ldg(args.w_scale);
+    return (args.w_scale_kind == 1 && n < args.N) ? __ldg(args.w_scale + n) : 1.0f;
+  };
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_w);
     tma_prefetch_desc(&tmap_x);
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
+      // W8: a stage is free when the MMAs are done with its activation tile and the four converting warps with its bytes
+      mbar_init(empty_bar(s), Cfg::kIssuers + Cfg::kConvWarps);
     }
-    mbar_init(acc_full_bar, 1);
+    mbar_init(acc_full_bar, Cfg::kIssuers);
+    if constexpr (W8) {
+      for (int b = 0; b < Cfg::kABufs; ++b) {
+        mbar_init(wfull_bar(b), Cfg::kConvWarps / 2);  // a tile is written by one group of four warps
+        mbar_init(wempty_bar(b), 1);
+      }
+    }
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -445,48 +542,141 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const int pre = min(kb1 - kb0, Cfg::kStages);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(full_bar(i), Cfg::kStageBytes);
-        tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_w, full_bar(i), (kb0 + i) * kBK, tile * kBM);
+        tma_load_2d(smem_base + i * Cfg::kStageBytes, &tmap_w, full_bar(i), (kb0 + i) * Cfg::kKB, tile * kBM);
       }
       // ... and the weight tiles behind them are asked into L2, so that HBM keeps streaming this kernel's weights for
       // as long as the predecessor's tail lasts, not just until the ring is full
-      for (int kb = kb0 + pre; kb < min(kb1, kb0 + pre + args.l2_ahead); ++kb) tma_prefetch_l2_2d(&tmap_w, kb * kBK, tile * kBM);
+      for (int kb = kb0 + pre; kb < min(kb1, kb0 + pre + args.l2_ahead); ++kb)
+        tma_prefetch_l2_2d(&tmap_w, kb * Cfg::kKB, tile * kBM);
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d(smem_base + i * Cfg::kStageBytes + Cfg::kStageP, &tmap_x, full_bar(i), (kb0 + i) * kBK, 0);
+      auto load_x = [&](uint32_t sq, uint32_t bar, int kb) {  // the activation tile(s) of one stage: 64 k each
+        tma_load_2d(sq, &tmap_x, bar, kb * Cfg::kKB, 0);
+        if constexpr (W8) tma_load_2d(sq + BN * kBK * 2, &tmap_x, bar, kb * Cfg::kKB + kBK, 0);
+      };
+      for (int i = 0; i < pre; ++i) load_x(smem_base + i * Cfg::kStageBytes + Cfg::kStageP, full_bar(i), kb0 + i);
       int stage = pre == Cfg::kStages ? 0 : pre;
       uint32_t phase = pre == Cfg::kStages ? 1 : 0;
       for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1, err, DEVERR_GEMM_PRODUCER)) break;
         const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
         mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
-        tma_load_2d(sp, &tmap_w, full_bar(stage), kb * kBK, tile * kBM);
-        tma_load_2d(sp + Cfg::kStageP, &tmap_x, full_bar(stage), kb * kBK, 0);
+        tma_load_2d(sp, &tmap_w, full_bar(stage), kb * Cfg::kKB, tile * kBM);
+        load_x(sp + Cfg::kStageP, full_bar(stage), kb);
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
       }
     } else {
       pdl_wait();
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || (Cfg::kIssuers == 2 && warp == 2 + Cfg::kConvWarps)) {
     pdl_wait();
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      TRACE_ONLY(long long m_full = 0, m_wfull = 0, m_issue = 0, c0; const long long m_begin = clock64();)
+      // W8 with two issuers: warp 1 takes half 0 of every stage into the first accumulator, the other MMA warp half 1
+      // into the second
+      const int h_first = (W8 && warp != 1) ? 1 : 0, h_step = Cfg::kIssuers;
+      const uint32_t acc = tmem_base + ((W8 && warp != 1) ? Cfg::kAcc1 : 0);
       for (int kb = kb0; kb < kb1; ++kb) {
+        TRACE_ONLY(c0 = clock64();)
         if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_MMA)) { ok = false; break; }
-        tc_fence_after();
+        TRACE_ONLY(m_full += clock64() - c0;)
         const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
-        issue_kblock<BN, false>(tmem_base, sp, sp + Cfg::kStageP, kb == kb0);
+        if constexpr (W8) {
+          for (int h = h_first; h < 2; h += h_step) {
+            const int q = 2 * (kb - kb0) + h, j = q & 3;  // the q-th 64-k block goes through weight tile q % 4
+            TRACE_ONLY(c0 = clock64();)
+            if (!mbar_wait(wfull_bar(j), (q >> 2) & 1, err, DEVERR_GEMM_MMA)) { ok = false; break; }
+            TRACE_ONLY(m_wfull += clock64() - c0; c0 = clock64();)
+            tc_fence_after();
+            constexpr uint32_t idesc = make_idesc_bf16(kBM, BN, false, false);
+            const uint64_t xdesc = make_smem_desc_sw128(sp + Cfg::kStageP + h * BN * kBK * 2, 16, 1024);
+            const uint32_t a_tmem = tmem_base + Cfg::kTmemA + j * 32;
+            umma_bf16_ts_x4<2>(acc, a_tmem, xdesc, idesc, q >= h_step ? 1u : 0u);  // an issuer's first block overwrites
+            umma_commit(wempty_bar(j));
+            TRACE_ONLY(m_issue += clock64() - c0;)
+          }
+          if (!ok) break;
+        } else {
+          tc_fence_after();
+          issue_kblock<BN, false>(tmem_base, sp, sp + Cfg::kStageP, kb == kb0);
+        }
         umma_commit(empty_bar(stage));
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
       }
       if (ok) umma_commit(acc_full_bar);
+      TRACE_VALUE(0, W8 && blockIdx.y == 0 && warp == 1, clock64() - m_begin);
+      TRACE_VALUE(1, W8 && blockIdx.y == 0 && warp == 1, m_full);
+      TRACE_VALUE(2, W8 && blockIdx.y == 0 && warp == 1, m_wfull);
+      TRACE_VALUE(3, W8 && blockIdx.y == 0 && warp == 1, m_issue);
     }
   } else {
     pdl_wait();
+    if constexpr (W8) {
+      // ---- main loop of the converting warps: the q-th 64-k block of weights -> weight tile q % 4 in tensor memory ----
+      // Two groups of four warps: group g takes half g of every stage, so two blocks are always under way (one group's
+      // loads, bit operations and tensor-memory stores overlap the other's).  A warp reaches the 32 lanes (weight rows)
+      // of its quarter, warp % 4: a thread reads the 64 bytes of its row (four 16-byte chunks; the tile lies in the
+      // 128-byte swizzle TMA wrote, chunk c of row r at chunk c ^ (r & 7), which also keeps a quarter warp's loads on
+      // distinct banks), converts them and stores 32 columns of bf16 pairs.
+      const int quarter = warp & 3, h = (warp - 2) >> 2;
+      const int r = quarter * 32 + lane;
+      const bool by_group = args.w_scale_kind == 2;
+      const int groups_per_row = by_group ? (args.K + args.w_group - 1) / args.w_group : 0;
+      const int wrow = tile * kBM + r;
+      int stage = 0;
+      uint32_t phase = 0;
+      TRACE_ONLY(long long c_full = 0, c_empty = 0, c_conv = 0, c_sig = 0, c0; const long long c_begin = clock64();)
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int q = 2 * (kb - kb0) + h, j = q & 3;
+        float sc = 1.0f;
+        if (by_group) {  // one scale per (weight row, 64 k); requested before the wait below
+          const int g = (kb * Cfg::kKB + h * kBK) / args.w_group;
+          if (wrow < args.N && g < groups_per_row) sc = __ldg(args.w_scale + static_cast<size_t>(wrow) * groups_per_row + g);
+        }
+        TRACE_ONLY(c0 = clock64();)
+        if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_EPILOGUE)) break;
+        TRACE_ONLY(c_full += clock64() - c0; c0 = clock64();)
+        const uint8_t* row_gen = smem_gen + stage * Cfg::kStageBytes + r * 128;
+        uint4 in[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) in[c] = *reinterpret_cast<const uint4*>(row_gen + (((4 * h + c) ^ (r & 7)) << 4));
+        uint32_t o[32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t w[4] = {in[c].x, in[c].y, in[c].z, in[c].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) e4m3x4_to_bf16x4(w[e], args.w_mul16, o[8 * c + 2 * e], o[8 * c + 2 * e + 1]);
+        }
+        if (by_group) {  // the group's scale goes into the weight: bf16(value * scale), as the large-M path stores it
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = pack_bf16x2(bf16_lo(o[e]) * sc, bf16_hi(o[e]) * sc);
+        }
+        TRACE_ONLY(c_conv += clock64() - c0; c0 = clock64();)
+        if (q >= 4 && !mbar_wait(wempty_bar(j), ((q >> 2) - 1) & 1, err, DEVERR_GEMM_EPILOGUE)) break;
+        TRACE_ONLY(c_empty += clock64() - c0; c0 = clock64();)
+        tc_fence_after();
+        tmem_st_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + Cfg::kTmemA + j * 32, o);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(wfull_bar(j));
+          mbar_arrive(empty_bar(stage));
+        }
+        TRACE_ONLY(c_sig += clock64() - c0;)
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1; }
+      }
+      TRACE_VALUE(4, threadIdx.x == 64 && blockIdx.y == 0, clock64() - c_begin);
+      TRACE_VALUE(5, threadIdx.x == 64 && blockIdx.y == 0, c_full);
+      TRACE_VALUE(6, threadIdx.x == 64 && blockIdx.y == 0, c_empty);
+      TRACE_VALUE(7, threadIdx.x == 64 && blockIdx.y == 0, c_conv);
+      TRACE_VALUE(8, threadIdx.x == 64 && blockIdx.y == 0, c_sig);
+    }
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
-    if (mbar_wait(acc_full_bar, 0, err, DEVERR_GEMM_EPILOGUE)) {
+    if (warp < 6 && mbar_wait(acc_full_bar, 0, err, DEVERR_GEMM_EPILOGUE)) {
       TRACE_MARK(1, threadIdx.x == 64);
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -494,11 +684,19 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const bool direct = (S == 1) && !args.swiglu;
       const int n = tile * kBM + row;
       const float bias = (direct && args.bias && n < args.N) ? __bfloat162float(args.bias[n]) : 0.0f;
+      const float wsc = direct ? row_scale(n) : 1.0f;
       const unsigned stamp = (direct && args.push_recv) ? __ldcg(args.push_epoch) * 1024u + args.push_round + 1u : 0u;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
         if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
+        if constexpr (Cfg::kIssuers == 2) {  // the two issuers' accumulators: halves 0 and halves 1 of the stages
+          uint32_t r1[kChunk];
+          if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + Cfg::kAcc1 + c0, r1); else tmem_ld_32x16(t_addr + Cfg::kAcc1 + c0, r1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < kChunk; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r1[e]));
+        }
         tmem_wait_ld();
         if (direct) {
           // the whole K range was this CTA's: registers -> global, a warp's 32 rows side by side in each token row
@@ -507,7 +705,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
             for (int e = 0; e < kChunk; ++e) {
               const int c = c0 + e;
               if (c < args.M) {
-                const float v = __uint_as_float(r[e]) + bias;
+                const float v = W8 ? fmaf(__uint_as_float(r[e]), wsc, bias) : __uint_as_float(r[e]) + bias;
                 if (args.push_recv) {
                   const size_t off = static_cast<size_t>(c) * args.N + n;
                   const int p0 = args.push_owner_rows > 0 ? c / args.push_owner_rows : 0;
@@ -538,7 +736,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   if (S > 1) cluster_sync_all(); else if (reduce) __syncthreads();
   TRACE_MARK(2, threadIdx.x == 64);
 
-  if (warp >= 2 && reduce) {
+  if (warp >= 2 && warp < 6 && reduce) {
     // CTA `rank` finishes token columns [rank * cw, (rank + 1) * cw): per 16-byte unit (4 weight rows of one token
     // column) all S partial values are requested at once and summed in rank order
     const int cw = (BN + static_cast<int>(S) - 1) / static_cast<int>(S);  // columns per rank (last rank may get fewer)
@@ -564,6 +762,11 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
           us.x += uv[q].x; us.y += uv[q].y; us.z += uv[q].z; us.w += uv[q].w;
         }
         const int n_out = tile * 64 + 4 * j;
+        if constexpr (W8) {  // gate rows of this tile are weight rows tile * 128 + [0, 64), up rows the 64 behind them
+          const int wr = tile * kBM + 4 * j;
+          gs.x *= row_scale(wr); gs.y *= row_scale(wr + 1); gs.z *= row_scale(wr + 2); gs.w *= row_scale(wr + 3);
+          us.x *= row_scale(wr + 64); us.y *= row_scale(wr + 65); us.z *= row_scale(wr + 66); us.w *= row_scale(wr + 67);
+        }
         if (c < args.M) {
           const float o[4] = {swiglu_f(gs.x, us.x), swiglu_f(gs.y, us.y), swiglu_f(gs.z, us.z), swiglu_f(gs.w, us.w)};
           bf16* dst = args.y + static_cast<size_t>(c) * args.ldy + n_out;
@@ -592,6 +795,10 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const int n = tile * kBM + 4 * j;
         if (c < args.M && n < args.N) {
           float o[4] = {acc.x, acc.y, acc.z, acc.w};
+          if constexpr (W8) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] *= row_scale(n + e);
+          }
           if (args.bias) {
 #pragma unroll
             for (int e = 0; e < 4; ++e)
@@ -657,14 +864,14 @@ int prepare_variant() {
   return 0;
 }
 
-template <int BN>
+template <int BN, bool W8 = false>
 int prepare_skinny() {
   static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
-  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       SkinnyCfg<BN>::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SkinnyCfg<BN, W8>::kSmemBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
@@ -678,13 +885,27 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs&
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int BN>
+template <int BN, bool W8 = false>
 int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int split, int tiles,
                   cudaStream_t st) {
-  const int rc = prepare_skinny<BN>();
+  const int rc = prepare_skinny<BN, W8>();
   if (rc) return rc;
-  return launch_kernel(gemm_bf16_skinny_kernel<BN>, dim3(split, tiles, 1), dim3(kNumThreads, 1, 1),
-                       SkinnyCfg<BN>::kSmemBytes, st, static_cast<unsigned>(split), tw, tx, a);
+  return launch_kernel(gemm_bf16_skinny_kernel<BN, W8>, dim3(split, tiles, 1), dim3(SkinnyCfg<BN, W8>::kThreads, 1, 1),
+                       SkinnyCfg<BN, W8>::kSmemBytes, st, static_cast<unsigned>(split), tw, tx, a);
+}
+
+// Cluster width (K split) of the skinny kernel for `tiles` 128-row weight tiles.
+int skinny_split(int tiles, int k_blocks, int sms) {
+  const int slots = sms * 2;
+  int split = (slots * 85 / 100) / tiles;
+  if (split > 8) split = 8;
+  {  // TEENY_SKINNY_SPLIT: fixed cluster width, for measurements
+    static const int forced = [] { const char* e = getenv("TEENY_SKINNY_SPLIT"); return e ? atoi(e) : 0; }();
+    if (forced > 0 && forced <= 8) split = forced;
+  }
+  while (split > 1 && (ceil_div(k_blocks, split) < 4 || ceil_div(k_blocks, split) * (split - 1) >= k_blocks))
+    --split;  // too thin, or a rank would be left without k-blocks
+  return split < 1 ? 1 : split;
 }
 
 // Largest token count that takes the swapped (weights on the 128-row MMA side) assignment.
@@ -706,7 +927,11 @@ int gemm_bf16_prepare() {
   if ((rc = prepare_skinny<16>())) return rc;
   if ((rc = prepare_skinny<32>())) return rc;
   if ((rc = prepare_skinny<64>())) return rc;
-  return prepare_skinny<128>();
+  if ((rc = prepare_skinny<128>())) return rc;
+  if ((rc = prepare_skinny<16, true>())) return rc;
+  if ((rc = prepare_skinny<32, true>())) return rc;
+  if ((rc = prepare_skinny<64, true>())) return rc;
+  return prepare_skinny<128, true>();
 }
 
 bool gemm_bf16_uses_2cta(int M, int N) {
@@ -788,16 +1013,7 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
       // Few weight tiles: cluster split-K.  Measured on B200 (batch 32, K = 4096 / 12288): the kernel is fastest
       // when all its CTAs are resident at once (two per SM) and share HBM evenly -- about 0.85 of the slots -- and a
       // wider cluster than that only adds barrier and reduction cost; with at least as many tiles as SMs no split.
-      const int slots = sms * 2;
-      int split = (slots * 85 / 100) / tiles;
-      if (split > 8) split = 8;
-      {  // TEENY_SKINNY_SPLIT: fixed cluster width, for measurements
-        static const int forced = [] { const char* e = getenv("TEENY_SKINNY_SPLIT"); return e ? atoi(e) : 0; }();
-        if (forced > 0 && forced <= 8) split = forced;
-      }
-      while (split > 1 && (ceil_div(a.k_blocks, split) < 4 || ceil_div(a.k_blocks, split) * (split - 1) >= a.k_blocks))
-        --split;  // too thin, or a rank would be left without k-blocks
-      if (split < 1) split = 1;
+      const int split = skinny_split(tiles, a.k_blocks, sms);
       a.kb_per_split = ceil_div(a.k_blocks, split);
       {  // what the CTAs ask into L2 ahead of time must stay well inside it (126 MB): at most 48 MB over the grid
         const long long per_cta = (48ll << 20) / (static_cast<long long>(kBM * kBK * 2) * split * tiles);
@@ -834,6 +1050,60 @@ int gemm_bf16(const bf16* x, int ldx, const bf16* w, int ldw, bool w_is_kn, cons
   }
   if (bn == 128) return launch_variant<128, false, false>(tmx, tmw, a, grid, stream);
   return launch_variant<256, false, false>(tmx, tmw, a, grid, stream);
+}
+
+// Y[M, N] = X[M, K] (bf16) * dequant(Wq[N, K])^T for M <= 128: the skinny kernel's W8 variant at every N (one CTA per
+// weight tile where the tiles alone fill the GPU).
+int gemm_w8a16_skinny(const bf16* x, int ldx, const uint8_t* wq, int ldw, const float* w_scale, int scale_kind,
+                      int group, const bf16* bias, bf16* y, int ldy, int M, int N, int K, cudaStream_t stream, bool swiglu,
+                      const GemmPush* push) {
+  if (!x || !wq || !w_scale || !y || M <= 0 || M > kSwapMaxM || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  if (scale_kind < 0 || scale_kind > 2 || (scale_kind == 2 && (group <= 0 || group % kBK != 0))) return TEENY_ERR_BAD_ARG;
+  if (swiglu && (bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15) || (ldx & 7) || (ldw & 15))
+    return TEENY_ERR_ALIGNMENT;
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
+  a.k_blocks = ceil_div(K, 2 * kBK);  // a stage of the W8 variant is 128 k wide
+  a.swiglu = swiglu ? 1 : 0;
+  a.w_scale = w_scale; a.w_scale_kind = scale_kind; a.w_group = group; a.w_mul16 = 16u;
+  if (push) {
+    if (swiglu || !push->recv || !push->epoch || push->world < 2 || push->round >= 1023) return TEENY_ERR_BAD_ARG;
+    a.push_recv = push->recv;
+    a.push_epoch = push->epoch;
+    a.push_round = push->round;
+    a.push_world = push->world;
+    a.push_owner_rows = push->owner_rows;
+  }
+  a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;
+  const int bn = swap_bn(M);
+  CUtensorMap tmx, tmw;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldx) * 2};
+    const uint32_t box[2] = {kBK, static_cast<uint32_t>(bn)};
+    const int rc = encode_tensor_map_bf16(&tmx, x, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldw)};
+    const uint32_t box[2] = {2 * kBK, kBM};
+    const int rc = encode_tensor_map_u8(&tmw, wq, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  const int tiles = ceil_div(N, kBM);
+  if (tiles > 65535) return TEENY_ERR_BAD_ARG;
+  const int split = skinny_split(tiles, a.k_blocks, sm_count());
+  a.kb_per_split = ceil_div(a.k_blocks, split);
+  a.l2_ahead = 0;
+  switch (bn) {
+    case 16: return launch_skinny<16, true>(tmw, tmx, a, split, tiles, stream);
+    case 32: return launch_skinny<32, true>(tmw, tmx, a, split, tiles, stream);
+    case 64: return launch_skinny<64, true>(tmw, tmx, a, split, tiles, stream);
+    default: return launch_skinny<128, true>(tmw, tmx, a, split, tiles, stream);
+  }
 }
 
 }  // namespace teeny

@@ -57,6 +57,23 @@ int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int wor
                                    uint4* const* bcast, const unsigned* epoch, unsigned round, bf16* residual,
                                    long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N, float eps,
                                    cudaStream_t st, unsigned long long wait_limit_ns = 0);
+// ---- FP8 (E4M3) weight-only linear ----
+// W as bytes [N, K] (row stride ldw bytes) plus f32 scales: kind 0 = one scale, 1 = one per weight row (N), 2 = one per
+// `group` consecutive k of a row ([N][ceil(K / group)], group a multiple of 64).  value = decode(byte) * scale.
+// M <= 128: the bytes are streamed and converted inside the GEMM (swiglu and the tensor-parallel push as in gemm_bf16);
+// larger M: converted once into `scratch` (linear_w8a16_scratch_bytes) as bf16(value * scale), then the bf16 GEMM.
+int gemm_w8a16_skinny(const bf16* x, int ldx, const uint8_t* wq, int ldw, const float* w_scale, int scale_kind,
+                      int group, const bf16* bias, bf16* y, int ldy, int M, int N, int K, cudaStream_t stream,
+                      bool swiglu = false, const GemmPush* push = nullptr);
+int dequant_e4m3_bf16(const uint8_t* wq, long long ldw, const float* scale, int kind, int group, bf16* out, long long ldo,
+                      int N, int K, cudaStream_t st);
+// *count <- number of NaN encodings (0x7f, 0xff) among n bytes; the in-GEMM conversion does not reproduce them
+int e4m3_count_nan(const uint8_t* p, size_t n, unsigned* count, cudaStream_t st);
+size_t linear_w8a16_scratch_bytes(int M, int N, int K);
+int linear_w8a16(const bf16* x, int ldx, const uint8_t* wq, int ldw, const float* scale, int kind, int group,
+                 const bf16* bias, bf16* y, int ldy, int M, int N, int K, void* scratch, size_t scratch_bytes,
+                 cudaStream_t st, bool swiglu = false, const GemmPush* push = nullptr);
+
 // Large-M path on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); same contract as gemm_bf16 without the options.
 // With `qkv` the GEMM is the fused [q | k | v] projection of a prefill (N = (Hq + 2 Hkv) * 128, token t = sequence
 // t / S at position pos0 + t % S) and its epilogue does what qk_norm_rope_kv_bf16 does in a pass of its own: per-head

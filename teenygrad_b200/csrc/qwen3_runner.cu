@@ -299,8 +299,18 @@ size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
+// A projection weight in the form it was given: bf16 [N, K], or FP8 (E4M3) bytes [N, K] with f32 scales
+// (teeny_qwen3_set_weight_fp8; kinds as in teeny_linear_w8a16_forward).
+struct Weight {
+  const bf16* w = nullptr;
+  const uint8_t* q = nullptr;
+  const float* scale = nullptr;
+  int kind = 0, group = 0;
+  bool set() const { return w || q; }
+};
+
 struct LayerWeights {
-  const bf16 *qkv = nullptr, *o = nullptr, *gate_up = nullptr, *down = nullptr;
+  Weight qkv, o, gate_up, down;
   const bf16 *input_ln = nullptr, *post_ln = nullptr, *q_norm = nullptr, *k_norm = nullptr;
 };
 
@@ -320,7 +330,10 @@ struct teeny_qwen3 {
   teeny_qwen3_config cfg;
   int Hq, Hkv, I, Vl;  // local (per-rank) q heads, kv heads, intermediate, vocab rows
   std::vector<LayerWeights> layers;
-  const bf16 *embed = nullptr, *final_norm = nullptr, *lm_head = nullptr;
+  const bf16 *embed = nullptr, *final_norm = nullptr;
+  Weight lm_head;
+  void* fp8_scratch = nullptr;  // where a large prefill converts one FP8 projection at a time to bf16
+  size_t fp8_scratch_bytes = 0;
   const float* inv_freq = nullptr;
   uint8_t* ws = nullptr;
   Workspace off;
@@ -430,26 +443,44 @@ int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
   return g_nccl.AllReduce(buf, buf, count, ncclBfloat16, ncclSum, m->comm, st) == ncclSuccess ? 0 : TEENY_ERR_NCCL;
 }
 
+// y[T, N] = x[T, K] W^T for one of the model's projection weights, in whichever form it was given.  FP8 weights are
+// streamed as bytes while T <= 128 (decode) and converted into the model's FP8 scratch for a larger T (prefill), where
+// the bf16 kernels -- the QKV projection's fused epilogue included -- then run on the converted copy.
+int project(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* y, int ldy, int T, int N, int K,
+            cudaStream_t st, bool swiglu = false, const GemmPush* push = nullptr, const QkvEpilogue* fuse = nullptr) {
+  void* gs = m->at<void>(m->off.gemm_scratch);
+  const bf16* wb = w.w;
+  const int w_rows = N;  // rows of W ([N, K]; for swiglu N counts gate and up rows)
+  if (w.q) {
+    if (T <= 128) return linear_w8a16(x, ldx, w.q, K, w.scale, w.kind, w.group, nullptr, y, ldy, T, N, K, nullptr, 0, st, swiglu, push);
+    const size_t need = static_cast<size_t>(w_rows) * K * sizeof(bf16);
+    if (!m->fp8_scratch || m->fp8_scratch_bytes < need || (K & 7)) return TEENY_ERR_SCRATCH;
+    TEENY_TRY(dequant_e4m3_bf16(w.q, K, w.scale, w.kind, w.group, static_cast<bf16*>(m->fp8_scratch), K, w_rows, K, st));
+    wb = static_cast<const bf16*>(m->fp8_scratch);
+  }
+  if (fuse) return gemm_bf16_2cta(x, ldx, wb, K, nullptr, y, ldy, T, N, K, st, false, fuse);
+  return gemm_bf16(x, ldx, wb, K, false, nullptr, y, ldy, T, N, K, gs, m->off.gemm_scratch_bytes, st, swiglu, push);
+}
+
 // Row-parallel projection delta = x W^T followed by the cross-rank sum.  Decode with peer buffers: the GEMM pushes
 // its f32 rows into every rank's receive buffer and the sum happens inside the next norm kernel (pending_gather);
 // otherwise GEMM to `delta` and, with tp > 1, an NCCL all-reduce.
-int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const bf16* w, bf16* delta, int T, int N, int K, bool decode,
+int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* delta, int T, int N, int K, bool decode,
                  cudaStream_t st) {
-  void* gs = m->at<void>(m->off.gemm_scratch);
   TpContext* tp = m->tp;
   if (decode && tp && tp->peer_ok && T <= static_cast<int>(tp->rows) && N == static_cast<int>(tp->cols)) {
     const int parity = m->push_round & 1;
     const int owner_rows = tp->two_hop ? (T + tp->world - 1) / tp->world : 0;
     GemmPush push{tp->recv_tab + parity * tp->world, tp->world, tp->epoch(), static_cast<unsigned>(m->push_round),
                   owner_rows};
-    TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st, false, &push));
+    TEENY_TRY(project(m, x, ldx, w, delta, N, T, N, K, st, false, &push));
     m->pending_gather = true;
     m->pending_parity = parity;
     m->pending_round = static_cast<unsigned>(m->push_round);
     ++m->push_round;
     return 0;
   }
-  TEENY_TRY(gemm_bf16(x, ldx, w, ldx, false, nullptr, delta, N, T, N, K, gs, m->off.gemm_scratch_bytes, st));
+  TEENY_TRY(project(m, x, ldx, w, delta, N, T, N, K, st));
   return all_reduce(m, delta, static_cast<size_t>(T) * N, st);
 }
 
@@ -485,8 +516,6 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
   bf16 *h = m->at<bf16>(m->off.h), *y = m->at<bf16>(m->off.y), *qkv = m->at<bf16>(m->off.qkv);
   bf16 *attn = m->at<bf16>(m->off.attn), *delta = m->at<bf16>(m->off.delta);
   bf16* act = m->at<bf16>(m->off.act);
-  void* gs = m->at<void>(m->off.gemm_scratch);
-  const size_t gsb = m->off.gemm_scratch_bytes;
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   // (Asking the QKV and gate/up weights into L2 while the norm in front of them waits for the other ranks' partial sums
   // was measured under tensor parallelism: 3.29 ms per decode step against 3.25 ms without, 2 ranks.  Not used.)
@@ -502,9 +531,9 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     if (!decode && !pos_dev && qkv_fuse_enabled() && gemm_bf16_uses_2cta(T, qkv_n)) {
       const QkvEpilogue fuse{w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin), kc, vc,
                              S, Hq, Hkv, c.max_len, pos0, c.eps};
-      TEENY_TRY(gemm_bf16_2cta(y, H, w.qkv, H, nullptr, qkv, qkv_n, T, qkv_n, H, st, false, &fuse));
+      TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, T, qkv_n, H, st, false, nullptr, &fuse));
     } else {
-      TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, T, qkv_n, H, gs, gsb, st));
+      TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, T, qkv_n, H, st));
       if (!decode)
         TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
                                        kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
@@ -535,7 +564,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     }
     TEENY_TRY(row_parallel(m, attn, Hq * D, w.o, delta, T, H, Hq * D, decode, st));
     TEENY_TRY(residual_norm(m, delta, h, H, y, w.post_ln, T, st));
-    TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, act, I, T, 2 * I, H, gs, gsb, st, /*swiglu=*/true));
+    TEENY_TRY(project(m, y, H, w.gate_up, act, I, T, 2 * I, H, st, /*swiglu=*/true));
     TEENY_TRY(row_parallel(m, act, I, w.down, delta, T, H, I, decode, st));
   }
   return 0;
@@ -559,8 +588,6 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
   const teeny_qwen3_config& c = m->cfg;
   const int Bh = B / 2, Th = Bh * S, H = c.hidden, D = c.head_dim, Hq = m->Hq, Hkv = m->Hkv, I = m->I;
   const int qkv_n = (Hq + 2 * Hkv) * D;
-  void* gs = m->at<void>(m->off.gemm_scratch);
-  const size_t gsb = m->off.gemm_scratch_bytes;
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
   cudaStream_t sc = m->comm_stream;
   struct SmLimit {
@@ -605,9 +632,9 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
       if (qkv_fuse_enabled() && gemm_bf16_uses_2cta(Th, qkv_n)) {  // head norms, RoPE and the cache fill in the projection's epilogue
         const QkvEpilogue fuse{w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
                                kc + hf * cache_half, vc + hf * cache_half, S, Hq, Hkv, c.max_len, 0, c.eps};
-        TEENY_TRY(gemm_bf16_2cta(y, H, w.qkv, H, nullptr, qkv, qkv_n, Th, qkv_n, H, st, false, &fuse));
+        TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, Th, qkv_n, H, st, false, nullptr, &fuse));
       } else {
-        TEENY_TRY(gemm_bf16(y, H, w.qkv, H, false, nullptr, qkv, qkv_n, Th, qkv_n, H, gs, gsb, st));
+        TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, Th, qkv_n, H, st));
         TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
                                        kc + hf * cache_half, vc + hf * cache_half, Th, S, Hq, Hkv, D, c.max_len, 0, nullptr,
                                        c.eps, st));
@@ -620,7 +647,7 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
       a.o_sb = static_cast<long long>(S) * Hq * D; a.o_sh = D; a.o_ss = static_cast<long long>(Hq) * D;
       a.Sq = S; a.Skv = S; a.causal = 1;
       TEENY_TRY(attention_prefill_bf16(qkv, kc + hf * cache_half, vc + hf * cache_half, attn, nullptr, a, st));
-      TEENY_TRY(gemm_bf16(attn, Hq * D, w.o, Hq * D, false, nullptr, delta, H, Th, H, Hq * D, gs, gsb, st));
+      TEENY_TRY(project(m, attn, Hq * D, w.o, delta, H, Th, H, Hq * D, st));
       TEENY_TRY(reduce_async(delta, hf));
     }
     for (int hf = 0; hf < 2; ++hf) {  // MLP blocks
@@ -628,8 +655,8 @@ int run_layers_prefill_overlap(teeny_qwen3* m, int B, int S, cudaStream_t st) {
       half_ptrs(hf, h, y, qkv, attn, delta, act);
       TEENY_TRY(wait_reduced(hf));  // O projection
       TEENY_TRY(add_rms_norm_bf16(delta, H, h, H, y, H, w.post_ln, Th, H, c.eps, st));
-      TEENY_TRY(gemm_bf16(y, H, w.gate_up, H, false, nullptr, act, I, Th, 2 * I, H, gs, gsb, st, /*swiglu=*/true));
-      TEENY_TRY(gemm_bf16(act, I, w.down, I, false, nullptr, delta, H, Th, H, I, gs, gsb, st));
+      TEENY_TRY(project(m, y, H, w.gate_up, act, I, Th, 2 * I, H, st, /*swiglu=*/true));
+      TEENY_TRY(project(m, act, I, w.down, delta, H, Th, H, I, st));
       TEENY_TRY(reduce_async(delta, hf));
     }
   }
@@ -649,8 +676,7 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st, const int* step_dev 
   const long long ld = static_cast<long long>(S) * H;
   // residual add + final norm on rows (b, S-1); y rows are packed [B, H]
   TEENY_TRY(residual_norm(m, delta + last, h + last, ld, y, m->final_norm, B, st));
-  TEENY_TRY(gemm_bf16(y, H, m->lm_head, H, false, nullptr, logits, Vl, B, Vl, H, m->at<void>(m->off.gemm_scratch),
-                      m->off.gemm_scratch_bytes, st));
+  TEENY_TRY(project(m, y, H, m->lm_head, logits, Vl, B, Vl, H, st));
   float* cv = m->at<float>(m->off.cand_val);
   int* ci = m->at<int>(m->off.cand_idx);
   int* next = m->at<int>(m->off.next_ids);
@@ -816,7 +842,7 @@ int teeny_qwen3_set_weight(teeny_qwen3* m, int layer, int which, const void* ptr
     switch (which) {
       case TEENY_QWEN3_W_EMBED: m->embed = p; return 0;
       case TEENY_QWEN3_W_FINAL_NORM: m->final_norm = p; return 0;
-      case TEENY_QWEN3_W_LM_HEAD: m->lm_head = p; return 0;
+      case TEENY_QWEN3_W_LM_HEAD: m->lm_head = Weight{p}; return 0;
       case TEENY_QWEN3_W_INV_FREQ: m->inv_freq = static_cast<const float*>(ptr); m->tables_ready = false; return 0;
       default: return TEENY_ERR_BAD_ARG;
     }
@@ -824,10 +850,10 @@ int teeny_qwen3_set_weight(teeny_qwen3* m, int layer, int which, const void* ptr
   if (layer < 0 || layer >= m->cfg.num_layers) return TEENY_ERR_BAD_ARG;
   LayerWeights& w = m->layers[layer];
   switch (which) {
-    case TEENY_QWEN3_W_QKV: w.qkv = p; break;
-    case TEENY_QWEN3_W_O: w.o = p; break;
-    case TEENY_QWEN3_W_GATE_UP: w.gate_up = p; break;
-    case TEENY_QWEN3_W_DOWN: w.down = p; break;
+    case TEENY_QWEN3_W_QKV: w.qkv = Weight{p}; break;
+    case TEENY_QWEN3_W_O: w.o = Weight{p}; break;
+    case TEENY_QWEN3_W_GATE_UP: w.gate_up = Weight{p}; break;
+    case TEENY_QWEN3_W_DOWN: w.down = Weight{p}; break;
     case TEENY_QWEN3_W_INPUT_LN: w.input_ln = p; break;
     case TEENY_QWEN3_W_POST_LN: w.post_ln = p; break;
     case TEENY_QWEN3_W_Q_NORM: w.q_norm = p; break;
@@ -837,10 +863,50 @@ int teeny_qwen3_set_weight(teeny_qwen3* m, int layer, int which, const void* ptr
   return 0;
 }
 
+int teeny_qwen3_set_weight_fp8(teeny_qwen3* m, int layer, int which, const void* bytes, const float* scales,
+                               int scale_kind, int group_size) {
+  if (!m || !bytes || !scales || scale_kind < 0 || scale_kind > 2) return TEENY_ERR_BAD_ARG;
+  if (scale_kind == 2 && (group_size <= 0 || group_size % 64 != 0)) return TEENY_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(bytes) & 15) return TEENY_ERR_ALIGNMENT;
+  Weight v;
+  v.q = static_cast<const uint8_t*>(bytes);
+  v.scale = scales;
+  v.kind = scale_kind;
+  v.group = group_size;
+  if (which == TEENY_QWEN3_W_LM_HEAD) { m->lm_head = v; return 0; }
+  if (layer < 0 || layer >= m->cfg.num_layers) return TEENY_ERR_BAD_ARG;
+  LayerWeights& w = m->layers[layer];
+  switch (which) {
+    case TEENY_QWEN3_W_QKV: w.qkv = v; break;
+    case TEENY_QWEN3_W_O: w.o = v; break;
+    case TEENY_QWEN3_W_GATE_UP: w.gate_up = v; break;
+    case TEENY_QWEN3_W_DOWN: w.down = v; break;
+    default: return TEENY_ERR_BAD_ARG;  // norms, the embedding table and inv_freq stay in their own types
+  }
+  return 0;
+}
+
+size_t teeny_qwen3_fp8_scratch_bytes(const teeny_qwen3_config* cfg) {
+  if (!cfg || cfg->tp_size <= 0) return 0;
+  const size_t H = static_cast<size_t>(cfg->hidden), D = static_cast<size_t>(cfg->head_dim);
+  const size_t qkv = (static_cast<size_t>(cfg->num_q_heads) + 2 * static_cast<size_t>(cfg->num_kv_heads)) / cfg->tp_size * D;
+  const size_t gate_up = 2 * static_cast<size_t>(cfg->intermediate) / cfg->tp_size;
+  const size_t rows = qkv > gate_up ? qkv : gate_up;  // O and down have no more elements than these two
+  return (rows > H ? rows : H) * H * sizeof(bf16);
+}
+
+int teeny_qwen3_set_fp8_scratch(teeny_qwen3* m, void* scratch, size_t bytes) {
+  if (!m || (scratch && (reinterpret_cast<uintptr_t>(scratch) & 15))) return TEENY_ERR_BAD_ARG;
+  m->fp8_scratch = scratch;
+  m->fp8_scratch_bytes = scratch ? bytes : 0;
+  return 0;
+}
+
 static int check_ready(teeny_qwen3* m, cudaStream_t st) {
-  if (!m->embed || !m->final_norm || !m->lm_head || !m->inv_freq) return TEENY_ERR_BAD_ARG;
+  if (!m->embed || !m->final_norm || !m->lm_head.set() || !m->inv_freq) return TEENY_ERR_BAD_ARG;
   for (const LayerWeights& w : m->layers)
-    if (!w.qkv || !w.o || !w.gate_up || !w.down || !w.input_ln || !w.post_ln || !w.q_norm || !w.k_norm)
+    if (!w.qkv.set() || !w.o.set() || !w.gate_up.set() || !w.down.set() || !w.input_ln || !w.post_ln || !w.q_norm ||
+        !w.k_norm)
       return TEENY_ERR_BAD_ARG;
   if (!m->tables_ready) {
     TEENY_TRY(rope_table_bf16(m->inv_freq, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin), m->cfg.max_len,

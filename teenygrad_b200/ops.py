@@ -219,6 +219,53 @@ def linear_swiglu(x, w_interleaved, out=None):
     return out
 
 
+SCALE_KINDS = {"tensor": 0, "channel": 1, "group": 2}
+
+
+def _as_bytes(w):
+    if w.dtype == torch.uint8:
+        return w
+    if w.dtype == torch.float8_e4m3fn:
+        return w.view(torch.uint8)
+    raise ValueError(f"FP8 weight must be uint8 or float8_e4m3fn, got {w.dtype}")
+
+
+def linear_w8a16(x, w_fp8, w_scale, strategy="channel", group_size=0, bias=None, out=None, scratch=None, swiglu=False):
+    """x [M, K] bf16 times an FP8 (E4M3) weight [N, K] with float32 scales (``strategy`` "tensor" | "channel" | "group",
+    the reference quantiser's names); swiglu: rows interleaved by ``interleave_gate_up`` (scales too), out [M, N/2].
+    M > 128 needs ``scratch`` of ``lib.teeny_linear_w8a16_scratch_bytes`` bytes (allocated here when not given)."""
+    _req(x, _BF16, "x"); _req(w_scale, _F32, "w_scale")
+    w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8")
+    M, K = x.shape
+    N = w.shape[0]
+    out = torch.empty(M, N // 2 if swiglu else N, dtype=_BF16, device=x.device) if out is None else out
+    need = lib.teeny_linear_w8a16_scratch_bytes(M, N, K)
+    if need and scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+    check(lib.teeny_linear_w8a16_forward(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(w_scale), SCALE_KINDS[strategy],
+                                         group_size, _ptr(bias), _ptr(out), out.stride(0), M, N, K, int(swiglu),
+                                         _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()),
+          "linear_w8a16")
+    return out
+
+
+def dequant_fp8(w_fp8, w_scale, strategy="channel", group_size=0, out=None):
+    """bf16(decode(byte) * scale) of an FP8 (E4M3) tensor [N, K]."""
+    w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8"); _req(w_scale, _F32, "w_scale")
+    N, K = w.shape
+    out = torch.empty(N, K, dtype=_BF16, device=w.device) if out is None else out
+    check(lib.teeny_dequant_fp8_e4m3_bf16(_ptr(w), w.stride(0), _ptr(w_scale), SCALE_KINDS[strategy], group_size, _ptr(out),
+                                          out.stride(0), N, K, _stream()), "dequant_fp8")
+    return out
+
+
+def fp8_count_nan(w_fp8):
+    w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8").contiguous()
+    count = torch.zeros(1, dtype=torch.int32, device=w.device)
+    check(lib.teeny_fp8_e4m3_count_nan(_ptr(w), w.numel(), _ptr(count), _stream()), "fp8_count_nan")
+    return int(count.item())
+
+
 def rope_table(inv_freq, max_pos):
     _req(inv_freq, _F32, "inv_freq")
     D = inv_freq.numel() * 2

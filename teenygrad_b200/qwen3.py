@@ -28,6 +28,9 @@ SIGNATURES = {
     "teeny_qwen3_create": (i32, [C.POINTER(_Cfg), vp, sz, vp, vp, C.POINTER(vp)]),
     "teeny_qwen3_destroy": (None, [vp]),
     "teeny_qwen3_set_weight": (i32, [vp, i32, i32, vp]),
+    "teeny_qwen3_set_weight_fp8": (i32, [vp, i32, i32, vp, vp, i32, i32]),
+    "teeny_qwen3_fp8_scratch_bytes": (sz, [C.POINTER(_Cfg)]),
+    "teeny_qwen3_set_fp8_scratch": (i32, [vp, vp, sz]),
     "teeny_qwen3_prefill": (i32, [vp, vp, i32, i32, vp]),
     "teeny_qwen3_decode": (i32, [vp, vp]),
     "teeny_qwen3_set_sampling": (i32, [vp, f32, i32, f32, C.c_ulonglong]),
@@ -137,6 +140,69 @@ class Qwen3Runner:
         self._set(0, W_EMBED, shards["embed"].to(_BF16))
         self._set(0, W_FINAL_NORM, shards["final_norm"].to(_BF16))
         self._set(0, W_LM_HEAD, shards["lm_head"].to(_BF16))
+        inv = default_inv_freq(self.cfg) if inv_freq is None else inv_freq
+        self._set(0, W_INV_FREQ, inv.to(torch.float32))
+
+    # ---- FP8 weights (the reference quantiser's float-quantized checkpoints, see quant.py) ----
+    def _set_fp8(self, layer, which, w):
+        from . import ops
+        w = w.to(self.device)
+        if ops.fp8_count_nan(w.q):
+            raise ValueError("FP8 weight holds NaN encodings (0x7f / 0xff), which the streaming GEMM does not reproduce")
+        self._weights += [w.q, w.scale]
+        kind = 2 if w.group_size else 1
+        check(lib.teeny_qwen3_set_weight_fp8(self._h, layer, which, C.c_void_p(w.q.data_ptr()),
+                                             C.c_void_p(w.scale.data_ptr()), kind, w.group_size), "teeny_qwen3_set_weight_fp8")
+        if self._c.max_tokens > 128 and getattr(self, "_fp8_scratch", None) is None:
+            # a prefill of more than 128 tokens converts one projection at a time into this buffer
+            n = lib.teeny_qwen3_fp8_scratch_bytes(C.byref(self._c))
+            self._fp8_scratch = torch.empty(n, dtype=torch.uint8, device=self.device)
+            check(lib.teeny_qwen3_set_fp8_scratch(self._h, C.c_void_p(self._fp8_scratch.data_ptr()), n),
+                  "teeny_qwen3_set_fp8_scratch")
+
+    def load_layer_shards_fp8(self, layer, shards):
+        """``shards``: name -> quant.Fp8Weight for the four projections, bf16 tensors for the norms."""
+        for name, slot in _LAYER_SLOTS.items():
+            t = shards[name]
+            if isinstance(t, torch.Tensor):
+                self._set(layer, slot, t.to(_BF16))
+            else:
+                self._set_fp8(layer, slot, t)
+
+    def load_quantized(self, tensors, scheme, inv_freq=None):
+        """A float-quantized checkpoint: ``tensors`` maps HF names to tensors (``*.weight`` as FP8 bytes next to
+        ``*.weight_scale``, norms in a float type), ``scheme`` is quant.parse_quantization_config's.  Projections and the
+        LM head stay FP8; the embedding table is converted back to bf16 (on this device) for the lookup."""
+        from . import ops, quant
+
+        def get(name):
+            return quant.Fp8Weight.from_tensors(tensors[name], tensors[name + "_scale"], scheme)
+
+        def norms(i):
+            p = f"model.layers.{i}."
+            return {"input_ln": tensors[p + "input_layernorm.weight"], "post_ln": tensors[p + "post_attention_layernorm.weight"],
+                    "q_norm": tensors[p + "self_attn.q_norm.weight"], "k_norm": tensors[p + "self_attn.k_norm.weight"]}
+
+        for i in range(self.cfg.num_layers):
+            shards = quant.shard_layer_fp8(get, self.cfg, i, self.tp_rank, self.tp_size)
+            shards.update(norms(i))
+            self.load_layer_shards_fp8(i, shards)
+        emb_name = "model.embed_tokens.weight"
+        if emb_name + "_scale" in tensors:
+            e = get(emb_name).to(self.device)
+            if ops.fp8_count_nan(e.q):
+                raise ValueError("embedding table holds FP8 NaN encodings")
+            embed = ops.dequant_fp8(e.q, e.scale, e.strategy, e.group_size)
+        else:
+            embed = tensors[emb_name].to(_BF16)
+        self._set(0, W_EMBED, embed)
+        self._set(0, W_FINAL_NORM, tensors["model.norm.weight"].to(_BF16))
+        head_name = emb_name if self.cfg.tied else "lm_head.weight"
+        vl = self.cfg.vocab // self.tp_size
+        if head_name + "_scale" in tensors:
+            self._set_fp8(0, W_LM_HEAD, get(head_name).rows(self.tp_rank * vl, (self.tp_rank + 1) * vl))
+        else:
+            self._set(0, W_LM_HEAD, tensors[head_name][self.tp_rank * vl:(self.tp_rank + 1) * vl].to(_BF16))
         inv = default_inv_freq(self.cfg) if inv_freq is None else inv_freq
         self._set(0, W_INV_FREQ, inv.to(torch.float32))
 

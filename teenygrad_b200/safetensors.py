@@ -24,6 +24,8 @@ _DTYPES = {
     "F64": (np.float64, torch.float64), "I64": (np.int64, torch.int64), "I32": (np.int32, torch.int32),
     "I16": (np.int16, torch.int16), "I8": (np.int8, torch.int8), "U8": (np.uint8, torch.uint8),
     "BOOL": (np.uint8, torch.bool),
+    # the two FP8 encodings of the format (what the reference's quantiser writes its float-quantized weights as)
+    "F8_E4M3": (np.uint8, torch.float8_e4m3fn), "F8_E5M2": (np.uint8, torch.float8_e5m2),
 }
 _NAMES = {v[1]: k for k, v in _DTYPES.items()}
 
@@ -94,7 +96,7 @@ class SafeTensors(Mapping):
         b, e = info["data_offsets"]
         raw = self._maps[i][self._data0[i] + b:self._data0[i] + e]
         t = torch.from_numpy(raw.view(np_dtype) if e > b else np.empty(0, dtype=np_dtype))
-        if torch_dtype in (torch.bfloat16, torch.bool):
+        if torch_dtype in (torch.bfloat16, torch.bool, torch.float8_e4m3fn, torch.float8_e5m2):
             t = t.view(torch_dtype)
         return t.view(*info["shape"]) if info["shape"] else t.view(())
 
@@ -107,7 +109,8 @@ def save_file(tensors, path, metadata=None):
         if t.dtype not in _NAMES:
             raise ValueError(f"{name}: dtype {t.dtype} has no safetensors name")
         raw = t.view(torch.uint16).numpy().tobytes() if t.dtype == torch.bfloat16 else (
-            t.view(torch.uint8).numpy().tobytes() if t.dtype == torch.bool else t.numpy().tobytes())
+            t.view(torch.uint8).numpy().tobytes() if t.dtype in (torch.bool, torch.float8_e4m3fn, torch.float8_e5m2)
+            else t.numpy().tobytes())
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         blobs.append(raw)
         offset += len(raw)
