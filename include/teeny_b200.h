@@ -197,6 +197,14 @@ size_t teeny_linear_w8a16_scratch_bytes(int M, int N, int K);
  * utilities/teeny-quant/src/quant/fp8.rs:262-268 with one rounding to bf16, every byte value handled (NaN included). */
 int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w_scale, int scale_kind, int group_size,
                                 teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t stream);
+/* The quantiser's integer schemes ("int-quantized": I8 in the weight's shape; "pack-quantized": 4-bit values two per
+ * byte over the flattened tensor, the first in the low nibble, utilities/teeny-quant/src/quant/pack4.rs:31-40) back to
+ * bf16: out[N, K] = bf16((q - zero_point) * scale), dequantize_affine of utilities/teeny-quant/src/quant/affine.rs:151-161
+ * with one rounding.  bits = 8 or 4; zero_point = the I32 vector of `foo.weight_zero_point` or NULL for a symmetric
+ * scheme; scale kinds as above, any group_size.  There is no streaming integer GEMM: such weights are converted once
+ * when they are loaded and run through the bf16 kernels. */
+int teeny_dequant_int_bf16(const void* q, int bits, const float* w_scale, const int* zero_point, int scale_kind,
+                           int group_size, teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t stream);
 /* *count (device word) <- how many of the n bytes are E4M3 NaN encodings. */
 int teeny_fp8_e4m3_count_nan(const void* bytes, size_t n, unsigned* count, teeny_stream_t stream);
 /* cos/sin tables [max_pos, D] from inv_freq[D/2] (f32 angles, one rounding to bf16). */

@@ -136,6 +136,7 @@ extern "C" {
     pub fn teeny_linear_w8a16_forward(x: *const u16, ldx: c_longlong, w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, bias: *const u16, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, swiglu: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
     pub fn teeny_linear_w8a16_scratch_bytes(m: c_int, n: c_int, k: c_int) -> usize;
     pub fn teeny_dequant_fp8_e4m3_bf16(w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, out: *mut u16, ldo: c_longlong, n: c_int, k: c_int, stream: CUstream) -> c_int;
+    pub fn teeny_dequant_int_bf16(q: *const c_void, bits: c_int, w_scale: *const f32, zero_point: *const c_int, scale_kind: c_int, group_size: c_int, out: *mut u16, ldo: c_longlong, n: c_int, k: c_int, stream: CUstream) -> c_int;
     pub fn teeny_fp8_e4m3_count_nan(bytes: *const c_void, n: usize, count: *mut c_uint, stream: CUstream) -> c_int;
     pub fn teeny_rope_table_bf16(inv_freq: *const f32, cos_table: *mut u16, sin_table: *mut u16, max_pos: c_int, d: c_int, stream: CUstream) -> c_int;
     pub fn teeny_qk_norm_rope_kv_bf16(qkv: *mut u16, ld: c_longlong, q_norm_w: *const u16, k_norm_w: *const u16, cos_table: *const u16, sin_table: *const u16, k_cache: *mut u16, v_cache: *mut u16, t: c_int, s: c_int, hq: c_int, hkv: c_int, d: c_int, max_len: c_int, pos0: c_int, pos0_dev: *const c_int, eps: f32, stream: CUstream) -> c_int;

@@ -1,7 +1,8 @@
-"""CPU restatement of the reference's FP8 weight quantiser (test infrastructure: only tests/, the smoke check and
-bench.py's CPU leg may import this).
+"""CPU restatement of the reference's weight quantiser, FP8 and integer schemes (test infrastructure: only tests/, the
+smoke check and bench.py's CPU leg may import this).
 
-Follows utilities/teeny-quant/src/quant/fp8.rs and groups.rs of the reference:
+Follows utilities/teeny-quant/src/quant/fp8.rs, groups.rs, affine.rs and pack4.rs of the reference (the integer
+functions cite their lines where they stand, at the end of the file):
 
   * ``f32_to_f8`` (fp8.rs:100-171): OCP FP8, round to nearest even at the target mantissa, magnitudes beyond the
     largest finite value saturate (E4M3: to 448, there is no infinity; E5M2: to infinity), anything below the smallest
@@ -16,7 +17,8 @@ Follows utilities/teeny-quant/src/quant/fp8.rs and groups.rs of the reference:
     dequantised f32 weight, accumulated in float32 (float64 here), rounded once to bf16.  The reference has no such
     kernel; this states the contract of include/teeny_b200.h's teeny_linear_w8a16_forward.
 
-Pinned by tests/test_oracle_quant.py against every known-answer case of fp8.rs's own unit tests (fp8.rs:270-357), and
+Pinned by tests/test_oracle_quant.py against every known-answer case of fp8.rs's own unit tests (fp8.rs:270-357), of
+affine.rs:163-288 and of pack4.rs:66-93, and
 against PyTorch's float8_e4m3fn / float8_e5m2 casts: decode for all 256 bytes of both formats, encode on the values
 where the two definitions agree (PyTorch keeps subnormal results, the reference flushes them; PyTorch's E4M3 cast of an
 out-of-range value gives NaN, the reference saturates).
@@ -121,3 +123,62 @@ def linear_w8a16(x_bf16_as_f32, q, scales, strategy="channel", axis=0, group_siz
     if bias is not None:
         y = y + np.asarray(bias, dtype=np.float64)
     return y.astype(np.float32)
+
+
+# ---- integer schemes: utilities/teeny-quant/src/quant/affine.rs and pack4.rs ----
+def _round_half_away(x):
+    """Rust's f32::round: halves away from zero."""
+    return np.sign(x) * np.floor(np.abs(x) + np.float32(0.5))
+
+
+def qrange(bits, symmetric):
+    """affine.rs:46-51: 8 bits -> [-127, 127] symmetric, [-128, 127] asymmetric; 4 bits -> [-7, 7] / [-8, 7]."""
+    qmax = (1 << (bits - 1)) - 1
+    return (-qmax if symmetric else -qmax - 1), qmax
+
+
+def quantize_affine(w, bits=8, symmetric=True, strategy="channel", axis=0, group_size=None):
+    """(int8 values of w's shape, float32 scales [groups], int32 zero points [groups]) -- affine.rs:55-148: per group
+    lo = min(min x, 0), hi = max(max x, 0); symmetric: scale = max(|lo|, |hi|) / qmax (1 if 0), zero point 0;
+    asymmetric: scale = (hi - lo) / (qmax - qmin) (1 if hi == lo), zero point = round(qmin - lo / scale) clamped;
+    q = clamp(round(x / scale) + zero point)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    qmin, qmax = qrange(bits, symmetric)
+    groups, n = assign_groups(w.shape, strategy, axis, group_size)
+    lo = np.full(n, np.inf, dtype=np.float32)
+    hi = np.full(n, -np.inf, dtype=np.float32)
+    np.minimum.at(lo, groups.ravel(), w.ravel())
+    np.maximum.at(hi, groups.ravel(), w.ravel())
+    lo, hi = np.minimum(lo, np.float32(0)), np.maximum(hi, np.float32(0))
+    if symmetric:
+        amax = np.maximum(np.abs(lo), np.abs(hi))
+        scale = np.where(amax == 0, np.float32(1), amax / np.float32(qmax)).astype(np.float32)
+        zp = np.zeros(n, dtype=np.int32)
+    else:
+        scale = np.where(hi == lo, np.float32(1), (hi - lo) / np.float32(qmax - qmin)).astype(np.float32)
+        zp = np.clip(_round_half_away(np.float32(qmin) - lo / scale).astype(np.int64), qmin, qmax).astype(np.int32)
+    q = _round_half_away((w / scale[groups]).astype(np.float32)).astype(np.int64) + zp[groups]
+    return np.clip(q, qmin, qmax).astype(np.int8), scale, zp
+
+
+def dequantize_affine(q, scales, zero_points=None, strategy="channel", axis=0, group_size=None):
+    """float32 (q - zero point) * scale -- affine.rs:151-161."""
+    groups, _ = assign_groups(q.shape, strategy, axis, group_size)
+    zp = np.zeros(len(scales), dtype=np.int32) if zero_points is None else np.asarray(zero_points, dtype=np.int32)
+    return ((q.astype(np.int32) - zp[groups]).astype(np.float32) * np.asarray(scales, dtype=np.float32)[groups])
+
+
+def pack_i4(values):
+    """pack4.rs:31-40: two consecutive elements (row-major, flattened) per byte, the first in the low nibble; an odd
+    count leaves the last high nibble zero."""
+    v = np.asarray(values, dtype=np.int8).ravel().astype(np.uint8) & 0x0F
+    if v.size % 2:
+        v = np.concatenate([v, np.zeros(1, dtype=np.uint8)])
+    return (v[0::2] | (v[1::2] << 4)).astype(np.uint8)
+
+
+def unpack_i4(packed, n):
+    """pack4.rs:43-64: n sign-extended nibbles."""
+    b = np.asarray(packed, dtype=np.uint8)
+    nib = np.stack([b & 0x0F, b >> 4], axis=1).ravel()[:n].astype(np.int16)
+    return np.where(nib >= 8, nib - 16, nib).astype(np.int8)

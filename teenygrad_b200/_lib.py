@@ -57,6 +57,7 @@ SIGNATURES = {
     "teeny_linear_w8a16_scratch_bytes": (sz, [i32, i32, i32]),
     "teeny_dequant_fp8_e4m3_bf16": (i32, [vp, i64, vp, i32, i32, vp, i64, i32, i32, vp]),
     "teeny_fp8_e4m3_count_nan": (i32, [vp, sz, vp, vp]),
+    "teeny_dequant_int_bf16": (i32, [vp, i32, vp, vp, i32, i32, vp, i64, i32, i32, vp]),
     "teeny_rope_table_bf16": (i32, [vp, vp, vp, i32, i32, vp]),
     "teeny_qk_norm_rope_kv_bf16": (i32, [vp, i64, vp, vp, vp, vp, vp, vp] + [i32] * 7 + [vp, f32, vp]),
     "teeny_embedding_bf16": (i32, [vp, vp, vp, i32, i32, i32, vp]),

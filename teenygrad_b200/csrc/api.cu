@@ -323,6 +323,10 @@ int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w
                                 teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t s) {
   return dequant_e4m3_bf16(static_cast<const uint8_t*>(w_fp8), ldw, w_scale, scale_kind, group_size, B(out), ldo, N, K, S(s));
 }
+int teeny_dequant_int_bf16(const void* q, int bits, const float* w_scale, const int* zero_point, int scale_kind,
+                           int group_size, teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t s) {
+  return dequant_int_bf16(q, bits, w_scale, zero_point, scale_kind, group_size, B(out), ldo, N, K, S(s));
+}
 int teeny_fp8_e4m3_count_nan(const void* bytes, size_t n, unsigned* count, teeny_stream_t s) {
   return e4m3_count_nan(static_cast<const uint8_t*>(bytes), n, count, S(s));
 }

@@ -65,6 +65,36 @@ dequant_e4m3_bf16_kernel(const uint8_t* __restrict__ wq, long long ldw, const fl
   }
 }
 
+// Integer schemes (utilities/teeny-quant/src/quant/affine.rs:151-161): value = (q - zero point) * scale, q an int8 or a
+// sign-extended nibble (two per byte over the flattened tensor, the first in the low nibble, pack4.rs:31-40).  One
+// thread per 8 consecutive k of a row.
+__global__ void __launch_bounds__(256)
+dequant_int_bf16_kernel(const uint8_t* __restrict__ q, int bits, const float* __restrict__ scale,
+                        const int* __restrict__ zero_point, int kind, int group, bf16* __restrict__ out, long long ldo,
+                        int N, int K) {
+  const int pieces = (K + 7) / 8;
+  const long long total = static_cast<long long>(N) * pieces;
+  const int groups_per_row = kind == 2 ? (K + group - 1) / group : 0;
+  for (long long p = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; p < total;
+       p += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int n = static_cast<int>(p / pieces), k0 = static_cast<int>(p % pieces) * 8;
+    for (int e = 0; e < 8 && k0 + e < K; ++e) {
+      const int k = k0 + e;
+      const long long i = static_cast<long long>(n) * K + k;
+      int v;
+      if (bits == 8) {
+        v = static_cast<int8_t>(q[i]);
+      } else {
+        const int nib = (q[i >> 1] >> ((i & 1) * 4)) & 0xf;
+        v = nib >= 8 ? nib - 16 : nib;
+      }
+      const size_t g = kind == 0 ? 0 : (kind == 1 ? static_cast<size_t>(n) : static_cast<size_t>(n) * groups_per_row + k / group);
+      const int zp = zero_point ? __ldg(zero_point + g) : 0;
+      out[n * ldo + k] = __float2bfloat16_rn(static_cast<float>(v - zp) * __ldg(scale + g));
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) e4m3_count_nan_kernel(const uint8_t* __restrict__ p, size_t n, unsigned* count) {
   unsigned found = 0;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -85,6 +115,17 @@ int dequant_e4m3_bf16(const uint8_t* wq, long long ldw, const float* scale, int 
   const long long want = (total + 255) / 256;
   const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
   return launch_kernel(dequant_e4m3_bf16_kernel, dim3(grid), dim3(256), 0, st, 1, wq, ldw, scale, kind, group, out, ldo, N, K);
+}
+
+int dequant_int_bf16(const void* q, int bits, const float* scale, const int* zero_point, int kind, int group, bf16* out,
+                     long long ldo, int N, int K, cudaStream_t st) {
+  if (!q || !scale || !out || N <= 0 || K <= 0 || (bits != 4 && bits != 8) || kind < 0 || kind > 2 || (kind == 2 && group <= 0))
+    return TEENY_ERR_BAD_ARG;
+  const long long total = static_cast<long long>(N) * ((K + 7) / 8);
+  const long long want = (total + 255) / 256;
+  const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+  return launch_kernel(dequant_int_bf16_kernel, dim3(grid), dim3(256), 0, st, 1, static_cast<const uint8_t*>(q), bits, scale,
+                       zero_point, kind, group, out, ldo, N, K);
 }
 
 int e4m3_count_nan(const uint8_t* p, size_t n, unsigned* count, cudaStream_t st) {

@@ -67,6 +67,11 @@ int gemm_w8a16_skinny(const bf16* x, int ldx, const uint8_t* wq, int ldw, const 
                       bool swiglu = false, const GemmPush* push = nullptr);
 int dequant_e4m3_bf16(const uint8_t* wq, long long ldw, const float* scale, int kind, int group, bf16* out, long long ldo,
                       int N, int K, cudaStream_t st);
+// out[N, K] = bf16((q - zero point) * scale) for the integer schemes: bits 8 (int8 [N, K]) or 4 (nibbles packed two per
+// byte over the flattened tensor, low nibble first); zero_point null for symmetric schemes; scale kinds as above (any
+// group size).
+int dequant_int_bf16(const void* q, int bits, const float* scale, const int* zero_point, int kind, int group, bf16* out,
+                     long long ldo, int N, int K, cudaStream_t st);
 // *count <- number of NaN encodings (0x7f, 0xff) among n bytes; the in-GEMM conversion does not reproduce them
 int e4m3_count_nan(const uint8_t* p, size_t n, unsigned* count, cudaStream_t st);
 size_t linear_w8a16_scratch_bytes(int M, int N, int K);

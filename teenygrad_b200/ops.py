@@ -259,6 +259,22 @@ def dequant_fp8(w_fp8, w_scale, strategy="channel", group_size=0, out=None):
     return out
 
 
+def dequant_int(q, bits, w_scale, zero_point, shape, strategy="channel", group_size=0, out=None):
+    """bf16((q - zero_point) * scale) of an integer-quantised matrix of logical ``shape`` [N, K]: ``q`` int8 [N, K]
+    (bits 8) or the packed uint8 vector of the 4-bit scheme (bits 4); ``zero_point`` int32 per group or None."""
+    N, K = shape
+    q = q.contiguous()
+    _req(q, name="q"); _req(w_scale, _F32, "w_scale")
+    if zero_point is not None:
+        _req(zero_point, torch.int32, "zero_point")
+    if q.numel() != (N * K if bits == 8 else (N * K + 1) // 2):
+        raise ValueError("quantised tensor does not have the size its logical shape implies")
+    out = torch.empty(N, K, dtype=_BF16, device=q.device) if out is None else out
+    check(lib.teeny_dequant_int_bf16(_ptr(q), bits, _ptr(w_scale), _ptr(zero_point), SCALE_KINDS[strategy], group_size,
+                                     _ptr(out), out.stride(0), N, K, _stream()), "dequant_int")
+    return out
+
+
 def fp8_count_nan(w_fp8):
     w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8").contiguous()
     count = torch.zeros(1, dtype=torch.int32, device=w.device)

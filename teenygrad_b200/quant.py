@@ -23,18 +23,40 @@ class Fp8Scheme:
     group_size: int = 0    # elements of k per scale ("group" only)
 
 
+@dataclass
+class IntScheme:
+    """An integer scheme of the quantiser ("int-quantized" = 8 bits as I8, "pack-quantized" = 4 bits, two per byte):
+    converted back to bf16 when loaded (teeny_dequant_int_bf16); there is no streaming integer GEMM."""
+    bits: int
+    symmetric: bool
+    strategy: str
+    group_size: int = 0
+    packed_shapes: dict = None   # name -> logical shape of a nibble-packed tensor (format.rs:86-96)
+
+
 def parse_quantization_config(metadata):
     """The scheme of a float-quantized checkpoint from its header metadata; raises ValueError for what the kernels do
     not take (integer schemes, E5M2, channel scales along the input axis, group sizes that are not multiples of 64)."""
     if QUANTIZATION_CONFIG_KEY not in metadata:
         raise ValueError("no quantization_config in the file's metadata")
     cfg = json.loads(metadata[QUANTIZATION_CONFIG_KEY])
-    if cfg.get("quant_method") != "compressed-tensors" or cfg.get("format") != "float-quantized":
+    if cfg.get("quant_method") != "compressed-tensors" or cfg.get("format") not in (
+            "float-quantized", "int-quantized", "pack-quantized"):
         raise ValueError(f"unsupported quantization format {cfg.get('quant_method')!r} / {cfg.get('format')!r}")
     groups = cfg.get("config_groups", {})
     if len(groups) != 1:
         raise ValueError("expected exactly one config group")
     w = next(iter(groups.values()))["weights"]
+    if cfg["format"] != "float-quantized":
+        bits = {"int-quantized": 8, "pack-quantized": 4}[cfg["format"]]
+        if w.get("type") != "int" or w.get("num_bits") != bits:
+            raise ValueError(f"{cfg['format']} expects {bits}-bit integer weights, got {w}")
+        strategy = w.get("strategy")
+        if strategy not in ("tensor", "channel", "group") or (strategy == "channel" and w.get("axis", 0) != 0) or (
+                strategy == "group" and (w.get("axis", 1) != 1 or int(w.get("group_size") or 0) <= 0)):
+            raise ValueError(f"unsupported integer granularity {w}")
+        shapes = {k: tuple(v["logical_shape"]) for k, v in cfg.get("teenygrad_packed_int4", {}).items()}
+        return IntScheme(bits, bool(w.get("symmetric", True)), strategy, int(w.get("group_size") or 0), shapes), cfg.get("ignore", [])
     if w.get("type") != "float" or w.get("num_bits") != 8 or w.get("fp8_variant", "e4m3") != "e4m3":
         raise ValueError(f"only FP8 E4M3 weights are supported, got {w}")
     strategy = w.get("strategy")
@@ -119,6 +141,29 @@ class Fp8Weight:
         if not self.group_size:
             return w * self.scale[:, None]
         return w * self.scale.repeat_interleave(self.group_size, dim=1)[:, :w.shape[1]]
+
+
+def dequantize_int_state_dict(tensors, scheme, device):
+    """bf16 state dict (on ``device``) of an integer-quantised checkpoint: every ``name`` that has a ``name_scale``
+    beside it is converted by the library's kernel, the rest is passed through as bf16."""
+    from . import ops
+    out = {}
+    for name in tensors:
+        if name.endswith("_scale") or name.endswith("_zero_point"):
+            continue
+        t = tensors[name]
+        if name + "_scale" not in tensors:
+            out[name] = t.to(device).to(torch.bfloat16)
+            continue
+        shape = scheme.packed_shapes.get(name) if scheme.bits == 4 else tuple(t.shape)
+        if shape is None or len(shape) < 2:
+            raise ValueError(f"{name}: no logical shape for a packed 4-bit tensor")
+        N, K = shape[0], int(torch.tensor(shape[1:]).prod())
+        zp = tensors.get(name + "_zero_point") if (name + "_zero_point") in tensors else None
+        w = ops.dequant_int(t.to(device), scheme.bits, tensors[name + "_scale"].to(device).float(),
+                            None if zp is None else zp.to(device).to(torch.int32), (N, K), scheme.strategy, scheme.group_size)
+        out[name] = w.view(*shape)
+    return out
 
 
 def quantize_fp8(w, strategy="channel", group_size=0):

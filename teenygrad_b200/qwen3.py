@@ -170,10 +170,13 @@ class Qwen3Runner:
                 self._set_fp8(layer, slot, t)
 
     def load_quantized(self, tensors, scheme, inv_freq=None):
-        """A float-quantized checkpoint: ``tensors`` maps HF names to tensors (``*.weight`` as FP8 bytes next to
-        ``*.weight_scale``, norms in a float type), ``scheme`` is quant.parse_quantization_config's.  Projections and the
-        LM head stay FP8; the embedding table is converted back to bf16 (on this device) for the lookup."""
+        """A checkpoint of the reference's quantiser: ``tensors`` maps HF names to tensors (``*.weight`` quantised next to
+        ``*.weight_scale``, norms in a float type), ``scheme`` is quant.parse_quantization_config's.  FP8: projections
+        and the LM head stay FP8, the embedding table is converted back to bf16 (on this device) for the lookup.
+        Integer schemes: everything is converted back to bf16 on this device."""
         from . import ops, quant
+        if isinstance(scheme, quant.IntScheme):  # integer schemes: back to bf16 here, then the ordinary path
+            return self.load_state_dict(quant.dequantize_int_state_dict(tensors, scheme, self.device), inv_freq)
 
         def get(name):
             return quant.Fp8Weight.from_tensors(tensors[name], tensors[name + "_scale"], scheme)

@@ -119,6 +119,20 @@ def test_linear_w8a16_swiglu(ops, M, I, K):
     assert rel(out, want) < BF16_TOL
 
 
+def _check_generation(got_logits, got_ids, want_logits, want_ids):
+    """Rows are comparable until their first token flip: logits within the bf16 bar up to there, and a flip must be a
+    near-tie in the oracle's own logits (the chosen token within the bar of the best one)."""
+    for i, g in enumerate(got_logits):
+        same = (got_ids[:, :i] == want_ids[:, :i]).all(dim=1)
+        if same.any():
+            assert rel(g[same.cuda()], want_logits[same, i]) < BF16_TOL
+        flipped = same & (got_ids[:, i] != want_ids[:, i])
+        for b in torch.nonzero(flipped).flatten().tolist():
+            row = want_logits[b, i].float()
+            assert row.max() - row[got_ids[b, i]] < BF16_TOL * row.abs().max()
+    assert (got_ids[:, 0] == want_ids[:, 0]).all()
+
+
 def _quantized_checkpoint(ocfg, seed, strategy, group_size):
     """A random Qwen3 state dict quantised as the reference's quantiser does it (oracle/quant.py, its encoder restated):
     (tensors as they go into the file, metadata, state dict of the dequantised float32 weights)."""
@@ -174,13 +188,69 @@ def test_runner_on_a_float_quantized_checkpoint(tmp_path, strategy, group_size, 
         got.append(r.logits().clone())
     assert qwen3.lib.teeny_device_error(1) == 0
     got_ids = r.history()[:steps].t().cpu().long()
-    for i, g in enumerate(got):
-        # rows are comparable until their first token flip; a flip must be a near-tie in the oracle's logits
-        same = (got_ids[:, :i] == want_ids[:, :i]).all(dim=1)
-        if same.any():
-            assert rel(g[same.cuda()], want_logits[same, i]) < BF16_TOL
-        flipped = same & (got_ids[:, i] != want_ids[:, i])
-        for b in torch.nonzero(flipped).flatten().tolist():
-            row = want_logits[b, i].float()
-            assert row.max() - row[got_ids[b, i]] < BF16_TOL * row.abs().max()
-    assert (got_ids[:, 0] == want_ids[:, 0]).all()
+    _check_generation(got, got_ids, want_logits, want_ids)
+
+
+@pytest.mark.parametrize("bits,symmetric,strategy,group_size", [(8, True, "channel", 0), (8, False, "tensor", 0),
+                                                                (4, True, "group", 32), (4, False, "channel", 0)])
+def test_dequant_int_equals_the_oracle(ops, bits, symmetric, strategy, group_size):
+    """Integer schemes (int8, nibble-packed int4; symmetric and with zero points): bit-equal to the oracle's
+    dequantisation rounded once to bf16.  Odd K puts rows on nibble boundaries inside a byte."""
+    from oracle import quant as oq
+    rng = np.random.default_rng(7)
+    N, K = 37, 75
+    w = (rng.standard_normal((N, K)) * 0.1 + 0.03).astype(np.float32)
+    kw = {"tensor": {}, "channel": {"axis": 0}, "group": {"axis": 1, "group_size": group_size}}[strategy]
+    q, s, zp = oq.quantize_affine(w, bits, symmetric, strategy, **kw)
+    want = torch.from_numpy(oq.dequantize_affine(q, s, zp, strategy, **kw)).bfloat16()
+    stored = torch.from_numpy(q) if bits == 8 else torch.from_numpy(oq.pack_i4(q))
+    got = ops.dequant_int(stored.cuda(), bits, torch.from_numpy(s).cuda(), None if symmetric else torch.from_numpy(zp).cuda(),
+                          (N, K), strategy, group_size)
+    assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+
+
+def test_runner_on_a_pack_quantized_int4_checkpoint(tmp_path):
+    """4-bit checkpoint in the quantiser's layout (packed U8 vectors, logical shapes in the metadata) -> reader ->
+    runner (weights converted to bf16 at load) against the CPU oracle on the same dequantised bf16 weights."""
+    import json
+
+    from oracle import quant as oq
+    from oracle import qwen3 as oqw
+    from teenygrad_b200 import qwen3, quant
+    from teenygrad_b200 import safetensors as st
+    ocfg = oqw.OracleQwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False)
+    sd = oqw.make_weights(ocfg, 21)
+    tensors, deq, shapes, ignore = {}, {}, {}, []
+    for name, t in sd.items():
+        if t.dim() >= 2:
+            q, s, zp = oq.quantize_affine(t.float().numpy(), 4, False, "group", axis=1, group_size=64)
+            tensors[name] = torch.from_numpy(oq.pack_i4(q))
+            tensors[name + "_scale"] = torch.from_numpy(s)
+            tensors[name + "_zero_point"] = torch.from_numpy(zp)
+            shapes[name] = {"logical_shape": list(t.shape), "elements": t.numel()}
+            deq[name] = torch.from_numpy(oq.dequantize_affine(q, s, zp, "group", axis=1, group_size=64)).bfloat16()
+        else:
+            tensors[name] = t
+            deq[name] = t
+            ignore.append(name)
+    weights = dict(num_bits=4, type="int", symmetric=False, strategy="group", axis=1, group_size=64)
+    meta = {"quantization_config": json.dumps({
+        "quant_method": "compressed-tensors", "format": "pack-quantized",
+        "config_groups": {"group_0": {"weights": weights, "targets": ["*"]}}, "ignore": ignore,
+        "teenygrad_packed_int4": shapes})}
+    st.save_file(tensors, tmp_path / "model.safetensors", metadata=meta)
+    ck = st.SafeTensors(tmp_path / "model.safetensors")
+    scheme, _ = quant.parse_quantization_config(ck.metadata)
+    assert isinstance(scheme, quant.IntScheme) and scheme.bits == 4 and not scheme.symmetric
+    B, S, steps = 2, 24, 8
+    ids = torch.randint(0, ocfg.vocab, (B, S), generator=torch.Generator().manual_seed(22))
+    want_ids, want_logits = oqw.OracleQwen3(ocfg, deq).generate(ids, steps, return_logits=True)
+    r = qwen3.Qwen3Runner(qwen3.Qwen3Config(2, 256, 4, 2, 128, 512, 1024, tied=False), max_batch=B, max_len=S + steps,
+                          max_new_tokens=steps)
+    r.load_quantized({k: ck[k] for k in ck}, scheme)
+    r.prefill(ids)
+    got = [r.logits().clone()]
+    for _ in range(steps - 1):
+        r.decode_step(graph=True)
+        got.append(r.logits().clone())
+    _check_generation(got, r.history()[:steps].t().cpu().long(), want_logits, want_ids)

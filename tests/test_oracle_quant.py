@@ -96,3 +96,33 @@ def test_quantize_dequantize_error_bound_and_linear_contract():
         x = torch.randn(8, 256, generator=torch.Generator().manual_seed(2)).bfloat16().float().numpy()
         y = oq.linear_w8a16(x, q, s, strategy, **kw)
         assert np.allclose(y, x.astype(np.float64) @ back.astype(np.float64).T, rtol=1e-6, atol=1e-6)
+
+
+# ---- integer schemes: the known answers of affine.rs:163-288 and pack4.rs:66-93 ----
+def test_pack4_known_answers():
+    values = np.arange(-8, 8, dtype=np.int8)
+    packed = oq.pack_i4(values)
+    assert packed.size == 8 and np.array_equal(oq.unpack_i4(packed, 16), values)     # pack4.rs:70-77
+    odd = np.array([-8, 7, -1], dtype=np.int8)
+    p = oq.pack_i4(odd)
+    assert p.size == 2 and p.tolist() == [0x78, 0x0F] and np.array_equal(oq.unpack_i4(p, 3), odd)  # pack4.rs:80-86
+    assert oq.pack_i4(np.array([], dtype=np.int8)).size == 0 and oq.unpack_i4(np.array([], dtype=np.uint8), 0).size == 0
+
+
+def test_affine_ranges_and_round_trips():
+    assert oq.qrange(8, True) == (-127, 127) and oq.qrange(8, False) == (-128, 127)  # affine.rs:46-51
+    assert oq.qrange(4, True) == (-7, 7) and oq.qrange(4, False) == (-8, 7)
+    data = np.array([-1.0, -0.5, 0.0, 0.5, 1.0], dtype=np.float32)
+    q, s, zp = oq.quantize_affine(data, 8, True, "tensor")
+    assert zp.tolist() == [0] and np.isclose(s[0], 1.0 / 127) and q.tolist() == [-127, -64, 0, 64, 127]  # halves away from zero
+    assert np.abs(oq.dequantize_affine(q, s, zp, "tensor") - data).max() < 0.01
+    pos = np.array([0.0, 1.0, 2.0, 3.0], dtype=np.float32)          # all-positive: asymmetric uses the whole range
+    q, s, zp = oq.quantize_affine(pos, 8, False, "tensor")
+    assert q.min() == -128 and q.max() == 127 and zp.tolist() == [-128] and np.isclose(s[0], 3.0 / 255)
+    rows = np.array([[0.01, -0.01], [100.0, -100.0]], dtype=np.float32)
+    q, s, zp = oq.quantize_affine(rows, 8, True, "channel", axis=0)
+    assert np.allclose(s, [0.01 / 127, 100.0 / 127]) and np.abs(q).min() == 127
+    q, _, _ = oq.quantize_affine(np.array([-10.0, 10.0], dtype=np.float32), 4, True, "tensor")
+    assert q.tolist() == [-7, 7]                                      # affine.rs:280-287: clamped to the 4-bit range
+    z, s, _ = oq.quantize_affine(np.zeros(4, dtype=np.float32), 8, True, "tensor")
+    assert s.tolist() == [1.0] and not z.any()

@@ -94,3 +94,24 @@ def test_torch_encoder_equals_the_reference_encoder_on_normal_values():
     ours = quant.quantize_fp8(w, "channel")
     q, s = oq.quantize_fp8(w.numpy(), "channel", axis=0)
     assert np.array_equal(ours.scale.numpy(), s) and np.array_equal(ours.q.numpy(), q)
+
+
+def test_parse_quantization_config_integer_formats():
+    meta = {"quantization_config": json.dumps({
+        "quant_method": "compressed-tensors", "format": "pack-quantized",
+        "config_groups": {"group_0": {"weights": dict(num_bits=4, type="int", symmetric=False, strategy="group", axis=1,
+                                                      group_size=64), "targets": ["*"]}},
+        "teenygrad_packed_int4": {"a.weight": {"logical_shape": [4, 8], "elements": 32}}})}
+    s, _ = quant.parse_quantization_config(meta)
+    assert isinstance(s, quant.IntScheme) and (s.bits, s.symmetric, s.strategy, s.group_size) == (4, False, "group", 64)
+    assert s.packed_shapes == {"a.weight": (4, 8)}
+    meta8 = {"quantization_config": json.dumps({
+        "quant_method": "compressed-tensors", "format": "int-quantized",
+        "config_groups": {"group_0": {"weights": dict(num_bits=8, type="int", symmetric=True, strategy="channel", axis=0),
+                                      "targets": ["*"]}}})}
+    s, _ = quant.parse_quantization_config(meta8)
+    assert (s.bits, s.symmetric, s.strategy) == (8, True, "channel")
+    bad = json.loads(meta8["quantization_config"])
+    bad["config_groups"]["group_0"]["weights"]["num_bits"] = 4  # int-quantized is the 8-bit format
+    with pytest.raises(ValueError):
+        quant.parse_quantization_config({"quantization_config": json.dumps(bad)})
