@@ -64,6 +64,9 @@ def parse_args():
     p.add_argument("--batch", type=int, default=None)
     p.add_argument("--prefill", type=int, default=None)
     p.add_argument("--new-tokens", type=int, default=None)
+    p.add_argument("--weights", default="bf16", choices=["bf16", "fp8"],
+                   help="config 4/5 only: fp8 = projections and LM head as FP8 E4M3 with per-channel scales (weight-only; "
+                        "the arithmetic stays bf16 x bf16 -> f32).  A variant beside the headline, not the headline.")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-verify", action="store_true", help="skip the CPU-oracle check of sequence 0 after the timing")
     return p.parse_args()
@@ -516,7 +519,8 @@ def generation_config(args):
     cfg = qwen3.Qwen3Config(**cfg_kwargs)
     runner = qwen3.Qwen3Runner(cfg, max_batch=B, max_len=S + NEW, max_tokens=B * S, max_new_tokens=NEW,
                                tp_rank=rank, tp_size=world, comm=comm)
-    qwen3.load_random_weights(runner, seed=seed)
+    fp8 = args.weights == "fp8"
+    qwen3.load_random_weights(runner, seed=seed, fp8=fp8)
     tp_mode = "none" if world == 1 else ("peer-push" if lib.teeny_tp_peer_enabled(comm) else "nccl-allreduce")
     g = torch.Generator().manual_seed(seed)
     prompts_host = torch.randint(0, cfg.vocab, (B, S), generator=g, dtype=torch.int32).pin_memory()
@@ -618,13 +622,22 @@ def generation_config(args):
             torch.set_num_threads(host_threads())
             t0 = time.perf_counter()
             sd = {name: t.cpu() for name, t in qwen3.random_weights_device(cfg, seed, dev)}
-            oracle = oq.OracleQwen3(oq.OracleQwen3Config(**cfg_kwargs), sd)
+            if fp8:  # the oracle sees the dequantised weights (f32) and multiplies bf16 activations with them in f32
+                from teenygrad_b200 import quant
+                for name in list(sd):
+                    if sd[name].dim() >= 2 and name != "model.embed_tokens.weight":
+                        sd[name] = quant.quantize_fp8(sd[name]).dequantize()
+            oracle = oq.OracleQwen3(oq.OracleQwen3Config(**cfg_kwargs), sd, f32_twin=fp8)
             want = oracle.forward(prompts_host[:1].long())[0].float()
             # The 2e-2 bar is a per-kernel bar (the GPU tests hold every kernel and one whole layer to it).  Through a
             # deep stack two correct bf16 evaluations drift apart: the oracle's own f32-accumulating twin (same graph,
             # same rounding points, another summation order) measures by how much at this depth, and the GPU must be
             # as close to the oracle as that twin is (x 1.5), or within 2e-2.
-            twin = oq.OracleQwen3(oq.OracleQwen3Config(**cfg_kwargs), sd, f32_twin=True).forward(prompts_host[:1].long())[0].float()
+            if fp8:
+                # here the oracle itself is the f32-accumulating evaluation (bf16 activations x f32 weights); its twin is
+                # the plain bf16 evaluation on the same weights rounded to bf16, which is what a large prefill computes
+                sd = {k: v.to(torch.bfloat16) for k, v in sd.items()}
+            twin = oq.OracleQwen3(oq.OracleQwen3Config(**cfg_kwargs), sd, f32_twin=not fp8).forward(prompts_host[:1].long())[0].float()
             got = row.float().cpu()
             scale = float(want.abs().max())
             rel = float((got - want).abs().max()) / scale
@@ -656,13 +669,15 @@ def generation_config(args):
     head_params = cfg.vocab * H
     prefill_flop = (2.0 * L * layer_params * T + 2.0 * head_params * B + L * 2.0 * B * cfg.num_q_heads * S * S * D) / world
     mean_len = S + (NEW - 1) / 2.0 + 0.5
-    decode_bytes = (2.0 * (L * layer_params + head_params) + L * 2.0 * B * cfg.num_kv_heads * D * 2.0 * mean_len) / world
+    wbytes = 1.0 if fp8 else 2.0  # bytes per matmul parameter as it is streamed in decode
+    decode_bytes = (wbytes * (L * layer_params + head_params) + L * 2.0 * B * cfg.num_kv_heads * D * 2.0 * mean_len) / world
     metric, unit = METRIC[args.config]
     line = {
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": args.warmup,
         "warmup_run": warm, "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {**workload_config(args, world), "tp_decode_reduction": tp_mode, "tp_prefill_reduction":
+        "config": {**workload_config(args, world), "weights": "fp8-e4m3, per-channel scales, weight-only" if fp8 else "bf16",
+                   "tp_decode_reduction": tp_mode, "tp_prefill_reduction":
                    "none" if world == 1 else ("nccl-allreduce, overlapped with the other half-batch's compute"
                                               if prefill_overlap else "nccl-allreduce")},
         "phases": {"prefill_ms": prefill_ms / steps, "decode_ms": decode_ms / steps,

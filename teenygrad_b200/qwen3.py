@@ -139,7 +139,10 @@ class Qwen3Runner:
     def load_head_shards(self, shards, inv_freq=None):
         self._set(0, W_EMBED, shards["embed"].to(_BF16))
         self._set(0, W_FINAL_NORM, shards["final_norm"].to(_BF16))
-        self._set(0, W_LM_HEAD, shards["lm_head"].to(_BF16))
+        if isinstance(shards["lm_head"], torch.Tensor):
+            self._set(0, W_LM_HEAD, shards["lm_head"].to(_BF16))
+        else:  # a quant.Fp8Weight
+            self._set_fp8(0, W_LM_HEAD, shards["lm_head"])
         inv = default_inv_freq(self.cfg) if inv_freq is None else inv_freq
         self._set(0, W_INV_FREQ, inv.to(torch.float32))
 
@@ -304,8 +307,11 @@ def random_weights_device(cfg, seed, device, std=0.02):
         yield "lm_head.weight", nrm(2, cfg.vocab, H)
 
 
-def load_random_weights(runner, seed):
-    """Fill a runner with ``random_weights_device`` tensors, sharding layer by layer (peak extra memory = one layer)."""
+def load_random_weights(runner, seed, fp8=False):
+    """Fill a runner with ``random_weights_device`` tensors, sharding layer by layer (peak extra memory = one layer).
+    fp8: the projections and the LM head go in as FP8 E4M3 with one scale per output channel (quant.quantize_fp8 of the
+    same random tensors), everything else as bf16."""
+    from . import quant
     cfg, dev = runner.cfg, runner.device
     pending, head = {}, {}
     for name, t in random_weights_device(cfg, seed, dev):
@@ -313,9 +319,22 @@ def load_random_weights(runner, seed):
             layer = int(name.split(".")[2])
             pending[name] = t
             if len(pending) == 11:
-                runner.load_layer_shards(layer, tpmod.shard_layer(pending, cfg, layer, runner.tp_rank, runner.tp_size))
+                if fp8:
+                    shards = quant.shard_layer_fp8(lambda n: quant.quantize_fp8(pending[n]), cfg, layer, runner.tp_rank,
+                                                   runner.tp_size)
+                    p = f"model.layers.{layer}."
+                    shards.update({"input_ln": pending[p + "input_layernorm.weight"],
+                                   "post_ln": pending[p + "post_attention_layernorm.weight"],
+                                   "q_norm": pending[p + "self_attn.q_norm.weight"],
+                                   "k_norm": pending[p + "self_attn.k_norm.weight"]})
+                    runner.load_layer_shards_fp8(layer, shards)
+                else:
+                    runner.load_layer_shards(layer, tpmod.shard_layer(pending, cfg, layer, runner.tp_rank, runner.tp_size))
                 pending = {}
         else:
             head[name] = t
-    runner.load_head_shards(tpmod.shard_head(head, cfg, runner.tp_rank, runner.tp_size))
+    shards = tpmod.shard_head(head, cfg, runner.tp_rank, runner.tp_size)
+    if fp8:
+        shards["lm_head"] = quant.quantize_fp8(shards["lm_head"])
+    runner.load_head_shards(shards)
 
