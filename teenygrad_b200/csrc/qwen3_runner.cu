@@ -178,10 +178,10 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
   const size_t total_bytes = c->bcast_off + bcast_bytes;
   {
     // One hop (every rank gets every partial) costs world x the tensor per rank.  Measured per decode step: 2 ranks
-    // 3.25 ms in one hop against 3.53 ms in two; 8 ranks 3.51 ms against 3.25 ms.  4 ranks: one hop measured (2.96 ms),
-    // two hops not yet, so the switch sits at 8.  TEENY_TP_HOPS=1|2 overrides.
+    // 3.25 ms in one hop against 3.53 ms in two; 4 ranks 2.94 ms against 2.89 ms; 8 ranks 3.51 ms against 3.25 ms.  So two
+    // hops from 4 ranks on.  TEENY_TP_HOPS=1|2 overrides.
     const char* e = getenv("TEENY_TP_HOPS");
-    c->two_hop = e ? (e[0] == '2') : (c->world >= 8);
+    c->two_hop = e ? (e[0] == '2') : (c->world >= 4);
   }
   cudaIpcMemHandle_t mine;
   std::memset(&mine, 0, sizeof(mine));

@@ -93,6 +93,23 @@ def time_skinny():
         print(f"linear bf16 {M}x{N}x{K}: {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s | cuBLAS {t2 * 1e3:.1f} us {by / t2 / 1e6:.0f} GB/s", flush=True)
 
 
+def time_w8():
+    """The decode GEMM shapes with bf16 weights and with FP8 (E4M3, per-channel scales) weights."""
+    from . import quant
+    for (M, N, K, swiglu) in [(32, 6144, 4096, False), (32, 4096, 4096, False), (32, 24576, 4096, True), (32, 4096, 12288, False),
+                              (32, 151936, 4096, False), (1, 4096, 4096, False), (128, 4096, 4096, False)]:
+        n = max(2, int(300e6 // (N * K)) + 1)
+        ws = [_rand(N, K) for _ in range(n)]
+        qs = [quant.quantize_fp8(w) for w in ws]
+        x = _rand(M, K)
+        y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device="cuda")
+        f16 = [(lambda w=w: (ops.linear_swiglu if swiglu else ops.linear_forward)(x, w, out=y)) for w in ws]
+        f8 = [(lambda q=q: ops.linear_w8a16(x, q.q, q.scale, "channel", out=y, swiglu=swiglu)) for q in qs]
+        t16, t8 = _graph_time(f16), _graph_time(f8)
+        print(f"linear {M}x{N}x{K}{' + SwiGLU' if swiglu else ''}: bf16 weights {t16 * 1e3:.1f} us ({N * K * 2 / t16 / 1e6:.0f} GB/s)"
+              f" | FP8 weights {t8 * 1e3:.1f} us ({N * K / t8 / 1e6:.0f} GB/s)", flush=True)
+
+
 def time_prefill():
     for (B, S) in [(4, 4096), (32, 2048)]:
         q = torch.randn(B, HQ, S, D, device="cuda").bfloat16()
@@ -158,6 +175,14 @@ def case(which):
         y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
         for w in ws:
             ops.linear_forward(x, w, out=y)
+    elif which == "w8":  # the gate/up projection of the decode step with FP8 weights
+        from . import quant
+        M, N, K = 32, 24576, 4096
+        x = _rand(M, K)
+        qs = [quant.quantize_fp8(_rand(N, K)) for _ in range(3)]
+        y = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+        for q in qs:
+            ops.linear_w8a16(x, q.q, q.scale, "channel", out=y, swiglu=True)
     elif which == "prefill":
         B, S = 4, 4096
         q = torch.randn(B, HQ, S, D, device="cuda").bfloat16()
@@ -337,7 +362,7 @@ def main(argv):
         what = argv[1:] or ["gemm", "skinny", "prefill", "decode", "elementwise", "sampling"]
         for name in what:
             {"gemm": time_gemm, "skinny": time_skinny, "prefill": time_prefill, "decode": time_decode,
-             "elementwise": time_elementwise, "sampling": time_sampling}[name]()
+             "elementwise": time_elementwise, "sampling": time_sampling, "w8": time_w8}[name]()
     elif mode == "case":
         case(argv[1])
     elif mode == "probe":
