@@ -193,6 +193,20 @@ int teeny_linear_w8a16_forward(const teeny_bf16* x, long long ldx, const void* w
                                int N, int K, int swiglu, void* global_scratch, size_t global_scratch_bytes,
                                teeny_stream_t stream);
 size_t teeny_linear_w8a16_scratch_bytes(int M, int N, int K);
+/* The same product with the ACTIVATIONS in FP8 too, for the projections whose input a norm kernel writes anyway: every
+ * bf16 activation is split into two E4M3 terms, x * s = hi + lo with s the power of two that brings the row's largest
+ * magnitude into [128, 256).  A bf16 value has 8 significant bits and an E4M3 number 4, so the split is exact while both
+ * terms are normal numbers: for every element within 2^10 of its row's maximum (lo is stored times 16); smaller
+ * elements keep fewer bits (4 down to 2^-13 of the maximum, none below 2^-17).  teeny_split_fp8_e4m3 writes
+ * out[2 * M, K] bytes (the hi rows, then the lo rows; row stride ldo bytes, a multiple of 16) and x_scale[M] = 1 / s;
+ * teeny_linear_w8a8x2_forward multiplies them with FP8 weights as they are (tcgen05.mma kind::f8f6f4, no conversion
+ * inside the kernel): Y[m, n] = x_scale[m] * w_scale[n] * sum_k w[n, k] * (hi[m, k] + lo[m, k] / 16), M <= 128,
+ * scale_kind 0 or 1.  Where the split is exact this is teeny_linear_w8a16_forward's result. */
+int teeny_split_fp8_e4m3(const teeny_bf16* x, long long ldx, void* out, long long ldo, float* x_scale, int M, int K,
+                         teeny_stream_t stream);
+int teeny_linear_w8a8x2_forward(const void* x_fp8, long long ldx, const float* x_scale, const void* w_fp8, long long ldw,
+                                const float* w_scale, int scale_kind, const teeny_bf16* bias, teeny_bf16* y, long long ldy,
+                                int M, int N, int K, int swiglu, teeny_stream_t stream);
 /* out[N, K] (bf16, row stride ldo elements) = bf16(f8_to_f32(w_fp8) * scale): dequantize_fp8 of
  * utilities/teeny-quant/src/quant/fp8.rs:262-268 with one rounding to bf16, every byte value handled (NaN included). */
 int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w_scale, int scale_kind, int group_size,

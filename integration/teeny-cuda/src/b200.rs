@@ -135,6 +135,8 @@ extern "C" {
     pub fn teeny_linear_swiglu_bf16(x: *const u16, ldx: c_longlong, w: *const u16, ldw: c_longlong, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, stream: CUstream) -> c_int;
     pub fn teeny_linear_w8a16_forward(x: *const u16, ldx: c_longlong, w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, bias: *const u16, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, swiglu: c_int, global_scratch: *mut c_void, global_scratch_bytes: usize, stream: CUstream) -> c_int;
     pub fn teeny_linear_w8a16_scratch_bytes(m: c_int, n: c_int, k: c_int) -> usize;
+    pub fn teeny_split_fp8_e4m3(x: *const u16, ldx: c_longlong, out: *mut c_void, ldo: c_longlong, x_scale: *mut f32, m: c_int, k: c_int, stream: CUstream) -> c_int;
+    pub fn teeny_linear_w8a8x2_forward(x_fp8: *const c_void, ldx: c_longlong, x_scale: *const f32, w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, bias: *const u16, y: *mut u16, ldy: c_longlong, m: c_int, n: c_int, k: c_int, swiglu: c_int, stream: CUstream) -> c_int;
     pub fn teeny_dequant_fp8_e4m3_bf16(w_fp8: *const c_void, ldw: c_longlong, w_scale: *const f32, scale_kind: c_int, group_size: c_int, out: *mut u16, ldo: c_longlong, n: c_int, k: c_int, stream: CUstream) -> c_int;
     pub fn teeny_dequant_int_bf16(q: *const c_void, bits: c_int, w_scale: *const f32, zero_point: *const c_int, scale_kind: c_int, group_size: c_int, out: *mut u16, ldo: c_longlong, n: c_int, k: c_int, stream: CUstream) -> c_int;
     pub fn teeny_fp8_e4m3_count_nan(bytes: *const c_void, n: usize, count: *mut c_uint, stream: CUstream) -> c_int;

@@ -182,3 +182,29 @@ def unpack_i4(packed, n):
     b = np.asarray(packed, dtype=np.uint8)
     nib = np.stack([b & 0x0F, b >> 4], axis=1).ravel()[:n].astype(np.int16)
     return np.where(nib >= 8, nib - 16, nib).astype(np.int8)
+
+
+# ---- two-term FP8 activations (the F8 variant of the weight-only GEMM; not part of the reference) ----
+def split_e4m3(x_bf16_as_f32):
+    """(hi, lo16, inv_s): per row s = 2^(7 - floor(log2 max|x|)) (1 for an all-zero row), hi = e4m3(x s), lo16 =
+    e4m3((x s - hi) 16), both round to nearest even with subnormals kept (PyTorch's float8_e4m3fn cast, which
+    tests/test_oracle_quant.py holds f8_to_f32 to for all 256 bytes); the value represented is (hi + lo16 / 16) inv_s."""
+    import torch
+    x = torch.as_tensor(np.asarray(x_bf16_as_f32, dtype=np.float32))
+    amax = x.abs().amax(dim=1)
+    e = torch.floor(torch.log2(torch.where(amax > 0, amax, torch.ones_like(amax))))
+    p = torch.where(amax > 0, (7 - e).clamp(-100, 100), torch.zeros_like(e))
+    s = torch.pow(torch.tensor(2.0, dtype=torch.float64), p.double()).float()[:, None]
+    xs = x * s
+    hi = xs.to(torch.float8_e4m3fn)
+    lo = ((xs - hi.float()) * 16.0).to(torch.float8_e4m3fn)
+    return hi.view(torch.uint8).numpy(), lo.view(torch.uint8).numpy(), (1.0 / s[:, 0]).numpy()
+
+
+def linear_w8a8x2(hi, lo16, inv_s, q, scales, strategy="channel", axis=0, bias=None):
+    """y = inv_s * ((hi + lo16 / 16) @ dequantize(q)^T) (+ bias) in float64; the caller rounds to bf16."""
+    x = (f8_to_f32(hi).astype(np.float64) + f8_to_f32(lo16).astype(np.float64) / 16.0) * np.asarray(inv_s, dtype=np.float64)[:, None]
+    y = x @ dequantize_fp8(q, scales, strategy, axis).astype(np.float64).T
+    if bias is not None:
+        y = y + np.asarray(bias, dtype=np.float64)
+    return y.astype(np.float32)

@@ -55,6 +55,8 @@ SIGNATURES = {
     "teeny_linear_swiglu_bf16": (i32, [vp, i64, vp, i64, vp, i64, i32, i32, i32, vp]),
     "teeny_linear_w8a16_forward": (i32, [vp, i64, vp, i64, vp, i32, i32, vp, vp, i64, i32, i32, i32, i32, vp, sz, vp]),
     "teeny_linear_w8a16_scratch_bytes": (sz, [i32, i32, i32]),
+    "teeny_split_fp8_e4m3": (i32, [vp, i64, vp, i64, vp, i32, i32, vp]),
+    "teeny_linear_w8a8x2_forward": (i32, [vp, i64, vp, vp, i64, vp, i32, vp, vp, i64, i32, i32, i32, i32, vp]),
     "teeny_dequant_fp8_e4m3_bf16": (i32, [vp, i64, vp, i32, i32, vp, i64, i32, i32, vp]),
     "teeny_fp8_e4m3_count_nan": (i32, [vp, sz, vp, vp]),
     "teeny_dequant_int_bf16": (i32, [vp, i32, vp, vp, i32, i32, vp, i64, i32, i32, vp]),

@@ -318,6 +318,18 @@ int teeny_linear_w8a16_forward(const teeny_bf16* x, long long ldx, const void* w
                       scale_kind, group_size, B(bias), B(y), static_cast<int>(ldy), M, N, K, global_scratch,
                       global_scratch_bytes, S(s), swiglu != 0);
 }
+int teeny_split_fp8_e4m3(const teeny_bf16* x, long long ldx, void* out, long long ldo, float* x_scale, int M, int K,
+                         teeny_stream_t s) {
+  return split_e4m3(B(x), ldx, static_cast<uint8_t*>(out), ldo, x_scale, M, K, S(s));
+}
+int teeny_linear_w8a8x2_forward(const void* x_fp8, long long ldx, const float* x_scale, const void* w_fp8, long long ldw,
+                                const float* w_scale, int scale_kind, const teeny_bf16* bias, teeny_bf16* y, long long ldy,
+                                int M, int N, int K, int swiglu, teeny_stream_t s) {
+  if (ldx > 0x7fffffffLL || ldw > 0x7fffffffLL || ldy > 0x7fffffffLL || ldx < K || ldw < K) return TEENY_ERR_BAD_ARG;
+  return gemm_w8a8x2_skinny(static_cast<const uint8_t*>(x_fp8), static_cast<int>(ldx), x_scale,
+                            static_cast<const uint8_t*>(w_fp8), static_cast<int>(ldw), w_scale, scale_kind, B(bias), B(y),
+                            static_cast<int>(ldy), M, N, K, S(s), swiglu != 0);
+}
 size_t teeny_linear_w8a16_scratch_bytes(int M, int N, int K) { return linear_w8a16_scratch_bytes(M, N, K); }
 int teeny_dequant_fp8_e4m3_bf16(const void* w_fp8, long long ldw, const float* w_scale, int scale_kind, int group_size,
                                 teeny_bf16* out, long long ldo, int N, int K, teeny_stream_t s) {

@@ -4,6 +4,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -379,6 +380,32 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_m
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a_mn_major) << 15) |
          (static_cast<uint32_t>(b_mn_major) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// The same descriptor for kind::f8f6f4 with both operands E4M3 (format code 0), K-major, f32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------------------------------------
+// two-term FP8 activations (see split_e4m3_kernel, gemm_w8a16.cu)
+// ------------------------------------------------------------------------------------------------
+// Exponent p of the row scale s = 2^p that brings a row maximum `amax` into [128, 256) (0 for a zero / non-finite row;
+// clamped so that s and 1 / s are normal f32 numbers).
+__device__ __forceinline__ int split_scale_exponent(float amax) {
+  if (!(amax > 0.0f) || !(amax < INFINITY)) return 0;
+  int e;
+  frexpf(amax, &e);  // amax = f * 2^e, f in [0.5, 1): floor(log2 amax) = e - 1
+  return min(100, max(-100, 8 - e));
+}
+// a, b (already multiplied by the row scale) -> hi = e4m3(x), lo = e4m3((x - hi) * 16), two elements per 16-bit result
+// (a in the low byte), round to nearest even, saturating
+__device__ __forceinline__ void split_e4m3_pair(float a, float b, unsigned short& hi, unsigned short& lo) {
+  const __nv_fp8x2_storage_t h = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(h, __NV_E4M3);
+  const float2 hf = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+  lo = __nv_cvt_float2_to_fp8x2(make_float2((a - hf.x) * 16.0f, (b - hf.y) * 16.0f), __NV_SATFINITE, __NV_E4M3);
+  hi = h;
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -30,6 +30,19 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+__device__ __forceinline__ float block_max(float v, float* red) {  // of non-negative values
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+  __syncthreads();
+  return t;
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x * (1.0f / (1.0f + expf(-x))); }
 
 struct OpSilu { __device__ float operator()(float a, float) const { return silu_f(a); } };
@@ -123,10 +136,14 @@ __global__ void rms_norm_f32_kernel(const float* __restrict__ x, float* __restri
 
 // ---- RMSNorm, bf16, Qwen3 rounding.  One CTA per row; the row stays in registers between the two phases. ----
 // VPT = 16-byte vectors per thread (N <= VPT * 8 * blockDim).  ADD: x is added into `res` first (bf16 add).
+// y8 != null: the normed row is ALSO written as two-term FP8 (hi bytes to row `row` of y8, lo bytes to row gridDim.x +
+// row; row stride ld8 bytes; y8_scale[row] = 1 / s), what split_e4m3_kernel would make of y, for the GEMM variant that
+// takes its activations that way.
 template <int VPT, bool ADD>
 __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ res,
                                      long long ldr, bf16* __restrict__ y, long long ldy, const bf16* __restrict__ w,
-                                     float* __restrict__ rrms, int N, float eps) {
+                                     float* __restrict__ rrms, int N, float eps, uint8_t* __restrict__ y8 = nullptr,
+                                     long long ld8 = 0, float* __restrict__ y8_scale = nullptr) {
   // the norm weights are written by no kernel: fetch them while the producer of x is still running, and let the
   // consumer of y become resident (and fetch its own weights) as soon as this kernel's input is complete
   const int nv = N >> 3;
@@ -186,6 +203,7 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
   if (threadIdx.x == 0 && rrms) rrms[row] = rr;
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * ldy);
+  float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int idx = threadIdx.x + i * blockDim.x;
@@ -197,8 +215,31 @@ __global__ void rms_norm_bf16_kernel(const bf16* __restrict__ x, long long ldx, 
         const float lo = bf16_round(v[i][2 * e] * rr) * bf16_lo(gw[e]);
         const float hi = bf16_round(v[i][2 * e + 1] * rr) * bf16_hi(gw[e]);
         ow[e] = pack_bf16x2(lo, hi);
+        // the bf16 values just stored, for the FP8 copy below
+        v[i][2 * e] = bf16_lo(ow[e]);
+        v[i][2 * e + 1] = bf16_hi(ow[e]);
+        amax = fmaxf(amax, fmaxf(fabsf(v[i][2 * e]), fabsf(v[i][2 * e + 1])));
       }
       yr[idx] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+  if (y8) {
+    amax = block_max(amax, red);
+    const int p = split_scale_exponent(amax);
+    const float s = ldexpf(1.0f, p);
+    if (threadIdx.x == 0) y8_scale[row] = ldexpf(1.0f, -p);
+    uint2* hr = reinterpret_cast<uint2*>(y8 + static_cast<size_t>(row) * ld8);
+    uint2* lr = reinterpret_cast<uint2*>(y8 + (static_cast<size_t>(gridDim.x) + row) * ld8);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * blockDim.x;
+      if (idx < nv) {
+        unsigned short h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) split_e4m3_pair(v[i][2 * e] * s, v[i][2 * e + 1] * s, h[e], l[e]);
+        hr[idx] = make_uint2(h[0] | (static_cast<uint32_t>(h[1]) << 16), h[2] | (static_cast<uint32_t>(h[3]) << 16));
+        lr[idx] = make_uint2(l[0] | (static_cast<uint32_t>(l[1]) << 16), l[2] | (static_cast<uint32_t>(l[3]) << 16));
+      }
     }
   }
   TRACE_END();
@@ -235,8 +276,9 @@ __global__ void rms_norm_bf16_scalar_kernel(const bf16* __restrict__ x, long lon
 
 template <bool ADD>
 int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16* y, long long ldy, const bf16* w, float* rrms,
-                    int M, int N, float eps, cudaStream_t st) {
+                    int M, int N, float eps, cudaStream_t st, uint8_t* y8 = nullptr, long long ld8 = 0, float* y8_scale = nullptr) {
   if (!x || !y || !w || (ADD && !res) || M < 0 || N <= 0) return TEENY_ERR_BAD_ARG;
+  if (y8 && (!y8_scale || (ld8 & 7) || ld8 < N || (reinterpret_cast<uintptr_t>(y8) & 7))) return TEENY_ERR_BAD_ARG;
   if (M == 0) return TEENY_OK;
   const bool vec = (N % 8 == 0) && (ldx % 8 == 0) && (ldy % 8 == 0) && aligned16(x) && aligned16(y) && aligned16(w) &&
                    (!ADD || (aligned16(res) && ldr % 8 == 0));
@@ -250,13 +292,15 @@ int launch_rms_bf16(const bf16* x, long long ldx, bf16* res, long long ldr, bf16
     if (M <= 512 && nv > threads) threads = nv >= 512 ? 512 : (nv + 31) / 32 * 32;
     const int vpt = (nv + threads - 1) / threads;
 #define TEENY_RMS_CASE(V)                                                                                    \
-  launch_kernel(rms_norm_bf16_kernel<V, ADD>, dim3(M), dim3(threads), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps)
+  launch_kernel(rms_norm_bf16_kernel<V, ADD>, dim3(M), dim3(threads), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps, y8, \
+                ld8, y8_scale)
     if (vpt <= 1) TEENY_RMS_CASE(1);
     else if (vpt <= 2) TEENY_RMS_CASE(2);
     else if (vpt <= 4) TEENY_RMS_CASE(4);
     else TEENY_RMS_CASE(8);
 #undef TEENY_RMS_CASE
   } else {
+    if (y8) return TEENY_ERR_ALIGNMENT;  // the FP8 copy exists only in the vector kernel
     launch_kernel(rms_norm_bf16_scalar_kernel<ADD>, dim3(M), dim3(256), 0, st, 1, x, ldx, res, ldr, y, ldy, w, rrms, N, eps);
   }
   return static_cast<int>(cudaGetLastError());
@@ -768,12 +812,12 @@ int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, i
   return static_cast<int>(cudaGetLastError());
 }
 int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
-                  float eps, cudaStream_t st) {
-  return launch_rms_bf16<false>(x, ldx, nullptr, 0, y, ldy, w, rrms, M, N, eps, st);
+                  float eps, cudaStream_t st, uint8_t* y8, long long ld8, float* y8_scale) {
+  return launch_rms_bf16<false>(x, ldx, nullptr, 0, y, ldy, w, rrms, M, N, eps, st, y8, ld8, y8_scale);
 }
 int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ldr, bf16* y, long long ldy,
-                      const bf16* w, int M, int N, float eps, cudaStream_t st) {
-  return launch_rms_bf16<true>(x, ldx, residual, ldr, y, ldy, w, nullptr, M, N, eps, st);
+                      const bf16* w, int M, int N, float eps, cudaStream_t st, uint8_t* y8, long long ld8, float* y8_scale) {
+  return launch_rms_bf16<true>(x, ldx, residual, ldr, y, ldy, w, nullptr, M, N, eps, st, y8, ld8, y8_scale);
 }
 int gather_add_rms_norm_bf16(const uint2* recv, size_t slot_elems, int world, const unsigned* epoch, unsigned round,
                              bf16* residual, long long ldr, bf16* y, long long ldy, const bf16* w, int M, int N,

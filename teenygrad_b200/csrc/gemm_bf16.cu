@@ -64,6 +64,10 @@ struct GemmArgs {
   int w_scale_kind;
   int w_group;                // w_scale_kind 2: elements of k per scale, a multiple of 64
   unsigned w_mul16;           // the constant 16, in a register (see e4m3x4_to_bf16x4)
+  // F8 variant: the activations come as two FP8 (E4M3) terms per element, x = (hi + lo / 16) * x_scale[row]; the tensor
+  // map covers both, the rows of the lo term x_lo_row rows behind those of the hi term
+  const float* x_scale;
+  int x_lo_row;
   int* err;
 };
 
@@ -114,6 +118,20 @@ __device__ __forceinline__ void umma_bf16_ss_x4(uint32_t d_tmem, uint64_t a_desc
       "add.u64 a, %1, %9;\n\t add.u64 b, %2, %10;\n\t tcgen05.mma.cta_group::1.kind::f16 [%0], a, b, %3, t;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "n"(A_STEP), "n"(B_STEP), "n"(2 * A_STEP),
         "n"(2 * B_STEP), "n"(3 * A_STEP), "n"(3 * B_STEP)
+      : "memory");
+}
+// The same for kind::f8f6f4 with both operands FP8 (E4M3) in shared memory: four K = 32 steps over 128 k, 32 bytes each.
+__device__ __forceinline__ void umma_f8_ss_x4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, t;\n\t.reg .b64 a, b;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 t, %3, %3;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "add.u64 a, %1, 2;\n\t add.u64 b, %2, 2;\n\t tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, 4;\n\t add.u64 b, %2, 4;\n\t tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, t;\n\t"
+      "add.u64 a, %1, 6;\n\t add.u64 b, %2, 6;\n\t tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], a, b, %3, t;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first)
       : "memory");
 }
 template <int B_STEP>
@@ -392,8 +410,13 @@ constexpr int kL2Ahead = 0;
 // MMA takes it as its A operand.  Converting through shared memory instead (bytes in, bf16 tile out, tile read by the
 // MMA) costs six bytes of shared-memory traffic per weight byte, more than the SM has at the rate HBM delivers the
 // bytes -- that version ran no faster than the bf16 kernel; this one reads every weight byte from shared memory once.
-template <int BN, bool W8 = false>
+// F8 (with W8): the activations are FP8 as well -- every element split beforehand into two E4M3 terms, which represent
+// a bf16 value exactly over twelve binades below its row's maximum (split_e4m3 in gemm_w8a16.cu) -- so the weight bytes
+// are the MMA's A operand as TMA delivered them (kind::f8f6f4, K = 32 per instruction) and nothing is converted: two
+// products per stage half, W * hi and W * lo, into two accumulators that the epilogue combines.
+template <int BN, bool W8 = false, bool F8 = false>
 struct SkinnyCfg {
+  static_assert(W8 || !F8, "F8 activations go with FP8 weights");
   static constexpr int kKB = W8 ? 2 * kBK : kBK;       // k per stage
   static constexpr int kStageP = kBM * kBK * 2;        // 16 KB of weights either way
   static constexpr int kStageQ = BN * kKB * 2;
@@ -405,22 +428,24 @@ struct SkinnyCfg {
   static constexpr int kPartialBytes = BN * kBM * 4;  // f32 partial tile, column-major [BN][128]; reuses the ring
   static_assert(kPartialBytes <= kStages * kStageBytes, "partial tile must fit in the stage ring");
   // W8: 64 k of 128 weight rows as bf16 pairs are 32 columns of tensor memory; four such tiles behind the accumulator
-  static constexpr int kABufs = W8 ? 4 : 0;
+  static constexpr int kABufs = (W8 && !F8) ? 4 : 0;
   static constexpr int kAccCols = BN < 32 ? 32 : BN;
   static constexpr int kTmemA = 128;                   // first column of the weight tiles
-  static constexpr int kTmemCols = W8 ? 256 : kAccCols;
+  static constexpr int kTmemCols = F8 ? (BN <= 64 ? 128 : 256) : (W8 ? 256 : kAccCols);
   // W8: four more warps behind the epilogue warps, all eight convert (a lone warp per scheduler cannot hide the latency
   // of its own dependent bit operations); only the first four run the epilogue
-  static constexpr int kConvWarps = W8 ? 8 : 0;
+  static constexpr int kConvWarps = (W8 && !F8) ? 8 : 0;
   // W8: one thread issues a tcgen05.mma only every ~90 cycles, and a 64-k block of FP8 weights is half the bytes of a
   // bf16 one for the same four instructions: two issuing threads (a second MMA warp behind the converting warps), one
   // per half of a stage, each with its own accumulator (the epilogue adds the two); BN = 128 has no columns left for a
   // second accumulator and keeps one issuer
-  static constexpr int kIssuers = (W8 && BN <= 64) ? 2 : 1;
-  static constexpr int kAcc1 = 64;                     // first column of the second accumulator
-  static constexpr int kThreads = W8 ? 64 + 32 * kConvWarps + (kIssuers == 2 ? 32 : 0) : kNumThreads;
-  static_assert(kTmemA + kABufs * 32 <= 256 && kAccCols <= kTmemA && (kIssuers == 1 || kAcc1 + kAccCols <= kTmemA),
+  static constexpr int kIssuers = (W8 && !F8 && BN <= 64) ? 2 : 1;
+  static constexpr int kAcc1 = (F8 && BN > 64) ? 128 : 64;  // first column of the second accumulator (F8: of the lo products)
+  static constexpr bool kTwoAcc = kIssuers == 2 || F8;
+  static constexpr int kThreads = (W8 && !F8) ? 64 + 32 * kConvWarps + (kIssuers == 2 ? 32 : 0) : kNumThreads;
+  static_assert(F8 || (kTmemA + kABufs * 32 <= 256 && kAccCols <= kTmemA && (kIssuers == 1 || kAcc1 + kAccCols <= kTmemA)),
                 "accumulators and weight tiles share the allocation");
+  static_assert(!F8 || kAcc1 + kAccCols <= kTmemCols, "two accumulators share the allocation");
   static constexpr int kBarOffset = kStages * kStageBytes;
   static constexpr int kSmemBytes = kBarOffset + 1024 + 256;
 };
@@ -473,11 +498,11 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t
 }
 
 // grid (S, tiles): blockIdx.x = cluster rank = k-split, blockIdx.y = 128-row weight tile.
-template <int BN, bool W8 = false>
-__global__ void __launch_bounds__((SkinnyCfg<BN, W8>::kThreads), 2)
+template <int BN, bool W8 = false, bool F8 = false>
+__global__ void __launch_bounds__((SkinnyCfg<BN, W8, F8>::kThreads), 2)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const GemmArgs args) {
-  using Cfg = SkinnyCfg<BN, W8>;
+  using Cfg = SkinnyCfg<BN, W8, F8>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // The partial tile is written after the last MMA has completed, i.e. when no stage is in use any more, so it
@@ -518,7 +543,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       mbar_init(empty_bar(s), Cfg::kIssuers + Cfg::kConvWarps);
     }
     mbar_init(acc_full_bar, Cfg::kIssuers);
-    if constexpr (W8) {
+    if constexpr (W8 && !F8) {
       for (int b = 0; b < Cfg::kABufs; ++b) {
         mbar_init(wfull_bar(b), Cfg::kConvWarps / 2);  // a tile is written by one group of four warps
         mbar_init(wempty_bar(b), 1);
@@ -551,7 +576,8 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       pdl_wait();
       auto load_x = [&](uint32_t sq, uint32_t bar, int kb) {  // the activation tile(s) of one stage: 64 k each
         tma_load_2d(sq, &tmap_x, bar, kb * Cfg::kKB, 0);
-        if constexpr (W8) tma_load_2d(sq + BN * kBK * 2, &tmap_x, bar, kb * Cfg::kKB + kBK, 0);
+        if constexpr (F8) tma_load_2d(sq + BN * kBK * 2, &tmap_x, bar, kb * Cfg::kKB, args.x_lo_row);  // the lo terms
+        else if constexpr (W8) tma_load_2d(sq + BN * kBK * 2, &tmap_x, bar, kb * Cfg::kKB + kBK, 0);
       };
       for (int i = 0; i < pre; ++i) load_x(smem_base + i * Cfg::kStageBytes + Cfg::kStageP, full_bar(i), kb0 + i);
       int stage = pre == Cfg::kStages ? 0 : pre;
@@ -583,7 +609,16 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (!mbar_wait(full_bar(stage), phase, err, DEVERR_GEMM_MMA)) { ok = false; break; }
         TRACE_ONLY(m_full += clock64() - c0;)
         const uint32_t sp = smem_base + stage * Cfg::kStageBytes;
-        if constexpr (W8) {
+        if constexpr (F8) {
+          tc_fence_after();
+          constexpr uint32_t idesc = make_idesc_e4m3(kBM, BN);
+          const uint64_t wdesc = make_smem_desc_sw128(sp, 16, 1024);
+          const uint64_t hdesc = make_smem_desc_sw128(sp + Cfg::kStageP, 16, 1024);
+          const uint64_t ldesc = make_smem_desc_sw128(sp + Cfg::kStageP + BN * kBK * 2, 16, 1024);
+          // 128 k of the stage = four K = 32 steps of 32 bytes (+2 in both address fields); hi products, then lo
+          umma_f8_ss_x4(tmem_base, wdesc, hdesc, idesc, kb == kb0 ? 0u : 1u);
+          umma_f8_ss_x4(tmem_base + Cfg::kAcc1, wdesc, ldesc, idesc, kb == kb0 ? 0u : 1u);
+        } else if constexpr (W8) {
           for (int h = h_first; h < 2; h += h_step) {
             const int q = 2 * (kb - kb0) + h, j = q & 3;  // the q-th 64-k block goes through weight tile q % 4
             TRACE_ONLY(c0 = clock64();)
@@ -613,7 +648,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
   } else {
     pdl_wait();
-    if constexpr (W8) {
+    if constexpr (W8 && !F8) {
       // ---- main loop of the converting warps: the q-th 64-k block of weights -> weight tile q % 4 in tensor memory ----
       // Two groups of four warps: group g takes half g of every stage, so two blocks are always under way (one group's
       // loads, bit operations and tensor-memory stores overlap the other's).  A warp reaches the 32 lanes (weight rows)
@@ -690,12 +725,21 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       for (int c0 = 0; c0 < BN; c0 += kChunk) {
         uint32_t r[kChunk];
         if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + c0, r); else tmem_ld_32x16(t_addr + c0, r);
-        if constexpr (Cfg::kIssuers == 2) {  // the two issuers' accumulators: halves 0 and halves 1 of the stages
+        if constexpr (Cfg::kTwoAcc) {
+          // two accumulators: the two issuers' (halves 0 and halves 1 of the stages), or the hi and the lo products of the
+          // F8 variant (the lo terms were stored times 16); F8 also applies the token's activation scale here
           uint32_t r1[kChunk];
           if constexpr (kChunk == 32) tmem_ld_32x32(t_addr + Cfg::kAcc1 + c0, r1); else tmem_ld_32x16(t_addr + Cfg::kAcc1 + c0, r1);
           tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < kChunk; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r1[e]));
+          for (int e = 0; e < kChunk; ++e) {
+            if constexpr (F8) {
+              const float xs = (c0 + e < args.M) ? __ldg(args.x_scale + c0 + e) : 0.0f;
+              r[e] = __float_as_uint(fmaf(__uint_as_float(r1[e]), 0.0625f, __uint_as_float(r[e])) * xs);
+            } else {
+              r[e] = __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(r1[e]));
+            }
+          }
         }
         tmem_wait_ld();
         if (direct) {
@@ -864,14 +908,14 @@ int prepare_variant() {
   return 0;
 }
 
-template <int BN, bool W8 = false>
+template <int BN, bool W8 = false, bool F8 = false>
 int prepare_skinny() {
   static std::atomic<unsigned long long> done{0};  // one bit per device; threads may race to set it
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && (done.load(std::memory_order_acquire) >> dev) & 1ull) return 0;
-  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN, W8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       SkinnyCfg<BN, W8>::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<BN, W8, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       SkinnyCfg<BN, W8, F8>::kSmemBytes);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 64) done.fetch_or(1ull << dev, std::memory_order_release);
   return 0;
@@ -885,13 +929,14 @@ int launch_variant(const CUtensorMap& tp, const CUtensorMap& tq, const GemmArgs&
   return static_cast<int>(cudaGetLastError());
 }
 
-template <int BN, bool W8 = false>
+template <int BN, bool W8 = false, bool F8 = false>
 int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int split, int tiles,
                   cudaStream_t st) {
-  const int rc = prepare_skinny<BN, W8>();
+  const int rc = prepare_skinny<BN, W8, F8>();
   if (rc) return rc;
-  return launch_kernel(gemm_bf16_skinny_kernel<BN, W8>, dim3(split, tiles, 1), dim3(SkinnyCfg<BN, W8>::kThreads, 1, 1),
-                       SkinnyCfg<BN, W8>::kSmemBytes, st, static_cast<unsigned>(split), tw, tx, a);
+  return launch_kernel(gemm_bf16_skinny_kernel<BN, W8, F8>, dim3(split, tiles, 1),
+                       dim3(SkinnyCfg<BN, W8, F8>::kThreads, 1, 1), SkinnyCfg<BN, W8, F8>::kSmemBytes, st,
+                       static_cast<unsigned>(split), tw, tx, a);
 }
 
 // Cluster width (K split) of the skinny kernel for `tiles` 128-row weight tiles.
@@ -931,7 +976,11 @@ int gemm_bf16_prepare() {
   if ((rc = prepare_skinny<16, true>())) return rc;
   if ((rc = prepare_skinny<32, true>())) return rc;
   if ((rc = prepare_skinny<64, true>())) return rc;
-  return prepare_skinny<128, true>();
+  if ((rc = prepare_skinny<128, true>())) return rc;
+  if ((rc = prepare_skinny<16, true, true>())) return rc;
+  if ((rc = prepare_skinny<32, true, true>())) return rc;
+  if ((rc = prepare_skinny<64, true, true>())) return rc;
+  return prepare_skinny<128, true, true>();
 }
 
 bool gemm_bf16_uses_2cta(int M, int N) {
@@ -1103,6 +1152,60 @@ int gemm_w8a16_skinny(const bf16* x, int ldx, const uint8_t* wq, int ldw, const 
     case 32: return launch_skinny<32, true>(tmw, tmx, a, split, tiles, stream);
     case 64: return launch_skinny<64, true>(tmw, tmx, a, split, tiles, stream);
     default: return launch_skinny<128, true>(tmw, tmx, a, split, tiles, stream);
+  }
+}
+
+// The same with the activations already split into two FP8 terms (split_e4m3): x8 = [2 * M, K] bytes (hi rows, then lo
+// rows; row stride ldx8 bytes), x_scale[M].  Nothing is converted inside: kind::f8f6f4 on the bytes as they are.
+int gemm_w8a8x2_skinny(const uint8_t* x8, int ldx8, const float* x_scale, const uint8_t* wq, int ldw, const float* w_scale,
+                       int scale_kind, const bf16* bias, bf16* y, int ldy, int M, int N, int K, cudaStream_t stream,
+                       bool swiglu, const GemmPush* push) {
+  if (!x8 || !x_scale || !wq || !w_scale || !y || M <= 0 || M > kSwapMaxM || N <= 0 || K <= 0) return TEENY_ERR_BAD_ARG;
+  if (scale_kind < 0 || scale_kind > 1) return TEENY_ERR_BAD_ARG;  // per-group weight scales need the converting variant
+  if (swiglu && (bias || N % 128 != 0)) return TEENY_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x8) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15) || (ldx8 & 15) || (ldw & 15))
+    return TEENY_ERR_ALIGNMENT;
+  GemmArgs a{};
+  a.M = M; a.N = N; a.K = K; a.ldy = ldy; a.y = y; a.bias = bias;
+  a.k_blocks = ceil_div(K, 2 * kBK);
+  a.swiglu = swiglu ? 1 : 0;
+  a.w_scale = w_scale; a.w_scale_kind = scale_kind; a.w_group = 0; a.w_mul16 = 16u;
+  a.x_scale = x_scale; a.x_lo_row = M;
+  if (push) {
+    if (swiglu || !push->recv || !push->epoch || push->world < 2 || push->round >= 1023) return TEENY_ERR_BAD_ARG;
+    a.push_recv = push->recv;
+    a.push_epoch = push->epoch;
+    a.push_round = push->round;
+    a.push_world = push->world;
+    a.push_owner_rows = push->owner_rows;
+  }
+  a.err = device_error_word();
+  if (!a.err) return TEENY_ERR_DRIVER;
+  const int bn = swap_bn(M);
+  CUtensorMap tmx, tmw;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(2 * M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldx8)};
+    const uint32_t box[2] = {2 * kBK, static_cast<uint32_t>(bn)};
+    const int rc = encode_tensor_map_u8(&tmx, x8, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldw)};
+    const uint32_t box[2] = {2 * kBK, kBM};
+    const int rc = encode_tensor_map_u8(&tmw, wq, 2, dims, strides, box);
+    if (rc) return rc;
+  }
+  const int tiles = ceil_div(N, kBM);
+  if (tiles > 65535) return TEENY_ERR_BAD_ARG;
+  const int split = skinny_split(tiles, a.k_blocks, sm_count());
+  a.kb_per_split = ceil_div(a.k_blocks, split);
+  switch (bn) {
+    case 16: return launch_skinny<16, true, true>(tmw, tmx, a, split, tiles, stream);
+    case 32: return launch_skinny<32, true, true>(tmw, tmx, a, split, tiles, stream);
+    case 64: return launch_skinny<64, true, true>(tmw, tmx, a, split, tiles, stream);
+    default: return launch_skinny<128, true, true>(tmw, tmx, a, split, tiles, stream);
   }
 }
 

@@ -95,6 +95,51 @@ dequant_int_bf16_kernel(const uint8_t* __restrict__ q, int bits, const float* __
   }
 }
 
+// Activations for the F8 GEMM variant: a bf16 value has 8 significant bits, an E4M3 number 4, so x * s = hi + lo with
+// hi = e4m3(x * s) (round to nearest even) and lo = x * s - hi holds exactly while both terms stay normal in E4M3.  s is
+// the power of two that brings the row's largest magnitude into [128, 256); lo is stored times 16 (it is at most half
+// an ulp of hi, so lo * 16 <= |hi|: no overflow) which keeps it normal for |x * s| >= 2^-3, i.e. the split is EXACT for
+// every element within 2^10 of its row's maximum and loses low bits gradually below (4 significant bits down to 2^-13
+// of the maximum, zero below 2^-17).  out: [2 * M, K] bytes (hi rows, then the lo rows), scale[m] = 1 / s.
+// One CTA per row.
+__global__ void __launch_bounds__(256)
+split_e4m3_kernel(const bf16* __restrict__ x, long long ldx, uint8_t* __restrict__ out, long long ldo, float* __restrict__ scale,
+                  int M, int K) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float red[8];
+  const int m = blockIdx.x;
+  const bf16* row = x + m * ldx;
+  float amax = 0.0f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(__bfloat162float(row[k])));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 16));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 8));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+  for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) amax = fmaxf(amax, red[w]);
+  const int p = split_scale_exponent(amax);
+  const float s = ldexpf(1.0f, p);
+  if (threadIdx.x == 0) scale[m] = ldexpf(1.0f, -p);
+  uint8_t* hi_row = out + m * ldo;
+  uint8_t* lo_row = out + (static_cast<long long>(M) + m) * ldo;
+  for (int k = 2 * threadIdx.x; k < K; k += 2 * blockDim.x) {
+    const bool two = k + 1 < K;
+    const float a = __bfloat162float(row[k]) * s, b = two ? __bfloat162float(row[k + 1]) * s : 0.0f;
+    unsigned short h, l;
+    split_e4m3_pair(a, b, h, l);
+    hi_row[k] = static_cast<uint8_t>(h & 0xff);
+    lo_row[k] = static_cast<uint8_t>(l & 0xff);
+    if (two) {
+      hi_row[k + 1] = static_cast<uint8_t>(h >> 8);
+      lo_row[k + 1] = static_cast<uint8_t>(l >> 8);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) e4m3_count_nan_kernel(const uint8_t* __restrict__ p, size_t n, unsigned* count) {
   unsigned found = 0;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
@@ -126,6 +171,11 @@ int dequant_int_bf16(const void* q, int bits, const float* scale, const int* zer
   const int grid = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
   return launch_kernel(dequant_int_bf16_kernel, dim3(grid), dim3(256), 0, st, 1, static_cast<const uint8_t*>(q), bits, scale,
                        zero_point, kind, group, out, ldo, N, K);
+}
+
+int split_e4m3(const bf16* x, long long ldx, uint8_t* out, long long ldo, float* scale, int M, int K, cudaStream_t st) {
+  if (!x || !out || !scale || M <= 0 || K <= 0 || ldo < K) return TEENY_ERR_BAD_ARG;
+  return launch_kernel(split_e4m3_kernel, dim3(M), dim3(256), 0, st, 1, x, ldx, out, ldo, scale, M, K);
 }
 
 int e4m3_count_nan(const uint8_t* p, size_t n, unsigned* count, cudaStream_t st) {

@@ -65,6 +65,12 @@ int gather_add_rms_norm_owner_bf16(const uint2* recv, size_t slot_elems, int wor
 int gemm_w8a16_skinny(const bf16* x, int ldx, const uint8_t* wq, int ldw, const float* w_scale, int scale_kind,
                       int group, const bf16* bias, bf16* y, int ldy, int M, int N, int K, cudaStream_t stream,
                       bool swiglu = false, const GemmPush* push = nullptr);
+// FP8 weights AND two-term FP8 activations (split_e4m3 writes them: x = (hi + lo / 16) * x_scale[row], exact for
+// elements within 2^10 of their row's maximum): kind::f8f6f4 on the bytes as they are, M <= 128, scale kinds 0 and 1.
+int split_e4m3(const bf16* x, long long ldx, uint8_t* out, long long ldo, float* scale, int M, int K, cudaStream_t st);
+int gemm_w8a8x2_skinny(const uint8_t* x8, int ldx8, const float* x_scale, const uint8_t* wq, int ldw, const float* w_scale,
+                       int scale_kind, const bf16* bias, bf16* y, int ldy, int M, int N, int K, cudaStream_t stream,
+                       bool swiglu = false, const GemmPush* push = nullptr);
 int dequant_e4m3_bf16(const uint8_t* wq, long long ldw, const float* scale, int kind, int group, bf16* out, long long ldo,
                       int N, int K, cudaStream_t st);
 // out[N, K] = bf16((q - zero point) * scale) for the integer schemes: bits 8 (int8 [N, K]) or 4 (nibbles packed two per
@@ -164,11 +170,14 @@ int attention_generic(const T* q, const T* k, const T* v, T* o, float* lse, cons
 // ---- normalisation / elementwise ----------------------------------------------------------------
 int rms_norm_f32(const float* x, float* y, const float* w, float* rrms, int M, int N, float eps, cudaStream_t st);
 // bf16 with the Qwen3 rounding points: f32 statistics, round to bf16, then multiply by the bf16 weight.
+// y8 != null: y is also written as two-term FP8 activations (hi rows, then M lo rows; row stride ld8 bytes;
+// y8_scale[M]), as split_e4m3 would split it.
 int rms_norm_bf16(const bf16* x, long long ldx, bf16* y, long long ldy, const bf16* w, float* rrms, int M, int N,
-                  float eps, cudaStream_t st);
+                  float eps, cudaStream_t st, uint8_t* y8 = nullptr, long long ld8 = 0, float* y8_scale = nullptr);
 // residual <- bf16(residual + x); y <- rms_norm(residual) (same rounding as rms_norm_bf16).
 int add_rms_norm_bf16(const bf16* x, long long ldx, bf16* residual, long long ldr, bf16* y, long long ldy,
-                      const bf16* w, int M, int N, float eps, cudaStream_t st);
+                      const bf16* w, int M, int N, float eps, cudaStream_t st, uint8_t* y8 = nullptr, long long ld8 = 0,
+                      float* y8_scale = nullptr);
 int silu_f32(const float* x, float* y, long long n, cudaStream_t st);
 int silu_bf16(const bf16* x, bf16* y, long long n, cudaStream_t st);
 int mul_f32(const float* a, const float* b, float* o, long long n, cudaStream_t st);

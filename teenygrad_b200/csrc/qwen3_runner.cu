@@ -318,6 +318,8 @@ struct Workspace {
   // offsets into the caller's workspace
   size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters, sample_u;
   size_t sample_cand, sample_gather;  // tensor-parallel sampling: this rank's candidate lists, all ranks' lists
+  size_t y8, y8_scale;                // the norm kernels' output as two-term FP8 activations (0 bytes when max_batch > 128)
+  size_t y8_rows;
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
   size_t gemm_scratch_bytes, attn_scratch_bytes, attn_counter_bytes, cache_layer_elems;
 };
@@ -416,6 +418,10 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.attn_scratch = take(w.attn_scratch_bytes);
   w.attn_counter_bytes = Bm * static_cast<size_t>(c.num_kv_heads) * 4;  // arrival counters of the split-sequence merge
   w.attn_counters = take(w.attn_counter_bytes);
+  // FP8 weights: a decode step's norm outputs (and the head's) also as two-term FP8, hi rows then lo rows
+  w.y8_rows = (tp == 1 && Bm <= 128 && H % 16 == 0) ? Bm : 0;
+  w.y8 = take(2 * w.y8_rows * H);
+  w.y8_scale = take(w.y8_rows * 4);
   w.sample_u = take(Bm * 4);
   w.sample_cand = take(tp > 1 ? Bm * 1024 * 8 : 0);
   w.sample_gather = take(tp > 1 ? Bm * 1024 * 8 * tp : 0);
@@ -446,11 +452,17 @@ int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
 // y[T, N] = x[T, K] W^T for one of the model's projection weights, in whichever form it was given.  FP8 weights are
 // streamed as bytes while T <= 128 (decode) and converted into the model's FP8 scratch for a larger T (prefill), where
 // the bf16 kernels -- the QKV projection's fused epilogue included -- then run on the converted copy.
+// x8 true: x has also been written as two-term FP8 activations into the model's y8 buffer (by the norm kernel in front)
+// and the weight's scales allow it: the conversion-free FP8 x FP8 kernel runs.
 int project(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* y, int ldy, int T, int N, int K,
-            cudaStream_t st, bool swiglu = false, const GemmPush* push = nullptr, const QkvEpilogue* fuse = nullptr) {
+            cudaStream_t st, bool swiglu = false, const GemmPush* push = nullptr, const QkvEpilogue* fuse = nullptr,
+            bool x8 = false) {
   void* gs = m->at<void>(m->off.gemm_scratch);
   const bf16* wb = w.w;
   const int w_rows = N;  // rows of W ([N, K]; for swiglu N counts gate and up rows)
+  if (w.q && x8 && T <= 128 && w.kind <= 1)
+    return gemm_w8a8x2_skinny(m->at<uint8_t>(m->off.y8), K, m->at<float>(m->off.y8_scale), w.q, K, w.scale, w.kind, nullptr, y,
+                              ldy, T, N, K, st, swiglu, push);
   if (w.q) {
     if (T <= 128) return linear_w8a16(x, ldx, w.q, K, w.scale, w.kind, w.group, nullptr, y, ldy, T, N, K, nullptr, 0, st, swiglu, push);
     const size_t need = static_cast<size_t>(w_rows) * K * sizeof(bf16);
@@ -484,8 +496,16 @@ int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* 
   return all_reduce(m, delta, static_cast<size_t>(T) * N, st);
 }
 
+// Whether the projection behind a norm takes its input as two-term FP8: an FP8 weight with per-tensor or per-channel
+// scales, at most 128 rows, one GPU (the gather kernels of the tensor-parallel path write no FP8 copy).
+bool wants_x8(const teeny_qwen3* m, const Weight& w, int M) {
+  return w.q && w.kind <= 1 && !m->tp && M > 0 && static_cast<size_t>(M) <= m->off.y8_rows;
+}
+
 // residual += projection; y = rms_norm(residual) on M rows (row strides ld for delta / residual, H for y).
-int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, const bf16* w, int M, cudaStream_t st) {
+// split: also write y as two-term FP8 into the model's y8 buffer.
+int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, const bf16* w, int M, cudaStream_t st,
+                  bool split = false) {
   const teeny_qwen3_config& c = m->cfg;
   if (m->pending_gather) {
     m->pending_gather = false;
@@ -497,7 +517,8 @@ int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, c
     return gather_add_rms_norm_bf16(tp->local_recv(m->pending_parity), tp->slot_elems, tp->world, tp->epoch(),
                                     m->pending_round, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
   }
-  return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st);
+  return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st,
+                           split ? m->at<uint8_t>(m->off.y8) : nullptr, c.hidden, split ? m->at<float>(m->off.y8_scale) : nullptr);
 }
 
 // TEENY_QKV_FUSE=0 keeps head norms / RoPE / cache fill in their own kernel behind the QKV projection (for A/B timing).
@@ -523,8 +544,11 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     const LayerWeights& w = m->layers[l];
     bf16* kc = m->at<bf16>(m->off.kcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
     bf16* vc = m->at<bf16>(m->off.vcache) + static_cast<size_t>(l) * m->off.cache_layer_elems;
-    if (l == 0) TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st));
-    else TEENY_TRY(residual_norm(m, delta, h, H, y, w.input_ln, T, st));
+    const bool qkv8 = wants_x8(m, w.qkv, T), mlp8 = wants_x8(m, w.gate_up, T);
+    if (l == 0)
+      TEENY_TRY(rms_norm_bf16(h, H, y, H, w.input_ln, nullptr, T, H, c.eps, st, qkv8 ? m->at<uint8_t>(m->off.y8) : nullptr, H,
+                              qkv8 ? m->at<float>(m->off.y8_scale) : nullptr));
+    else TEENY_TRY(residual_norm(m, delta, h, H, y, w.input_ln, T, st, qkv8));
     // Head norms, RoPE and the cache fill: in a large prefill they run in the epilogue of the QKV projection itself (k
     // and v never pass through the projection buffer); in a small one as one pass over the projection; in decode the
     // attention kernel does them for its own (sequence, kv head) on the way in.
@@ -533,7 +557,7 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
                              S, Hq, Hkv, c.max_len, pos0, c.eps};
       TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, T, qkv_n, H, st, false, nullptr, &fuse));
     } else {
-      TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, T, qkv_n, H, st));
+      TEENY_TRY(project(m, y, H, w.qkv, qkv, qkv_n, T, qkv_n, H, st, false, nullptr, nullptr, qkv8));
       if (!decode)
         TEENY_TRY(qk_norm_rope_kv_bf16(qkv, qkv_n, w.q_norm, w.k_norm, m->at<bf16>(m->off.cos), m->at<bf16>(m->off.sin),
                                        kc, vc, T, S, Hq, Hkv, D, c.max_len, pos0, pos_dev, c.eps, st));
@@ -563,8 +587,8 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
       TEENY_TRY(attention_prefill_bf16(qkv, kc, vc, attn, nullptr, a, st));
     }
     TEENY_TRY(row_parallel(m, attn, Hq * D, w.o, delta, T, H, Hq * D, decode, st));
-    TEENY_TRY(residual_norm(m, delta, h, H, y, w.post_ln, T, st));
-    TEENY_TRY(project(m, y, H, w.gate_up, act, I, T, 2 * I, H, st, /*swiglu=*/true));
+    TEENY_TRY(residual_norm(m, delta, h, H, y, w.post_ln, T, st, mlp8));
+    TEENY_TRY(project(m, y, H, w.gate_up, act, I, T, 2 * I, H, st, /*swiglu=*/true, nullptr, nullptr, mlp8));
     TEENY_TRY(row_parallel(m, act, I, w.down, delta, T, H, I, decode, st));
   }
   return 0;
@@ -675,8 +699,9 @@ int run_head(teeny_qwen3* m, int B, int S, cudaStream_t st, const int* step_dev 
   const size_t last = static_cast<size_t>(S - 1) * H;
   const long long ld = static_cast<long long>(S) * H;
   // residual add + final norm on rows (b, S-1); y rows are packed [B, H]
-  TEENY_TRY(residual_norm(m, delta + last, h + last, ld, y, m->final_norm, B, st));
-  TEENY_TRY(project(m, y, H, m->lm_head, logits, Vl, B, Vl, H, st));
+  const bool head8 = wants_x8(m, m->lm_head, B);
+  TEENY_TRY(residual_norm(m, delta + last, h + last, ld, y, m->final_norm, B, st, head8));
+  TEENY_TRY(project(m, y, H, m->lm_head, logits, Vl, B, Vl, H, st, false, nullptr, nullptr, head8));
   float* cv = m->at<float>(m->off.cand_val);
   int* ci = m->at<int>(m->off.cand_idx);
   int* next = m->at<int>(m->off.next_ids);

@@ -105,9 +105,12 @@ def time_w8():
         y = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device="cuda")
         f16 = [(lambda w=w: (ops.linear_swiglu if swiglu else ops.linear_forward)(x, w, out=y)) for w in ws]
         f8 = [(lambda q=q: ops.linear_w8a16(x, q.q, q.scale, "channel", out=y, swiglu=swiglu)) for q in qs]
-        t16, t8 = _graph_time(f16), _graph_time(f8)
+        x8, xs = ops.split_fp8(x)
+        f88 = [(lambda q=q: ops.linear_w8a8x2(x8, xs, q.q, q.scale, "channel", out=y, swiglu=swiglu)) for q in qs]
+        t16, t8, t88 = _graph_time(f16), _graph_time(f8), _graph_time(f88)
         print(f"linear {M}x{N}x{K}{' + SwiGLU' if swiglu else ''}: bf16 weights {t16 * 1e3:.1f} us ({N * K * 2 / t16 / 1e6:.0f} GB/s)"
-              f" | FP8 weights {t8 * 1e3:.1f} us ({N * K / t8 / 1e6:.0f} GB/s)", flush=True)
+              f" | FP8 weights {t8 * 1e3:.1f} us ({N * K / t8 / 1e6:.0f} GB/s)"
+              f" | FP8 weights, two-term FP8 activations {t88 * 1e3:.1f} us ({N * K / t88 / 1e6:.0f} GB/s)", flush=True)
 
 
 def time_prefill():

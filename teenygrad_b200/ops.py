@@ -249,6 +249,30 @@ def linear_w8a16(x, w_fp8, w_scale, strategy="channel", group_size=0, bias=None,
     return out
 
 
+def split_fp8(x, out=None, scale=None):
+    """x [M, K] bf16 -> (bytes [2 * M, K]: the E4M3 hi terms, then the lo terms times 16; x_scale [M] = 1 / s), with
+    x * s = hi + lo exactly wherever both terms are normal E4M3 numbers."""
+    _req(x, _BF16, "x")
+    M, K = x.shape
+    out = torch.empty(2 * M, (K + 15) // 16 * 16, dtype=torch.uint8, device=x.device)[:, :K] if out is None else out
+    scale = torch.empty(M, dtype=_F32, device=x.device) if scale is None else scale
+    check(lib.teeny_split_fp8_e4m3(_ptr(x), x.stride(0), _ptr(out), out.stride(0), _ptr(scale), M, K, _stream()), "split_fp8")
+    return out, scale
+
+
+def linear_w8a8x2(x8, x_scale, w_fp8, w_scale, strategy="channel", bias=None, out=None, swiglu=False):
+    """FP8 weights times two-term FP8 activations (``split_fp8``): [M, N] bf16 (or [M, N / 2] with swiglu), M <= 128."""
+    _req(x8, torch.uint8, "x8"); _req(x_scale, _F32, "x_scale"); _req(w_scale, _F32, "w_scale")
+    w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8")
+    M, K = x8.shape[0] // 2, x8.shape[1]
+    N = w.shape[0]
+    out = torch.empty(M, N // 2 if swiglu else N, dtype=_BF16, device=x8.device) if out is None else out
+    check(lib.teeny_linear_w8a8x2_forward(_ptr(x8), x8.stride(0), _ptr(x_scale), _ptr(w), w.stride(0), _ptr(w_scale),
+                                          SCALE_KINDS[strategy], _ptr(bias), _ptr(out), out.stride(0), M, N, K, int(swiglu),
+                                          _stream()), "linear_w8a8x2")
+    return out
+
+
 def dequant_fp8(w_fp8, w_scale, strategy="channel", group_size=0, out=None):
     """bf16(decode(byte) * scale) of an FP8 (E4M3) tensor [N, K]."""
     w = _req(_as_bytes(w_fp8), torch.uint8, "w_fp8"); _req(w_scale, _F32, "w_scale")

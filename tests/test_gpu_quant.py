@@ -254,3 +254,59 @@ def test_runner_on_a_pack_quantized_int4_checkpoint(tmp_path):
         r.decode_step(graph=True)
         got.append(r.logits().clone())
     _check_generation(got, r.history()[:steps].t().cpu().long(), want_logits, want_ids)
+
+
+def test_split_fp8_equals_the_oracle_split(ops):
+    """The two-term E4M3 split of bf16 activations: bytes and scales equal to the oracle's, bit for bit."""
+    from oracle import quant as oq
+    g = torch.Generator().manual_seed(31)
+    x = (torch.randn(37, 1000, generator=g) * torch.logspace(-3, 3, 37)[:, None]).bfloat16()
+    x[4] = 0
+    x[9, ::3] *= 1e-4                      # elements far below their row's maximum
+    hi, lo, inv_s = oq.split_e4m3(x.float().numpy())
+    out, scale = ops.split_fp8(x.cuda())
+    assert torch.equal(out[:37].cpu(), torch.from_numpy(hi)) and torch.equal(out[37:].cpu(), torch.from_numpy(lo))
+    assert torch.equal(scale.cpu(), torch.from_numpy(inv_s))
+
+
+@pytest.mark.parametrize("strategy", ["tensor", "channel"])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 512, 1024), (32, 4096, 4096), (7, 1000, 528), (64, 2048, 2048),
+                                   (128, 1024, 4096), (5, 333, 1024), (4, 24576, 512)])
+def test_linear_w8a8x2(ops, M, N, K, strategy):
+    """FP8 weights x two-term FP8 activations (kind::f8f6f4, nothing converted in the kernel): equal to the oracle
+    evaluated on the split activations, and -- the split being exact for all but tiny elements -- to the weight-only
+    result on the bf16 activations themselves."""
+    from oracle import quant as oq
+    x, q, s, kw = _case(M, N, K, strategy, 0)
+    hi, lo, inv_s = oq.split_e4m3(x.float().numpy())
+    want_split = oq.linear_w8a8x2(hi, lo, inv_s, q, s, strategy, **kw)
+    want_exact = oq.linear_w8a16(x.float().numpy(), q, s, strategy, **kw)
+    x8, xs = ops.split_fp8(x.cuda())
+    qd, sd = torch.from_numpy(q).cuda(), torch.from_numpy(s).cuda()
+    first = None
+    for _ in range(2):
+        y = ops.linear_w8a8x2(x8, xs, qd, sd, strategy)
+        assert rel(y, want_split) < 8e-3 and rel(y, want_exact) < 8e-3
+        first = y if first is None else first
+        assert torch.equal(y, first)
+
+
+def test_linear_w8a8x2_swiglu_and_bias(ops):
+    from oracle import cpu as oc
+    from oracle import quant as oq
+    M, I, K = 32, 3072, 1024
+    g = torch.Generator().manual_seed(33)
+    x = (torch.randn(M, K, generator=g) * 0.5).bfloat16()
+    wg = (torch.randn(I, K, generator=g) * 0.05).float().numpy()
+    wu = (torch.randn(I, K, generator=g) * 0.05).float().numpy()
+    (qg, sg), (qu, su) = oq.quantize_fp8(wg, "channel", axis=0), oq.quantize_fp8(wu, "channel", axis=0)
+    yg = torch.from_numpy(oq.linear_w8a16(x.float().numpy(), qg, sg, "channel", axis=0)).bfloat16()
+    yu = torch.from_numpy(oq.linear_w8a16(x.float().numpy(), qu, su, "channel", axis=0)).bfloat16()
+    qi = ops.interleave_gate_up(torch.from_numpy(qg), torch.from_numpy(qu))
+    si = ops.interleave_gate_up(torch.from_numpy(sg)[:, None], torch.from_numpy(su)[:, None])[:, 0].contiguous()
+    x8, xs = ops.split_fp8(x.cuda())
+    out = ops.linear_w8a8x2(x8, xs, qi.cuda(), si.cuda(), "channel", swiglu=True)
+    assert rel(out, oc.silu_mul_bf16(yg, yu)) < BF16_TOL
+    b = (torch.arange(I).float() * 0.01).bfloat16()
+    yb = ops.linear_w8a8x2(x8, xs, torch.from_numpy(qg).cuda(), torch.from_numpy(sg).cuda(), "channel", bias=b.cuda())
+    assert rel(yb, oq.linear_w8a16(x.float().numpy(), qg, sg, "channel", axis=0, bias=b.float().numpy())) < BF16_TOL

@@ -126,3 +126,20 @@ def test_affine_ranges_and_round_trips():
     assert q.tolist() == [-7, 7]                                      # affine.rs:280-287: clamped to the 4-bit range
     z, s, _ = oq.quantize_affine(np.zeros(4, dtype=np.float32), 8, True, "tensor")
     assert s.tolist() == [1.0] and not z.any()
+
+
+def test_two_term_split_is_exact_within_ten_binades_of_the_row_maximum():
+    """A bf16 value (8 significant bits) is the sum of two E4M3 numbers (4 bits each) while both stay normal."""
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(16, 512, generator=g) * torch.logspace(-2, 2, 16)[:, None]).bfloat16().float()
+    x[3] = 0.0
+    x[5, 7] = 0.0
+    hi, lo, inv_s = oq.split_e4m3(x.numpy())
+    back = (oq.f8_to_f32(hi).astype(np.float64) + oq.f8_to_f32(lo).astype(np.float64) / 16) * inv_s[:, None]
+    amax = x.abs().amax(dim=1, keepdim=True).numpy()
+    big = np.abs(x.numpy()) >= amax * 2.0 ** -10
+    assert np.array_equal(back[big], x.numpy().astype(np.float64)[big])
+    assert np.all(np.abs(back - x.numpy()) <= amax * 2.0 ** -17 + 1e-30)   # elsewhere: a small absolute error
+    assert inv_s[3] == 1.0 and not hi[3].any() and not lo[3].any()
+    scaled = np.abs(x.numpy()).max(axis=1) / inv_s
+    assert np.all((scaled[scaled > 0] >= 128) & (scaled[scaled > 0] < 256))
