@@ -499,6 +499,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
                               static_cast<unsigned>(q[0][7]));
       }
     }
+    TRACE_MARK(3, threadIdx.x == 0);  // a row owned elsewhere: its broadcast has arrived
     pdl_wait();
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -508,6 +509,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
         yr[idx] = got_y[i];
       }
     }
+    TRACE_END();
     return;
   }
   float v[VPT][8];
@@ -539,6 +541,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
       for (int e = 0; e < 8; ++e) sq += v[i][e] * v[i][e];
     }
   }
+  TRACE_MARK(1, threadIdx.x == 0);  // an owned row: every rank's partial has arrived
   sq = block_sum(sq, red);
   const float rr = 1.0f / sqrtf(sq * (1.0f / static_cast<float>(N)) + eps);
   uint32_t yw[VPT][4];
@@ -561,6 +564,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
       }
     }
   }
+  TRACE_MARK(2, threadIdx.x == 0);  // ... and its broadcast is on its way
   pdl_wait();
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -570,6 +574,7 @@ __global__ void __launch_bounds__(512) gather_add_rms_norm_owner_kernel(const ui
       yr[idx] = make_uint4(yw[i][0], yw[i][1], yw[i][2], yw[i][3]);
     }
   }
+  TRACE_END();
 }
 
 // ---- SiLU(gate) * up on the fused [T, 2*inter] projection ----
