@@ -593,6 +593,10 @@ def generation_config(args):
     ybuf = torch.empty(T * max(2 * I // world, qkv_n), dtype=torch.bfloat16, device=dev)
     for (m, n, k) in shapes:
         xv, wv, yv = x[:, :k], wbuf[:n * k].view(n, k), ybuf[:m * n].view(m, n)
+        # "alone" as the burst peak it is divided by was measured: from an idle GPU, not on the heels of seconds of
+        # power-capped generation (the in-step figure against the sustained peak is roofline_prefill)
+        torch.cuda.synchronize()
+        time.sleep(1.0)
         for _ in range(2):
             ops.linear_forward(xv, wv, out=yv)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -691,7 +695,7 @@ def generation_config(args):
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "the tcgen05 GEMM on this run's prefill QKV / O / gate-up / down shapes "
-                                                  "(gemm_bf16_2cta_kernel at config 5), timed alone after the generation",
+                                                  "(gemm_bf16_2cta_kernel at config 5), timed alone after the generation (each shape from a GPU left idle for 1 s)",
                      "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["bf16_tflops"],
                      "peak_source": peaks["source"] + " (burst cuBLAS bf16: the kernel is timed alone, a few launches)",
