@@ -209,7 +209,7 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
     for (int q = 0; q < c->world; ++q) ok &= host[q];
     if (nccl_failed) ok = 0;
   };
-  // round 1: [handle | ok] records
+  // first exchange: [handle | ok] records
   std::memcpy(host.data() + rec * c->rank, &mine, sizeof(mine));
   host[rec * c->rank + sizeof(mine)] = static_cast<uint8_t>(ok);
   cudaMemcpyAsync(xbuf + rec * c->rank, host.data() + rec * c->rank, rec, cudaMemcpyHostToDevice, st);
@@ -233,7 +233,7 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
       }
     }
   }
-  // round 2: did every rank map every peer?
+  // second exchange: did every rank map every peer?
   if (!nccl_failed) agree();
   if (ok) {
     std::vector<uint2*> rt(2 * c->world);
@@ -250,7 +250,7 @@ int tp_enable_peer(TpContext* c, size_t rows, size_t cols, cudaStream_t st) {
     if (ok && cudaMalloc(&c->bcast_tab, bt.size() * sizeof(uint4*)) != cudaSuccess) { c->bcast_tab = nullptr; ok = 0; }
     if (ok && cudaMemcpy(c->bcast_tab, bt.data(), bt.size() * sizeof(uint4*), cudaMemcpyHostToDevice) != cudaSuccess) ok = 0;
   }
-  // round 3: does every rank hold its tables?  Only then do all ranks switch to the peer path together.
+  // third exchange: does every rank hold its tables?  Only then do all ranks switch to the peer path together.
   if (!nccl_failed) agree();
   cudaFree(xbuf);
   if (!ok) {
