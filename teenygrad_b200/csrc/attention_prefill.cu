@@ -67,6 +67,8 @@ struct PrefillArgs {
   long long o_sb, o_sh, o_ss;
   float scale_log2;
   int causal;
+  int n_pair_tiles;  // 256-row query tiles per (batch, head)
+  int n_items;       // n_pair_tiles * Hq * B work items; CTA pair p takes items p, p + pairs, ...
   int* err;
 };
 
@@ -142,7 +144,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
   // threads signal them across the pair); the others exist and are used in both CTAs
   constexpr int Q_READY = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
                 S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 1,
-                M_READY = PV_DONE + 2, kNumBars = M_READY + 2;
+                M_READY = PV_DONE + 2, O_FREE = M_READY + 2, kNumBars = O_FREE + 1;
   static_assert(8 * kNumBars + 8 <= 256, "barrier block");
   const uint32_t tmem_slot = bar0 + 8u * kNumBars;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
@@ -152,23 +154,34 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
   const bool leader = rank == 0;
   int* err = args.err;
 
-  // heavier (later) query tiles first: with causal masking they have the most key tiles
-  const int n_pair_tiles = gridDim.x >> 1;
-  const int pt = n_pair_tiles - 1 - static_cast<int>(blockIdx.x >> 1);
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (args.Hq / args.Hkv);
-  const int q0 = pt * 2 * kQT + static_cast<int>(rank) * kQT;   // this CTA's first query row
+  // Work items = (query tile of 256 rows, head, batch), the heavier (later) query tiles first: with causal masking they
+  // have the most key tiles.  The pair walks items pair_id, pair_id + n_pairs, ...; every role walks the same list and
+  // counts key tiles across items (`g`), so ring stages, buffer parities and barrier phases simply continue from one
+  // item into the next: the loads of the next item's keys and values, and its first products, overlap the current
+  // item's last softmax steps and output.
+  const int pair_id = static_cast<int>(blockIdx.x >> 1), n_pairs = static_cast<int>(gridDim.x >> 1);
   const int off = args.Skv - args.Sq;                           // causal: query i sees keys <= i + off
-  int kv_end = args.Skv;
-  if (args.causal) kv_end = min(args.Skv, pt * 2 * kQT + 2 * kQT + off);   // of the pair's last row
-  const int n_tiles = (kv_end + kKT - 1) / kKT;  // >= 1 (host guarantees Skv >= Sq >= 1 when causal)
+  const int heads_x_batch = args.Hq * args.B;
+  struct Item { int pt, h, b, hk, n_tiles; };
+  auto item_at = [&](int item) {
+    Item it;
+    it.pt = args.n_pair_tiles - 1 - item / heads_x_batch;
+    const int rest = item % heads_x_batch;
+    it.b = rest / args.Hq;
+    it.h = rest % args.Hq;
+    it.hk = it.h / (args.Hq / args.Hkv);
+    int kv_end = args.Skv;
+    if (args.causal) kv_end = min(args.Skv, it.pt * 2 * kQT + 2 * kQT + off);   // of the pair's last row
+    it.n_tiles = (kv_end + kKT - 1) / kKT;  // >= 1 (host guarantees Skv >= Sq >= 1 when causal)
+    return it;
+  };
 
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     for (int i = 0; i < kNumBars; ++i) {
       uint32_t count = 1;
-      if (i == Q_READY) count = 512;                        // both softmax groups of both CTAs
+      if (i == Q_READY || i == O_FREE) count = 512;         // both softmax groups of both CTAs
       else if (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) count = 256;  // one softmax group of each CTA
       else if (i >= M_READY) count = 128;
       mbar_init(bar(i), count);
@@ -193,25 +206,34 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
   asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
   if (warp == 0) {
     if (lane == 0) {  // this CTA's 64 keys of every K tile
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j % kKV;
-        const uint32_t ph = (j / kKV) & 1;
-        if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
-        if (leader) mbar_expect_tx(bar(K_FULL + st), 2 * kHalfBytes);  // both CTAs' halves
-        const uint32_t dst = base + kSmemK + st * kHalfBytes;
-        const int key0 = j * kKT + static_cast<int>(rank) * 64;
-        tma_load_4d_pair(dst, &tmap_k, bar(K_FULL + st), 0, key0, hk, b);
-        tma_load_4d_pair(dst + kKBoxBytes, &tmap_k, bar(K_FULL + st), 64, key0, hk, b);
+      bool ok = true;
+      for (int item = pair_id, g = 0; ok && item < args.n_items; item += n_pairs) {
+        const Item it = item_at(item);
+        for (int j = 0; j < it.n_tiles; ++j, ++g) {
+          const int st = g % kKV;
+          const uint32_t ph = (g / kKV) & 1;
+          if (!mbar_wait(bar(K_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) { ok = false; break; }
+          if (leader) mbar_expect_tx(bar(K_FULL + st), 2 * kHalfBytes);  // both CTAs' halves
+          const uint32_t dst = base + kSmemK + st * kHalfBytes;
+          const int key0 = j * kKT + static_cast<int>(rank) * 64;
+          tma_load_4d_pair(dst, &tmap_k, bar(K_FULL + st), 0, key0, it.hk, it.b);
+          tma_load_4d_pair(dst + kKBoxBytes, &tmap_k, bar(K_FULL + st), 64, key0, it.hk, it.b);
+        }
       }
     }
   } else if (warp == 3) {
     if (lane == 0) {  // this CTA's 64 d columns of every V tile
-      for (int j = 0; j < n_tiles; ++j) {
-        const int st = j % kKV;
-        const uint32_t ph = (j / kKV) & 1;
-        if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) break;
-        if (leader) mbar_expect_tx(bar(V_FULL + st), 2 * kHalfBytes);
-        tma_load_4d_pair(base + kSmemV + st * kHalfBytes, &tmap_v, bar(V_FULL + st), static_cast<int>(rank) * 64, j * kKT, hk, b);
+      bool ok = true;
+      for (int item = pair_id, g = 0; ok && item < args.n_items; item += n_pairs) {
+        const Item it = item_at(item);
+        for (int j = 0; j < it.n_tiles; ++j, ++g) {
+          const int st = g % kKV;
+          const uint32_t ph = (g / kKV) & 1;
+          if (!mbar_wait(bar(V_EMPTY + st), ph ^ 1, err, DEVERR_ATTN_PRODUCER)) { ok = false; break; }
+          if (leader) mbar_expect_tx(bar(V_FULL + st), 2 * kHalfBytes);
+          tma_load_4d_pair(base + kSmemV + st * kHalfBytes, &tmap_v, bar(V_FULL + st), static_cast<int>(rank) * 64, j * kKT,
+                           it.hk, it.b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -220,30 +242,35 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     // neither waits for the other's barriers, and together they keep the tensor pipe fed.
     if (leader && lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(2 * kQT, kKT, false, false);
-      bool ok = mbar_wait(bar(Q_READY), 0, err, DEVERR_ATTN_MMA);
       // K-major B: 8-row groups 1 KB apart; ring stage s is kHalfBytes further on
       const uint64_t kdesc0 = make_smem_desc_sw128(base + kSmemK, 16, 1024);
       // development builds: cycles this thread spends waiting for K and for a free S buffer (summed over the tiles)
       TRACE_ONLY(long long w_k = 0, w_se = 0, c0; const long long c_begin = clock64();)
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int sb = j & 1, kst = j % kKV;  // S buffer / K ring stage
-        const uint32_t ph = (j >> 1) & 1, kph = (j / kKV) & 1;
-        TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(K_FULL + kst), kph, err, DEVERR_ATTN_MMA)) break;
-        TRACE_ONLY(w_k += clock64() - c0; c0 = clock64();)
-        // an S buffer is free again as soon as its softmax groups (of both CTAs) have the rows in registers
-        if (!mbar_wait(bar(S_EMPTY + sb), ph ^ 1, err, DEVERR_ATTN_MMA)) break;
-        TRACE_ONLY(w_se += clock64() - c0;)
-        tc_fence_after();
-        // 16 d per step: 8 tensor-memory columns of Q; 32 bytes along a K box row, the second box 8 KB further on
-        constexpr int B2 = kKBoxBytes >> 4;
-        umma_bf16_ts_pair_x8<2, 4, 6, B2, B2 + 2, B2 + 4, B2 + 6>(tmem_s0 + sb * 128, tmem_q,
-                                                                   kdesc0 + static_cast<uint64_t>(kst * (kHalfBytes >> 4)),
-                                                                   idesc_qk, 0u);
-        umma_commit_pair(bar(K_EMPTY + kst));
-        umma_commit_pair(bar(S_FULL + sb));
+      bool ok = true;
+      int g = 0;
+      for (int item = pair_id, seq = 0; ok && item < args.n_items; item += n_pairs, ++seq) {
+        const Item it = item_at(item);
+        if (!mbar_wait(bar(Q_READY), seq & 1, err, DEVERR_ATTN_MMA)) break;  // this item's Q is in tensor memory
+        for (int j = 0; j < it.n_tiles; ++j, ++g) {
+          const int sb = g & 1, kst = g % kKV;  // S buffer / K ring stage
+          const uint32_t ph = (g >> 1) & 1, kph = (g / kKV) & 1;
+          TRACE_ONLY(c0 = clock64();)
+          if (!mbar_wait(bar(K_FULL + kst), kph, err, DEVERR_ATTN_MMA)) { ok = false; break; }
+          TRACE_ONLY(w_k += clock64() - c0; c0 = clock64();)
+          // an S buffer is free again as soon as its softmax groups (of both CTAs) have the rows in registers
+          if (!mbar_wait(bar(S_EMPTY + sb), ph ^ 1, err, DEVERR_ATTN_MMA)) { ok = false; break; }
+          TRACE_ONLY(w_se += clock64() - c0;)
+          tc_fence_after();
+          // 16 d per step: 8 tensor-memory columns of Q; 32 bytes along a K box row, the second box 8 KB further on
+          constexpr int B2 = kKBoxBytes >> 4;
+          umma_bf16_ts_pair_x8<2, 4, 6, B2, B2 + 2, B2 + 4, B2 + 6>(tmem_s0 + sb * 128, tmem_q,
+                                                                     kdesc0 + static_cast<uint64_t>(kst * (kHalfBytes >> 4)),
+                                                                     idesc_qk, 0u);
+          umma_commit_pair(bar(K_EMPTY + kst));
+          umma_commit_pair(bar(S_FULL + sb));
+        }
       }
-      TRACE_VALUE(0, true, n_tiles);
+      TRACE_VALUE(0, true, g);
       TRACE_VALUE(1, true, clock64() - c_begin);
       TRACE_VALUE(2, true, w_k);
       TRACE_VALUE(3, true, w_se);
@@ -255,21 +282,28 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       // MN-major B, this CTA's V half: rows = keys (128 B = its 64 d each), 8-key groups 1 KB apart; 16 keys = 2 KB per step
       const uint64_t vdesc0 = make_smem_desc_sw128(base + kSmemV, kHalfBytes, 1024);
       TRACE_ONLY(long long w_v = 0, w_p = 0, c0; const long long c_begin = clock64();)
-      for (int j = 0; j < n_tiles; ++j) {
-        const int sb = j & 1, vst = j % kKV;  // tile parity / V ring stage
-        const uint32_t vph = (j / kKV) & 1;
-        TRACE_ONLY(c0 = clock64();)
-        if (!mbar_wait(bar(V_FULL + vst), vph, err, DEVERR_ATTN_MMA)) break;
-        TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
-        if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(j & 1), err, DEVERR_ATTN_MMA)) break;  // one phase per tile
-        TRACE_ONLY(w_p += clock64() - c0;)
-        tc_fence_after();
-        // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory, 2 KB of the V tile
-        umma_bf16_ts_pair_x8<128, 256, 384, 512, 640, 768, 896>(tmem_o, tmem_p,
-                                                                vdesc0 + static_cast<uint64_t>(vst * (kHalfBytes >> 4)),
-                                                                idesc_pv, j > 0 ? 1u : 0u);
-        umma_commit_pair(bar(V_EMPTY + vst));
-        umma_commit_pair(bar(PV_DONE + sb));
+      bool ok = true;
+      int g = 0;
+      for (int item = pair_id, seq = 0; ok && item < args.n_items; item += n_pairs, ++seq) {
+        const Item it = item_at(item);
+        // the output accumulator is free once the softmax threads have read the previous item's out of it
+        if (seq > 0 && !mbar_wait(bar(O_FREE), (seq - 1) & 1, err, DEVERR_ATTN_MMA)) break;
+        for (int j = 0; j < it.n_tiles; ++j, ++g) {
+          const int sb = g & 1, vst = g % kKV;  // tile parity / V ring stage
+          const uint32_t vph = (g / kKV) & 1;
+          TRACE_ONLY(c0 = clock64();)
+          if (!mbar_wait(bar(V_FULL + vst), vph, err, DEVERR_ATTN_MMA)) { ok = false; break; }
+          TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
+          if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(g & 1), err, DEVERR_ATTN_MMA)) { ok = false; break; }  // one phase per tile
+          TRACE_ONLY(w_p += clock64() - c0;)
+          tc_fence_after();
+          // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory, 2 KB of the V tile
+          umma_bf16_ts_pair_x8<128, 256, 384, 512, 640, 768, 896>(tmem_o, tmem_p,
+                                                                  vdesc0 + static_cast<uint64_t>(vst * (kHalfBytes >> 4)),
+                                                                  idesc_pv, j > 0 ? 1u : 0u);
+          umma_commit_pair(bar(V_EMPTY + vst));
+          umma_commit_pair(bar(PV_DONE + sb));
+        }
       }
       TRACE_VALUE(12, true, clock64() - c_begin);
       TRACE_VALUE(4, true, w_v);
@@ -281,20 +315,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     const int quarter = warp & 3;
     const int wg = (warp - 4) >> 2;     // softmax warpgroup: key tiles j = wg, wg + 2, ...; S buffer wg
     const int r = quarter * 32 + lane;  // query row in this CTA's tile == TMEM lane
-    const int qi = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_s0 + lane_addr + wg * 128;
     const uint32_t p_full_leader = map_to_leader(bar(P_FULL)), s_empty_leader = map_to_leader(bar(S_EMPTY + wg));
     float* m_sh = reinterpret_cast<float*>(gen + kSmemXch);  // [128] running maximum, log2 domain
     float* l_sh = m_sh + 128;                                // [2 groups][128] row sums
-    float m_used = -INFINITY, l = 0.0f;                      // the maximum this group's sums are relative to
     bool ok = true;
 
-    // ---- Q rows into tensor memory: group w copies d columns [64 w, 64 w + 64) of its thread's row ----
-    {
-      uint32_t qw[32];
+    // Q rows of an item into tensor memory: group w copies d columns [64 w, 64 w + 64) of its thread's row
+    uint32_t qw[32];
+    auto fetch_q = [&](const Item& it) {
+      const int qi = it.pt * 2 * kQT + static_cast<int>(rank) * kQT + r;
       if (qi < args.Sq) {
-        const uint4* src = reinterpret_cast<const uint4*>(args.q + b * args.q_sb + h * args.q_sh +
+        const uint4* src = reinterpret_cast<const uint4*>(args.q + it.b * args.q_sb + it.h * args.q_sh +
                                                           static_cast<long long>(qi) * args.q_ss + wg * 64);
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
@@ -305,117 +338,179 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
 #pragma unroll
         for (int v = 0; v < 32; ++v) qw[v] = 0u;
       }
+    };
+    auto put_q = [&]() {
       tmem_st_32x32(tmem_q + lane_addr + wg * 32, qw);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_cluster(map_to_leader(bar(Q_READY)));
+    };
+    if (pair_id < args.n_items) {
+      fetch_q(item_at(pair_id));
+      put_q();
     }
 
     // development builds: cycles of thread 128 per phase (wait for S, load + scan, decision, exp, wait for the P buffer)
     TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, c0; const long long c_begin = clock64();)
-    for (int j = wg; j < n_tiles; j += 2) {
-      const uint32_t ph = (j >> 1) & 1;
-      TRACE_ONLY(c0 = clock64();)
-      if (!mbar_wait(bar(S_FULL + wg), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
-      TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
-      tc_fence_after();
-      // the S row into registers (raw scores: the scale is folded into the exponent)
-      float s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32(s_addr + c * 32, t);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
-      }
-      tc_fence_before();
-      mbar_arrive_cluster(s_empty_leader);  // the buffer can take QK^T of tile j+2 (once the peer's group is here too)
-      const int k0 = j * kKT;
-      const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
-      if (need_mask) {
-        const int limit = args.causal ? min(args.Skv - 1, qi + off) : args.Skv - 1;  // last visible key
-#pragma unroll
-        for (int e = 0; e < 128; ++e)
-          if (k0 + e > limit) s[e] = -INFINITY;
-      }
-      // row maximum: four independent chains
-      float tm[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-      for (int e = 4; e < 128; e += 4) {
-        tm[0] = fmaxf(tm[0], s[e]);
-        tm[1] = fmaxf(tm[1], s[e + 1]);
-        tm[2] = fmaxf(tm[2], s[e + 2]);
-        tm[3] = fmaxf(tm[3], s[e + 3]);
-      }
-      const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * args.scale_log2;  // log2 domain (scale > 0)
-      TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
-      // ---- the running maximum: tile j's decision follows tile j-1's (made by the other group) ----
-      float m;
-      if (j == 0) {
-        m = tmax;  // key 0 is visible to every row, so m is finite from here on
-      } else {
-        if (!mbar_wait(bar(M_READY + (wg ^ 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
-        m = m_sh[r];
-        const float m_new = fmaxf(m, tmax);
-        const bool grow = m_new > m + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, grow)) {
-          // O must be final for tile j-1 before it is rescaled
-          if (!mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
-          tc_fence_after();
-          const float alpha = fast_exp2(m - m_new);
-          m = m_new;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t t[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
-            tmem_st_32x32(tmem_o + lane_addr + c * 32, t);
-          }
-          tmem_wait_st();
-          tc_fence_before();
-        }
-      }
-      m_sh[r] = m;
-      mbar_arrive(bar(M_READY + wg));  // tile j + 1 may decide (and rescale O) now
-      if (m_used != m) {                // this group's sums follow the maximum (no-op while l == 0)
-        l *= fast_exp2(m_used - m);
-        m_used = m;
-      }
-      TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
-      // probabilities as bf16 pairs (the A operand of P V), into registers first: the one P buffer in tensor memory is
-      // free only when P V of the previous tile (the other group's) has completed, and that must not hold up the
-      // exponentials
-      float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const float neg_m = -m;
-      uint32_t pk[64];
-#pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        const float p0 = fast_exp2(fmaf(s[2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
-        const float p1 = fast_exp2(fmaf(s[2 * e + 1], args.scale_log2, neg_m));
-        ls[(2 * e) & 3] += p0;
-        ls[(2 * e + 1) & 3] += p1;
-        pk[e] = pack_bf16x2(p0, p1);
-      }
-      TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
-      if (j >= 1) {
-        if (!mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+    int g0 = 0;  // key tiles of the items before this one: tile j of the item is tile g0 + j of the pair
+#pragma unroll 1
+    for (int item = pair_id; item < args.n_items; item += n_pairs) {
+      const Item it = item_at(item);
+      const int n_tiles = it.n_tiles;
+      const int q0 = it.pt * 2 * kQT + static_cast<int>(rank) * kQT;   // this CTA's first query row
+      const int qi = q0 + r;
+      float m_used = -INFINITY, l = 0.0f;                              // the maximum this group's sums are relative to
+      // this group takes the pair's tiles of parity wg (S buffer wg), whichever items they belong to
+#pragma unroll 1
+      for (int j = (wg ^ (g0 & 1)); ok && j < n_tiles; j += 2) {
+        const int g = g0 + j;
+        const uint32_t ph = (g >> 1) & 1;
+        TRACE_ONLY(c0 = clock64();)
+        if (!mbar_wait(bar(S_FULL + wg), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+        TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
         tc_fence_after();
-      }
-      TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
+        // the S row into registers (raw scores: the scale is folded into the exponent)
+        float s[128];
 #pragma unroll
-      for (int hc = 0; hc < 2; ++hc) {  // 64 keys = 32 packed columns per store
-        uint32_t part[32];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t t[32];
+          tmem_ld_32x32(s_addr + c * 32, t);
+          tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) part[e] = pk[hc * 32 + e];
-        tmem_st_32x32(tmem_p + lane_addr + hc * 32, part);
+          for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
+        }
+        tc_fence_before();
+        mbar_arrive_cluster(s_empty_leader);  // the buffer can take QK^T of tile g + 2 (once the peer's group is here too)
+        const int k0 = j * kKT;
+        const bool need_mask = (k0 + kKT > args.Skv) || (args.causal && (k0 + kKT - 1 > q0 + off));
+        if (need_mask) {
+          const int limit = args.causal ? min(args.Skv - 1, qi + off) : args.Skv - 1;  // last visible key
+#pragma unroll
+          for (int e = 0; e < 128; ++e)
+            if (k0 + e > limit) s[e] = -INFINITY;
+        }
+        // row maximum: four independent chains
+        float tm[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+        for (int e = 4; e < 128; e += 4) {
+          tm[0] = fmaxf(tm[0], s[e]);
+          tm[1] = fmaxf(tm[1], s[e + 1]);
+          tm[2] = fmaxf(tm[2], s[e + 2]);
+          tm[3] = fmaxf(tm[3], s[e + 3]);
+        }
+        const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * args.scale_log2;  // log2 domain (scale > 0)
+        TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
+        // ---- the running maximum: tile j's decision follows tile j-1's (made by the other group) ----
+        float m;
+        if (j == 0) {
+          m = tmax;  // key 0 is visible to every row, so m is finite from here on
+        } else {
+          if (!mbar_wait(bar(M_READY + (wg ^ 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+          m = m_sh[r];
+          const float m_new = fmaxf(m, tmax);
+          const bool grow = m_new > m + kRescaleThreshold;
+          if (__any_sync(0xffffffffu, grow)) {
+            // O must be final for tile j-1 before it is rescaled
+            if (!mbar_wait(bar(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+            tc_fence_after();
+            const float alpha = fast_exp2(m - m_new);
+            m = m_new;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t t[32];
+              tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) t[e] = __float_as_uint(__uint_as_float(t[e]) * alpha);
+              tmem_st_32x32(tmem_o + lane_addr + c * 32, t);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+          }
+        }
+        m_sh[r] = m;
+        mbar_arrive(bar(M_READY + wg));  // tile j + 1 may decide (and rescale O) now
+        if (m_used != m) {                // this group's sums follow the maximum (no-op while l == 0)
+          l *= fast_exp2(m_used - m);
+          m_used = m;
+        }
+        TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
+        // probabilities as bf16 pairs (the A operand of P V), into registers first: the one P buffer in tensor memory is
+        // free only when P V of the previous tile (the other group's) has completed, and that must not hold up the
+        // exponentials
+        float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float neg_m = -m;
+        uint32_t pk[64];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+          const float p0 = fast_exp2(fmaf(s[2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
+          const float p1 = fast_exp2(fmaf(s[2 * e + 1], args.scale_log2, neg_m));
+          ls[(2 * e) & 3] += p0;
+          ls[(2 * e + 1) & 3] += p1;
+          pk[e] = pack_bf16x2(p0, p1);
+        }
+        TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
+        if (j >= 1) {  // (an item's first tile finds the buffer free: the item before was finished only after its last P V)
+          if (!mbar_wait(bar(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+          tc_fence_after();
+        }
+        TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
+#pragma unroll
+        for (int hc = 0; hc < 2; ++hc) {  // 64 keys = 32 packed columns per store
+          uint32_t part[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) part[e] = pk[hc * 32 + e];
+          tmem_st_32x32(tmem_p + lane_addr + hc * 32, part);
+        }
+        tmem_wait_st();
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        tc_fence_before();
+        mbar_arrive_cluster(p_full_leader);
       }
-      tmem_wait_st();
-      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      tc_fence_before();
-      mbar_arrive_cluster(p_full_leader);
+      // ---- both groups: final maximum, total row sum, then half of the output columns each ----
+      const int glast = g0 + n_tiles - 1;
+      if (ok) ok = mbar_wait(bar(M_READY + ((glast & 1) ^ 0)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+      const float m_fin = m_sh[r];
+      if (m_used != m_fin) l *= fast_exp2(m_used - m_fin);  // a group without tiles has l = 0 and m_used = -inf
+      l_sh[wg * 128 + r] = l;
+      named_barrier_sync(1, 256);  // every softmax thread gets here, also after a failed wait
+      l = l_sh[r] + l_sh[128 + r];
+      // the next item's Q rows are requested now: the loads fly while the last P V completes
+      const bool more = item + n_pairs < args.n_items;
+      if (more) fetch_q(item_at(item + n_pairs));
+      if (ok) ok = mbar_wait(bar(PV_DONE + (glast & 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+      const int col0 = wg * 64;
+      if (ok) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        const bool valid = qi < args.Sq;
+        bf16* dst = args.o + it.b * args.o_sb + it.h * args.o_sh + static_cast<long long>(qi) * args.o_ss + col0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t t[32];
+          tmem_ld_32x32(tmem_o + lane_addr + col0 + c * 32, t);
+          tmem_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o4;
+              o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
+              o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
+              o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
+              o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
+            }
+          }
+        }
+        tc_fence_before();
+        if (valid && args.lse && wg == 0)
+          args.lse[(static_cast<long long>(it.b) * args.Hq + it.h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
+      }
+      // The accumulator and (every product with Q being complete) the Q columns now belong to the next item.
+      named_barrier_sync(1, 256);  // nobody overwrites l_sh or m_sh before every thread has read them
+      mbar_arrive_cluster(map_to_leader(bar(O_FREE)));
+      if (more) put_q();
+      g0 += n_tiles;
     }
     TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
     TRACE_VALUE(7, threadIdx.x == 128, w_s);
@@ -423,41 +518,6 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     TRACE_VALUE(9, threadIdx.x == 128, t_max);
     TRACE_VALUE(10, threadIdx.x == 128, w_pv);
     TRACE_VALUE(11, threadIdx.x == 128, t_exp);
-    // ---- both groups: final maximum, total row sum, then half of the output columns each ----
-    const int last = n_tiles - 1;
-    if (ok) ok = mbar_wait(bar(M_READY + (last & 1)), (last >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
-    const float m_fin = m_sh[r];
-    if (m_used != m_fin) l *= fast_exp2(m_used - m_fin);  // a group without tiles has l = 0 and m_used = -inf
-    l_sh[wg * 128 + r] = l;
-    named_barrier_sync(1, 256);  // every softmax thread gets here, also after a failed wait
-    l = l_sh[r] + l_sh[128 + r];
-    if (ok) ok = mbar_wait(bar(PV_DONE + (last & 1)), (last >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
-    if (ok) {
-      tc_fence_after();
-      const float inv = 1.0f / l;
-      const bool valid = qi < args.Sq;
-      const int col0 = wg * 64;
-      bf16* dst = args.o + b * args.o_sb + h * args.o_sh + static_cast<long long>(qi) * args.o_ss + col0;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32(tmem_o + lane_addr + col0 + c * 32, t);
-        tmem_wait_ld();
-        if (valid) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o4;
-            o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
-            o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
-            o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
-            o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
-          }
-        }
-      }
-      if (valid && args.lse && wg == 0)
-        args.lse[(static_cast<long long>(b) * args.Hq + h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
-    }
   }
 
   tc_fence_before();
@@ -527,8 +587,18 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
     if (prc) return prc;
   }
   const int pair_tiles = (s.Sq + 2 * kQT - 1) / (2 * kQT);
-  dim3 grid(2 * pair_tiles, s.Hq, s.B);
-  launch_kernel(attention_prefill_kernel, dim3(grid), dim3(kThreads), kSmemTotal, stream, 2, mk, mv, a);
+  const long long items = static_cast<long long>(pair_tiles) * s.Hq * s.B;
+  if (items > 0x7fffffffLL) return TEENY_ERR_BAD_ARG;
+  a.n_pair_tiles = pair_tiles;
+  a.n_items = static_cast<int>(items);
+  // One CTA pair per SM pair, each walking its share of the items (TEENY_ATTN_PERSISTENT=0: one pair per item, for A/B
+  // timing).
+  static const bool persistent = [] { const char* e = getenv("TEENY_ATTN_PERSISTENT"); return !(e && e[0] == '0'); }();
+  long long pairs = persistent ? sm_count() / 2 : items;
+  if (pairs > items) pairs = items;
+  if (pairs < 1) pairs = 1;
+  if (pairs > 0x3fffffffLL) return TEENY_ERR_BAD_ARG;
+  launch_kernel(attention_prefill_kernel, dim3(static_cast<unsigned>(2 * pairs)), dim3(kThreads), kSmemTotal, stream, 2, mk, mv, a);
   return static_cast<int>(cudaGetLastError());
 }
 
