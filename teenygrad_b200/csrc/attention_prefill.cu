@@ -52,8 +52,9 @@ constexpr int kKV = 4;                          // stages of the K ring and of t
 constexpr int kSmemK = 0;
 constexpr int kSmemV = kSmemK + kKV * kHalfBytes;
 constexpr int kSmemBar = kSmemV + kKV * kHalfBytes;
-constexpr int kSmemXch = kSmemBar + 256;        // running maximum per row (128 floats), row sums of both groups (256)
-constexpr int kSmemTotal = kSmemXch + 384 * 4 + 1024;
+constexpr int kSmemXch = kSmemBar + 256;        // per item parity: running maximum per row, and the row sum / maximum the
+                                                // group that leaves an item early hands to the one that finishes it
+constexpr int kSmemTotal = kSmemXch + 2 * 3 * 128 * 4 + 1024;
 static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address -> leader
@@ -144,7 +145,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
   // threads signal them across the pair); the others exist and are used in both CTAs
   constexpr int Q_READY = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
                 S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 1,
-                M_READY = PV_DONE + 2, O_FREE = M_READY + 2, kNumBars = O_FREE + 1;
+                M_READY = PV_DONE + 2, O_FREE = M_READY + 2, L_READY = O_FREE + 1, kNumBars = L_READY + 2;
   static_assert(8 * kNumBars + 8 <= 256, "barrier block");
   const uint32_t tmem_slot = bar0 + 8u * kNumBars;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
@@ -181,9 +182,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     tma_prefetch_desc(&tmap_v);
     for (int i = 0; i < kNumBars; ++i) {
       uint32_t count = 1;
-      if (i == Q_READY || i == O_FREE) count = 512;         // both softmax groups of both CTAs
-      else if (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) count = 256;  // one softmax group of each CTA
-      else if (i >= M_READY) count = 128;
+      if (i == Q_READY || i == O_FREE) count = 256;         // one softmax group of each CTA
+      else if (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) count = 256;
+      else if (i == M_READY || i == M_READY + 1 || i >= L_READY) count = 128;
       mbar_init(bar(i), count);
     }
     mbar_fence_init();
@@ -318,48 +319,49 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_s0 + lane_addr + wg * 128;
     const uint32_t p_full_leader = map_to_leader(bar(P_FULL)), s_empty_leader = map_to_leader(bar(S_EMPTY + wg));
-    float* m_sh = reinterpret_cast<float*>(gen + kSmemXch);  // [128] running maximum, log2 domain
-    float* l_sh = m_sh + 128;                                // [2 groups][128] row sums
+    float* xch = reinterpret_cast<float*>(gen + kSmemXch);  // [item parity][m | l | mu][128]
     bool ok = true;
 
-    // Q rows of an item into tensor memory: group w copies d columns [64 w, 64 w + 64) of its thread's row
-    uint32_t qw[32];
-    auto fetch_q = [&](const Item& it) {
+    // All 128 d columns of this thread's Q row of an item, global -> tensor memory (by the ONE group that opens the item)
+    auto put_q = [&](const Item& it) {
       const int qi = it.pt * 2 * kQT + static_cast<int>(rank) * kQT + r;
-      if (qi < args.Sq) {
-        const uint4* src = reinterpret_cast<const uint4*>(args.q + it.b * args.q_sb + it.h * args.q_sh +
-                                                          static_cast<long long>(qi) * args.q_ss + wg * 64);
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const uint4 t = __ldg(src + v);
-          qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
+      for (int half = 0; half < 2; ++half) {
+        uint32_t qw[32];
+        if (qi < args.Sq) {
+          const uint4* src = reinterpret_cast<const uint4*>(args.q + it.b * args.q_sb + it.h * args.q_sh +
+                                                            static_cast<long long>(qi) * args.q_ss + half * 64);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint4 t = __ldg(src + v);
+            qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 32; ++v) qw[v] = 0u;
         }
-      } else {
-#pragma unroll
-        for (int v = 0; v < 32; ++v) qw[v] = 0u;
+        tmem_st_32x32(tmem_q + lane_addr + half * 32, qw);
       }
-    };
-    auto put_q = [&]() {
-      tmem_st_32x32(tmem_q + lane_addr + wg * 32, qw);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_cluster(map_to_leader(bar(Q_READY)));
     };
-    if (pair_id < args.n_items) {
-      fetch_q(item_at(pair_id));
-      put_q();
-    }
+    // The first item: group 1 brings Q in while group 0, which takes tile 0, has nothing else to do either.
+    if (wg == 1 && pair_id < args.n_items) put_q(item_at(pair_id));
 
     // development builds: cycles of thread 128 per phase (wait for S, load + scan, decision, exp, wait for the P buffer)
-    TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, c0; const long long c_begin = clock64();)
+    TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, t_end = 0, c0; const long long c_begin = clock64();)
     int g0 = 0;  // key tiles of the items before this one: tile j of the item is tile g0 + j of the pair
 #pragma unroll 1
-    for (int item = pair_id; item < args.n_items; item += n_pairs) {
+    for (int item = pair_id, seq = 0; item < args.n_items; item += n_pairs, ++seq) {
       const Item it = item_at(item);
       const int n_tiles = it.n_tiles;
       const int q0 = it.pt * 2 * kQT + static_cast<int>(rank) * kQT;   // this CTA's first query row
       const int qi = q0 + r;
-      float m_used = -INFINITY, l = 0.0f;                              // the maximum this group's sums are relative to
+      float* m_sh = xch + (seq & 1) * 384;  // running maximum of the item's rows, log2 domain
+      float* l_sh = m_sh + 128;             // row sum ...
+      float* mu_sh = m_sh + 256;            // ... and the maximum it is relative to, of the group that leaves first
+      float m_used = -INFINITY, l = 0.0f;   // the maximum this group's sums are relative to
       // this group takes the pair's tiles of parity wg (S buffer wg), whichever items they belong to
 #pragma unroll 1
       for (int j = (wg ^ (g0 & 1)); ok && j < n_tiles; j += 2) {
@@ -450,7 +452,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           pk[e] = pack_bf16x2(p0, p1);
         }
         TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
-        if (j >= 1) {  // (an item's first tile finds the buffer free: the item before was finished only after its last P V)
+        if (g >= 1) {  // the previous tile of the pair -- of this item or of the one before -- has been multiplied
           if (!mbar_wait(bar(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
         }
@@ -467,49 +469,61 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         tc_fence_before();
         mbar_arrive_cluster(p_full_leader);
       }
-      // ---- both groups: final maximum, total row sum, then half of the output columns each ----
+      TRACE_ONLY(c0 = clock64();)
+      // ---- the item's end.  The group that took the last tile finishes the item (row sums, output); the other group
+      // has been free since its own last tile: it hands over its row sum and moves on -- it opens the next item (Q into
+      // tensor memory as soon as the last Q K^T of this item is complete) and takes that item's first tile, while the
+      // first group is still on this item's last tile and output. ----
       const int glast = g0 + n_tiles - 1;
-      if (ok) ok = mbar_wait(bar(M_READY + ((glast & 1) ^ 0)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
-      const float m_fin = m_sh[r];
-      if (m_used != m_fin) l *= fast_exp2(m_used - m_fin);  // a group without tiles has l = 0 and m_used = -inf
-      l_sh[wg * 128 + r] = l;
-      named_barrier_sync(1, 256);  // every softmax thread gets here, also after a failed wait
-      l = l_sh[r] + l_sh[128 + r];
-      // the next item's Q rows are requested now: the loads fly while the last P V completes
+      const bool closer = (glast & 1) == wg;
       const bool more = item + n_pairs < args.n_items;
-      if (more) fetch_q(item_at(item + n_pairs));
-      if (ok) ok = mbar_wait(bar(PV_DONE + (glast & 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
-      const int col0 = wg * 64;
-      if (ok) {
-        tc_fence_after();
-        const float inv = 1.0f / l;
-        const bool valid = qi < args.Sq;
-        bf16* dst = args.o + it.b * args.o_sb + it.h * args.o_sh + static_cast<long long>(qi) * args.o_ss + col0;
+      if (!closer) {
+        l_sh[r] = l;
+        mu_sh[r] = m_used;  // -inf (and l = 0) if this group had no tile in the item
+        mbar_arrive(bar(L_READY + (seq & 1)));
+        if (more) {
+          // every product with this item's Q: complete when the last S tile is (the other group's buffer)
+          if (ok) ok = mbar_wait(bar(S_FULL + (wg ^ 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+          put_q(item_at(item + n_pairs));
+        }
+      } else {
+        const float m_fin = m_used;  // this group decided the last tile
+        if (ok) ok = mbar_wait(bar(L_READY + (seq & 1)), (seq >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+        l += l_sh[r] * fast_exp2(mu_sh[r] - m_fin);  // 0 * 2^-inf = 0 for a group without tiles
+        if (ok) ok = mbar_wait(bar(PV_DONE + (glast & 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
+        if (ok) {
+          tc_fence_after();
+          const float inv = 1.0f / l;
+          const bool valid = qi < args.Sq;
+          bf16* dst = args.o + it.b * args.o_sb + it.h * args.o_sh + static_cast<long long>(qi) * args.o_ss;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t t[32];
-          tmem_ld_32x32(tmem_o + lane_addr + col0 + c * 32, t);
-          tmem_wait_ld();
-          if (valid) {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t t[32];
+            tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
+            tmem_wait_ld();
+            if (c == 3) {  // the accumulator belongs to the next item from here on
+              tc_fence_before();
+              mbar_arrive_cluster(map_to_leader(bar(O_FREE)));
+            }
+            if (valid) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o4;
-              o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
-              o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
-              o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
-              o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
+              for (int v = 0; v < 4; ++v) {
+                uint4 o4;
+                o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
+                o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
+                o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
+                o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
+              }
             }
           }
+          if (valid && args.lse)
+            args.lse[(static_cast<long long>(it.b) * args.Hq + it.h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
+        } else {
+          mbar_arrive_cluster(map_to_leader(bar(O_FREE)));  // after a failed wait: let the issuer run into its own limit, not hang on this
         }
-        tc_fence_before();
-        if (valid && args.lse && wg == 0)
-          args.lse[(static_cast<long long>(it.b) * args.Hq + it.h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
       }
-      // The accumulator and (every product with Q being complete) the Q columns now belong to the next item.
-      named_barrier_sync(1, 256);  // nobody overwrites l_sh or m_sh before every thread has read them
-      mbar_arrive_cluster(map_to_leader(bar(O_FREE)));
-      if (more) put_q();
+      TRACE_ONLY(t_end += clock64() - c0;)
       g0 += n_tiles;
     }
     TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
@@ -518,6 +532,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     TRACE_VALUE(9, threadIdx.x == 128, t_max);
     TRACE_VALUE(10, threadIdx.x == 128, w_pv);
     TRACE_VALUE(11, threadIdx.x == 128, t_exp);
+    TRACE_VALUE(13, threadIdx.x == 128, t_end);
   }
 
   tc_fence_before();
