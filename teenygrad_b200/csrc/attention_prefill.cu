@@ -78,6 +78,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ uint32_t pair_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -391,16 +396,18 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           for (int e = 0; e < 128; ++e)
             if (k0 + e > limit) s[e] = -INFINITY;
         }
-        // row maximum: four independent chains
+        // row maximum: four independent chains of three-input maxima
         float tm[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-        for (int e = 4; e < 128; e += 4) {
-          tm[0] = fmaxf(tm[0], s[e]);
-          tm[1] = fmaxf(tm[1], s[e + 1]);
-          tm[2] = fmaxf(tm[2], s[e + 2]);
-          tm[3] = fmaxf(tm[3], s[e + 3]);
+        for (int e = 4; e + 8 <= 128; e += 8) {
+          tm[0] = fmax3(tm[0], s[e], s[e + 1]);
+          tm[1] = fmax3(tm[1], s[e + 2], s[e + 3]);
+          tm[2] = fmax3(tm[2], s[e + 4], s[e + 5]);
+          tm[3] = fmax3(tm[3], s[e + 6], s[e + 7]);
         }
-        const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * args.scale_log2;  // log2 domain (scale > 0)
+        tm[0] = fmax3(tm[0], s[124], s[125]);
+        tm[1] = fmax3(tm[1], s[126], s[127]);
+        const float tmax = fmaxf(fmax3(tm[0], tm[1], tm[2]), tm[3]) * args.scale_log2;  // log2 domain (scale > 0)
         TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
         // ---- the running maximum: tile j's decision follows tile j-1's (made by the other group) ----
         float m;
@@ -440,16 +447,16 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         // probabilities as bf16 pairs (the A operand of P V), into registers first: the one P buffer in tensor memory is
         // free only when P V of the previous tile (the other group's) has completed, and that must not hold up the
         // exponentials
-        float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const float neg_m = -m;
+        // (two scores per multiply-add and per addition: the packed fp32 forms halve the issue slots next to the exponentials)
+        float2 ls[2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};
+        const float2 sc2 = {args.scale_log2, args.scale_log2}, neg_m2 = {-m, -m};
         uint32_t pk[64];
 #pragma unroll
         for (int e = 0; e < 64; ++e) {
-          const float p0 = fast_exp2(fmaf(s[2 * e], args.scale_log2, neg_m));  // masked scores are -inf -> 0
-          const float p1 = fast_exp2(fmaf(s[2 * e + 1], args.scale_log2, neg_m));
-          ls[(2 * e) & 3] += p0;
-          ls[(2 * e + 1) & 3] += p1;
-          pk[e] = pack_bf16x2(p0, p1);
+          const float2 x = __ffma2_rn(make_float2(s[2 * e], s[2 * e + 1]), sc2, neg_m2);  // masked scores are -inf -> 0
+          const float2 pr = {fast_exp2(x.x), fast_exp2(x.y)};
+          ls[e & 1] = __fadd2_rn(ls[e & 1], pr);
+          pk[e] = pack_bf16x2(pr.x, pr.y);
         }
         TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
         if (g >= 1) {  // the previous tile of the pair -- of this item or of the one before -- has been multiplied
@@ -465,7 +472,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           tmem_st_32x32(tmem_p + lane_addr + hc * 32, part);
         }
         tmem_wait_st();
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        l += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
         tc_fence_before();
         mbar_arrive_cluster(p_full_leader);
       }
