@@ -51,9 +51,11 @@ constexpr int kKBoxBytes = 64 * 64 * 2;         // 8 KB: [64 keys][64 d]
 constexpr int kKV = 4;                          // stages of the K ring and of the V ring
 constexpr int kSmemK = 0;
 constexpr int kSmemV = kSmemK + kKV * kHalfBytes;
-constexpr int kSmemBar = kSmemV + kKV * kHalfBytes;
-constexpr int kSmemXch = kSmemBar + 256;        // per item parity: running maximum per row, and the row sum / maximum the
-                                                // group that leaves an item early hands to the one that finishes it
+constexpr int kSmemQ = kSmemV + kKV * kHalfBytes;   // 32 KB: the next item's Q rows of this CTA, two [128 rows][64 d] boxes
+constexpr int kSmemO = kSmemQ + 2 * kQT * 128;      // 32 KB: output rows on their way out, per warp quarter two [32 rows][64 d] boxes
+constexpr int kSmemBar = kSmemO + 2 * kQT * 128;
+constexpr int kSmemXch = kSmemBar + 512;        // per item parity: running maximum per row, and the row sum / maximum the
+                                                // group that leaves an item first hands to the one that finishes it
 constexpr int kSmemTotal = kSmemXch + 2 * 3 * 128 * 4 + 1024;
 static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
@@ -78,6 +80,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+#ifdef TEENY_TRACE
+#define TL(id, g, c) do { if ((c) && blockIdx.x == 0 && (g) >= 196 && (g) < 216) tl_sh[id][(g) - 196] = clock64(); } while (0)
+#else
+#define TL(id, g, c) do {} while (0)
+#endif
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -106,6 +113,15 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & kPeerBitMask), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// Rows of shared memory (128-byte-swizzled boxes) -> global through the tensor map, as one bulk group of the calling thread.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every bulk store of this thread has read its shared memory (immediate for a thread that issued none)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // The eight K-steps of one 128-deep product for the pair, D[tmem] (+)= A[tmem] * B[smem] (rows 0-127 in the leader,
 // 128-255 in the peer), as one block of straight-line code: A advances eight tensor-memory columns per step, the
 // address field of the B descriptor by the compile-time offsets O1..O7 (16-byte units).  One thread issues a
@@ -140,6 +156,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 
 __global__ void __launch_bounds__(kThreads, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                         const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_o,
                          const PrefillArgs args) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -150,8 +167,9 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
   // threads signal them across the pair); the others exist and are used in both CTAs
   constexpr int Q_READY = 0, K_FULL = 1, K_EMPTY = K_FULL + kKV, V_FULL = K_EMPTY + kKV, V_EMPTY = V_FULL + kKV,
                 S_FULL = V_EMPTY + kKV, S_EMPTY = S_FULL + 2, P_FULL = S_EMPTY + 2, PV_DONE = P_FULL + 1,
-                M_READY = PV_DONE + 2, O_FREE = M_READY + 2, L_READY = O_FREE + 1, kNumBars = L_READY + 2;
-  static_assert(8 * kNumBars + 8 <= 256, "barrier block");
+                M_READY = PV_DONE + 2, O_FREE = M_READY + 4, L_READY = O_FREE + 1, QS_FULL = L_READY + 2,
+                QS_FREE = QS_FULL + 1, kNumBars = QS_FREE + 1;
+  static_assert(8 * kNumBars + 8 <= 512, "barrier block");
   const uint32_t tmem_slot = bar0 + 8u * kNumBars;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kSmemBar + 8 * kNumBars);
 
@@ -182,14 +200,17 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     return it;
   };
 
+  TRACE_ONLY(__shared__ long long tl_sh[12][20]; if (threadIdx.x < 240) (&tl_sh[0][0])[threadIdx.x] = 0;)
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_o);
     for (int i = 0; i < kNumBars; ++i) {
       uint32_t count = 1;
       if (i == Q_READY || i == O_FREE) count = 256;         // one softmax group of each CTA
       else if (i == S_EMPTY || i == S_EMPTY + 1 || i == P_FULL) count = 256;
-      else if (i == M_READY || i == M_READY + 1 || i >= L_READY) count = 128;
+      else if ((i >= M_READY && i < M_READY + 4) || i == L_READY || i == L_READY + 1 || i == QS_FREE) count = 128;
       mbar_init(bar(i), count);
     }
     mbar_fence_init();
@@ -266,6 +287,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           // an S buffer is free again as soon as its softmax groups (of both CTAs) have the rows in registers
           if (!mbar_wait(bar(S_EMPTY + sb), ph ^ 1, err, DEVERR_ATTN_MMA)) { ok = false; break; }
           TRACE_ONLY(w_se += clock64() - c0;)
+          TL(0, g, true);
           tc_fence_after();
           // 16 d per step: 8 tensor-memory columns of Q; 32 bytes along a K box row, the second box 8 KB further on
           constexpr int B2 = kKBoxBytes >> 4;
@@ -274,6 +296,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
                                                                      idesc_qk, 0u);
           umma_commit_pair(bar(K_EMPTY + kst));
           umma_commit_pair(bar(S_FULL + sb));
+          TL(1, g, true);
         }
       }
       TRACE_VALUE(0, true, g);
@@ -302,6 +325,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           TRACE_ONLY(w_v += clock64() - c0; c0 = clock64();)
           if (!mbar_wait(bar(P_FULL), static_cast<uint32_t>(g & 1), err, DEVERR_ATTN_MMA)) { ok = false; break; }  // one phase per tile
           TRACE_ONLY(w_p += clock64() - c0;)
+          TL(2, g, true);
           tc_fence_after();
           // 16 keys per step: 8 columns of packed bf16 pairs of P in tensor memory, 2 KB of the V tile
           umma_bf16_ts_pair_x8<128, 256, 384, 512, 640, 768, 896>(tmem_o, tmem_p,
@@ -309,6 +333,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
                                                                   idesc_pv, j > 0 ? 1u : 0u);
           umma_commit_pair(bar(V_EMPTY + vst));
           umma_commit_pair(bar(PV_DONE + sb));
+          TL(9, g, true);
         }
       }
       TRACE_VALUE(12, true, clock64() - c_begin);
@@ -328,35 +353,43 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     bool ok = true;
 
     // All 128 d columns of this thread's Q row of an item, global -> tensor memory (by the ONE group that opens the item)
-    auto put_q = [&](const Item& it) {
-      const int qi = it.pt * 2 * kQT + static_cast<int>(rank) * kQT + r;
+    // An item's Q rows of this CTA, global -> the staging boxes in shared memory (one thread; an item ahead of their use)
+    auto fetch_q = [&](const Item& it) {
+      const int y = it.pt * 2 * kQT + static_cast<int>(rank) * kQT;
+      mbar_expect_tx(bar(QS_FULL), 2 * kQT * 128);
+      tma_load_4d(base + kSmemQ, &tmap_q, bar(QS_FULL), 0, y, it.h, it.b);
+      tma_load_4d(base + kSmemQ + kQT * 128, &tmap_q, bar(QS_FULL), 64, y, it.h, it.b);
+    };
+    // ... and from there into tensor memory, each thread its row (by the ONE group that opens the item; n = how many
+    // items this pair opened before).  Row r's 16-byte chunk c of a box sits at chunk c ^ (r & 7) of its 128 bytes.
+    auto put_q = [&](int n) {
+      if (ok) ok = mbar_wait(bar(QS_FULL), n & 1, err, DEVERR_ATTN_SOFTMAX);
+      const uint8_t* row = gen + kSmemQ + r * 128;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int hb = 0; hb < 2; ++hb) {
         uint32_t qw[32];
-        if (qi < args.Sq) {
-          const uint4* src = reinterpret_cast<const uint4*>(args.q + it.b * args.q_sb + it.h * args.q_sh +
-                                                            static_cast<long long>(qi) * args.q_ss + half * 64);
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            const uint4 t = __ldg(src + v);
-            qw[4 * v] = t.x; qw[4 * v + 1] = t.y; qw[4 * v + 2] = t.z; qw[4 * v + 3] = t.w;
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < 32; ++v) qw[v] = 0u;
+        for (int c = 0; c < 8; ++c) {
+          const uint4 t = *reinterpret_cast<const uint4*>(row + hb * (kQT * 128) + ((c ^ (r & 7)) << 4));
+          qw[4 * c] = t.x; qw[4 * c + 1] = t.y; qw[4 * c + 2] = t.z; qw[4 * c + 3] = t.w;
         }
-        tmem_st_32x32(tmem_q + lane_addr + half * 32, qw);
+        tmem_st_32x32(tmem_q + lane_addr + hb * 32, qw);
       }
+      mbar_arrive(bar(QS_FREE));  // the boxes can take the item after this one
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_cluster(map_to_leader(bar(Q_READY)));
     };
     // The first item: group 1 brings Q in while group 0, which takes tile 0, has nothing else to do either.
-    if (wg == 1 && pair_id < args.n_items) put_q(item_at(pair_id));
+    if (wg == 1 && pair_id < args.n_items) {
+      if (r == 0) fetch_q(item_at(pair_id));
+      put_q(0);
+    }
 
     // development builds: cycles of thread 128 per phase (wait for S, load + scan, decision, exp, wait for the P buffer)
-    TRACE_ONLY(long long w_s = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, t_end = 0, c0; const long long c_begin = clock64();)
+    TRACE_ONLY(long long w_s = 0, w_s0 = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, t_end = 0, t_close = 0, c0; const long long c_begin = clock64();)
     int g0 = 0;  // key tiles of the items before this one: tile j of the item is tile g0 + j of the pair
+    uint32_t m_seen0 = 0, m_seen1 = 0;
 #pragma unroll 1
     for (int item = pair_id, seq = 0; item < args.n_items; item += n_pairs, ++seq) {
       const Item it = item_at(item);
@@ -367,6 +400,21 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       float* l_sh = m_sh + 128;             // row sum ...
       float* mu_sh = m_sh + 256;            // ... and the maximum it is relative to, of the group that leaves first
       float m_used = -INFINITY, l = 0.0f;   // the maximum this group's sums are relative to
+      const int glast = g0 + n_tiles - 1;
+      const bool closer = (glast & 1) == wg;  // this group takes the item's last tile and writes its output
+      // The "maximum decided" barriers alternate with the item like the values they guard: the group that opens the
+      // next item decides its first tile before the other group has looked at this item's last decision, and one
+      // barrier would then be two completions ahead of that wait.  The other group's tiles of the item are j_other,
+      // j_other + 2, ...; m_seen counts the completions of its barrier before this item.
+      const int m_ready = M_READY + (seq & 1) * 2;
+      const int j_other = (wg ^ 1) ^ (g0 & 1);
+      const uint32_t m_seen = (seq & 1) ? m_seen1 : m_seen0;
+      const bool more = item + n_pairs < args.n_items;
+      if (!closer && more && r == 0) {
+        // this group brings the next item's Q in, an item from now: fetch it as soon as this item's has left the boxes
+        if (ok) ok = mbar_wait(bar(QS_FREE), seq & 1, err, DEVERR_ATTN_SOFTMAX);
+        if (ok) fetch_q(item_at(item + n_pairs));
+      }
       // this group takes the pair's tiles of parity wg (S buffer wg), whichever items they belong to
 #pragma unroll 1
       for (int j = (wg ^ (g0 & 1)); ok && j < n_tiles; j += 2) {
@@ -374,17 +422,25 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         const uint32_t ph = (g >> 1) & 1;
         TRACE_ONLY(c0 = clock64();)
         if (!mbar_wait(bar(S_FULL + wg), ph, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
-        TRACE_ONLY(w_s += clock64() - c0; c0 = clock64();)
+        TRACE_ONLY(w_s += clock64() - c0; if (j < 2) w_s0 += clock64() - c0; c0 = clock64();)
+        TL(3, g, r == 0);
         tc_fence_after();
         // the S row into registers (raw scores: the scale is folded into the exponent)
         float s[128];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t t[32];
-          tmem_ld_32x32(s_addr + c * 32, t);
+        {
+          uint32_t t0[32], t1[32], t2[32], t3[32];  // four loads in flight, one wait
+          tmem_ld_32x32(s_addr, t0);
+          tmem_ld_32x32(s_addr + 32, t1);
+          tmem_ld_32x32(s_addr + 64, t2);
+          tmem_ld_32x32(s_addr + 96, t3);
           tmem_wait_ld();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) s[c * 32 + e] = __uint_as_float(t[e]);
+          for (int e = 0; e < 32; ++e) {
+            s[e] = __uint_as_float(t0[e]);
+            s[32 + e] = __uint_as_float(t1[e]);
+            s[64 + e] = __uint_as_float(t2[e]);
+            s[96 + e] = __uint_as_float(t3[e]);
+          }
         }
         tc_fence_before();
         mbar_arrive_cluster(s_empty_leader);  // the buffer can take QK^T of tile g + 2 (once the peer's group is here too)
@@ -409,12 +465,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         tm[1] = fmax3(tm[1], s[126], s[127]);
         const float tmax = fmaxf(fmax3(tm[0], tm[1], tm[2]), tm[3]) * args.scale_log2;  // log2 domain (scale > 0)
         TRACE_ONLY(t_ld += clock64() - c0; c0 = clock64();)
+        TL(4, g, r == 0);
         // ---- the running maximum: tile j's decision follows tile j-1's (made by the other group) ----
         float m;
         if (j == 0) {
           m = tmax;  // key 0 is visible to every row, so m is finite from here on
         } else {
-          if (!mbar_wait(bar(M_READY + (wg ^ 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
+          if (!mbar_wait(bar(m_ready + (wg ^ 1)), (m_seen + ((j - 1 - j_other) >> 1)) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
           m = m_sh[r];
           const float m_new = fmaxf(m, tmax);
           const bool grow = m_new > m + kRescaleThreshold;
@@ -438,12 +495,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           }
         }
         m_sh[r] = m;
-        mbar_arrive(bar(M_READY + wg));  // tile j + 1 may decide (and rescale O) now
+        mbar_arrive(bar(m_ready + wg));  // tile j + 1 may decide (and rescale O) now
         if (m_used != m) {                // this group's sums follow the maximum (no-op while l == 0)
           l *= fast_exp2(m_used - m);
           m_used = m;
         }
         TRACE_ONLY(t_max += clock64() - c0; c0 = clock64();)
+        TL(5, g, r == 0);
         // probabilities as bf16 pairs (the A operand of P V), into registers first: the one P buffer in tensor memory is
         // free only when P V of the previous tile (the other group's) has completed, and that must not hold up the
         // exponentials
@@ -459,11 +517,13 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           pk[e] = pack_bf16x2(pr.x, pr.y);
         }
         TRACE_ONLY(t_exp += clock64() - c0; c0 = clock64();)
+        TL(6, g, r == 0);
         if (g >= 1) {  // the previous tile of the pair -- of this item or of the one before -- has been multiplied
           if (!mbar_wait(bar(PV_DONE + ((g - 1) & 1)), ((g - 1) >> 1) & 1, err, DEVERR_ATTN_SOFTMAX)) { ok = false; break; }
           tc_fence_after();
         }
         TRACE_ONLY(w_pv += clock64() - c0; c0 = clock64();)
+        TL(7, g, r == 0);
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {  // 64 keys = 32 packed columns per store
           uint32_t part[32];
@@ -475,15 +535,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         l += (ls[0].x + ls[0].y) + (ls[1].x + ls[1].y);
         tc_fence_before();
         mbar_arrive_cluster(p_full_leader);
+        TL(8, g, r == 0);
       }
       TRACE_ONLY(c0 = clock64();)
       // ---- the item's end.  The group that took the last tile finishes the item (row sums, output); the other group
       // has been free since its own last tile: it hands over its row sum and moves on -- it opens the next item (Q into
       // tensor memory as soon as the last Q K^T of this item is complete) and takes that item's first tile, while the
       // first group is still on this item's last tile and output. ----
-      const int glast = g0 + n_tiles - 1;
-      const bool closer = (glast & 1) == wg;
-      const bool more = item + n_pairs < args.n_items;
+      bulk_wait_read();  // this thread's last output rows have left shared memory: whichever group writes there next has
+      __syncwarp();      // waited for this point, here or through L_READY
       if (!closer) {
         l_sh[r] = l;
         mu_sh[r] = m_used;  // -inf (and l = 0) if this group had no tile in the item
@@ -491,7 +551,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         if (more) {
           // every product with this item's Q: complete when the last S tile is (the other group's buffer)
           if (ok) ok = mbar_wait(bar(S_FULL + (wg ^ 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
-          put_q(item_at(item + n_pairs));
+          put_q(seq + 1);
         }
       } else {
         const float m_fin = m_used;  // this group decided the last tile
@@ -502,27 +562,36 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           tc_fence_after();
           const float inv = 1.0f / l;
           const bool valid = qi < args.Sq;
-          bf16* dst = args.o + it.b * args.o_sb + it.h * args.o_sh + static_cast<long long>(qi) * args.o_ss;
+          uint32_t t[4][32];  // the whole row in flight, so that the accumulator is free for the next item at once
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_o + lane_addr + c * 32, t[c]);
+          tmem_wait_ld();
+          tc_fence_before();
+          mbar_arrive_cluster(map_to_leader(bar(O_FREE)));
+          // bf16 rows into this warp's boxes (the swizzle the tensor map expects), then one bulk store per box: the
+          // rows leave as full lines instead of 16 bytes per thread and row
+          uint8_t* orow = gen + kSmemO + quarter * (32 * 256) + lane * 128;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint32_t t[32];
-            tmem_ld_32x32(tmem_o + lane_addr + c * 32, t);
-            tmem_wait_ld();
-            if (c == 3) {  // the accumulator belongs to the next item from here on
-              tc_fence_before();
-              mbar_arrive_cluster(map_to_leader(bar(O_FREE)));
-            }
-            if (valid) {
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 o4;
-                o4.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
-                o4.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
-                o4.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
-                o4.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
-                *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o4;
-              }
+            for (int v = 0; v < 4; ++v) {
+              uint4 o4;
+              o4.x = pack_bf16x2(__uint_as_float(t[c][v * 8 + 0]) * inv, __uint_as_float(t[c][v * 8 + 1]) * inv);
+              o4.y = pack_bf16x2(__uint_as_float(t[c][v * 8 + 2]) * inv, __uint_as_float(t[c][v * 8 + 3]) * inv);
+              o4.z = pack_bf16x2(__uint_as_float(t[c][v * 8 + 4]) * inv, __uint_as_float(t[c][v * 8 + 5]) * inv);
+              o4.w = pack_bf16x2(__uint_as_float(t[c][v * 8 + 6]) * inv, __uint_as_float(t[c][v * 8 + 7]) * inv);
+              const int ch = (c & 1) * 4 + v;  // chunk of the box's 128-byte row; columns 64.. are the second box
+              *reinterpret_cast<uint4*>(orow + (c >> 1) * (32 * 128) + ((ch ^ (lane & 7)) << 4)) = o4;
             }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          const int y = q0 + quarter * 32;
+          if (lane == 0 && y < args.Sq) {  // rows past the end are clipped by the copy
+            const uint32_t src = base + kSmemO + quarter * (32 * 256);
+            tma_store_4d(&tmap_o, src, 0, y, it.h, it.b);
+            tma_store_4d(&tmap_o, src + 32 * 128, 64, y, it.h, it.b);
+            bulk_commit();
           }
           if (valid && args.lse)
             args.lse[(static_cast<long long>(it.b) * args.Hq + it.h) * args.Sq + qi] = 0.6931471805599453f * (m_fin + log2f(l));
@@ -530,9 +599,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           mbar_arrive_cluster(map_to_leader(bar(O_FREE)));  // after a failed wait: let the issuer run into its own limit, not hang on this
         }
       }
-      TRACE_ONLY(t_end += clock64() - c0;)
+      TRACE_ONLY(t_end += clock64() - c0; if (closer) t_close += clock64() - c0;)
+      TL(closer ? 10 : 11, glast, r == 0);
+      if (seq & 1) m_seen1 += (n_tiles - j_other + 1) >> 1; else m_seen0 += (n_tiles - j_other + 1) >> 1;
       g0 += n_tiles;
     }
+    bulk_wait_read();  // shared memory must outlive the output stores that read it
     TRACE_VALUE(6, threadIdx.x == 128, clock64() - c_begin);
     TRACE_VALUE(7, threadIdx.x == 128, w_s);
     TRACE_VALUE(8, threadIdx.x == 128, t_ld);
@@ -540,11 +612,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     TRACE_VALUE(10, threadIdx.x == 128, w_pv);
     TRACE_VALUE(11, threadIdx.x == 128, t_exp);
     TRACE_VALUE(13, threadIdx.x == 128, t_end);
+    TRACE_VALUE(14, threadIdx.x == 128, w_s0);  // ... of which for the group's first tile of an item
+    TRACE_VALUE(15, threadIdx.x == 128, t_close);  // ... of which as the group that writes the output
   }
 
   tc_fence_before();
   __syncthreads();
   pair_sync();  // the peer may still be signalling this CTA's barriers or waiting on a commit from the leader
+  TRACE_ONLY(if (threadIdx.x == 0 && blockIdx.x == 0) for (int i = 0; i < 240; ++i) { const long long c = (&tl_sh[0][0])[i]; if (c) trace_put(16 + i / 20, (static_cast<unsigned long long>(196 + i % 20) << 40) | (static_cast<unsigned long long>(c) & ((1ull << 40) - 1)), __LINE__); })
   if (warp == 2) {
     if (*reinterpret_cast<volatile int*>(err) != 0) {
       const uint64_t t0 = global_timer_ns();
@@ -588,12 +663,14 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
        reinterpret_cast<uintptr_t>(o)) & 15)
     return TEENY_ERR_ALIGNMENT;
   if (s.Hq > 65535 || s.B > 65535) return TEENY_ERR_BAD_ARG;
-  CUtensorMap mk, mv;
+  CUtensorMap mk, mv, mq, mo;
   int rc;
   // a dimension of extent 1 still needs a legal (multiple-of-16-byte, non-zero) stride
   auto fix = [](long long st, long long fallback) { return st > 0 ? st : fallback; };
   if ((rc = make_map(&mk, k, s.Skv, s.Hkv, s.B, s.k_ss, fix(s.k_sh, s.k_ss), fix(s.k_sb, s.k_ss), 64))) return rc;
   if ((rc = make_map(&mv, v, s.Skv, s.Hkv, s.B, s.v_ss, fix(s.v_sh, s.v_ss), fix(s.v_sb, s.v_ss), 128))) return rc;
+  if ((rc = make_map(&mq, q, s.Sq, s.Hq, s.B, s.q_ss, fix(s.q_sh, s.q_ss), fix(s.q_sb, s.q_ss), kQT))) return rc;
+  if ((rc = make_map(&mo, o, s.Sq, s.Hq, s.B, s.o_ss, fix(s.o_sh, s.o_ss), fix(s.o_sb, s.o_ss), 32))) return rc;
 
   PrefillArgs a{};
   a.q = q; a.o = o; a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
@@ -620,7 +697,7 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
   if (pairs > items) pairs = items;
   if (pairs < 1) pairs = 1;
   if (pairs > 0x3fffffffLL) return TEENY_ERR_BAD_ARG;
-  launch_kernel(attention_prefill_kernel, dim3(static_cast<unsigned>(2 * pairs)), dim3(kThreads), kSmemTotal, stream, 2, mk, mv, a);
+  launch_kernel(attention_prefill_kernel, dim3(static_cast<unsigned>(2 * pairs)), dim3(kThreads), kSmemTotal, stream, 2, mk, mv, mq, mo, a);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -216,6 +216,29 @@ def test_flash_attn_prefill_bf16(ops, B, Hq, Hkv, Sq, Skv, causal):
     assert (lse.cpu() - el).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Skv,causal", [
+    (16, 32, 8, 256, 256, True),    # 512 items of two key tiles each: every CTA pair walks several short items in a row
+    (8, 32, 8, 640, 640, True),     # 2, 4 and 5 key tiles: the softmax group that finishes an item alternates
+    (4, 32, 8, 300, 900, False),    # ragged query tile, eight key tiles per item
+    (24, 16, 4, 100, 100, True),    # one key tile per item
+])
+def test_flash_attn_prefill_many_items_per_cta_pair(ops, B, Hq, Hkv, Sq, Skv, causal):
+    """More (query tile, head, batch) items than CTA pairs, so that one item's output overlaps the next item's start."""
+    from oracle import cpu as oc
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(B, Hq, Sq, 128, generator=g).bfloat16()
+    k = torch.randn(B, Hkv, Skv, 128, generator=g).bfloat16()
+    v = torch.randn(B, Hkv, Skv, 128, generator=g).bfloat16()
+    o, lse = ops.flash_attn_fwd(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, causal=causal, want_lse=True)
+    assert ops.device_error() == 0
+    eo, el = oc.attention_bf16(q, k, v, 128 ** -0.5, causal=causal)
+    assert rel(o, eo) < BF16_TOL
+    assert (lse.cpu() - el).abs().max() < 2e-2
+    # per (batch, head) as well: a mixed-up item would vanish in the norm over the whole tensor
+    per = ((o.cpu().float() - eo.float()).flatten(2).norm(dim=2) / eo.float().flatten(2).norm(dim=2)).max()
+    assert per < BF16_TOL
+
+
 def test_flash_attn_token_major_views(ops):
     """The layout the Qwen3 runner uses: q inside a fused [T, (Hq+2Hkv)*D] projection, output [B, S, Hq*D]."""
     from oracle import cpu as oc
