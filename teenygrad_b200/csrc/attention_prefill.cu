@@ -22,16 +22,27 @@
 //                from its [key][d] tile).  Two threads because a lone thread cannot issue these 64-cycle instructions
 //                fast enough, and so that neither stream waits behind the other's barriers.
 //   warp 2       also allocates / frees tensor memory (cta_group::2, both CTAs).
-//   warps 4-7, 8-11   two softmax warpgroups per CTA, thread = query row in both; warpgroup w takes the key tiles
-//                j = w mod 2 (S buffer w), so one group's exponentials run while the other scans its next tile.
-//                Before the loop the groups copy the CTA's Q rows from global memory into tensor memory.  Per tile:
-//                tcgen05.ld the S row in 32-column pieces, row maximum (causal / tail mask), agreement on the running
-//                maximum with the other group (shared memory; a tile's decision waits for the previous tile's), lazy
-//                rescale (O in tensor memory is only rescaled when the maximum grows by more than 2^8),
-//                P = exp2(s * scale - m) as bf16 pairs into the one P buffer in tensor memory (free once P V of the
-//                previous tile has completed), row sums in f32 per group.
+//   warps 4-7, 8-11   two softmax warpgroups per CTA, thread = query row in both; the groups take the pair's key tiles
+//                alternately (S buffer = tile parity), so one group's exponentials run while the other scans its next
+//                tile.  Per tile: tcgen05.ld the S row (four loads in flight), row maximum (causal / tail mask; three-
+//                input maxima), agreement on the running maximum with the other group (shared memory; a tile's
+//                decision waits for the previous tile's), lazy rescale (O in tensor memory is only rescaled when the
+//                maximum grows by more than 2^8), P = exp2(s * scale - m) (packed fp32 multiply-adds and adds) as bf16
+//                pairs into the one P buffer in tensor memory (free once P V of the previous tile has completed), row
+//                sums in f32 per group.
 //                (Registers re-divided with setmaxnreg: 224 per softmax thread, 56 per service thread.)
-// Epilogue: O / l to bf16, optional LSE = ln2 * (m + log2 l).
+//
+// The grid is persistent: one CTA pair per SM pair walks a list of (256-query tile, head, batch) items, heaviest first;
+// key tiles are counted across items, so ring stages, S-buffer parities and barrier phases carry on from one item into
+// the next and the producers and the Q K^T issuer run ahead into the next item.  At an item's end the two softmax
+// groups part: the one that took the last tile ("closer") adds the other's row sum to its own, waits for the last P V,
+// reads O out of tensor memory, frees it for the next item at once and sends the rows out (bf16 into swizzled boxes in
+// shared memory, one TMA store per warp and box; optional LSE = ln2 * (m + log2 l)); the other ("opener") hands over
+// its row sum and running maximum, copies the next item's Q rows -- fetched by TMA into a staging box an item ahead --
+// from shared into tensor memory as soon as the item's last Q K^T has completed, and goes on with the next item's first
+// tile.  Values the groups exchange (running maximum, row sums) and the barriers that guard them alternate with the
+// item, because the opener is up to one item ahead of the closer.  (Plain 16-byte-per-row loads of Q and stores of O
+// kept the load/store unit busy for ~2000 cycles per item each: a warp instruction touched 32 lines.)
 // Tensor memory columns per CTA: S0 0-127, S1 128-255 (f32 scores), O 256-383 (f32), Q 384-447, P 448-511 (bf16 pairs).
 #include <atomic>
 
@@ -61,13 +72,9 @@ static_assert(kSmemTotal <= 232448, "exceeds the 227 KB of shared memory a CTA c
 constexpr float kRescaleThreshold = 8.0f;       // log2 units
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address -> leader
 
-struct PrefillArgs {
-  const bf16* q;
-  bf16* o;
+struct PrefillArgs {  // (Q, K, V and O travel as tensor maps)
   float* lse;
   int B, Hq, Hkv, Sq, Skv;
-  long long q_sb, q_sh, q_ss;
-  long long o_sb, o_sh, o_ss;
   float scale_log2;
   int causal;
   int n_pair_tiles;  // 256-row query tiles per (batch, head)
@@ -80,6 +87,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Development builds: clock of event `id` at key tile g of CTA 0, for a window of twenty tiles in the middle of its list
+// (kept in shared memory and written out when the CTA is done, so that the stamps cost a store each;
+// `python -m teenygrad_b200.microbench timeline` prints them in order).
 #ifdef TEENY_TRACE
 #define TL(id, g, c) do { if ((c) && blockIdx.x == 0 && (g) >= 196 && (g) < 216) tl_sh[id][(g) - 196] = clock64(); } while (0)
 #else
@@ -673,9 +683,7 @@ int attention_prefill_bf16(const bf16* q, const bf16* k, const bf16* v, bf16* o,
   if ((rc = make_map(&mo, o, s.Sq, s.Hq, s.B, s.o_ss, fix(s.o_sh, s.o_ss), fix(s.o_sb, s.o_ss), 32))) return rc;
 
   PrefillArgs a{};
-  a.q = q; a.o = o; a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
-  a.q_sb = s.q_sb; a.q_sh = s.q_sh; a.q_ss = s.q_ss;
-  a.o_sb = s.o_sb; a.o_sh = s.o_sh; a.o_ss = s.o_ss;
+  a.lse = lse; a.B = s.B; a.Hq = s.Hq; a.Hkv = s.Hkv; a.Sq = s.Sq; a.Skv = s.Skv;
   a.scale_log2 = s.scale * 1.4426950408889634f;
   a.causal = s.causal;
   a.err = device_error_word();

@@ -5,13 +5,14 @@
     python -m teenygrad_b200.microbench layers [N]                                # N-layer Qwen3-8B-shaped prefill + 3 decode steps
     python -m teenygrad_b200.microbench trace [N [first [count [shard]]]]         # timeline of one graph-replayed decode step
     python -m teenygrad_b200.microbench tracecase gemm|skinny|prefill|decode      # phase counters of one kernel
+    python -m teenygrad_b200.microbench timeline                                  # event order inside one CTA pair of the prefill attention kernel
     python -m teenygrad_b200.microbench probe                                     # tcgen05.mma issue rate from one / two threads
 
 ``time`` prints achieved TFLOP/s or GB/s next to cuBLAS / cuDNN (torch) on the same inputs.  Large kernels are timed
 one launch at a time with an L2 flush (a 256 MB write) before each; the decode-shaped kernels, which last tens of
 microseconds, are captured in a CUDA graph over rotating copies of their inputs (larger than L2 together) so neither
 host launch overhead nor a warm L2 enters the number.  ``case`` and ``layers`` exist to be run under ``ncu``.
-``trace`` and ``tracecase`` need a library with per-CTA timer records: ``make -C teenygrad_b200/csrc OBJDIR=_obj_trace
+``trace``, ``tracecase``, ``timeline`` and ``probe`` need a library with per-CTA timer records: ``make -C teenygrad_b200/csrc OBJDIR=_obj_trace
 OUT=../libteeny_b200_trace.so EXTRA=-DTEENY_TRACE`` and ``TEENY_B200_LIB=teenygrad_b200/libteeny_b200_trace.so``.
 """
 import sys
@@ -329,9 +330,54 @@ def tracecase(which):
         n = lib.teeny_trace_dump(i, buf.ctypes.data, 1 << 18, 1)
         b = buf[:n]
         for r in b[(b[:, 0] >= 16) & (b[:, 0] < 32)]:
+            if int(r[1]) >> 40:  # a clock stamp of ``timeline``, not a counter
+                continue
             acc[(name, int(r[2]) & 0xFFFFFFFF, int(r[0]) - 16)].append(int(r[1]))
     for (name, line, vid), vals in sorted(acc.items()):
         print(f"{name}:{line} value {vid:2d}: n {len(vals):6d} mean {sum(vals) / len(vals):12.1f} sum {sum(vals):14d}")
+
+
+def timeline():
+    """Prints, in order, the clock stamps the prefill attention kernel keeps for twenty key tiles of its first CTA pair
+    (S buffer free / Q K^T issued / S arrived / row loaded / maximum decided / exponentials done / P buffer free /
+    P stored / P V issued / item closed or next item opened): the steady state of the pair and one item boundary.
+    Needs a -DTEENY_TRACE build."""
+    import ctypes
+
+    import numpy as np
+    lib = ops.lib
+    if not hasattr(lib, "teeny_trace_count"):
+        raise SystemExit("library was built without -DTEENY_TRACE")
+    lib.teeny_trace_name.restype = ctypes.c_char_p
+    lib.teeny_trace_name.argtypes = [ctypes.c_int]
+    lib.teeny_trace_dump.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint, ctypes.c_int]
+    names = {0: "QK issuer: S buffer free", 1: "QK issuer: issued", 2: "PV issuer: P full", 9: "PV issuer: issued",
+             3: "softmax: S arrived", 4: "softmax: row loaded, maximum", 5: "softmax: maximum decided",
+             6: "softmax: exponentials done", 7: "softmax: P buffer free", 8: "softmax: P stored",
+             10: "softmax: item closed (output on its way)", 11: "softmax: next item opened (Q in tensor memory)"}
+    B, S = 4, 4096
+    q = torch.randn(B, HQ, S, D, device="cuda").bfloat16()
+    k = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+    v = torch.randn(B, HKV, S, D, device="cuda").bfloat16()
+    o = torch.empty_like(q)
+    recs = []
+    for _ in range(3):  # the last launch is the one printed
+        ops.flash_attn_fwd(q, k, v, D ** -0.5, causal=True, out=o)
+        torch.cuda.synchronize()
+        recs = []
+        for i in range(lib.teeny_trace_count()):
+            buf = np.zeros((1 << 18, 4), dtype=np.uint64)
+            n = lib.teeny_trace_dump(i, buf.ctypes.data, 1 << 18, 1)
+            if b"attention_prefill" not in lib.teeny_trace_name(i):
+                continue
+            for r in buf[:n][(buf[:n, 0] >= 16) & (buf[:n, 0] < 32)]:
+                val = int(r[1])
+                if val >> 40:  # (key tile << 40) | clock
+                    recs.append((val & ((1 << 40) - 1), val >> 40, int(r[0]) - 16))
+    recs.sort()
+    print("cycles  key tile  group  event   (causal, batch 4, 32 / 8 heads, sequence 4096; CTA pair 0)")
+    for t, g, i in recs:
+        print(f"{t - recs[0][0]:7d}  {g:4d}  {'AB'[g & 1]}  {names.get(i, i)}")
 
 
 def probe():
@@ -372,6 +418,8 @@ def main(argv):
         probe()
     elif mode == "tracecase":
         tracecase(argv[1])
+    elif mode == "timeline":
+        timeline()
     elif mode == "layers":
         layers(int(argv[1]) if len(argv) > 1 else 6)
     elif mode == "trace":
