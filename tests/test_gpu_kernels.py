@@ -221,6 +221,7 @@ def test_flash_attn_prefill_bf16(ops, B, Hq, Hkv, Sq, Skv, causal):
     (8, 32, 8, 640, 640, True),     # 2, 4 and 5 key tiles: the softmax group that finishes an item alternates
     (4, 32, 8, 300, 900, False),    # ragged query tile, eight key tiles per item
     (24, 16, 4, 100, 100, True),    # one key tile per item
+    (8, 32, 8, 200, 712, True),     # queries at the end of a longer history (query i sees keys <= i + 512), six key tiles
 ])
 def test_flash_attn_prefill_many_items_per_cta_pair(ops, B, Hq, Hkv, Sq, Skv, causal):
     """More (query tile, head, batch) items than CTA pairs, so that one item's output overlaps the next item's start."""
