@@ -400,9 +400,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     TRACE_ONLY(long long w_s = 0, w_s0 = 0, t_ld = 0, t_max = 0, w_pv = 0, t_exp = 0, t_end = 0, t_close = 0, c0; const long long c_begin = clock64();)
     int g0 = 0;  // key tiles of the items before this one: tile j of the item is tile g0 + j of the pair
     uint32_t m_seen0 = 0, m_seen1 = 0;
+    Item next_it = item_at(pair_id < args.n_items ? pair_id : 0);
 #pragma unroll 1
     for (int item = pair_id, seq = 0; item < args.n_items; item += n_pairs, ++seq) {
-      const Item it = item_at(item);
+      const Item it = next_it;  // worked out during the previous item's last waits: the divisions are off this group's path
       const int n_tiles = it.n_tiles;
       const int q0 = it.pt * 2 * kQT + static_cast<int>(rank) * kQT;   // this CTA's first query row
       const int qi = q0 + r;
@@ -562,15 +563,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
           // every product with this item's Q: complete when the last S tile is (the other group's buffer)
           if (ok) ok = mbar_wait(bar(S_FULL + (wg ^ 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
           put_q(seq + 1);
+          next_it = item_at(item + n_pairs);  // (the first products of the next item are on their way meanwhile)
         }
       } else {
         const float m_fin = m_used;  // this group decided the last tile
+        if (more) next_it = item_at(item + n_pairs);  // (the last P V is still running)
         if (ok) ok = mbar_wait(bar(L_READY + (seq & 1)), (seq >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
         l += l_sh[r] * fast_exp2(mu_sh[r] - m_fin);  // 0 * 2^-inf = 0 for a group without tiles
         if (ok) ok = mbar_wait(bar(PV_DONE + (glast & 1)), (glast >> 1) & 1, err, DEVERR_ATTN_SOFTMAX);
         if (ok) {
           tc_fence_after();
-          const float inv = 1.0f / l;
+          float inv;
+          asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(l));  // l >= 1 (the row's maximum contributes 2^0); 1 ulp
+          const float2 inv2 = {inv, inv};
           const bool valid = qi < args.Sq;
           uint32_t t[4][32];  // the whole row in flight, so that the accumulator is free for the next item at once
 #pragma unroll
@@ -586,10 +591,14 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o4;
-              o4.x = pack_bf16x2(__uint_as_float(t[c][v * 8 + 0]) * inv, __uint_as_float(t[c][v * 8 + 1]) * inv);
-              o4.y = pack_bf16x2(__uint_as_float(t[c][v * 8 + 2]) * inv, __uint_as_float(t[c][v * 8 + 3]) * inv);
-              o4.z = pack_bf16x2(__uint_as_float(t[c][v * 8 + 4]) * inv, __uint_as_float(t[c][v * 8 + 5]) * inv);
-              o4.w = pack_bf16x2(__uint_as_float(t[c][v * 8 + 6]) * inv, __uint_as_float(t[c][v * 8 + 7]) * inv);
+              const float2 a0 = __fmul2_rn(make_float2(__uint_as_float(t[c][v * 8 + 0]), __uint_as_float(t[c][v * 8 + 1])), inv2);
+              const float2 a1 = __fmul2_rn(make_float2(__uint_as_float(t[c][v * 8 + 2]), __uint_as_float(t[c][v * 8 + 3])), inv2);
+              const float2 a2 = __fmul2_rn(make_float2(__uint_as_float(t[c][v * 8 + 4]), __uint_as_float(t[c][v * 8 + 5])), inv2);
+              const float2 a3 = __fmul2_rn(make_float2(__uint_as_float(t[c][v * 8 + 6]), __uint_as_float(t[c][v * 8 + 7])), inv2);
+              o4.x = pack_bf16x2(a0.x, a0.y);
+              o4.y = pack_bf16x2(a1.x, a1.y);
+              o4.z = pack_bf16x2(a2.x, a2.y);
+              o4.w = pack_bf16x2(a3.x, a3.y);
               const int ch = (c & 1) * 4 + v;  // chunk of the box's 128-byte row; columns 64.. are the second box
               *reinterpret_cast<uint4*>(orow + (c >> 1) * (32 * 128) + ((ch ^ (lane & 7)) << 4)) = o4;
             }
