@@ -319,6 +319,7 @@ struct Workspace {
   size_t h, y, qkv, attn, delta, act, logits, kcache, vcache, cos, sin, gemm_scratch, attn_scratch, attn_counters, sample_u;
   size_t sample_cand, sample_gather;  // tensor-parallel sampling: this rank's candidate lists, all ranks' lists
   size_t y8, y8_scale;                // the norm kernels' output as two-term FP8 activations (0 bytes when max_batch > 128)
+  size_t a8, a8_scale;                // ... and the MLP activation (the down projection's input), split by a kernel of its own
   size_t y8_rows;
   size_t cand_val, cand_idx, gather_val, gather_idx, next_ids, cur_ids, history, state, total;
   size_t gemm_scratch_bytes, attn_scratch_bytes, attn_counter_bytes, cache_layer_elems;
@@ -422,6 +423,8 @@ Workspace plan(const teeny_qwen3_config& c) {
   w.y8_rows = (tp == 1 && Bm <= 128 && H % 16 == 0) ? Bm : 0;
   w.y8 = take(2 * w.y8_rows * H);
   w.y8_scale = take(w.y8_rows * 4);
+  w.a8 = take(I % 16 == 0 ? 2 * w.y8_rows * I : 0);
+  w.a8_scale = take(w.y8_rows * 4);
   w.sample_u = take(Bm * 4);
   w.sample_cand = take(tp > 1 ? Bm * 1024 * 8 : 0);
   w.sample_gather = take(tp > 1 ? Bm * 1024 * 8 * tp : 0);
@@ -452,16 +455,18 @@ int all_reduce(teeny_qwen3* m, bf16* buf, size_t count, cudaStream_t st) {
 // y[T, N] = x[T, K] W^T for one of the model's projection weights, in whichever form it was given.  FP8 weights are
 // streamed as bytes while T <= 128 (decode) and converted into the model's FP8 scratch for a larger T (prefill), where
 // the bf16 kernels -- the QKV projection's fused epilogue included -- then run on the converted copy.
-// x8 true: x has also been written as two-term FP8 activations into the model's y8 buffer (by the norm kernel in front)
-// and the weight's scales allow it: the conversion-free FP8 x FP8 kernel runs.
+// x8 true: x has also been written as two-term FP8 activations into the model's y8 buffer (by the norm kernel in front;
+// mlp_act: into the a8 buffer, by split_e4m3 behind the gate/up projection) and the weight's scales allow it: the
+// conversion-free FP8 x FP8 kernel runs.
 int project(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* y, int ldy, int T, int N, int K,
             cudaStream_t st, bool swiglu = false, const GemmPush* push = nullptr, const QkvEpilogue* fuse = nullptr,
-            bool x8 = false) {
+            bool x8 = false, bool mlp_act = false) {
   void* gs = m->at<void>(m->off.gemm_scratch);
   const bf16* wb = w.w;
   const int w_rows = N;  // rows of W ([N, K]; for swiglu N counts gate and up rows)
   if (w.q && x8 && T <= 128 && w.kind <= 1)
-    return gemm_w8a8x2_skinny(m->at<uint8_t>(m->off.y8), K, m->at<float>(m->off.y8_scale), w.q, K, w.scale, w.kind, nullptr, y,
+    return gemm_w8a8x2_skinny(m->at<uint8_t>(mlp_act ? m->off.a8 : m->off.y8), K,
+                              m->at<float>(mlp_act ? m->off.a8_scale : m->off.y8_scale), w.q, K, w.scale, w.kind, nullptr, y,
                               ldy, T, N, K, st, swiglu, push);
   if (w.q) {
     if (T <= 128) return linear_w8a16(x, ldx, w.q, K, w.scale, w.kind, w.group, nullptr, y, ldy, T, N, K, nullptr, 0, st, swiglu, push);
@@ -478,7 +483,7 @@ int project(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* y, in
 // its f32 rows into every rank's receive buffer and the sum happens inside the next norm kernel (pending_gather);
 // otherwise GEMM to `delta` and, with tp > 1, an NCCL all-reduce.
 int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* delta, int T, int N, int K, bool decode,
-                 cudaStream_t st) {
+                 cudaStream_t st, bool act8 = false) {
   TpContext* tp = m->tp;
   if (decode && tp && tp->peer_ok && T <= static_cast<int>(tp->rows) && N == static_cast<int>(tp->cols)) {
     const int parity = m->push_round & 1;
@@ -492,7 +497,7 @@ int row_parallel(teeny_qwen3* m, const bf16* x, int ldx, const Weight& w, bf16* 
     ++m->push_round;
     return 0;
   }
-  TEENY_TRY(project(m, x, ldx, w, delta, N, T, N, K, st));
+  TEENY_TRY(project(m, x, ldx, w, delta, N, T, N, K, st, false, nullptr, nullptr, act8, act8));
   return all_reduce(m, delta, static_cast<size_t>(T) * N, st);
 }
 
@@ -519,6 +524,12 @@ int residual_norm(teeny_qwen3* m, bf16* delta, bf16* h, long long ld, bf16* y, c
   }
   return add_rms_norm_bf16(delta, ld, h, ld, y, c.hidden, w, M, c.hidden, c.eps, st,
                            split ? m->at<uint8_t>(m->off.y8) : nullptr, c.hidden, split ? m->at<float>(m->off.y8_scale) : nullptr);
+}
+
+// TEENY_FP8_DOWN_SPLIT=0 leaves the FP8 down projection on the converting kernel (for A/B timing).
+bool down8_enabled() {
+  static const bool on = [] { const char* e = getenv("TEENY_FP8_DOWN_SPLIT"); return !(e && e[0] == '0'); }();
+  return on;
 }
 
 // TEENY_QKV_FUSE=0 keeps head norms / RoPE / cache fill in their own kernel behind the QKV projection (for A/B timing).
@@ -589,7 +600,11 @@ int run_layers(teeny_qwen3* m, int B, int S, int pos0, const int* pos_dev, const
     TEENY_TRY(row_parallel(m, attn, Hq * D, w.o, delta, T, H, Hq * D, decode, st));
     TEENY_TRY(residual_norm(m, delta, h, H, y, w.post_ln, T, st, mlp8));
     TEENY_TRY(project(m, y, H, w.gate_up, act, I, T, 2 * I, H, st, /*swiglu=*/true, nullptr, nullptr, mlp8));
-    TEENY_TRY(row_parallel(m, act, I, w.down, delta, T, H, I, decode, st));
+    // (one GPU, FP8 down projection: its input as two-term FP8 costs a small kernel and saves the conversion of 50 M
+    // weight bytes next to the tensor core)
+    const bool down8 = down8_enabled() && wants_x8(m, w.down, T) && m->off.a8 != m->off.a8_scale;
+    if (down8) TEENY_TRY(split_e4m3(act, I, m->at<uint8_t>(m->off.a8), I, m->at<float>(m->off.a8_scale), T, I, st));
+    TEENY_TRY(row_parallel(m, act, I, w.down, delta, T, H, I, decode, st, down8));
   }
   return 0;
 }

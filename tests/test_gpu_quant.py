@@ -256,22 +256,23 @@ def test_runner_on_a_pack_quantized_int4_checkpoint(tmp_path):
     _check_generation(got, r.history()[:steps].t().cpu().long(), want_logits, want_ids)
 
 
-def test_split_fp8_equals_the_oracle_split(ops):
+@pytest.mark.parametrize("M,K", [(37, 1000), (37, 1003), (32, 12288)])   # 16-byte pieces / a ragged row / the MLP width
+def test_split_fp8_equals_the_oracle_split(ops, M, K):
     """The two-term E4M3 split of bf16 activations: bytes and scales equal to the oracle's, bit for bit."""
     from oracle import quant as oq
     g = torch.Generator().manual_seed(31)
-    x = (torch.randn(37, 1000, generator=g) * torch.logspace(-3, 3, 37)[:, None]).bfloat16()
+    x = (torch.randn(M, K, generator=g) * torch.logspace(-3, 3, M)[:, None]).bfloat16()
     x[4] = 0
     x[9, ::3] *= 1e-4                      # elements far below their row's maximum
     hi, lo, inv_s = oq.split_e4m3(x.float().numpy())
     out, scale = ops.split_fp8(x.cuda())
-    assert torch.equal(out[:37].cpu(), torch.from_numpy(hi)) and torch.equal(out[37:].cpu(), torch.from_numpy(lo))
+    assert torch.equal(out[:M].cpu(), torch.from_numpy(hi)) and torch.equal(out[M:].cpu(), torch.from_numpy(lo))
     assert torch.equal(scale.cpu(), torch.from_numpy(inv_s))
 
 
 @pytest.mark.parametrize("strategy", ["tensor", "channel"])
 @pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 512, 1024), (32, 4096, 4096), (7, 1000, 528), (64, 2048, 2048),
-                                   (128, 1024, 4096), (5, 333, 1024), (4, 24576, 512)])
+                                   (128, 1024, 4096), (5, 333, 1024), (4, 24576, 512), (32, 4096, 12288)])
 def test_linear_w8a8x2(ops, M, N, K, strategy):
     """FP8 weights x two-term FP8 activations (kind::f8f6f4, nothing converted in the kernel): equal to the oracle
     evaluated on the split activations, and -- the split being exact for all but tiny elements -- to the weight-only
